@@ -1,0 +1,45 @@
+// Host-side helpers shared by every translation unit of the native library:
+//   * the exported-symbol macro and launch-error convention (every entry point returns a
+//     cudaError_t-compatible int, 0 = success);
+//   * the device status word kernels use to report a bounded wait that ran out;
+//   * a cache of TMA tensor maps (cuTensorMapEncodeTiled is looked up through the runtime so the
+//     library does not link against libcuda).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define B200_API extern "C" __attribute__((visibility("default")))
+
+#define B200_CHECK(expr)                                                                      \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess) {                                                                  \
+      fprintf(stderr, "[b200] %s failed at %s:%d: %s\n", #expr, __FILE__, __LINE__,           \
+              cudaGetErrorString(_e));                                                        \
+      return static_cast<int>(_e);                                                            \
+    }                                                                                         \
+  } while (0)
+
+namespace b200 {
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+// Device pointer to a 4-int status block owned by the Python side:
+// [0] first error code, [1] kernel id that raised it, [2..3] free for detail.
+int* status_ptr();
+
+enum SwizzleMode { SWIZZLE_NONE_ = 0, SWIZZLE_128B_ = 3 };
+
+// Returns a pointer to a cached 2D tensor map for a row-major matrix of `rows` x `cols` elements
+// of `elem_bytes` bytes with a row pitch of `ld` elements. The box is box_cols x box_rows.
+// Returns nullptr (and prints why) when the matrix breaks a TMA rule (16-byte base / pitch).
+const CUtensorMap* get_tensor_map_2d(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                     uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle);
+
+int num_sms();
+
+}  // namespace b200

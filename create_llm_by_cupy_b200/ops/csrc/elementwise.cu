@@ -1,0 +1,544 @@
+// Bandwidth-bound kernels of the transformer block: RMSNorm (fwd, dx, dgamma), SwiGLU (fwd, bwd),
+// rotary embedding, embedding gather / scatter-add, residual add. All are 128-bit vectorised,
+// do their arithmetic in fp32 and read every input exactly once.
+//
+// They take the place of the NVRTC-compiled kernels of the reference:
+//   rope_inplace_kernel      model/fast_layers.py:27-61
+//   swiglu_fwd/bwd_kernel    model/fast_layers.py:681-704   (those evaluate exp in fp16; fp32 here)
+//   rmsnorm_fwd/dgamma/dx    model/fast_layers.py:834-1092  (dgamma there walks columns uncoalesced)
+//   TimeEmbedding_shard      model/fast_layers.py:1494-1512
+#include "common.cuh"
+
+namespace b200 {
+
+struct alignas(16) Pack8 {
+  bf162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const Pack8& p, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ Pack8 pack8(const float (&f)[8]) {
+  Pack8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ RMSNorm forward
+// One warp per row; the row stays in registers between the reduction and the scaling pass when
+// it fits (H <= 32 * 8 * NV), otherwise it is read a second time (served by L1/L2).
+template <int NV>
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, bf16* __restrict__ y,
+                   float* __restrict__ rstd, int M, int H, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= M) return;
+  const int nchunk = H >> 3;
+  const Pack8* xr = reinterpret_cast<const Pack8*>(x + size_t(row) * H);
+  const Pack8* gr = reinterpret_cast<const Pack8*>(gamma);
+  Pack8* yr = reinterpret_cast<Pack8*>(y + size_t(row) * H);
+  Pack8 cache[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nchunk) {
+      cache[i] = xr[c];
+      float f[8];
+      unpack8(cache[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+    }
+  }
+  for (int c = lane + NV * 32; c < nchunk; c += 32) {
+    float f[8];
+    unpack8(xr[c], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / float(H) + eps);
+  if (lane == 0) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nchunk) {
+      float f[8], g[8];
+      unpack8(cache[i], f);
+      unpack8(gr[c], g);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = f[e] * r * g[e];
+      yr[c] = pack8(f);
+    }
+  }
+  for (int c = lane + NV * 32; c < nchunk; c += 32) {
+    float f[8], g[8];
+    unpack8(xr[c], f);
+    unpack8(gr[c], g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = f[e] * r * g[e];
+    yr[c] = pack8(f);
+  }
+}
+
+// Any H (used when H is not a multiple of 8).
+__global__ void rmsnorm_fwd_scalar_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                          bf16* __restrict__ y, float* __restrict__ rstd, int M, int H, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;
+  if (row >= M) return;
+  const bf16* xr = x + size_t(row) * H;
+  float ss = 0.f;
+  for (int c = lane; c < H; c += 32) {
+    const float f = __bfloat162float(xr[c]);
+    ss += f * f;
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / float(H) + eps);
+  if (lane == 0) rstd[row] = r;
+  for (int c = lane; c < H; c += 32)
+    y[size_t(row) * H + c] = __float2bfloat16(__bfloat162float(xr[c]) * r * __bfloat162float(gamma[c]));
+}
+
+// ------------------------------------------------------------------ RMSNorm backward
+// dx = rstd * (dy*g - xhat * mean(dy*g*xhat)), xhat = x * rstd; optionally dx += add (the
+// residual-stream gradient). dgamma partials: every warp walks rows grid-stride and keeps its
+// column sums in registers; warps of a CTA are combined in shared memory and each CTA writes one
+// row of `partial` [gridDim.x, H] (coalesced), reduced by rmsnorm_dgamma_reduce_kernel.
+template <int NV>
+__global__ void __launch_bounds__(128)
+rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                   const float* __restrict__ rstd, const bf16* __restrict__ add, bf16* __restrict__ dx,
+                   float* __restrict__ partial, int M, int H) {
+  extern __shared__ float sred[];   // [4][H]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nchunk = H >> 3;
+  const Pack8* gr = reinterpret_cast<const Pack8*>(gamma);
+  float dg[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dg[i][e] = 0.f;
+
+  for (int row = blockIdx.x * 4 + warp; row < M; row += gridDim.x * 4) {
+    const Pack8* dyr = reinterpret_cast<const Pack8*>(dy + size_t(row) * H);
+    const Pack8* xr = reinterpret_cast<const Pack8*>(x + size_t(row) * H);
+    const Pack8* ar = add ? reinterpret_cast<const Pack8*>(add + size_t(row) * H) : nullptr;
+    Pack8* dxr = reinterpret_cast<Pack8*>(dx + size_t(row) * H);
+    const float r = rstd[row];
+    constexpr bool kCache = NV <= 8;   // wider rows are re-read in the second pass (L1/L2 hits)
+    float wdy[kCache ? NV : 1][8], xh[kCache ? NV : 1][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nchunk) {
+        float d[8], xv[8], g[8];
+        unpack8(dyr[c], d);
+        unpack8(xr[c], xv);
+        unpack8(gr[c], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xhe = xv[e] * r, w = d[e] * g[e];
+          if (kCache) { xh[i][e] = xhe; wdy[i][e] = w; }
+          dot += w * xhe;
+          dg[i][e] += d[e] * xhe;
+        }
+      }
+    }
+    dot = warp_sum(dot) / float(H);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nchunk) {
+        float o[8];
+        if (kCache) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = r * (wdy[i][e] - xh[i][e] * dot);
+        } else {
+          float d[8], xv[8], g[8];
+          unpack8(dyr[c], d);
+          unpack8(xr[c], xv);
+          unpack8(gr[c], g);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = r * (d[e] * g[e] - xv[e] * r * dot);
+        }
+        if (ar) {
+          float a[8];
+          unpack8(ar[c], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
+        dxr[c] = pack8(o);
+      }
+    }
+  }
+  // combine the 4 warps of this CTA
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nchunk) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sred[warp * H + c * 8 + e] = dg[i][e];
+    }
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < H; h += blockDim.x)
+    partial[size_t(blockIdx.x) * H + h] = sred[h] + sred[H + h] + sred[2 * H + h] + sred[3 * H + h];
+}
+
+// Generic-H variant: two passes over the row, atomics for dgamma partial rows.
+__global__ void rmsnorm_bwd_scalar_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                          const bf16* __restrict__ gamma, const float* __restrict__ rstd,
+                                          const bf16* __restrict__ add, bf16* __restrict__ dx,
+                                          float* __restrict__ partial, int M, int H) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * 4 + warp; row < M; row += gridDim.x * 4) {
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int c = lane; c < H; c += 32) {
+      const float d = __bfloat162float(dy[size_t(row) * H + c]);
+      const float xh = __bfloat162float(x[size_t(row) * H + c]) * r;
+      dot += d * __bfloat162float(gamma[c]) * xh;
+      atomicAdd(&partial[size_t(blockIdx.x) * H + c], d * xh);
+    }
+    dot = warp_sum(dot) / float(H);
+    for (int c = lane; c < H; c += 32) {
+      const float d = __bfloat162float(dy[size_t(row) * H + c]);
+      const float xh = __bfloat162float(x[size_t(row) * H + c]) * r;
+      float o = r * (d * __bfloat162float(gamma[c]) - xh * dot);
+      if (add) o += __bfloat162float(add[size_t(row) * H + c]);
+      dx[size_t(row) * H + c] = __float2bfloat16(o);
+    }
+  }
+}
+
+__global__ void rmsnorm_dgamma_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dgamma, int nrows,
+                                             int H, int accumulate) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int r = 0; r < nrows; ++r) s += partial[size_t(r) * H + h];
+  if (accumulate) s += __bfloat162float(dgamma[h]);
+  dgamma[h] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gate_val is [M, 2I] with pitch ld: gate = [:, :I], value = [:, I:]. act = silu(gate) * value.
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gv, bf16* __restrict__ act, int M, int I, int ld) {
+  const int chunks = I >> 3;
+  const size_t total = size_t(M) * chunks;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / chunks), c = int(i % chunks);
+    float g[8], v[8];
+    unpack8(*reinterpret_cast<const Pack8*>(gv + size_t(row) * ld + c * 8), g);
+    unpack8(*reinterpret_cast<const Pack8*>(gv + size_t(row) * ld + I + c * 8), v);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.f + __expf(-g[e])) * v[e];
+    *reinterpret_cast<Pack8*>(act + size_t(row) * I + c * 8) = pack8(g);
+  }
+}
+__global__ void swiglu_fwd_scalar_kernel(const bf16* __restrict__ gv, bf16* __restrict__ act, int M, int I, int ld) {
+  const size_t total = size_t(M) * I;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / I), c = int(i % I);
+    const float g = __bfloat162float(gv[size_t(row) * ld + c]);
+    const float v = __bfloat162float(gv[size_t(row) * ld + I + c]);
+    act[i] = __float2bfloat16(g / (1.f + __expf(-g)) * v);
+  }
+}
+// d_gate = dact * value * s * (1 + gate * (1 - s)),  d_value = dact * gate * s,  s = sigmoid(gate)
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ dact, const bf16* __restrict__ gv, bf16* __restrict__ dgv,
+                                  int M, int I, int ld) {
+  const int chunks = I >> 3;
+  const size_t total = size_t(M) * chunks;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / chunks), c = int(i % chunks);
+    float g[8], v[8], d[8], dg[8], dv[8];
+    unpack8(*reinterpret_cast<const Pack8*>(gv + size_t(row) * ld + c * 8), g);
+    unpack8(*reinterpret_cast<const Pack8*>(gv + size_t(row) * ld + I + c * 8), v);
+    unpack8(*reinterpret_cast<const Pack8*>(dact + size_t(row) * I + c * 8), d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float s = 1.f / (1.f + __expf(-g[e]));
+      dg[e] = d[e] * v[e] * s * (1.f + g[e] * (1.f - s));
+      dv[e] = d[e] * g[e] * s;
+    }
+    *reinterpret_cast<Pack8*>(dgv + size_t(row) * ld + c * 8) = pack8(dg);
+    *reinterpret_cast<Pack8*>(dgv + size_t(row) * ld + I + c * 8) = pack8(dv);
+  }
+}
+__global__ void swiglu_bwd_scalar_kernel(const bf16* __restrict__ dact, const bf16* __restrict__ gv,
+                                         bf16* __restrict__ dgv, int M, int I, int ld) {
+  const size_t total = size_t(M) * I;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / I), c = int(i % I);
+    const float g = __bfloat162float(gv[size_t(row) * ld + c]);
+    const float v = __bfloat162float(gv[size_t(row) * ld + I + c]);
+    const float d = __bfloat162float(dact[i]);
+    const float s = 1.f / (1.f + __expf(-g));
+    dgv[size_t(row) * ld + c] = __float2bfloat16(d * v * s * (1.f + g * (1.f - s)));
+    dgv[size_t(row) * ld + I + c] = __float2bfloat16(d * g * s);
+  }
+}
+
+// ------------------------------------------------------------------ rotary embedding
+// cos/sin table [T, D/2] fp32 with freq_j = base^(-2j/D).
+__global__ void rope_table_kernel(float* __restrict__ cs, float* __restrict__ sn, int T, int half, float base) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int t = i / half, j = i % half;
+  const float freq = powf(base, -float(2 * j) / float(2 * half));
+  float s, c;
+  sincosf(float(t) * freq, &s, &c);
+  cs[i] = c;
+  sn[i] = s;
+}
+// In place on `nheads` heads of width D that start at column col0 of a [M, ld] buffer; token m
+// has position pos0 + (m % T). Half-split pairing (j, j + D/2). sign = +1 rotates, -1 un-rotates.
+__global__ void rope_inplace_kernel(bf16* __restrict__ buf, const float* __restrict__ cs, const float* __restrict__ sn,
+                                    int M, int T, int nheads, int D, int ld, int col0, int pos0, float sign) {
+  const int half = D >> 1;
+  const size_t total = size_t(M) * nheads * half;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int j = int(i % half);
+    const int h = int((i / half) % nheads);
+    const int m = int(i / (size_t(half) * nheads));
+    const int pos = pos0 + (m % T);
+    bf16* p = buf + size_t(m) * ld + col0 + h * D + j;
+    const float x1 = __bfloat162float(p[0]), x2 = __bfloat162float(p[half]);
+    const float c = cs[size_t(pos) * half + j], s = sn[size_t(pos) * half + j] * sign;
+    p[0] = __float2bfloat16(x1 * c - x2 * s);
+    p[half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embedding_fwd_kernel(const bf16* __restrict__ W, const int* __restrict__ idx, bf16* __restrict__ out,
+                                     int M, int H, int pad_id) {
+  const int chunks = H >> 3;
+  const size_t total = size_t(M) * chunks;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / chunks), c = int(i % chunks);
+    const int id = idx[row];
+    Pack8 v;
+    if (id == pad_id || id < 0) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v.v[e] = __floats2bfloat162_rn(0.f, 0.f);
+    } else {
+      v = *reinterpret_cast<const Pack8*>(W + size_t(id) * H + c * 8);
+    }
+    *reinterpret_cast<Pack8*>(out + size_t(row) * H + c * 8) = v;
+  }
+}
+__global__ void embedding_fwd_scalar_kernel(const bf16* __restrict__ W, const int* __restrict__ idx,
+                                            bf16* __restrict__ out, int M, int H, int pad_id) {
+  const size_t total = size_t(M) * H;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / H), c = int(i % H);
+    const int id = idx[row];
+    out[i] = (id == pad_id || id < 0) ? __float2bfloat16(0.f) : W[size_t(id) * H + c];
+  }
+}
+// dW[idx[m], :] += dout[m, :] for idx != pad. dW is bf16 (packed atomics) or fp32.
+template <typename TW>
+__global__ void embedding_bwd_kernel(TW* __restrict__ dW, const int* __restrict__ idx, const bf16* __restrict__ dout,
+                                     int M, int H, int pad_id) {
+  const int pairs = H >> 1;
+  const size_t total = size_t(M) * pairs;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int row = int(i / pairs), c = int(i % pairs);
+    const int id = idx[row];
+    if (id == pad_id || id < 0) continue;
+    const bf162 d = *reinterpret_cast<const bf162*>(dout + size_t(row) * H + 2 * c);
+    if constexpr (sizeof(TW) == 2) {
+      atomicAdd(reinterpret_cast<bf162*>(dW + size_t(id) * H + 2 * c), d);
+    } else {
+      const float2 f = __bfloat1622float2(d);
+      atomicAdd(reinterpret_cast<float*>(dW) + size_t(id) * H + 2 * c, f.x);
+      atomicAdd(reinterpret_cast<float*>(dW) + size_t(id) * H + 2 * c + 1, f.y);
+    }
+  }
+}
+
+// out = a + b (bf16, n multiple of 8 handled vectorised; tail scalar)
+__global__ void add_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out,
+                                size_t n) {
+  const size_t chunks = n >> 3;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += size_t(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    unpack8(reinterpret_cast<const Pack8*>(a)[i], x);
+    unpack8(reinterpret_cast<const Pack8*>(b)[i], y);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] += y[e];
+    reinterpret_cast<Pack8*>(out)[i] = pack8(x);
+  }
+  if (blockIdx.x == 0)
+    for (size_t i = (chunks << 3) + threadIdx.x; i < n; i += blockDim.x)
+      out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+}
+
+static inline int grid_for(size_t work_items, int block) {
+  size_t g = (work_items + block - 1) / block;
+  const size_t cap = size_t(num_sms()) * 16;
+  return int(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+B200_API int b200_rmsnorm_fwd(const void* x, const void* gamma, void* y, void* rstd, int M, int H, float eps,
+                              cudaStream_t st) {
+  if (M <= 0) return 0;
+  const dim3 grid((M + 3) / 4), block(128);
+  const bf16* xp = static_cast<const bf16*>(x);
+  const bf16* gp = static_cast<const bf16*>(gamma);
+  bf16* yp = static_cast<bf16*>(y);
+  float* rp = static_cast<float*>(rstd);
+  if (H % 8 != 0) {
+    rmsnorm_fwd_scalar_kernel<<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  } else if (H <= 256) {
+    rmsnorm_fwd_kernel<1><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  } else if (H <= 1024) {
+    rmsnorm_fwd_kernel<4><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  } else if (H <= 2048) {
+    rmsnorm_fwd_kernel<8><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  } else {
+    rmsnorm_fwd_kernel<16><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Number of partial rows rmsnorm_bwd writes; the caller provides `partial` of [that, H] fp32.
+B200_API int b200_rmsnorm_bwd_partial_rows(int M) {
+  int g = (M + 3) / 4;
+  const int cap = num_sms() * 2;
+  return g < cap ? (g < 1 ? 1 : g) : cap;
+}
+
+B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const void* rstd, const void* add,
+                              void* dx, void* dgamma, void* partial, int M, int H, int accumulate_dgamma,
+                              cudaStream_t st) {
+  if (M <= 0) return 0;
+  const int rows = b200_rmsnorm_bwd_partial_rows(M);
+  const bf16* dyp = static_cast<const bf16*>(dy);
+  const bf16* xp = static_cast<const bf16*>(x);
+  const bf16* gp = static_cast<const bf16*>(gamma);
+  const float* rp = static_cast<const float*>(rstd);
+  const bf16* ap = static_cast<const bf16*>(add);
+  bf16* dxp = static_cast<bf16*>(dx);
+  float* pp = static_cast<float*>(partial);
+  const size_t smem = size_t(4) * H * sizeof(float);
+  if (H % 8 != 0 || H > 4096) {
+    B200_CHECK(cudaMemsetAsync(pp, 0, size_t(rows) * H * sizeof(float), st));
+    rmsnorm_bwd_scalar_kernel<<<rows, 128, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  } else if (H <= 256) {
+    rmsnorm_bwd_kernel<1><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  } else if (H <= 1024) {
+    rmsnorm_bwd_kernel<4><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  } else if (H <= 2048) {
+    rmsnorm_bwd_kernel<8><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      configured = true;
+    }
+    rmsnorm_bwd_kernel<16><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  }
+  B200_CHECK(cudaGetLastError());
+  rmsnorm_dgamma_reduce_kernel<<<(H + 127) / 128, 128, 0, st>>>(pp, static_cast<bf16*>(dgamma), rows, H,
+                                                                 accumulate_dgamma);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_swiglu_fwd(const void* gate_val, void* act, int M, int I, int ld, cudaStream_t st) {
+  if (M <= 0 || I <= 0) return 0;
+  const bf16* g = static_cast<const bf16*>(gate_val);
+  const bool vec = (I % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0);
+  if (vec) swiglu_fwd_kernel<<<grid_for(size_t(M) * (I / 8), 256), 256, 0, st>>>(g, static_cast<bf16*>(act), M, I, ld);
+  else swiglu_fwd_scalar_kernel<<<grid_for(size_t(M) * I, 256), 256, 0, st>>>(g, static_cast<bf16*>(act), M, I, ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_swiglu_bwd(const void* dact, const void* gate_val, void* d_gate_val, int M, int I, int ld,
+                             cudaStream_t st) {
+  if (M <= 0 || I <= 0) return 0;
+  const bf16* g = static_cast<const bf16*>(gate_val);
+  const bool vec = (I % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(g) & 15) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(d_gate_val) & 15) == 0);
+  if (vec)
+    swiglu_bwd_kernel<<<grid_for(size_t(M) * (I / 8), 256), 256, 0, st>>>(static_cast<const bf16*>(dact), g,
+                                                                           static_cast<bf16*>(d_gate_val), M, I, ld);
+  else
+    swiglu_bwd_scalar_kernel<<<grid_for(size_t(M) * I, 256), 256, 0, st>>>(static_cast<const bf16*>(dact), g,
+                                                                            static_cast<bf16*>(d_gate_val), M, I, ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_rope_table(void* cs, void* sn, int T, int D, float base, cudaStream_t st) {
+  const int half = D / 2;
+  const int n = T * half;
+  if (n <= 0) return 0;
+  rope_table_kernel<<<(n + 255) / 256, 256, 0, st>>>(static_cast<float*>(cs), static_cast<float*>(sn), T, half, base);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_rope_inplace(void* buf, const void* cs, const void* sn, int M, int T, int nheads, int D, int ld,
+                               int col0, int pos0, int inverse, cudaStream_t st) {
+  const size_t total = size_t(M) * nheads * (D / 2);
+  if (total == 0) return 0;
+  rope_inplace_kernel<<<grid_for(total, 256), 256, 0, st>>>(static_cast<bf16*>(buf), static_cast<const float*>(cs),
+                                                            static_cast<const float*>(sn), M, T, nheads, D, ld, col0,
+                                                            pos0, inverse ? -1.f : 1.f);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_embedding_fwd(const void* W, const void* idx, void* out, int M, int H, int pad_id,
+                                cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (H % 8 == 0)
+    embedding_fwd_kernel<<<grid_for(size_t(M) * (H / 8), 256), 256, 0, st>>>(
+        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id);
+  else
+    embedding_fwd_scalar_kernel<<<grid_for(size_t(M) * H, 256), 256, 0, st>>>(
+        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// H must be even. dw_fp32 selects the dtype of dW.
+B200_API int b200_embedding_bwd(void* dW, const void* idx, const void* dout, int M, int H, int pad_id, int dw_fp32,
+                                cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (H % 2 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const int grid = grid_for(size_t(M) * (H / 2), 256);
+  if (dw_fp32)
+    embedding_bwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(dW), static_cast<const int*>(idx),
+                                                      static_cast<const bf16*>(dout), M, H, pad_id);
+  else
+    embedding_bwd_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<bf16*>(dW), static_cast<const int*>(idx),
+                                                     static_cast<const bf16*>(dout), M, H, pad_id);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t st) {
+  if (n <= 0) return 0;
+  add_bf16_kernel<<<grid_for(size_t(n) / 8 + 1, 256), 256, 0, st>>>(static_cast<const bf16*>(a),
+                                                                    static_cast<const bf16*>(b),
+                                                                    static_cast<bf16*>(out), size_t(n));
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,77 @@
+"""bf16 GEMM front end: tcgen05 kernel on CUDA tensors, fp32 torch restatement on CPU tensors.
+
+Replaces the ``cp.matmul`` (cuBLAS) call sites of the reference
+(model/fast_layers.py:217,341,420,423,457,458,736,748,794,797,813,815,1328,1351,1435,1464,1471).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import native
+
+GEMM_OUT_F32 = 1
+GEMM_ADD_C = 2
+
+def _rowmajor_2d(t: torch.Tensor) -> tuple[torch.Tensor, int]:
+    """Return (tensor, pitch) for a 2-D view whose last dim is contiguous; copy if it is not."""
+    assert t.dim() == 2
+    if t.stride(1) != 1 or (t.size(0) > 1 and t.stride(0) < t.size(1)):
+        t = t.contiguous()
+    return t, (t.stride(0) if t.size(0) > 1 else max(t.size(1), t.stride(0)))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+         out: torch.Tensor | None = None, add: torch.Tensor | None = None,
+         out_dtype: torch.dtype | None = None, alpha: float = 1.0, bn: int = 0,
+         max_ctas: int = 0, force_fallback: bool = False) -> torch.Tensor:
+    """``out = alpha * op(a) @ op(b) (+ add)``.
+
+    ``a`` is ``[M, K]`` (``[K, M]`` with ``trans_a``); ``b`` is ``[K, N]`` (``[N, K]`` with
+    ``trans_b``). Inputs are bf16 on CUDA; ``out``/``add`` are bf16 or fp32 (same dtype) and
+    ``add`` may alias ``out`` (accumulation). Accumulation is fp32 in TMEM.
+    """
+    M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    Kb, N = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+    if K != Kb:
+        raise ValueError(f"gemm: inner dims differ ({K} vs {Kb})")
+    if out_dtype is None:
+        out_dtype = out.dtype if out is not None else (add.dtype if add is not None else a.dtype)
+
+    if not a.is_cuda:
+        af = a.float().t() if trans_a else a.float()
+        bf = b.float().t() if trans_b else b.float()
+        res = (af @ bf) * alpha
+        if add is not None:
+            res = res + add.float()
+        res = res.to(out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm: CUDA operands must be bf16")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("gemm: out dtype must be bf16 or fp32")
+    a, lda = _rowmajor_2d(a)
+    b, ldb = _rowmajor_2d(b)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    assert out.dim() == 2 and out.shape == (M, N) and out.stride(1) == 1 and out.dtype == out_dtype
+    ldd = out.stride(0) if M > 1 else max(N, out.stride(0))
+    flags = GEMM_OUT_F32 if out_dtype == torch.float32 else 0
+    ldc = 0
+    if add is not None:
+        assert add.shape == (M, N) and add.stride(1) == 1 and add.dtype == out_dtype
+        ldc = add.stride(0) if M > 1 else max(N, add.stride(0))
+        flags |= GEMM_ADD_C
+    native.status_tensor()
+    rc = native.lib().b200_gemm_bf16(
+        native.ptr(a), native.ptr(b), native.ptr(out), native.ptr(add),
+        M, N, K, lda, ldb, ldd, ldc, int(trans_a), int(not trans_b), flags,
+        ctypes.c_float(alpha), bn, max_ctas, int(force_fallback), native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16")
+    native.bump()
+    return out
