@@ -1,0 +1,489 @@
+"""Operator front ends used by the layers.
+
+Every function has two bodies: CUDA tensors go to the hand-written sm_100a kernels of the native
+library (bf16 storage, fp32 arithmetic); CPU tensors take a plain torch restatement of the same
+math in the tensor's own dtype. The CPU body is what the NumPy-oracle comparison, the gloo
+multi-process tests and the CPU smoke configuration run; it is never used for CUDA tensors.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import native
+from .gemm import gemm  # noqa: F401  (re-exported)
+
+_f = ctypes.c_float
+
+
+def _lib():
+    native.status_tensor()
+    return native.lib()
+
+
+def _bf16(*ts):
+    for t in ts:
+        if t is not None and t.dtype != torch.bfloat16:
+            raise TypeError("native kernels take bf16 tensors")
+
+
+# --------------------------------------------------------------------------- RMSNorm
+def rmsnorm_fwd(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6):
+    """y = x * rsqrt(mean(x^2) + eps) * gamma over the last dim. Returns (y, rstd[M] fp32)."""
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    M = x2.shape[0]
+    if not x.is_cuda:
+        xf = x2.float()
+        rstd = torch.rsqrt(xf.pow(2).mean(-1) + eps)
+        y = (xf * rstd[:, None] * gamma.float()).to(x.dtype)
+        return y.view(x.shape), rstd
+    _bf16(x, gamma)
+    x2 = x2.contiguous()
+    y = torch.empty_like(x2)
+    rstd = torch.empty(M, dtype=torch.float32, device=x.device)
+    native.check(_lib().b200_rmsnorm_fwd(native.ptr(x2), native.ptr(gamma), native.ptr(y), native.ptr(rstd),
+                                         M, H, _f(eps), native.stream_ptr()), "rmsnorm_fwd")
+    native.bump()
+    return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, gamma: torch.Tensor, rstd: torch.Tensor,
+                add: torch.Tensor | None = None):
+    """Returns (dx (+ add), dgamma). ``x`` is the layer INPUT; ``add`` is the residual gradient."""
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    dy2 = dy.reshape(-1, H)
+    M = x2.shape[0]
+    if not x.is_cuda:
+        xf, dyf, g = x2.float(), dy2.float(), gamma.float()
+        xh = xf * rstd[:, None]
+        wdy = dyf * g
+        dx = rstd[:, None] * (wdy - xh * (wdy * xh).mean(-1, keepdim=True))
+        if add is not None:
+            dx = dx + add.reshape(-1, H).float()
+        dgamma = (dyf * xh).sum(0)
+        return dx.to(x.dtype).view(x.shape), dgamma.to(gamma.dtype)
+    _bf16(dy, x, gamma, add)
+    x2 = x2.contiguous()
+    dy2 = dy2.contiguous()
+    add2 = add.reshape(-1, H).contiguous() if add is not None else None
+    dx = torch.empty_like(x2)
+    dgamma = torch.empty_like(gamma)
+    lib = _lib()
+    rows = lib.b200_rmsnorm_bwd_partial_rows(M)
+    partial = torch.empty((rows, H), dtype=torch.float32, device=x.device)
+    native.check(lib.b200_rmsnorm_bwd(native.ptr(dy2), native.ptr(x2), native.ptr(gamma), native.ptr(rstd),
+                                      native.ptr(add2), native.ptr(dx), native.ptr(dgamma), native.ptr(partial),
+                                      M, H, 0, native.stream_ptr()), "rmsnorm_bwd")
+    native.bump(2)
+    return dx.view(x.shape), dgamma
+
+
+# --------------------------------------------------------------------------- SwiGLU
+def swiglu_fwd(gate_val: torch.Tensor) -> torch.Tensor:
+    """gate_val [M, 2I] = [gate | value] -> silu(gate) * value  [M, I]."""
+    M, two_i = gate_val.shape
+    I = two_i // 2
+    if not gate_val.is_cuda:
+        g, v = gate_val[:, :I].float(), gate_val[:, I:].float()
+        return (torch.nn.functional.silu(g) * v).to(gate_val.dtype)
+    _bf16(gate_val)
+    assert gate_val.stride(1) == 1
+    act = torch.empty((M, I), dtype=gate_val.dtype, device=gate_val.device)
+    native.check(_lib().b200_swiglu_fwd(native.ptr(gate_val), native.ptr(act), M, I, gate_val.stride(0),
+                                        native.stream_ptr()), "swiglu_fwd")
+    native.bump()
+    return act
+
+
+def swiglu_bwd(dact: torch.Tensor, gate_val: torch.Tensor) -> torch.Tensor:
+    M, two_i = gate_val.shape
+    I = two_i // 2
+    if not gate_val.is_cuda:
+        g, v, d = gate_val[:, :I].float(), gate_val[:, I:].float(), dact.float()
+        s = torch.sigmoid(g)
+        dg = d * v * s * (1 + g * (1 - s))
+        dv = d * g * s
+        return torch.cat([dg, dv], 1).to(gate_val.dtype)
+    _bf16(dact, gate_val)
+    assert gate_val.is_contiguous()
+    dact = dact.contiguous()
+    out = torch.empty_like(gate_val)
+    native.check(_lib().b200_swiglu_bwd(native.ptr(dact), native.ptr(gate_val), native.ptr(out), M, I,
+                                        gate_val.stride(0), native.stream_ptr()), "swiglu_bwd")
+    native.bump()
+    return out
+
+
+# --------------------------------------------------------------------------- RoPE
+_rope_cache: dict = {}
+
+
+def rope_table(T: int, D: int, base: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [T, D/2] fp32 with freq_j = base^(-2j/D)."""
+    device = torch.device(device)
+    key = (T, D, float(base), device.type, device.index)
+    hit = _rope_cache.get(key)
+    if hit is not None:
+        return hit
+    if device.type != "cuda":
+        j = torch.arange(D // 2, dtype=torch.float32)
+        freq = torch.pow(torch.tensor(float(base)), -2.0 * j / D)
+        ang = torch.arange(T, dtype=torch.float32)[:, None] * freq[None, :]
+        res = (torch.cos(ang), torch.sin(ang))
+    else:
+        cs = torch.empty((T, D // 2), dtype=torch.float32, device=device)
+        sn = torch.empty_like(cs)
+        native.check(_lib().b200_rope_table(native.ptr(cs), native.ptr(sn), T, D, _f(base), native.stream_ptr()),
+                     "rope_table")
+        native.bump()
+        res = (cs, sn)
+    _rope_cache[key] = res
+    return res
+
+
+def rope_inplace(buf: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, T: int, nheads: int, D: int,
+                 col0: int = 0, pos0: int = 0, inverse: bool = False) -> torch.Tensor:
+    """Rotate ``nheads`` heads of width D starting at column ``col0`` of a [M, ld] buffer in place.
+
+    Token m sits at position pos0 + (m % T). Half-split pairing (j, j + D/2).
+    """
+    M = buf.shape[0]
+    if not buf.is_cuda:
+        pos = pos0 + (torch.arange(M) % T)
+        c = cos[pos][:, None, :]
+        s = sin[pos][:, None, :] * (-1.0 if inverse else 1.0)
+        v = buf[:, col0:col0 + nheads * D].reshape(M, nheads, D).float()
+        x1, x2 = v[..., :D // 2], v[..., D // 2:]
+        out = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).reshape(M, nheads * D)
+        buf[:, col0:col0 + nheads * D] = out.to(buf.dtype)
+        return buf
+    _bf16(buf)
+    assert buf.stride(1) == 1
+    native.check(_lib().b200_rope_inplace(native.ptr(buf), native.ptr(cos), native.ptr(sin), M, T, nheads, D,
+                                          buf.stride(0), col0, pos0, int(inverse), native.stream_ptr()),
+                 "rope_inplace")
+    native.bump()
+    return buf
+
+
+# --------------------------------------------------------------------------- embedding
+def embedding_fwd(W: torch.Tensor, idx: torch.Tensor, pad_id: int) -> torch.Tensor:
+    """out[m] = W[idx[m]], zeros where idx == pad_id. idx is int32 [M]."""
+    M = idx.numel()
+    H = W.shape[1]
+    if not W.is_cuda:
+        out = W[idx.long().clamp_min(0)]
+        out = out * (idx != pad_id).to(out.dtype)[:, None]
+        return out
+    _bf16(W)
+    assert idx.dtype == torch.int32 and W.is_contiguous()
+    out = torch.empty((M, H), dtype=W.dtype, device=W.device)
+    native.check(_lib().b200_embedding_fwd(native.ptr(W), native.ptr(idx), native.ptr(out), M, H, pad_id,
+                                           native.stream_ptr()), "embedding_fwd")
+    native.bump()
+    return out
+
+
+def embedding_bwd(dW: torch.Tensor, idx: torch.Tensor, dout: torch.Tensor, pad_id: int) -> torch.Tensor:
+    """dW[idx[m]] += dout[m] for idx != pad_id (dW is bf16 or fp32, updated in place)."""
+    M = idx.numel()
+    H = dW.shape[1]
+    if not dW.is_cuda:
+        keep = idx != pad_id
+        dW.index_add_(0, idx[keep].long(), dout[keep].to(dW.dtype))
+        return dW
+    _bf16(dout)
+    assert idx.dtype == torch.int32 and dW.is_contiguous()
+    dout = dout.contiguous()
+    native.check(_lib().b200_embedding_bwd(native.ptr(dW), native.ptr(idx), native.ptr(dout), M, H, pad_id,
+                                           int(dW.dtype == torch.float32), native.stream_ptr()), "embedding_bwd")
+    native.bump()
+    return dW
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if not a.is_cuda:
+        r = a + b
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    _bf16(a, b)
+    a = a.contiguous()
+    b = b.contiguous()
+    if out is None:
+        out = torch.empty_like(a)
+    native.check(_lib().b200_add_bf16(native.ptr(a), native.ptr(b), native.ptr(out), ctypes.c_longlong(a.numel()),
+                                      native.stream_ptr()), "add_bf16")
+    native.bump()
+    return out
+
+
+# --------------------------------------------------------------------------- flash attention
+def _strides3(t: torch.Tensor) -> list[int]:
+    """(batch, token, head) element strides of a [B, T, heads, D] view."""
+    assert t.dim() == 4 and t.stride(3) == 1
+    return [t.stride(0), t.stride(1), t.stride(2)]
+
+
+def _attn_reference(q, k, v, valid_len, scale, cos, sin):
+    """fp32 dense restatement on [B, T, heads, D] views; returns (o, lse, probs, q_rot, k_rot)."""
+    B, T, QH, D = q.shape
+    KVH = k.shape[2]
+    R = QH // KVH
+    qf, kf, vf = q.float(), k.float(), v.float()
+    if cos is not None:
+        def rot(x):
+            c, s = cos[:T][None, :, None, :], sin[:T][None, :, None, :]
+            x1, x2 = x[..., :D // 2], x[..., D // 2:]
+            return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
+        qf, kf = rot(qf), rot(kf)
+    kx = kf.repeat_interleave(R, dim=2)
+    vx = vf.repeat_interleave(R, dim=2)
+    s = torch.einsum("bthd,bshd->bhts", qf, kx) * scale
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device).tril()[None, None]
+    if valid_len is not None:
+        keyok = torch.arange(T, device=q.device)[None, :] < valid_len[:, None]
+        mask = mask & keyok[:, None, None, :]
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    p = torch.exp(s - lse[..., None])
+    p = torch.nan_to_num(p, nan=0.0)
+    o = torch.einsum("bhts,bshd->bthd", p, vx)
+    return o, lse, p, qf, kf
+
+
+def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
+    """Causal GQA attention. q [B,T,QH,D], k/v [B,T,KVH,D] (any strides with unit last stride).
+
+    ``rope`` = (cos, sin) tables [>=T, D/2] rotates Q and K inside the kernel. Returns
+    (o [B,T,QH,D] contiguous, lse [B,QH,T] fp32).
+    """
+    B, T, QH, D = q.shape
+    KVH = k.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    cos, sin = rope if rope is not None else (None, None)
+    if not q.is_cuda:
+        o, lse, _, _, _ = _attn_reference(q, k, v, valid_len, scale, cos, sin)
+        return o.to(q.dtype), lse
+    _bf16(q, k, v)
+    o = torch.empty((B, T, QH, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
+    strides = _strides3(q) + _strides3(k) + _strides3(v) + _strides3(o)
+    arr = (ctypes.c_longlong * 24)(*(strides + [0] * 12))
+    native.check(_lib().b200_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse),
+                                       native.ptr(valid_len), native.ptr(cos), native.ptr(sin), arr,
+                                       B, T, QH, KVH, D, _f(scale), native.stream_ptr()), "flash_fwd")
+    native.bump()
+    return o, lse
+
+
+def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None):
+    """Gradients (dq, dk, dv) w.r.t. the UN-rotated q, k and v.
+
+    ``out`` may give three preallocated [B,T,heads,D] views (e.g. slices of a packed d(KQV)
+    buffer) to write into.
+    """
+    B, T, QH, D = q.shape
+    KVH = k.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    cos, sin = rope if rope is not None else (None, None)
+    if not q.is_cuda:
+        R = QH // KVH
+        _, _, p, qf, kf = _attn_reference(q, k, v, valid_len, scale, cos, sin)
+        dof = dout.float()
+        vx = v.float().repeat_interleave(R, dim=2)
+        kx = kf.repeat_interleave(R, dim=2)
+        dvx = torch.einsum("bhts,bthd->bshd", p, dof)
+        dp = torch.einsum("bthd,bshd->bhts", dof, vx)
+        delta = (dof * o.float()).sum(-1).permute(0, 2, 1)          # [B, QH, T]
+        ds = p * (dp - delta[..., None]) * scale
+        dqf = torch.einsum("bhts,bshd->bthd", ds, kx)
+        dkx = torch.einsum("bhts,bthd->bshd", ds, qf)
+        dk_ = dkx.reshape(B, T, KVH, R, D).sum(3)
+        dv_ = dvx.reshape(B, T, KVH, R, D).sum(3)
+        if cos is not None:
+            def unrot(x):
+                c, s = cos[:T][None, :, None, :], sin[:T][None, :, None, :]
+                y1, y2 = x[..., :D // 2], x[..., D // 2:]
+                return torch.cat([y1 * c + y2 * s, y2 * c - y1 * s], -1)
+            dqf, dk_ = unrot(dqf), unrot(dk_)
+        res = (dqf.to(q.dtype), dk_.to(q.dtype), dv_.to(q.dtype))
+        if out is not None:
+            for dst, src in zip(out, res):
+                dst.copy_(src)
+            return out
+        return res
+    _bf16(dout, q, k, v, o)
+    if dout.stride(3) != 1:
+        dout = dout.contiguous()
+    if out is None:
+        dq = torch.empty((B, T, QH, D), dtype=q.dtype, device=q.device)
+        dk_ = torch.empty((B, T, KVH, D), dtype=q.dtype, device=q.device)
+        dv_ = torch.empty((B, T, KVH, D), dtype=q.dtype, device=q.device)
+    else:
+        dq, dk_, dv_ = out
+    delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
+    strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +
+               _strides3(dq) + _strides3(dk_) + _strides3(dv_))
+    arr = (ctypes.c_longlong * 24)(*strides)
+    native.check(_lib().b200_flash_bwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(dout),
+                                       native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
+                                       native.ptr(dv_), native.ptr(valid_len), native.ptr(cos), native.ptr(sin), arr,
+                                       B, T, QH, KVH, D, _f(scale), native.stream_ptr()), "flash_bwd")
+    native.bump(3)
+    return dq, dk_, dv_
+
+
+def decode_attn(q, kcache, vcache, lens, scale=None):
+    """One-token attention against a KV cache. q [B,QH,D]; caches [B,KVH,Tmax,D]; lens int32 [B]."""
+    B, QH, D = q.shape
+    KVH, Tmax = kcache.shape[1], kcache.shape[2]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        R = QH // KVH
+        kx = kcache.float().repeat_interleave(R, dim=1)
+        vx = vcache.float().repeat_interleave(R, dim=1)
+        s = torch.einsum("bhd,bhtd->bht", q.float(), kx) * scale
+        ok = torch.arange(Tmax)[None, None, :] < lens[:, None, None]
+        s = s.masked_fill(~ok, float("-inf"))
+        p = torch.softmax(s, -1)
+        return torch.einsum("bht,bhtd->bhd", p, vx).to(q.dtype)
+    _bf16(q, kcache, vcache)
+    assert q.is_contiguous() and kcache.is_contiguous() and vcache.is_contiguous() and lens.dtype == torch.int32
+    out = torch.empty_like(q)
+    native.check(_lib().b200_decode_attn(native.ptr(q), native.ptr(kcache), native.ptr(vcache), native.ptr(out),
+                                         native.ptr(lens), B, QH, KVH, Tmax, D, _f(scale), native.stream_ptr()),
+                 "decode_attn")
+    native.bump()
+    return out
+
+
+# --------------------------------------------------------------------------- cross-entropy rows
+def ce_stats(logits, targets, rmax, rsum, tlogit, col0: int, first: bool):
+    """Fold one fp32 logits chunk [M, C] (vocab ids col0..col0+C) into the running row statistics."""
+    M, C = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        mx = lf.max(-1).values
+        old = torch.full_like(mx, float("-inf")) if first else rmax.clone()
+        new = torch.maximum(old, mx)
+        s = torch.exp(lf - new[:, None]).sum(-1)
+        olds = torch.zeros_like(s) if first else rsum
+        rsum.copy_(olds * torch.exp(old - new) + s)
+        rmax.copy_(new)
+        t = targets.long() - col0
+        hit = (t >= 0) & (t < C)
+        rows = torch.nonzero(hit).flatten()
+        tlogit[rows] = lf[rows, t[rows]]
+        return
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and targets.dtype == torch.int32
+    native.check(_lib().b200_ce_stats(native.ptr(logits), native.ptr(targets), native.ptr(rmax), native.ptr(rsum),
+                                      native.ptr(tlogit), M, C, logits.stride(0), col0, int(first),
+                                      native.stream_ptr()), "ce_stats")
+    native.bump()
+
+
+def ce_loss(rmax, rsum, tlogit, targets, pad_id: int) -> torch.Tensor:
+    """Returns a 2-float tensor [sum of row losses over valid rows, number of valid rows]."""
+    M = targets.numel()
+    if not rmax.is_cuda:
+        valid = (targets != pad_id) & (targets >= 0)
+        loss = (rmax + torch.log(rsum) - tlogit)[valid].sum()
+        return torch.stack([loss, valid.sum().float()])
+    out = torch.zeros(2, dtype=torch.float32, device=rmax.device)
+    native.check(_lib().b200_ce_loss(native.ptr(rmax), native.ptr(rsum), native.ptr(tlogit), native.ptr(targets),
+                                     native.ptr(out), M, pad_id, native.stream_ptr()), "ce_loss")
+    native.bump()
+    return out
+
+
+def ce_dlogits(logits, targets, rmax, rsum, loss_cnt, col0: int, pad_id: int, gscale: float, out_dtype):
+    """(softmax - onehot) * valid * gscale / n_valid for one logits chunk, in ``out_dtype``."""
+    M, C = logits.shape
+    if not logits.is_cuda:
+        p = torch.exp(logits.float() - rmax[:, None]) / rsum[:, None]
+        t = targets.long() - col0
+        hit = (t >= 0) & (t < C)
+        rows = torch.nonzero(hit).flatten()
+        p[rows, t[rows]] -= 1.0
+        valid = ((targets != pad_id) & (targets >= 0)).float()
+        p = p * (valid * gscale / loss_cnt[1].clamp_min(1.0))[:, None]
+        return p.to(out_dtype)
+    assert out_dtype == torch.bfloat16
+    out = torch.empty((M, C), dtype=torch.bfloat16, device=logits.device)
+    native.check(_lib().b200_ce_dlogits(native.ptr(logits), native.ptr(targets), native.ptr(rmax), native.ptr(rsum),
+                                        native.ptr(loss_cnt), native.ptr(out), M, C, logits.stride(0), C, col0,
+                                        pad_id, _f(gscale), native.stream_ptr()), "ce_dlogits")
+    native.bump()
+    return out
+
+
+# --------------------------------------------------------------------------- optimizer side
+def adamw_step(grad, m, v, master, param, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+               max_grad_norm=0.0, stats=None):
+    """In-place AdamW on a flat shard: fp32 master/m/v, bf16 (or same-dtype) param written back.
+
+    ``stats`` = device tensor [sum g^2 (unscaled), non-finite flag]: when given, the clip
+    coefficient min(1, max_norm / (sqrt(stats[0]) * grad_scale + 1e-6)) is applied and the whole
+    update is skipped if stats[1] != 0, both decided on the device.
+    """
+    m_corr = 1.0 / (1.0 - beta1 ** step)
+    v_corr = 1.0 / (1.0 - beta2 ** step)
+    n = grad.numel()
+    if not grad.is_cuda:
+        gmul = grad_scale
+        if stats is not None:
+            if float(stats[1]) != 0.0:
+                return
+            if max_grad_norm > 0:
+                norm = math.sqrt(float(stats[0])) * grad_scale
+                gmul *= min(1.0, max_grad_norm / (norm + 1e-6))
+        g = grad.float() * gmul
+        m.mul_(beta1).add_(g, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        if weight_decay > 0:
+            master.mul_(1 - lr * weight_decay)
+        master.sub_(lr * (m * m_corr) / (torch.sqrt(v * v_corr) + eps))
+        param.copy_(master.to(param.dtype))
+        return
+    assert param.dtype == torch.bfloat16 and grad.dtype in (torch.bfloat16, torch.float32)
+    assert all(t.is_contiguous() for t in (grad, m, v, master, param))
+    native.check(_lib().b200_adamw(native.ptr(grad), int(grad.dtype == torch.float32), native.ptr(m), native.ptr(v),
+                                   native.ptr(master), native.ptr(param), ctypes.c_longlong(n), _f(lr), _f(beta1),
+                                   _f(beta2), _f(eps), _f(weight_decay), _f(m_corr), _f(v_corr), _f(grad_scale),
+                                   _f(max_grad_norm), native.ptr(stats), native.stream_ptr()), "adamw")
+    native.bump()
+
+
+def grad_stats(g: torch.Tensor, stats: torch.Tensor) -> None:
+    """stats[0] += sum of squares of the finite entries of g; stats[1] = 1 if any is NaN/Inf."""
+    if not g.is_cuda:
+        gf = g.float()
+        fin = torch.isfinite(gf)
+        stats[0] += (gf[fin] ** 2).sum()
+        if not bool(fin.all()):
+            stats[1] = 1.0
+        return
+    assert g.is_contiguous() and stats.dtype == torch.float32
+    native.check(_lib().b200_grad_stats(native.ptr(g), int(g.dtype == torch.float32), ctypes.c_longlong(g.numel()),
+                                        native.ptr(stats), native.stream_ptr()), "grad_stats")
+    native.bump()
+
+
+def accumulate(acc: torch.Tensor, g: torch.Tensor, scale: float = 1.0) -> None:
+    """acc (fp32) += g * scale."""
+    if not acc.is_cuda:
+        acc.add_(g.float(), alpha=scale)
+        return
+    assert acc.dtype == torch.float32 and acc.is_contiguous() and g.is_contiguous()
+    native.check(_lib().b200_accumulate(native.ptr(acc), native.ptr(g), int(g.dtype == torch.float32),
+                                        ctypes.c_longlong(acc.numel()), _f(scale), native.stream_ptr()), "accumulate")
+    native.bump()

@@ -1,0 +1,201 @@
+"""Numerics of every native kernel against the fp32 PyTorch restatement of the same op.
+
+The reference of each op is the CPU body of the same front-end function, fed fp32 copies of the
+bf16 inputs, so the comparison isolates the kernel (not input rounding).
+"""
+import math
+
+import pytest
+import torch
+
+from create_llm_by_cupy_b200.ops import functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bf(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16)
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a = a.float().cpu()
+    b = b.float().cpu()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"max err {err} vs ref scale {ref}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 328, 136), (1000, 520, 264), (72, 40, 8), (64, 100, 33)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm(M, N, K, ta, tb):
+    a = bf(*((K, M) if ta else (M, K)), seed=1)
+    b = bf(*((N, K) if tb else (K, N)), seed=2)
+    ref = F.gemm(a.float(), b.float(), trans_a=ta, trans_b=tb)
+    out = F.gemm(a.to(DEV), b.to(DEV), trans_a=ta, trans_b=tb)
+    close(out, ref, rtol=1e-2, atol=1e-2)
+    assert F.native.read_status() == (0, 0)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_accumulate_and_fp32(bn):
+    a, b = bf(300, 264, seed=3), bf(264, 520, seed=4)
+    c = torch.randn(300, 520)
+    ref = a.float() @ b.float() * 0.5 + c
+    out = F.gemm(a.to(DEV), b.to(DEV), add=c.to(DEV), out_dtype=torch.float32, alpha=0.5, bn=bn)
+    close(out, ref, rtol=1e-5, atol=1e-3)
+    # accumulate in place, bf16
+    acc = c.to(torch.bfloat16).to(DEV)
+    F.gemm(a.to(DEV), b.to(DEV), out=acc, add=acc, bn=bn)
+    close(acc, a.float() @ b.float() + c.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+
+def test_gemm_canary_bounds():
+    """Output rows/cols outside the logical matrix must stay untouched (ragged tile edges)."""
+    M, N, K = 130, 264, 72
+    a, b = bf(M, K, seed=5).to(DEV), bf(K, N, seed=6).to(DEV)
+    big = torch.full((M + 2, N + 16), 7.0, dtype=torch.bfloat16, device=DEV)
+    view = big[1:M + 1, 8:8 + N]
+    F.gemm(a, b, out=view)
+    torch.cuda.synchronize()
+    assert (big[0] == 7).all() and (big[-1] == 7).all()
+    assert (big[:, :8] == 7).all() and (big[:, 8 + N:] == 7).all()
+    close(view, a.float().cpu() @ b.float().cpu(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("M,H", [(37, 128), (512, 2048), (64, 4096), (9, 100)])
+def test_rmsnorm(M, H):
+    x, g, dy, res = bf(M, H, seed=1), bf(H, seed=2) * 0.1 + 1, bf(M, H, seed=3), bf(M, H, seed=4)
+    y_ref, r_ref = F.rmsnorm_fwd(x.float(), g.float())
+    y, r = F.rmsnorm_fwd(x.to(DEV), g.to(DEV))
+    close(y, y_ref)
+    close(r, r_ref, rtol=1e-4, atol=1e-5)
+    dx_ref, dg_ref = F.rmsnorm_bwd(dy.float(), x.float(), g.float(), r_ref, add=res.float())
+    dx, dg = F.rmsnorm_bwd(dy.to(DEV), x.to(DEV), g.to(DEV), r, add=res.to(DEV))
+    close(dx, dx_ref)
+    close(dg, dg_ref, rtol=2e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("M,I", [(33, 512), (256, 5504), (7, 37)])
+def test_swiglu(M, I):
+    gv, d = bf(M, 2 * I, seed=1), bf(M, I, seed=2)
+    close(F.swiglu_fwd(gv.to(DEV)), F.swiglu_fwd(gv.float()))
+    close(F.swiglu_bwd(d.to(DEV), gv.to(DEV)), F.swiglu_bwd(d.float(), gv.float()))
+
+
+def test_rope_roundtrip_and_reference():
+    T, D, H = 64, 32, 6
+    buf = bf(2 * T, 8 + H * D, seed=1)
+    cos_c, sin_c = F.rope_table(T, D, 10000.0, "cpu")
+    cos_g, sin_g = F.rope_table(T, D, 10000.0, DEV)
+    close(cos_g, cos_c, rtol=1e-4, atol=1e-4)
+    ref = F.rope_inplace(buf.float().clone(), cos_c, sin_c, T, H, D, col0=8)
+    out = F.rope_inplace(buf.to(DEV).clone(), cos_g, sin_g, T, H, D, col0=8)
+    close(out, ref)
+    back = F.rope_inplace(out.clone(), cos_g, sin_g, T, H, D, col0=8, inverse=True)
+    close(back, buf, rtol=3e-2, atol=3e-2)
+
+
+def test_embedding():
+    V, H, M, pad = 97, 64, 300, 2
+    W = bf(V, H, seed=1)
+    idx = torch.randint(0, V, (M,), dtype=torch.int32)
+    out = F.embedding_fwd(W.to(DEV), idx.to(DEV), pad)
+    close(out, F.embedding_fwd(W.float(), idx, pad), rtol=0, atol=0)
+    dout = bf(M, H, seed=2)
+    for dt in (torch.float32, torch.bfloat16):
+        dW = torch.zeros(V, H, dtype=dt, device=DEV)
+        F.embedding_bwd(dW, idx.to(DEV), dout.to(DEV), pad)
+        ref = F.embedding_bwd(torch.zeros(V, H), idx, dout.float(), pad)
+        close(dW, ref, rtol=2e-2, atol=6e-2)
+        assert (dW[pad] == 0).all()
+
+
+@pytest.mark.parametrize("D", [32, 64, 128])
+@pytest.mark.parametrize("rope", [False, True])
+def test_flash_attention(D, rope):
+    B, T, QH, KVH = 2, 200, 4, 2
+    packed = bf(B * T, (QH + 2 * KVH) * D, seed=D).to(DEV)        # [K | Q | V] columns
+    v3 = packed.view(B, T, -1)
+    k = v3[:, :, :KVH * D].unflatten(2, (KVH, D))
+    q = v3[:, :, KVH * D:(KVH + QH) * D].unflatten(2, (QH, D))
+    v = v3[:, :, (KVH + QH) * D:].unflatten(2, (KVH, D))
+    vl = torch.tensor([T, 150], dtype=torch.int32, device=DEV)
+    tabs = F.rope_table(T, D, 10000.0, DEV) if rope else None
+    tabs_c = F.rope_table(T, D, 10000.0, "cpu") if rope else None
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vl, rope=tabs)
+    qc, kc, vc = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    o_ref, lse_ref = F.flash_attn_fwd(qc, kc, vc, valid_len=vl.cpu(), rope=tabs_c)
+    close(o, o_ref)
+    close(lse, lse_ref, rtol=1e-2, atol=2e-2)
+    do = bf(B, T, QH, D, seed=9).to(DEV)
+    dq, dk, dv = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vl, rope=tabs)
+    dq_r, dk_r, dv_r = F.flash_attn_bwd(do.float().cpu(), qc, kc, vc, o_ref, lse_ref, valid_len=vl.cpu(), rope=tabs_c)
+    close(dq, dq_r, rtol=3e-2, atol=3e-2)
+    close(dk, dk_r, rtol=3e-2, atol=3e-2)
+    close(dv, dv_r, rtol=3e-2, atol=3e-2)
+
+
+def test_decode_attention():
+    B, QH, KVH, Tmax, D = 3, 8, 2, 77, 64
+    q, kc, vc = bf(B, QH, D, seed=1), bf(B, KVH, Tmax, D, seed=2), bf(B, KVH, Tmax, D, seed=3)
+    lens = torch.tensor([1, 40, 77], dtype=torch.int32)
+    out = F.decode_attn(q.to(DEV), kc.to(DEV), vc.to(DEV), lens.to(DEV))
+    close(out, F.decode_attn(q.float(), kc.float(), vc.float(), lens))
+
+
+def test_cross_entropy_rows():
+    M, V, C, pad = 100, 1000, 384, 2
+    logits = torch.randn(M, V) * 3
+    tg = torch.randint(0, V, (M,), dtype=torch.int32)
+    tg[::7] = pad
+    dev = lambda t: t.to(DEV)
+    st_g = [torch.empty(M, device=DEV) for _ in range(3)]
+    st_c = [torch.empty(M) for _ in range(3)]
+    for i, c0 in enumerate(range(0, V, C)):
+        ch = logits[:, c0:c0 + C].contiguous()
+        F.ce_stats(dev(ch), dev(tg), *st_g, c0, i == 0)
+        F.ce_stats(ch, tg, *st_c, c0, i == 0)
+    lc_g = F.ce_loss(*st_g, dev(tg), pad)
+    lc_c = F.ce_loss(*st_c, tg, pad)
+    close(lc_g, lc_c, rtol=1e-4, atol=1e-3)
+    ref = torch.nn.functional.cross_entropy(logits, tg.long(), ignore_index=pad, reduction="sum")
+    assert abs(lc_g[0].item() - ref.item()) < 1e-2 * abs(ref.item())
+    ch = logits[:, C:2 * C].contiguous()
+    d_g = F.ce_dlogits(dev(ch), dev(tg), st_g[0], st_g[1], lc_g, C, pad, 4.0, torch.bfloat16)
+    d_c = F.ce_dlogits(ch, tg, st_c[0], st_c[1], lc_c, C, pad, 4.0, torch.float32)
+    close(d_g, d_c, rtol=2e-2, atol=1e-4)
+
+
+@pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
+def test_adamw_and_stats(gdt):
+    n = 10007
+    g = torch.randn(n).to(gdt)
+    w = torch.randn(n)
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-6, weight_decay=0.1)
+    st_c = torch.zeros(2)
+    F.grad_stats(g.float(), st_c)
+    st_g = torch.zeros(2, device=DEV)
+    F.grad_stats(g.to(DEV), st_g)
+    close(st_g, st_c, rtol=1e-3, atol=1e-3)
+    mc, vc, wc, pc = torch.zeros(n), torch.zeros(n), w.clone(), torch.zeros(n)
+    mg, vg, wg = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV), w.to(DEV)
+    pg = torch.zeros(n, dtype=torch.bfloat16, device=DEV)
+    for step in (1, 2, 3):
+        F.adamw_step(g.float(), mc, vc, wc, pc, step=step, grad_scale=0.5, max_grad_norm=1.0, stats=st_c, **hp)
+        F.adamw_step(g.to(DEV), mg, vg, wg, pg, step=step, grad_scale=0.5, max_grad_norm=1.0, stats=st_g, **hp)
+    close(wg, wc, rtol=1e-4, atol=1e-5)
+    close(pg, pc, rtol=1e-2, atol=1e-2)
+    # non-finite gradient: flagged, and the update is skipped on the device
+    gb = g.clone().float()
+    gb[5] = float("inf")
+    st = torch.zeros(2, device=DEV)
+    F.grad_stats(gb.to(gdt).to(DEV), st)
+    assert st[1].item() == 1.0
+    before = wg.clone()
+    F.adamw_step(gb.to(gdt).to(DEV), mg, vg, wg, pg, step=4, stats=st, **hp)
+    assert torch.equal(before, wg)
+    acc = torch.zeros(n, device=DEV)
+    F.accumulate(acc, g.to(DEV), 0.25)
+    close(acc, g.float() * 0.25, rtol=1e-5, atol=1e-6)
