@@ -270,7 +270,7 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     cos, sin = rope if rope is not None else (None, None)
     if not q.is_cuda:
         o, lse, _, _, _ = _attn_reference(q, k, v, valid_len, scale, cos, sin)
-        return o.to(q.dtype), lse
+        return o.to(q.dtype).contiguous(), lse
     _bf16(q, k, v)
     o = torch.empty((B, T, QH, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)

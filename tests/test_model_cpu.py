@@ -1,0 +1,108 @@
+"""Tiny-config model on the CPU path against the NumPy float64 oracle (loss, every gradient,
+Adam steps, greedy decode), plus a finite-difference check of the oracle itself."""
+import numpy as np
+import pytest
+import torch
+
+from create_llm_by_cupy_b200.models.model import Cupa_ver4
+from create_llm_by_cupy_b200.models.oracle_np import Oracle, OracleConfig
+
+TINY = dict(vocab_size=64, hidden_size=32, layer_num=2, time_size=16, q_head=4, kv_head=2, padding_id=2,
+            dropout_rate=0, half_float=False, dtype="fp32", ffn_size=48, tie_embeddings=True, seed=3,
+            ce_chunk_size=24)
+
+
+def make(tied=True, **kw):
+    d = dict(TINY, tie_embeddings=tied, **kw)
+    m = Cupa_ver4(d, device="cpu")
+    o = Oracle(OracleConfig.from_model_dic(d), [p.double().numpy() for p in m.params])
+    return d, m, o
+
+
+def batch(d, B=3, seed=0, pad_tail=True):
+    rng = np.random.default_rng(seed)
+    x = rng.integers(3, d["vocab_size"], size=(B, d["time_size"]))
+    t = np.concatenate([x[:, 1:], np.full((B, 1), d["padding_id"])], 1)
+    vl = np.full(B, d["time_size"])
+    if pad_tail:
+        vl[1] = 11
+        x[1, 10:] = d["padding_id"]
+        t[1, 10:] = d["padding_id"]
+    return x, t, vl
+
+
+def test_oracle_gradients_match_finite_differences():
+    d, m, o = make()
+    x, t, vl = batch(d)
+    o.forward(x, t, vl)
+    grads = o.backward()
+    rng = np.random.default_rng(1)
+    for pi in (0, 1, 2, 3, 4, 6, 12, len(o.p) - 1):
+        p = o.p[pi]
+        for _ in range(3):
+            idx = tuple(rng.integers(0, s) for s in p.shape)
+            old = p[idx]
+            h = 1e-5
+            p[idx] = old + h
+            lp = o.forward(x, t, vl, keep=False)
+            p[idx] = old - h
+            lm = o.forward(x, t, vl, keep=False)
+            p[idx] = old
+            fd = (lp - lm) / (2 * h)
+            assert abs(fd - grads[pi][idx]) < 1e-6 + 1e-4 * abs(fd), (pi, idx, fd, grads[pi][idx])
+
+
+@pytest.mark.parametrize("tied", [True, False])
+@pytest.mark.parametrize("flash", ["b200", "none"])
+def test_torch_cpu_matches_oracle(tied, flash):
+    d, m, o = make(tied, flash_backend=flash)
+    x, t, vl = batch(d)
+    loss = m.forward(torch.from_numpy(x), torch.from_numpy(t), torch.from_numpy(vl).int())
+    ref = o.forward(x, t, vl)
+    assert abs(float(loss) - ref) < 1e-4
+    m.backward(GradScale=2.0)
+    g_ref = o.backward(2.0)
+    assert len(m.grads) == len(g_ref)
+    for i, (g, r) in enumerate(zip(m.grads, g_ref)):
+        np.testing.assert_allclose(g.double().numpy(), r, rtol=2e-3, atol=2e-5, err_msg=f"param {i}")
+
+
+def test_recompute_switches_give_same_gradients():
+    d, m, _ = make()
+    x, t, vl = batch(d)
+    X, Tt, V = torch.from_numpy(x), torch.from_numpy(t), torch.from_numpy(vl).int()
+    m.forward(X, Tt, V)
+    m.backward()
+    base = [g.clone() for g in m.grads]
+    m2 = Cupa_ver4(dict(d, gqa_cache_out_value=False, gqa_cache_kqv=False, swiglu_cache_gate=False,
+                        ce_cache_logits=False, keep_layer_num=2), device="cpu")
+    m2.forward(X, Tt, V)
+    m2.backward()
+    for a, b in zip(base, m2.grads):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+
+def test_predict_and_logits_and_greedy_generation():
+    d, m, o = make()
+    x, t, vl = batch(d, pad_tail=False)
+    lp = m.predict(torch.from_numpy(x), torch.from_numpy(t), None)
+    assert abs(float(lp) - o.forward(x, t, None, keep=False)) < 1e-4
+    lg = m.logits(torch.from_numpy(x))
+    np.testing.assert_allclose(lg.double().numpy(), o.logits(x), rtol=1e-3, atol=1e-4)
+    prompt = [5, 9, 33, 7]
+    out = m.generate(prompt, greedy=True, max_new_tokens=8)
+    assert out == o.greedy(prompt, 8)
+    out2 = m.generate(prompt, start_id=1, end_id=0, temp=0.7, top=0.9, penalty=1.2, seed=0)
+    assert all(0 <= tok < d["vocab_size"] and tok != d["padding_id"] for tok in out2)
+    out3 = m.chat_generate(prompt, user_id=4, bot_id=6, end_id=0, seed=0, max_new_tokens=4)
+    assert len(out3) <= 4
+
+
+def test_flat_weight_file_roundtrip(tmp_path):
+    d, m, _ = make()
+    p = tmp_path / "flat_params_f16.pkl.gz"
+    m.save_weights_to_flat_file(str(p))
+    m2 = Cupa_ver4(dict(d, seed=99), param_path=str(p), device="cpu")
+    for a, b in zip(m.params, m2.params):
+        torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-3)
+    assert m2.layers[0].params[0] is m2.params[0]
