@@ -1,0 +1,375 @@
+"""Per-rank training engine, the worker loop and the multi-process launcher.
+
+Counterparts in the reference: ``TrainMultiGPU`` (model/ZeRO3.py:653-726, model/ZeRO2_5.py:694-771),
+the worker ``training_worker_nccl_stream`` (model/ZeRO3.py:97-501, model/ZeRO2_5.py:95-542). The
+duplicated ZeRO-3 / ZeRO-2.5 halves of the reference are one implementation here, selected by
+``zero_stage``; the launcher adds what the reference lacks: a watchdog (child exit codes and
+per-rank heartbeats, first failure tears the job down instead of leaving ranks blocked in a
+collective), data partitioned across ranks, working validation, resume, and tokens/s accounting.
+"""
+from __future__ import annotations
+
+import math
+import os
+import time
+import traceback
+
+import numpy as np
+import torch
+
+from ..models.model import Cupa_ver4
+from ..optim.optimizer import ZeRO_Adam_Offload, ZeRO_Adam_ShardedGPU
+from ..utils import checkpoint as ckpt
+from ..utils.data import BatchStager, SplitDataset, get_batch, shard_for_rank, to_fixed_length
+from ..utils.functions import ScaleGrad, print_memory_status
+from ..utils.logging import MetricsLogger
+from ..utils.profiler import nvtx_range
+from .comm import SingleProcessComm, init_distributed, shutdown_distributed
+from .zero import MemoryZeRO2_5Manager, MemoryZeRO3Manager
+
+
+class Trainer:
+    """One rank of a ZeRO-3 / ZeRO-2.5 data-parallel job: model + manager + optimizer(s).
+
+    ``train_step(batches)`` runs ``len(batches)`` micro-batches (forward, backward, gradient
+    reduction overlapped with backward), then the global-norm clip, the non-finite check and the
+    AdamW update of this rank's shard, and returns host scalars.
+    """
+
+    def __init__(self, model_dic: dict, *, rank: int = 0, world_size: int = 1, comm=None, device=None,
+                 zero_stage: str = "3", optimizer_device: str = "gpu", accum_step: int = 1,
+                 lr_max: float = 3e-4, lr_mini: float = 3e-5, weight_decay: float = 0.1, warm_up: int = 100,
+                 total_steps: int = 1000, beta1: float = 0.9, beta2: float = 0.99, epsilon: float = 1e-6,
+                 max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
+                 profile_comm: bool = False, param_path: str | None = None):
+        self.rank, self.world_size = rank, world_size
+        self.comm = comm if comm is not None else SingleProcessComm()
+        self.accum_step = int(accum_step)
+        self.max_grads = float(max_grads)
+        self.logger = logger
+        self.model = Cupa_ver4(model_dic, param_path=param_path, device=device)
+        self.device = self.model.device
+        self.n_params = self.model.param_count()
+        mgr_cls = MemoryZeRO2_5Manager if str(zero_stage) in ("2.5", "2_5", "25") else MemoryZeRO3Manager
+        self.manager = mgr_cls(self.model, world_size, self.comm, rank, accum_steps=self.accum_step, fused=fused,
+                               profile_comm=profile_comm)
+        opt_cls = ZeRO_Adam_Offload if optimizer_device == "cpu" else ZeRO_Adam_ShardedGPU
+        okw = dict(lr_max=lr_max, lr_mini=lr_mini, total_steps=total_steps, warm_up=warm_up,
+                   weight_decay=weight_decay, beta1=beta1, beta2=beta2, epsilon=epsilon, logger=logger)
+        self.optimizer = opt_cls(self.manager.get_param_shard_view(), **okw)
+        self.replica_optimizer = None
+        if self.manager.replica_param_f16 is not None:
+            self.replica_optimizer = opt_cls(self.manager.get_replica_optimizer_shard_view(), **okw)
+        gs = dict(GradScale_dic or {})
+        # bf16 has fp32's exponent range: loss scaling is kept for API parity and off by default
+        self.scaler = ScaleGrad(gs.get("StartScale", 10.0), gs.get("UpRate", 2.0), gs.get("DownRate", 0.7),
+                                gs.get("Scale_Up_Step"), enabled=bool(gs.get("enabled", False)))
+        self.iteration = 0
+        self.last = {}
+
+    # ------------------------------------------------------------------ one optimizer step
+    def train_step(self, batches) -> dict:
+        mgr, model = self.manager, self.model
+        scale = float(self.scaler.Scale)
+        mgr.zero_grad()
+        loss_acc = None
+        for (x, t, x_pa) in batches:
+            with nvtx_range("forward"):
+                loss = model.forward(x, t, x_pa, mgr)
+            with nvtx_range("backward"):
+                model.backward(scale, mgr)
+            mgr.end_microbatch()
+            loss_acc = loss.detach().clone() if loss_acc is None else loss_acc + loss
+        n_micro = len(batches)
+        if getattr(self, "inject_nan_next", False):      # host-side fault injection (tests)
+            mgr.wait_reductions()
+            mgr.grad_shard_f16[:1] = float("nan")
+            self.inject_nan_next = False
+        with nvtx_range("optimizer"):
+            stats = mgr.calculate_global_grad_stats(to_host=False)
+            step_scale = 1.0 / (self.world_size * n_micro * scale)
+            if self.replica_optimizer is not None:
+                rgrad = mgr.prepare_replicated_grads_for_sharded_optimizer()
+                # the replica slices join the same global norm
+                from ..ops import functional as F
+                extra = torch.zeros_like(stats)
+                F.grad_stats(rgrad, extra)
+                if self.world_size > 1:
+                    self.comm.all_reduce(extra)
+                stats = stats + extra
+                stats[1] = (stats[1] != 0).float()
+            self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
+                                  out_shard=mgr.get_param_shard_view(), stats=stats, max_grad_norm=self.max_grads)
+            if self.replica_optimizer is not None:
+                self.replica_optimizer.update(rgrad, step_scale, False,
+                                              out_shard=mgr.get_replica_optimizer_shard_view(), stats=stats,
+                                              max_grad_norm=self.max_grads)
+                mgr.allgather_replicated_params_from_optimizer_shards()
+        # one host read per step: loss, gradient statistics
+        host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
+        loss_val = host[0] / n_micro
+        bad = host[2] != 0.0 or not math.isfinite(host[1])
+        if bad:   # the kernels skipped the update; keep the schedule where it was (reference: `continue`)
+            self.optimizer.t -= 1
+            if self.replica_optimizer is not None:
+                self.replica_optimizer.t -= 1
+        self.scaler.UpdateScale(bad)
+        self.iteration += 1
+        gnorm = math.sqrt(max(host[1], 0.0)) * step_scale if not bad else float("nan")
+        self.last = {"loss": loss_val, "grad_norm": gnorm, "skipped": bad, "GradScale": scale,
+                     "lr": self.optimizer.current_lr}
+        return self.last
+
+    @torch.no_grad()
+    def validate(self, batches) -> float:
+        """Mean validation loss over ``batches`` and over ranks (model/ZeRO3.py:388-449 intent)."""
+        tot = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for (x, t, x_pa) in batches:
+            tot += self.model.predict(x, t, x_pa, self.manager).float()
+        tot /= max(len(batches), 1)
+        if self.world_size > 1:
+            self.comm.all_reduce(tot)
+            tot /= self.world_size
+        return float(tot)
+
+    def generate(self, prompt, **kw):
+        """Generation on a sharded model: gather everything, decode, release."""
+        self.manager.materialize_all()
+        try:
+            return self.model.generate(prompt, **kw)
+        finally:
+            self.manager.release_all()
+
+    # ------------------------------------------------------------------ checkpoint
+    def save(self, directory: str, extra: dict | None = None):
+        state = {"iteration": self.iteration, "scaler": self.scaler.state_dict(),
+                 "torch_rng": torch.get_rng_state(), "numpy_rng": np.random.get_state(), "extra": extra or {}}
+        self.manager.synchronize()
+        ckpt.save_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer, state)
+        if self.world_size > 1:
+            self.comm.barrier()
+
+    def load(self, directory: str) -> dict | None:
+        st = ckpt.load_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer)
+        if st is not None:
+            self.iteration = int(st.get("iteration", 0))
+            self.scaler.load_state_dict(st.get("scaler", self.scaler.state_dict()))
+        return st
+
+
+# ------------------------------------------------------------------------------- worker
+class InjectedFault(RuntimeError):
+    pass
+
+
+def _maybe_inject(fault: dict | None, rank: int, it: int, trainer: Trainer | None = None):
+    """Host-side fault injection for the failure-detection tests: a rank raises, exits, stalls
+    (sleeps) or poisons its gradient with NaN at a chosen iteration. Nothing here touches a GPU in
+    a way that could fault it."""
+    if not fault or fault.get("rank") != rank or fault.get("iter") != it:
+        return
+    kind = fault.get("kind", "raise")
+    if kind == "raise":
+        raise InjectedFault(f"injected failure on rank {rank} at iteration {it}")
+    if kind == "exit":
+        os._exit(int(fault.get("code", 17)))
+    if kind == "stall":
+        time.sleep(float(fault.get("seconds", 3600)))
+    if kind == "nan" and trainer is not None:
+        trainer.inject_nan_next = True
+
+
+def _heartbeat(path: str | None, rank: int, it: int):
+    if path:
+        with open(os.path.join(path, f"heartbeat_rank{rank}"), "w") as f:
+            f.write(f"{time.time()} {it}\n")
+
+
+def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
+    """One process per device: bind the device, join the process group, build the trainer and run
+    the epoch / iteration loop with logging, validation and checkpoints."""
+    a = args
+    use_devices = a.get("use_devices") or list(range(world_size))
+    on_gpu = torch.cuda.is_available() and a.get("backend", None) != "gloo"
+    device = "cpu"
+    if on_gpu:
+        torch.cuda.set_device(use_devices[rank])
+        device = torch.device("cuda", use_devices[rank])
+    comm = init_distributed(rank, world_size, backend=a.get("backend"), master_port=int(a.get("master_port", 29511)),
+                            timeout_s=float(a.get("collective_timeout_s", 600.0)),
+                            device_id=use_devices[rank] if on_gpu else None)
+    logger = MetricsLogger(rank, wand=bool(a.get("wand", False)), config=a.get("model_dic"),
+                           jsonl_path=a.get("metrics_path"), console=bool(a.get("console", True)))
+    result = {}
+    try:
+        md = a["model_dic"]
+        B, T, accum = int(a["batch_size"]), int(md["time_size"]), int(a.get("accum_step", 1))
+        max_iters = int(a["max_iters"])
+        trainer = Trainer(md, rank=rank, world_size=world_size, comm=comm, device=device,
+                          zero_stage=a.get("zero_stage", "3"), optimizer_device=a.get("optimizer_device", "gpu"),
+                          accum_step=accum, lr_max=a.get("lr_max", 3e-4), lr_mini=a.get("lr_mini", 3e-5),
+                          weight_decay=a.get("weight_decay", 0.1), warm_up=a.get("warm_up", 100),
+                          total_steps=max_iters * int(a.get("max_epoch", 1)), beta1=a.get("beta1", 0.9),
+                          beta2=a.get("beta2", 0.99), epsilon=a.get("epsilon", 1e-6), max_grads=a.get("max_grads", 1.0),
+                          GradScale_dic=a.get("GradScale_dic"), logger=logger, param_path=a.get("train_continue_path"),
+                          profile_comm=bool(a.get("profile_timing", False)))
+        if a.get("resume_dir") and os.path.exists(ckpt.model_shard_path(a["resume_dir"], rank)):
+            trainer.load(a["resume_dir"])
+        if rank == 0:
+            logger.line(f"parameters: {trainer.n_params:,}; shard {trainer.manager.shard_size * 2 / 2**30:.3f} GiB/rank; "
+                        f"world {world_size}; ZeRO-{a.get('zero_stage', '3')}")
+            print_memory_status("after init", printer=logger.line)
+
+        pad = int(md["padding_id"])
+        if a.get("data_dir"):
+            from ..utils.data import load_input_ids_from_dir
+            ids, vl = to_fixed_length(load_input_ids_from_dir(a["data_dir"], int(a.get("max_samples", 100000))), T, pad)
+            ds = SplitDataset(ids, vl, n_val=B * accum * world_size if a.get("vali") else 0,
+                              n_gen=int(a.get("n_gen", 0)), seed=int(a.get("data_seed", 0)))
+        else:
+            n_train = int(a.get("synthetic_samples", max(B * accum * world_size * 4, 64)))
+            ds = SplitDataset.synthetic(int(md["vocab_size"]), T, n_train, B * accum * world_size,
+                                        int(a.get("n_gen", 4)), pad)
+        tr_ids, tr_vl = shard_for_rank(*ds.train, rank, world_size)
+        va_ids, va_vl = shard_for_rank(*ds.val, rank, world_size)
+        stager = BatchStager(B, T, device)
+        val_batches = None
+        tokens_per_step = B * T * accum * world_size
+        losses = []
+        time_idx = 0
+        hb = a.get("heartbeat_dir")
+        t_last = time.perf_counter()
+        for epoch in range(int(a.get("max_epoch", 1))):
+            for it in range(trainer.iteration % max_iters if epoch == 0 else 0, max_iters):
+                _heartbeat(hb, rank, it)
+                _maybe_inject(a.get("fault"), rank, it, trainer)
+                batches = []
+                for _ in range(accum):
+                    xb, vb, time_idx = get_batch(tr_ids, tr_vl, B, time_idx)
+                    batches.append(stager.stage(xb, vb, pad))
+                out = trainer.train_step(batches)
+                losses.append(out["loss"])
+                now = time.perf_counter()
+                tok_s = tokens_per_step / max(now - t_last, 1e-9)
+                t_last = now
+                logger.log({"loss": out["loss"], "Perplexity": math.exp(min(out["loss"], 30.0)),
+                            "Grad Norm": out["grad_norm"], "GradScale": out["GradScale"],
+                            "tokens_per_s": tok_s}, step=trainer.iteration)
+                logger.step_line(epoch, it + 1, max_iters, out["loss"],
+                                 {"gnorm": out["grad_norm"], "tok/s": tok_s, "skipped": out["skipped"]})
+                if a.get("vali") and (it + 1) % int(a.get("vali_step", 600)) == 0 and len(va_ids) >= B:
+                    if val_batches is None:
+                        val_batches = [stager.stage(va_ids[i:i + B], va_vl[i:i + B], pad)
+                                       for i in range(0, len(va_ids) - B + 1, B)]
+                    v = trainer.validate(val_batches)
+                    logger.log({"validation": v}, step=trainer.iteration)
+                    logger.line(f"validation loss {v:.4f}")
+                if a.get("save") and a.get("save_dir") and (it + 1) % int(a.get("save_step", 2000)) == 0:
+                    trainer.save(a["save_dir"])
+        trainer.manager.synchronize()
+        result = {"losses": losses, "iteration": trainer.iteration}
+        if a.get("result_dir"):
+            ckpt.atomic_pickle_gzip(result, os.path.join(a["result_dir"], f"result_rank{rank}.pkl.gz"))
+    except BaseException:
+        traceback.print_exc()
+        logger.close()
+        os._exit(13)      # leave without waiting on peers that may be blocked in a collective
+    logger.close()
+    if world_size > 1:
+        comm.barrier()
+        shutdown_distributed()
+    return result
+
+
+# ------------------------------------------------------------------------------- launcher
+class WorkerFailure(RuntimeError):
+    pass
+
+
+class TrainMultiGPU:
+    """Launcher: one process per entry of ``use_devices`` (spawn), watched until all finish.
+
+    ``fit(data_size)`` keeps the reference's contract (``max_iters = data_size // (batch_size *
+    accum_step)``, model/ZeRO3.py:692-693) except that the count is also divided by the number of
+    ranks, because here ranks consume different samples.
+    """
+
+    zero_stage = "3"
+
+    def __init__(self, model_dic, GradScale_dic=None, use_devices=(0,), batch_size=1, max_epoch=1, lr_max=3e-4,
+                 lr_mini=3e-5, weight_decay=0.1, warm_up=100, max_grads=1.0, accum_step=1, save=False,
+                 save_step=2000, vali=False, vali_step=600, wand=False, optimizer_device="gpu",
+                 train_continue_path=None, **extra):
+        self.args = dict(model_dic=dict(model_dic), GradScale_dic=dict(GradScale_dic or {}), use_devices=list(use_devices),
+                         batch_size=batch_size, max_epoch=max_epoch, lr_max=lr_max, lr_mini=lr_mini,
+                         weight_decay=weight_decay, warm_up=warm_up, max_grads=max_grads, accum_step=accum_step,
+                         save=save, save_step=save_step, vali=vali, vali_step=vali_step, wand=wand,
+                         optimizer_device=optimizer_device, train_continue_path=train_continue_path,
+                         zero_stage=self.zero_stage)
+        self.args.update(extra)
+        self.heartbeat_timeout_s = float(extra.get("heartbeat_timeout_s", 1800.0))
+
+    def fit(self, data_size: int):
+        a = self.args
+        world = len(a["use_devices"])
+        a["max_iters"] = max(1, int(data_size) // (int(a["batch_size"]) * int(a["accum_step"]) * world))
+        if world == 1 and not a.get("force_spawn"):
+            return [training_worker_nccl_stream(0, 1, a)]
+        return self._spawn(world)
+
+    def _spawn(self, world: int):
+        import tempfile
+        import torch.multiprocessing as mp
+        a = self.args
+        hb_dir = a.get("heartbeat_dir") or tempfile.mkdtemp(prefix="b200_hb_")
+        a["heartbeat_dir"] = hb_dir
+        a.setdefault("master_port", 29500 + (os.getpid() % 2000))
+        ctx = mp.get_context("spawn")
+        procs = [ctx.Process(target=training_worker_nccl_stream, args=(r, world, a), daemon=False) for r in range(world)]
+        for p in procs:
+            p.start()
+        t0 = time.time()
+        failure = None
+        while True:
+            alive = [p.is_alive() for p in procs]
+            codes = [p.exitcode for p in procs]
+            bad = [(r, c) for r, c in enumerate(codes) if c not in (None, 0)]
+            if bad:
+                failure = f"rank {bad[0][0]} exited with code {bad[0][1]}"
+                break
+            if not any(alive):
+                break
+            now = time.time()
+            for r in range(world):
+                hp = os.path.join(hb_dir, f"heartbeat_rank{r}")
+                last = os.path.getmtime(hp) if os.path.exists(hp) else t0
+                if alive[r] and now - last > self.heartbeat_timeout_s:
+                    failure = f"rank {r} stalled: no heartbeat for {now - last:.0f} s"
+                    break
+            if failure:
+                break
+            time.sleep(0.2)
+        if failure:
+            for p in procs:
+                if p.is_alive():
+                    p.terminate()
+            for p in procs:
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
+            raise WorkerFailure(failure)
+        for p in procs:
+            p.join()
+        return [p.exitcode for p in procs]
+
+
+class TrainMultiGPU_ZeRO25(TrainMultiGPU):
+    zero_stage = "2.5"
+
+    def __init__(self, model_dic, *args, zero25_replica_ratio=None, zero25_replica_policy=None, **kw):
+        md = dict(model_dic)
+        if zero25_replica_ratio is not None:
+            md["zero25_replica_ratio"] = zero25_replica_ratio
+        if zero25_replica_policy is not None:
+            md["zero25_replica_policy"] = zero25_replica_policy
+        super().__init__(md, *args, **kw)

@@ -1,0 +1,145 @@
+"""Trainer on CPU: single-process steps against the NumPy oracle's AdamW, gradient accumulation,
+NaN skip, ZeRO-2.5 equivalence, checkpoint round trip and resharding."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from create_llm_by_cupy_b200.models.oracle_np import Oracle, OracleConfig, cosine_lr
+from create_llm_by_cupy_b200.parallel.trainer import Trainer
+from create_llm_by_cupy_b200.utils import checkpoint as ckpt
+from create_llm_by_cupy_b200.utils.data import padding_proceccing, synthetic_token_stream
+
+TINY = dict(vocab_size=64, hidden_size=32, layer_num=2, time_size=16, q_head=4, kv_head=2, padding_id=2,
+            dropout_rate=0, half_float=False, dtype="fp32", ffn_size=48, tie_embeddings=False, seed=3,
+            ce_chunk_size=24)
+HP = dict(lr_max=3e-3, lr_mini=3e-4, weight_decay=0.1, warm_up=3, total_steps=10, beta1=0.9, beta2=0.95,
+          epsilon=1e-6, max_grads=1.0)
+
+
+def batches(n, B=4, seed_split="train"):
+    ids = synthetic_token_stream(n * B, TINY["time_size"], TINY["vocab_size"], seed_split, TINY["padding_id"], low=3)
+    out = []
+    for i in range(n):
+        chunk = ids[i * B:(i + 1) * B]
+        out.append(padding_proceccing(chunk, np.full(B, TINY["time_size"]), TINY["padding_id"]))
+    return out
+
+
+def full_params(trainer):
+    trainer.manager.materialize_all()
+    ps = [p.detach().double().numpy().copy() for p in trainer.model.params]
+    trainer.manager.release_all()
+    return ps
+
+
+def test_ten_adam_steps_match_oracle():
+    tr = Trainer(TINY, device="cpu", **HP)
+    orc = Oracle(OracleConfig.from_model_dic(TINY), full_params(tr))
+    orc.init_adam()
+    bs = batches(10)
+    for step, (x, t, pa) in enumerate(bs, 1):
+        out = tr.train_step([(x, t, pa)])
+        ref_loss = orc.forward(x.numpy(), t.numpy(), pa.numpy())
+        g = orc.backward()
+        orc.adam_step(g, cosine_lr(step, HP["lr_max"], HP["lr_mini"], HP["warm_up"], HP["total_steps"]),
+                      HP["beta1"], HP["beta2"], HP["epsilon"], HP["weight_decay"], HP["max_grads"])
+        assert abs(out["loss"] - ref_loss) < 2e-4 * max(1.0, abs(ref_loss)), (step, out["loss"], ref_loss)
+        assert not out["skipped"]
+    for a, b in zip(full_params(tr), orc.p):
+        np.testing.assert_allclose(a, b, rtol=2e-3, atol=2e-5)
+
+
+def test_grad_accumulation_equals_big_batch_of_same_tokens():
+    bs = batches(2)
+    tr1 = Trainer(TINY, device="cpu", accum_step=2, **HP)
+    o1 = tr1.train_step(bs)
+    tr2 = Trainer(TINY, device="cpu", accum_step=1, **HP)
+    big = tuple(torch.cat([bs[0][i], bs[1][i]]) for i in range(3))
+    o2 = tr2.train_step([big])
+    assert abs(o1["loss"] - o2["loss"]) < 1e-5
+    for a, b in zip(full_params(tr1), full_params(tr2)):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_nan_step_is_skipped_and_loss_scale_shrinks():
+    tr = Trainer(TINY, device="cpu", GradScale_dic=dict(StartScale=10, enabled=True), **HP)
+    before = full_params(tr)
+    tr.inject_nan_next = True
+    out = tr.train_step(batches(1))
+    assert out["skipped"] and tr.scaler.Scale == pytest.approx(7.0) and tr.optimizer.t == 0
+    for a, b in zip(before, full_params(tr)):
+        np.testing.assert_array_equal(a, b)
+    out = tr.train_step(batches(1))
+    assert not out["skipped"] and tr.optimizer.t == 1
+
+
+@pytest.mark.parametrize("ratio,policy", [(0.3, "largest_first"), (1.0, "first"), (0.5, "embedding_first")])
+def test_zero25_single_rank_matches_zero3(ratio, policy):
+    bs = batches(3)
+    ref = Trainer(TINY, device="cpu", accum_step=1, **HP)
+    md = dict(TINY, zero25_replica_ratio=ratio, zero25_replica_policy=policy)
+    z25 = Trainer(md, device="cpu", zero_stage="2.5", **HP)
+    assert z25.manager.replicated_param_indices
+    for b in bs:
+        a, c = ref.train_step([b]), z25.train_step([b])
+        assert abs(a["loss"] - c["loss"]) < 1e-5
+    for a, b in zip(full_params(ref), full_params(z25)):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_checkpoint_roundtrip_resume_flat_and_reshard(tmp_path):
+    bs = batches(4)
+    tr = Trainer(TINY, device="cpu", **HP)
+    tr.train_step([bs[0]])
+    tr.train_step([bs[1]])
+    d = str(tmp_path / "ck")
+    tr.save(d)
+    for f in ("model_shard_rank0.pkl.gz", "optimizer_rank0.pkl.gz", "trainer_state.pkl.gz"):
+        assert os.path.exists(os.path.join(d, f))
+    shard = ckpt.read_pickle_gzip(ckpt.model_shard_path(d, 0))
+    for k in ("param_shard_f16", "rank", "world_size", "shard_size", "padded_total", "param_offsets",
+              "param_shapes", "param_sizes"):
+        assert k in shard
+    opt = ckpt.read_pickle_gzip(ckpt.optimizer_path(d, 0))
+    assert set(("m", "v", "w_fp32", "t")) <= set(opt)
+    # resume: a fresh trainer continues exactly like the original
+    tr2 = Trainer(dict(TINY, seed=77), device="cpu", **HP)
+    st = tr2.load(d)
+    assert st["iteration"] == 2 and tr2.optimizer.t == 2
+    a, b = tr.train_step([bs[2]]), tr2.train_step([bs[2]])
+    assert abs(a["loss"] - b["loss"]) < 1e-6
+    for x, y in zip(full_params(tr), full_params(tr2)):
+        np.testing.assert_allclose(x, y, rtol=1e-6, atol=1e-7)
+    # shards -> flat (the reference's resume format) -> model
+    flat = str(tmp_path / "flat_params_f16.pkl.gz")
+    ckpt.shards_to_flat(d, flat)
+    from create_llm_by_cupy_b200.models.model import Cupa_ver4
+    m = Cupa_ver4(TINY, param_path=flat, device="cpu")
+    saved = ckpt.shards_to_param_list(d)
+    for p, q in zip(m.params, saved):
+        np.testing.assert_allclose(p.numpy(), q.numpy(), rtol=2e-3, atol=2e-3)
+    # reshard 1 -> 4 -> 1 keeps parameters and optimizer state
+    d4, d1 = str(tmp_path / "w4"), str(tmp_path / "w1")
+    ckpt.reshard_checkpoint(d, d4, 4)
+    assert os.path.exists(ckpt.optimizer_path(d4, 3))
+    ckpt.reshard_checkpoint(d4, d1, 1)
+    for p, q in zip(ckpt.shards_to_param_list(d1), saved):
+        np.testing.assert_array_equal(p.numpy(), q.numpy())
+    o1 = ckpt.read_pickle_gzip(ckpt.optimizer_path(d1, 0))
+    np.testing.assert_array_equal(o1["m"], opt["m"])
+    # flat -> shards for 2 ranks
+    d2 = str(tmp_path / "w2")
+    ckpt.flat_to_shards(flat, d2, [tuple(p.shape) for p in m.params], m.unit_defs(), 2, dtype_name="fp32")
+    for p, q in zip(ckpt.shards_to_param_list(d2), saved):
+        np.testing.assert_allclose(p.numpy(), q.numpy(), rtol=2e-3, atol=2e-3)
+
+
+def test_validation_and_generation_through_trainer():
+    tr = Trainer(TINY, device="cpu", **HP)
+    v = tr.validate(batches(2, seed_split="validation"))
+    assert math.isfinite(v) and abs(v - math.log(TINY["vocab_size"])) < 1.0
+    out = tr.generate([5, 6, 7], greedy=True, max_new_tokens=5)
+    assert len(out) == 5
