@@ -542,3 +542,48 @@ B200_API int b200_add_bf16(const void* a, const void* b, void* out, long long n,
                                                                     static_cast<bf16*>(out), size_t(n));
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// See b200_noalloc.h. The scratch for the dgamma partial sums lives in this translation unit; in
+// host code the array's name only stands for the symbol, so its device address is looked up once
+// per device and that pointer is what the kernels receive.
+#include "b200_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_rms_partial[B200_NOALLOC_RMS_ROWS * B200_NOALLOC_RMS_MAX_H];
+
+static int noalloc_rms_scratch(float** out) {
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  B200_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return static_cast<int>(cudaErrorInvalidDevice);
+  if (per_device[dev] == nullptr) {
+    float* p = nullptr;
+    B200_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_rms_partial));
+    per_device[dev] = p;
+  }
+  *out = per_device[dev];
+  return 0;
+}
+
+B200_API int b200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* gamma, const void* rstd,
+                                      const void* add, void* dx, void* dgamma, int M, int H, int accumulate_dgamma,
+                                      cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0 || H > B200_NOALLOC_RMS_MAX_H) {
+    fprintf(stderr, "[b200] rmsnorm_bwd_noalloc: hidden size %d is outside 1..%d, the size its built-in scratch "
+                    "was compiled for; use b200_rmsnorm_bwd with your own scratch\n", H, B200_NOALLOC_RMS_MAX_H);
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  const int rows = b200_rmsnorm_bwd_partial_rows(M);
+  if (rows > B200_NOALLOC_RMS_ROWS) {
+    fprintf(stderr, "[b200] rmsnorm_bwd_noalloc: %d partial rows needed, built-in scratch holds %d\n", rows,
+            B200_NOALLOC_RMS_ROWS);
+    return static_cast<int>(cudaErrorInvalidValue);
+  }
+  float* scratch = nullptr;
+  const int rc = noalloc_rms_scratch(&scratch);
+  if (rc != 0) return rc;
+  // Every partial row the kernels read is fully rewritten first (vector path) or zeroed with a
+  // memset on `stream` (generic-H path), so stale contents of an earlier call are never summed.
+  return b200_rmsnorm_bwd(dy, x, gamma, rstd, add, dx, dgamma, scratch, M, H, accumulate_dgamma, stream);
+}
