@@ -1,0 +1,355 @@
+// Symmetric-memory runtime and the fused gradient path over NVLink / NVSwitch peer memory.
+//
+// Every rank owns one heap (cudaMalloc) whose IPC handle is exchanged once; after that each rank
+// holds a table of W device pointers, one per peer heap, and buffers are addressed as
+// (heap base + offset) with the same offset on every rank. The first 64 KiB of a heap is its
+// signal pad: 32-bit epoch flags that peers write with st.release.sys and the owner polls with
+// ld.acquire.sys. Every poll loop has a wall-clock deadline; when it runs out the kernel records
+// ERR_PEER_TIMEOUT in the status word and returns (no trap, no endless spin).
+//
+// rs_reduce_kernel is the reduce-scatter of one gradient bucket fused with what follows it:
+//   start barrier (all ranks finished writing the bucket)  ->  each rank pulls ITS slice of all W
+//   peer buckets with 16-byte P2P loads, sums in fp32       ->  one of
+//       STORE      : write the reduced slice (bf16 or fp32) into the gradient shard
+//       ACCUMULATE : add it into the fp32 gradient shard (gradient accumulation)
+//       ADAM       : scale and apply AdamW directly (fp32 master/m/v, bf16 parameter shard)
+//   plus, fused in the same pass, the sum of squares / non-finite flag that the global-norm clip
+//   needs                                                   ->  end barrier (all ranks finished
+//   reading, so the bucket may be overwritten and updated parameters are visible).
+// It replaces ncclReduceScatter + cast + accumulate + grad_stats (+ AdamW) — the reference's
+// reduce(root=owner) + `grad_shard += tmp` + grad_stats_f16_kernel + adam_update_kernel
+// (model/ZeRO3.py:1362-1450, 746-796; model/optimizer.py:112-151).
+//
+// ag_pull_kernel is the matching all-gather by P2P pulls (used for units whose gather is not
+// fused into a GEMM). Blocks of one launch may stand for several "virtual ranks" (gridDim.y) so
+// that the multi-rank protocol can be exercised as ONE kernel on a single GPU.
+#include <string.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int SYMM_MAX_W = 8;
+constexpr int SYMM_PAD_BYTES = 64 * 1024;
+constexpr int SYMM_MAX_BLOCKS = 64;           // blocks (per virtual rank) that take part in a barrier
+// signal pad layout (uint32 index): channel c, block b, source rank r -> ((c * MAX_BLOCKS) + b) * MAX_W + r
+constexpr int SYMM_CHANNELS = 8;
+static_assert(SYMM_CHANNELS * SYMM_MAX_BLOCKS * SYMM_MAX_W * 4 <= SYMM_PAD_BYTES, "signal pad too small");
+
+struct SymmTable {
+  void* base[SYMM_MAX_W];      // heap base of every rank, as mapped into THIS process
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Barrier among the same-numbered blocks of all W ranks. Thread p < W signals rank p and waits
+// for rank p's signal. Returns false (for the whole block) when a wait ran out of time.
+__device__ bool peer_block_barrier(const SymmTable& tab, int rank, int W, int channel, uint32_t epoch,
+                                   unsigned long long wait_ns, int* status, int kernel_id) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  if (threadIdx.x < W) {
+    const int p = threadIdx.x;
+    const int slot = (channel * SYMM_MAX_BLOCKS + int(blockIdx.x)) * SYMM_MAX_W;
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(tab.base[p]) + slot + rank, epoch);
+    const uint32_t* mine = static_cast<const uint32_t*>(tab.base[rank]) + slot + p;
+    const uint64_t deadline = globaltimer_ns() + wait_ns;
+    uint32_t spins = 0;
+    while (int32_t(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 63) == 0 && globaltimer_ns() > deadline) {
+        s_fail = 1;
+        if (status != nullptr && atomicCAS(status, 0, ERR_PEER_TIMEOUT) == 0) {
+          status[1] = kernel_id;
+          status[2] = p;
+        }
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_fail == 0;
+}
+
+enum RsMode : int { RS_STORE = 0, RS_ACCUMULATE = 1, RS_ADAM = 2 };
+
+struct RsAdam {
+  float* m; float* v; float* master; bf16* param;
+  float lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale;
+};
+
+struct RsParams {
+  SymmTable tab[SYMM_MAX_W];     // tab[v]: peer table as seen by virtual rank v (production: only tab[0])
+  void* dst[SYMM_MAX_W];         // reduced slice destination of virtual rank v
+  float* stats[SYMM_MAX_W];      // [sum of squares, non-finite flag] or null
+  RsAdam adam[SYMM_MAX_W];
+  unsigned long long bucket_off; // byte offset of the bucket inside every heap
+  long long n_slice;             // elements per rank slice (multiple of 8)
+  int rank0, W, mode, dst_fp32, do_stats;
+  uint32_t epoch;
+  unsigned long long wait_ns;
+  int* status;
+};
+
+__device__ __forceinline__ void adam_apply(float g, float& m, float& v, float& w, const RsAdam& a) {
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  if (a.weight_decay > 0.f) w *= (1.f - a.lr * a.weight_decay);
+  w -= a.lr * (m * a.m_corr) / (sqrtf(v * a.v_corr) + a.eps);
+}
+
+__global__ void __launch_bounds__(512) rs_reduce_kernel(const RsParams p) {
+  const int vr = blockIdx.y;
+  const int rank = p.rank0 + vr;
+  const SymmTable& tab = p.tab[vr];
+  const int W = p.W;
+  if (!peer_block_barrier(tab, rank, W, 0, 2 * p.epoch - 1, p.wait_ns, p.status, 201)) return;
+
+  const uint4* src[SYMM_MAX_W];
+#pragma unroll
+  for (int q = 0; q < SYMM_MAX_W; ++q) {
+    // start with the next rank so that at any moment the ranks pull from different peers
+    const int peer = (rank + 1 + q) % W;
+    src[q] = reinterpret_cast<const uint4*>(static_cast<const char*>(tab.base[q < W ? peer : rank]) + p.bucket_off) +
+             size_t(rank) * (p.n_slice / 8);
+  }
+  const long long nvec = p.n_slice / 8;
+  float ss = 0.f;
+  int bad = 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    uint4 raw[SYMM_MAX_W];
+#pragma unroll
+    for (int q = 0; q < SYMM_MAX_W; ++q)
+      if (q < W) raw[q] = src[q][i];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < SYMM_MAX_W; ++q) {
+      if (q < W) {
+        const bf162* h = reinterpret_cast<const bf162*>(&raw[q]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+    }
+    if (p.mode == RS_ADAM) {
+      const RsAdam& a = p.adam[vr];
+      float4* m4 = reinterpret_cast<float4*>(a.m) + 2 * i;
+      float4* v4 = reinterpret_cast<float4*>(a.v) + 2 * i;
+      float4* w4 = reinterpret_cast<float4*>(a.master) + 2 * i;
+      float mm[8], vv[8], ww[8];
+      *reinterpret_cast<float4*>(mm) = m4[0]; *reinterpret_cast<float4*>(mm + 4) = m4[1];
+      *reinterpret_cast<float4*>(vv) = v4[0]; *reinterpret_cast<float4*>(vv + 4) = v4[1];
+      *reinterpret_cast<float4*>(ww) = w4[0]; *reinterpret_cast<float4*>(ww + 4) = w4[1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (!isfinite(acc[e])) bad = 1;
+        ss += acc[e] * acc[e];
+        adam_apply(acc[e] * a.grad_scale, mm[e], vv[e], ww[e], a);
+      }
+      m4[0] = *reinterpret_cast<float4*>(mm); m4[1] = *reinterpret_cast<float4*>(mm + 4);
+      v4[0] = *reinterpret_cast<float4*>(vv); v4[1] = *reinterpret_cast<float4*>(vv + 4);
+      w4[0] = *reinterpret_cast<float4*>(ww); w4[1] = *reinterpret_cast<float4*>(ww + 4);
+      uint4 o;
+      bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(ww[2 * e], ww[2 * e + 1]);
+      reinterpret_cast<uint4*>(a.param)[i] = o;
+    } else if (p.dst_fp32) {
+      float4* d4 = reinterpret_cast<float4*>(p.dst[vr]) + 2 * i;
+      if (p.mode == RS_ACCUMULATE) {
+        const float4 o0 = d4[0], o1 = d4[1];
+        acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
+        acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
+      }
+      d4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      d4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      if (p.do_stats) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (!isfinite(acc[e])) bad = 1; else ss += acc[e] * acc[e];
+        }
+      }
+    } else {
+      uint4 o;
+      bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      reinterpret_cast<uint4*>(p.dst[vr])[i] = o;
+      if (p.do_stats) {
+        // statistics of what is stored (the bf16-rounded value), as the separate pass would see it
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(o2[e]);
+          if (!isfinite(f.x) || !isfinite(f.y)) bad = 1; else ss += f.x * f.x + f.y * f.y;
+        }
+      }
+    }
+  }
+  if (p.do_stats && p.stats[vr] != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+      if (ss != 0.f) atomicAdd(&p.stats[vr][0], ss);
+      if (bad) p.stats[vr][1] = 1.f;
+    }
+  }
+  // all of this block's reads (and parameter writes) are done before peers are told so
+  peer_block_barrier(tab, rank, W, 0, 2 * p.epoch, p.wait_ns, p.status, 202);
+}
+
+struct AgParams {
+  SymmTable tab[SYMM_MAX_W];
+  void* out[SYMM_MAX_W];          // local gather buffer of virtual rank v (W * n_slice elements)
+  unsigned long long shard_off;   // byte offset of the unit's slice inside every heap
+  long long n_slice;              // elements per rank slice (multiple of 8)
+  int rank0, W;
+};
+
+// Plain all-gather by pulls: out[q * n_slice + i] = peer q's slice[i]. No barrier inside: parameter
+// shards only change in the optimizer step, which is fenced by symm_barrier_kernel.
+__global__ void __launch_bounds__(512) ag_pull_kernel(const AgParams p) {
+  const int vr = blockIdx.y;
+  const int rank = p.rank0 + vr;
+  const long long nvec = p.n_slice / 8;
+  const long long total = nvec * p.W;
+  uint4* out = static_cast<uint4*>(p.out[vr]);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int q = int(i / nvec);
+    const int peer = (rank + q) % p.W;
+    const long long j = i - (long long)q * nvec;
+    const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(p.tab[vr].base[peer]) + p.shard_off);
+    out[(long long)peer * nvec + j] = s[j];
+  }
+}
+
+struct BarrierParams {
+  SymmTable tab[SYMM_MAX_W];
+  int rank0, W, channel;
+  uint32_t epoch;
+  unsigned long long wait_ns;
+  int* status;
+};
+
+__global__ void symm_barrier_kernel(const BarrierParams p) {
+  peer_block_barrier(p.tab[blockIdx.y], p.rank0 + blockIdx.y, p.W, p.channel, p.epoch, p.wait_ns, p.status, 203);
+}
+
+// Waits on a flag nobody sets: exercises the time-out path (returns an error status, stays usable).
+__global__ void symm_wait_probe_kernel(const uint32_t* flag, uint32_t want, unsigned long long wait_ns, int* status) {
+  const uint64_t deadline = globaltimer_ns() + wait_ns;
+  uint32_t spins = 0;
+  while (int32_t(ld_acquire_sys(flag) - want) < 0) {
+    if ((++spins & 63) == 0 && globaltimer_ns() > deadline) {
+      if (status != nullptr && atomicCAS(status, 0, ERR_PEER_TIMEOUT) == 0) status[1] = 204;
+      return;
+    }
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// ---------------------------------------------------------------- heap + IPC
+B200_API int b200_symm_alloc(unsigned long long bytes, void** out) {
+  void* p = nullptr;
+  B200_CHECK(cudaMalloc(&p, bytes));
+  B200_CHECK(cudaMemset(p, 0, bytes));
+  *out = p;
+  return 0;
+}
+B200_API int b200_symm_free(void* p) { return static_cast<int>(cudaFree(p)); }
+B200_API int b200_symm_export(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  B200_CHECK(cudaIpcGetMemHandle(&h, p));
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+B200_API int b200_symm_import(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  B200_CHECK(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+B200_API int b200_symm_unimport(void* p) { return static_cast<int>(cudaIpcCloseMemHandle(p)); }
+B200_API int b200_symm_pad_bytes() { return SYMM_PAD_BYTES; }
+
+static int fill_tables(SymmTable* dst, const void* const* bases, int W, int vranks) {
+  // bases: vranks x W pointers (row v = table of virtual rank v)
+  for (int v = 0; v < vranks; ++v)
+    for (int r = 0; r < SYMM_MAX_W; ++r) dst[v].base[r] = r < W ? const_cast<void*>(bases[v * W + r]) : nullptr;
+  return 0;
+}
+
+// mode: 0 store, 1 accumulate (fp32 dst), 2 adam. adam_ptrs: vranks x 4 pointers (m, v, master, param);
+// adam_f: lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale.
+B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0, int vranks,
+                                      unsigned long long bucket_off, long long n_slice, void* const* dst, int dst_fp32,
+                                      int mode, void* const* stats, int do_stats, void* const* adam_ptrs,
+                                      const float* adam_f, unsigned int epoch, unsigned long long wait_ns, int blocks,
+                                      cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (n_slice == 0) return 0;
+  RsParams p = {};
+  fill_tables(p.tab, bases, W, vranks);
+  for (int v = 0; v < vranks; ++v) {
+    p.dst[v] = dst ? dst[v] : nullptr;
+    p.stats[v] = stats ? static_cast<float*>(stats[v]) : nullptr;
+    if (mode == RS_ADAM) {
+      p.adam[v] = RsAdam{static_cast<float*>(adam_ptrs[4 * v]), static_cast<float*>(adam_ptrs[4 * v + 1]),
+                         static_cast<float*>(adam_ptrs[4 * v + 2]), static_cast<bf16*>(adam_ptrs[4 * v + 3]),
+                         adam_f[0], adam_f[1], adam_f[2], adam_f[3], adam_f[4], adam_f[5], adam_f[6], adam_f[7]};
+    }
+  }
+  p.bucket_off = bucket_off; p.n_slice = n_slice; p.rank0 = rank0; p.W = W; p.mode = mode; p.dst_fp32 = dst_fp32;
+  p.do_stats = do_stats; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
+  if (blocks < 1) blocks = 1;
+  if (blocks > SYMM_MAX_BLOCKS) blocks = SYMM_MAX_BLOCKS;
+  rs_reduce_kernel<<<dim3(blocks, vranks), 512, 0, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_symm_all_gather(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,
+                                  long long n_slice, void* const* out, int blocks, cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (n_slice == 0) return 0;
+  AgParams p = {};
+  fill_tables(p.tab, bases, W, vranks);
+  for (int v = 0; v < vranks; ++v) p.out[v] = out[v];
+  p.shard_off = shard_off; p.n_slice = n_slice; p.rank0 = rank0; p.W = W;
+  if (blocks < 1) blocks = 1;
+  ag_pull_kernel<<<dim3(blocks, vranks), 512, 0, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int vranks, int channel, unsigned int epoch,
+                               unsigned long long wait_ns, cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || channel < 1 || channel >= SYMM_CHANNELS) return static_cast<int>(cudaErrorInvalidValue);
+  BarrierParams p = {};
+  fill_tables(p.tab, bases, W, vranks);
+  p.rank0 = rank0; p.W = W; p.channel = channel; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
+  symm_barrier_kernel<<<dim3(1, vranks), 32, 0, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_symm_wait_probe(const void* flag, unsigned int want, unsigned long long wait_ns, cudaStream_t st) {
+  symm_wait_probe_kernel<<<1, 1, 0, st>>>(static_cast<const uint32_t*>(flag), want, wait_ns, status_ptr());
+  return static_cast<int>(cudaGetLastError());
+}

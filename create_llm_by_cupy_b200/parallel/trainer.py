@@ -105,6 +105,7 @@ class Trainer:
                                               out_shard=mgr.get_replica_optimizer_shard_view(), stats=stats,
                                               max_grad_norm=self.max_grads)
                 mgr.allgather_replicated_params_from_optimizer_shards()
+            mgr.after_optimizer_step()
         # one host read per step: loss, gradient statistics
         host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
         loss_val = host[0] / n_micro

@@ -100,7 +100,10 @@ class MemoryZeRO3Manager:
         # model/ZeRO3.py:1396); with a single micro-batch the reduced bf16 gradient is used as is.
         self.grad_dtype = self.dtype if (self.accum_steps == 1) else torch.float32
         self.direct_grad = self.accum_steps == 1      # reduced gradients land in the shard as they are
-        self.param_shard_f16 = torch.zeros(max(self.shard_size, 1), dtype=self.dtype, device=self.device)[:self.shard_size]
+        if fused is not None:      # peers pull parameter slices straight out of this buffer
+            self.param_shard_f16 = fused.alloc(max(self.shard_size, 8), self.dtype)[:self.shard_size]
+        else:
+            self.param_shard_f16 = torch.zeros(max(self.shard_size, 1), dtype=self.dtype, device=self.device)[:self.shard_size]
         self.grad_shard_f16 = torch.zeros(max(self.shard_size, 1), dtype=self.grad_dtype, device=self.device)[:self.shard_size]
         self.live_param_to_idx = {}     # data_ptr of a live parameter view -> index in model.params
         self._replica_tmp = {}
@@ -108,7 +111,8 @@ class MemoryZeRO3Manager:
         self._initialize_param_shard_from_rank0()
 
         alloc = fused.alloc if fused is not None else None
-        self.gather_pool = _Pool(self.dtype, self.device, alloc if (fused is not None and fused.gather) else None)
+        self.gather_pool = _Pool(self.dtype, self.device, None)
+        self._params_ready_event = None   # recorded after the optimizer step; gathers wait on it
         self.grad_pool = _Pool(self.dtype, self.device, alloc)
         self.live = {}              # uid -> _Buf holding gathered parameters
         self.pending_gather = {}    # uid -> _Buf with an all-gather in flight
@@ -197,10 +201,10 @@ class MemoryZeRO3Manager:
             torch.cuda.synchronize(self.device)
 
     # ------------------------------------------------------------------ stream helpers
-    def _record(self, stream):
+    def _record(self, stream, timing: bool = False):
         if not self.cuda:
             return None
-        ev = torch.cuda.Event()
+        ev = torch.cuda.Event(enable_timing=timing)
         ev.record(stream)
         return ev
 
@@ -239,6 +243,7 @@ class MemoryZeRO3Manager:
         b.uid = uid
         with self._comm_ctx():
             self._wait(self.comm_stream, b.free_event)
+            self._wait(self.comm_stream, self._params_ready_event)
             if self.fused is not None and self.fused.gather:
                 self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.comm_stream)
             else:
@@ -260,9 +265,9 @@ class MemoryZeRO3Manager:
                 return None
         if b.ready_event is not None:
             if self.profile_comm:
-                e0 = self._record(self.compute_stream)
+                e0 = self._record(self.compute_stream, True)
                 self._wait(self.compute_stream, b.ready_event)
-                self.exposed_pairs.append((e0, self._record(self.compute_stream)))
+                self.exposed_pairs.append((e0, self._record(self.compute_stream, True)))
             else:
                 self._wait(self.compute_stream, b.ready_event)
         self.live[uid] = b
@@ -442,7 +447,8 @@ class MemoryZeRO3Manager:
                 self._wait(self.comm_stream, ev)
                 if self.fused is not None:
                     self.fused.reduce_scatter_accumulate(dst, b.t, accumulate=not self.direct_grad,
-                                                         stream=self.comm_stream)
+                                                         stream=self.comm_stream, stats=self._stats,
+                                                         do_stats=self.micro_index == self.accum_steps - 1)
                 elif self.direct_grad:
                     self.comm.reduce_scatter(dst, b.t)
                 else:
@@ -544,15 +550,17 @@ class MemoryZeRO3Manager:
         self.flush_buckets()
         if self.cuda and self.comm_stream is not self.compute_stream:
             if self.profile_comm:
-                e0 = self._record(self.compute_stream)
+                e0 = self._record(self.compute_stream, True)
                 self.compute_stream.wait_stream(self.comm_stream)
-                self.exposed_pairs.append((e0, self._record(self.compute_stream)))
+                self.exposed_pairs.append((e0, self._record(self.compute_stream, True)))
             else:
                 self.compute_stream.wait_stream(self.comm_stream)
 
     def zero_grad(self):
         self.progress_async_reduces(force=True)
         self.micro_index = 0
+        if self.fused is not None:
+            self._stats.zero_()       # the fused reduce kernels add this step's statistics into it
         if not self.direct_grad:
             self.grad_shard_f16.zero_()
         if self.replica_grad_shard is not None:
@@ -565,8 +573,9 @@ class MemoryZeRO3Manager:
         ``self.grad_stats_device`` for the optimizer's on-device clip / skip."""
         self.wait_reductions()
         st = self._stats
-        st.zero_()
-        F.grad_stats(self.grad_shard_f16, st)
+        if self.fused is None or self.world_size == 1:
+            st.zero_()
+            F.grad_stats(self.grad_shard_f16, st)
         if self.replica_grad_shard is not None:
             F.grad_stats(self.replica_grad_shard, st)
         if self.world_size > 1:
@@ -591,6 +600,16 @@ class MemoryZeRO3Manager:
         if self.world_size > 1:
             self.comm.all_reduce(st)
         return float(st[0]) ** 0.5
+
+    def after_optimizer_step(self):
+        """Order the next gathers after the parameter update: locally with an event the comm stream
+        waits on, and across GPUs (fused mode, where peers read this shard directly) with a
+        device-side barrier."""
+        if not self.cuda or self.world_size == 1:
+            return
+        if self.fused is not None:
+            self.fused.barrier(self.compute_stream)
+        self._params_ready_event = self._record(self.compute_stream)
 
     def get_param_shard_view(self):
         return self.param_shard_f16

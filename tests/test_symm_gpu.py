@@ -1,0 +1,143 @@
+"""Fused peer-memory collectives. On one GPU the W ranks are virtual: W heaps on the same device
+and ONE launch whose gridDim.y enumerates the ranks. On >= 2 GPUs the real thing runs in child
+processes (NCCL for the baseline comparison, NVLS off)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from create_llm_by_cupy_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_virtual_ranks_reduce_scatter_store_accumulate_and_stats(W):
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    vr = LocalVirtualRanks(W)
+    n_slice = 8 * 1000 + 8
+    off, buckets = vr.alloc(n_slice * W, torch.bfloat16)
+    for r, b in enumerate(buckets):
+        b.copy_((torch.randn(n_slice * W, generator=torch.Generator().manual_seed(r)) * 2).to(torch.bfloat16))
+    full = torch.stack([b.float() for b in buckets]).sum(0)
+    # store (bf16) with statistics
+    dsts = [torch.empty(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    stats = [torch.zeros(2, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, dsts, stats=stats, do_stats=True)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for r in range(W):
+        ref = full[r * n_slice:(r + 1) * n_slice]
+        assert (dsts[r].float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+        assert abs(stats[r][0].item() - (dsts[r].float() ** 2).sum().item()) <= 1e-3 * stats[r][0].item()
+        assert stats[r][1].item() == 0
+    # accumulate into fp32 twice
+    acc = [torch.ones(n_slice, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, acc, accumulate=True)
+    vr.reduce_scatter(off, n_slice, acc, accumulate=True, stats=stats, do_stats=False)
+    torch.cuda.synchronize()
+    for r in range(W):
+        ref = 1 + 2 * full[r * n_slice:(r + 1) * n_slice]
+        assert (acc[r] - ref).abs().max().item() < 1e-3
+    # a NaN in one rank's bucket is flagged on the rank that owns that slice
+    buckets[1][n_slice + 5] = float("nan")
+    st2 = [torch.zeros(2, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, dsts, stats=st2, do_stats=True)
+    torch.cuda.synchronize()
+    assert st2[1][1].item() == 1.0 and st2[0][1].item() == 0.0
+    assert native.read_status() == (0, 0)
+    vr.close()
+
+
+def test_virtual_ranks_fused_adam_matches_separate_kernels():
+    from create_llm_by_cupy_b200.ops import functional as F
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    W, n_slice = 4, 8 * 500
+    vr = LocalVirtualRanks(W)
+    off, buckets = vr.alloc(n_slice * W, torch.bfloat16)
+    for r, b in enumerate(buckets):
+        b.copy_(torch.randn(n_slice * W, generator=torch.Generator().manual_seed(10 + r)).to(torch.bfloat16))
+    full = torch.stack([b.float() for b in buckets]).sum(0)
+    hp = dict(lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-6, weight_decay=0.1)
+    st = dict(m=[], v=[], master=[], param=[])
+    ref = []
+    for r in range(W):
+        w0 = torch.randn(n_slice, device="cuda", generator=torch.Generator(device="cuda").manual_seed(r))
+        st["m"].append(torch.zeros(n_slice, device="cuda"))
+        st["v"].append(torch.zeros(n_slice, device="cuda"))
+        st["master"].append(w0.clone())
+        st["param"].append(torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda"))
+        m, v, w, p = torch.zeros(n_slice, device="cuda"), torch.zeros(n_slice, device="cuda"), w0.clone(), \
+            torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda")
+        F.adamw_step(full[r * n_slice:(r + 1) * n_slice].contiguous(), m, v, w, p, step=1, grad_scale=0.25, **hp)
+        ref.append((w, p))
+    adam = dict(st, lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"], weight_decay=hp["weight_decay"],
+                m_corr=1 / (1 - 0.9), v_corr=1 / (1 - 0.95), grad_scale=0.25)
+    dummy = [torch.empty(8, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, dummy, adam=adam)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for r in range(W):
+        assert (st["master"][r] - ref[r][0]).abs().max().item() < 1e-5
+        assert (st["param"][r].float() - ref[r][1].float()).abs().max().item() < 1e-2
+    vr.close()
+
+
+def test_virtual_ranks_all_gather_and_barrier():
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    W, n = 4, 8 * 333
+    vr = LocalVirtualRanks(W)
+    off, shards = vr.alloc(n, torch.bfloat16)
+    for r, s in enumerate(shards):
+        s.copy_(torch.full((n,), float(r + 1)).to(torch.bfloat16))
+    outs = [torch.zeros(n * W, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    vr.barrier()
+    vr.all_gather(off, n, outs)
+    vr.barrier()
+    torch.cuda.synchronize()
+    ref = torch.cat([torch.full((n,), float(r + 1)) for r in range(W)])
+    for o in outs:
+        assert torch.equal(o.float().cpu(), ref)
+    assert native.read_status() == (0, 0)
+    vr.close()
+
+
+def test_wait_on_a_flag_nobody_sets_times_out_with_an_error_status():
+    """Failure detection on the device: the wait gives up after its (short) budget, records
+    ERR_PEER_TIMEOUT and returns; the context stays usable."""
+    lib = native.lib()
+    native.status_tensor()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    import ctypes
+    native.check(lib.b200_symm_wait_probe(ctypes.c_void_p(flag.data_ptr()), ctypes.c_uint(1),
+                                          ctypes.c_ulonglong(50_000_000), native.stream_ptr()), "wait_probe")
+    torch.cuda.synchronize()
+    code, kid = native.read_status()
+    assert (code, kid) == (2, 204)
+    assert native.read_status() == (0, 0)           # cleared, and the device still answers
+    x = torch.ones(16, device="cuda")
+    assert float(x.sum()) == 16.0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
+    outs = {}
+    for mode in ("nccl", "fused"):
+        out = tmp_path / f"{mode}.pt"
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+               "--master-addr", "127.0.0.1", "--master-port", str(29600 + (os.getpid() % 300) + (mode == "fused")),
+               script, mode, str(out)]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        outs[mode] = torch.load(out)
+    a, b = outs["nccl"], outs["fused"]
+    for la, lb in zip(a["losses"], b["losses"]):
+        assert abs(la - lb) < 3e-2, (a["losses"], b["losses"])
+    assert abs(a["param_norm"] - b["param_norm"]) < 1e-2 * a["param_norm"]
