@@ -27,6 +27,24 @@ def init_weight(shape, std: float, dtype, device, generator=None) -> torch.Tenso
     return w.to(device=device, dtype=dtype)
 
 
+def _weight_gemm(layer, a: torch.Tensor, widx: int, *, trans_b: bool = False, add=None) -> torch.Tensor:
+    """``a @ W`` (or ``a @ W^T``) for ``W = layer.params[widx]``. When the ZeRO manager deferred the
+    all-gather of this layer's unit, this GEMM is the one that carries it: the fused kernel pulls
+    the unit from the peers while it multiplies (``pending_gather`` is set by the manager and names
+    each parameter by its index in ``model.params``)."""
+    pg = getattr(layer, "pending_gather", None)
+    if pg is not None:
+        layer.pending_gather = None
+        idx = layer._zero3_param_indices[widx]
+        if not pg.done and pg.mgr.layout.slots[idx].unit == pg.uid and a.is_cuda:
+            out = pg.gemm(a, idx, trans_b=trans_b, add=add)
+            pg.mgr.deferred.pop(pg.uid, None)
+            return out
+        pg.flush()
+        pg.mgr.deferred.pop(pg.uid, None)
+    return F.gemm(a, layer.params[widx], trans_b=trans_b, add=add)
+
+
 def _store_grad(dst: torch.Tensor | None, src: torch.Tensor) -> torch.Tensor:
     if dst is None:
         return src
@@ -100,7 +118,21 @@ class GroupedQueryAttention:
     def _rope(self, T, device):
         return F.rope_table(max(T, self.T), self.D, self.rope_base, device)
 
+    def _prerotate(self, x) -> bool:
+        """head_dim 128 on CUDA runs the tcgen05 attention kernels, which take Q and K already
+        rotated: the rotary embedding is then applied in place to the [K|Q] columns of the packed
+        projection (one pass over 5/6 of it) and undone on d[K|Q] after the backward kernels."""
+        return x.is_cuda and self.D == 128 and self.flash_backend != "none" and F.FLASH_TC
+
+    def _project(self, x, T, tabs, first: bool):
+        kqv = _weight_gemm(self, x, 0) if first else F.gemm(x, self.params[0])
+        if self._prerotate(x):
+            F.rope_inplace(kqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0)
+        return kqv
+
     def _attend(self, q, k, v, valid_len, tabs):
+        if self._prerotate(q):
+            return F.flash_attn_fwd(q, k, v, valid_len=valid_len, scale=self.scale, rope=None)
         if self.flash_backend == "none":
             o, lse, _, _, _ = F._attn_reference(q, k, v, valid_len, self.scale, tabs[0], tabs[1])
             return o.to(q.dtype).contiguous(), lse
@@ -110,9 +142,9 @@ class GroupedQueryAttention:
     def forward(self, x: torch.Tensor, B: int, T: int, valid_len=None, residual=None,
                 train_flg: bool = True) -> torch.Tensor:
         """x: normed input [M, H]. Returns W_O(attn) (+ residual) as [M, H]."""
-        kqv = F.gemm(x, self.params[0])
-        q, k, v = self._split(kqv, B, T)
         tabs = self._rope(T, x.device)
+        kqv = self._project(x, T, tabs, True)
+        q, k, v = self._split(kqv, B, T)
         o, lse = self._attend(q, k, v, valid_len, tabs)
         out = F.gemm(o.view(B * T, self.H), self.params[1], add=residual)
         if train_flg:
@@ -126,7 +158,7 @@ class GroupedQueryAttention:
         x, B, T, valid_len, kqv, o, lse = self.cache
         tabs = self._rope(T, x.device)
         if kqv is None:
-            kqv = F.gemm(x, self.params[0])
+            kqv = self._project(x, T, tabs, False)
         q, k, v = self._split(kqv, B, T)
         if o is None:
             o, lse = self._attend(q, k, v, valid_len, tabs)
@@ -142,6 +174,10 @@ class GroupedQueryAttention:
                                    rope=tuple(t.cpu() for t in tabs))
             for dst, src in zip((dq, dk, dv), res):
                 dst.copy_(src.to(dst.device, dst.dtype))
+        elif self._prerotate(x):
+            F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
+                             scale=self.scale, rope=None, out=(dq, dk, dv))
+            F.rope_inplace(dkqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0, inverse=True)
         else:
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
                              scale=self.scale, rope=tabs, out=(dq, dk, dv))
@@ -222,11 +258,11 @@ class SwiGLU:
     def backward(self, dout: torch.Tensor, grad_out=None) -> torch.Tensor:
         x, gv, act = self.cache
         if gv is None:
-            gv = F.gemm(x, self.params[0])
+            gv = _weight_gemm(self, x, 0)
             act = F.swiglu_fwd(gv)
         go = grad_out if grad_out else (None, None)
         dW_out = F.gemm(act, dout, trans_a=True, out=go[1])
-        dact = F.gemm(dout, self.params[1], trans_b=True)
+        dact = _weight_gemm(self, dout, 1, trans_b=True)
         dgv = F.swiglu_bwd(dact, gv)
         dW_gv = F.gemm(x, dgv, trans_a=True, out=go[0])
         dx = F.gemm(dgv, self.params[0], trans_b=True)

@@ -288,6 +288,7 @@ class Cupa_ver4:
         positions >= x_pa are masked) or None. Returns the mean CE loss as a device scalar."""
         manager = manager if manager is not None else self._local_manager()
         self._manager = manager
+        manager.phase = "fwd"
         self.grads = []
         B, T = x.shape
         self._BT = (B, T)
@@ -328,6 +329,7 @@ class Cupa_ver4:
 
     def backward(self, GradScale: float = 1.0, manager=None):
         manager = manager if manager is not None else getattr(self, "_manager", None) or self._local_manager()
+        manager.phase = "bwd"
         W = manager.get_live_embedding()
         if W is None:
             W = manager.gather_embedding()

@@ -40,6 +40,9 @@ enum SwizzleMode { SWIZZLE_NONE_ = 0, SWIZZLE_128B_ = 3 };
 const CUtensorMap* get_tensor_map_2d(const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                      uint32_t box_rows, uint32_t box_cols, int elem_bytes, int swizzle);
 
+const CUtensorMap* get_tensor_map_bthd(const void* base, uint64_t B, uint64_t T, uint64_t heads, uint64_t D,
+                                       uint64_t bs, uint64_t ts, uint64_t hs, uint32_t box_t, uint32_t box_d);
+
 int num_sms();
 
 }  // namespace b200

@@ -878,3 +878,19 @@ B200_API int b200_decode_attn(const void* q, const void* kcache, const void* vca
 #undef B200_DEC
   return static_cast<int>(cudaGetLastError());
 }
+
+// delta[b, h, t] = sum_d dO * O (fp32), the row term of the softmax gradient. strides: o (3), dout (3).
+B200_API int b200_flash_delta(const void* o, const void* dout, void* delta, const long long* strides, int B, int T,
+                              int QH, int D, cudaStream_t st) {
+  if (B <= 0 || T <= 0) return 0;
+  FlashParams p = {};
+  p.o = const_cast<bf16*>(static_cast<const bf16*>(o));
+  p.dout = static_cast<const bf16*>(dout);
+  p.delta = static_cast<float*>(delta);
+  p.o_bs = strides[0]; p.o_ts = strides[1]; p.o_hs = strides[2];
+  p.do_bs = strides[3]; p.do_ts = strides[4]; p.do_hs = strides[5];
+  p.B = B; p.T = T; p.QH = QH;
+  const int total_warps = B * QH * T;
+  flash_delta_kernel<<<(total_warps + 7) / 8, 256, 0, st>>>(p, D);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,500 @@
+// Causal GQA flash-attention BACKWARD on the 5th-generation tensor cores (head_dim 128).
+//
+// Two kernels, both TMA-fed with accumulators in TMEM and the element-wise softmax-gradient math
+// done by two warpgroups that split the columns of each score tile:
+//
+//   flash_bwd_dq_tc  : CTA = 128 queries of one (batch, head); loops over 128-key tiles.
+//        S  = Q K_j^T          (SS MMA)            dP = dO V_j^T        (SS MMA)
+//        dS = exp2(S*c - lse) * (dP - delta) * scale   -> bf16 into TMEM
+//        dQ += dS K_j          (A = dS from TMEM, B = K_j MN-major), accumulated in TMEM over j
+//   flash_bwd_dkv_tc : CTA = 128 keys of one (batch, kv head); loops over the query heads of the
+//        group and over 64-query tiles at or below the diagonal, working on transposed scores so
+//        that key rows are TMEM lanes:
+//        S^T = K Q_i^T (SS)    dP^T = V dO_i^T (SS)   P^T, dS^T -> bf16 into TMEM
+//        dV += P^T dO_i        dK += dS^T Q_i      (A from TMEM, B = the same Q_i / dO_i tiles read
+//                                                   MN-major), accumulated in TMEM over all i
+// Q and K are expected already rotated; dQ and dK are gradients w.r.t. the rotated tensors (the
+// caller un-rotates). No atomics and no fp32 scratch; S and dP are recomputed by both kernels.
+//
+// Reference counterpart: cupy_flash_gqa_backward (model/flash_attention.py:109-176).
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int FB_D = 128;
+constexpr int FBT_THREADS = 384;          // warps 0-3: producer / MMA / TMEM; warps 4-11: two math warpgroups
+constexpr int FB_TILE = 128 * FB_D * 2;   // 32 KiB
+constexpr float kFbLog2e = 1.4426950408889634f;
+
+struct FlashBwdTcParams {
+  bf16* dq; bf16* dk; bf16* dv;
+  const float* lse;      // [B, QH, T]
+  const float* delta;    // [B, QH, T]
+  const int* valid_len;
+  long long dq_bs, dq_ts, dq_hs;
+  long long dk_bs, dk_ts, dk_hs;
+  long long dv_bs, dv_ts, dv_hs;
+  int B, T, QH, KVH;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Store one accumulator row (fp32 columns of this thread's TMEM lane) as bf16 to global. The TMEM
+// load is warp-collective (.sync.aligned): every lane of the warp must call this; `active` only
+// predicates the global stores (rows past the end of the sequence).
+__device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, bf16* grow, int col_lo, int col_hi, bool active) {
+  for (int c = col_lo; c < col_hi; c += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(taddr + c, r);
+    tmem_ld_wait();
+    if (!active) continue;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 v;
+      bf162* v2 = reinterpret_cast<bf162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        v2[e] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * e]), __uint_as_float(r[i + 2 * e + 1]));
+      *reinterpret_cast<uint4*>(grow + c + i) = v;
+    }
+  }
+}
+
+// =================================================================== dQ
+struct FdqSmem {
+  static constexpr int kQ = 0, kDO = FB_TILE, kKV = 2 * FB_TILE;           // KV stage s: K, V
+  static constexpr int kBar = kKV + 2 * 2 * FB_TILE;
+  // qdo_full, kv_full[2], kv_empty[2], sdp_full, ds_full   = 7 barriers
+  static constexpr int kTotal = kBar + 7 * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(FBT_THREADS, 1)
+flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const FlashBwdTcParams p) {
+  extern __shared__ uint8_t fb_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fb_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FdqSmem::kBar);
+  uint64_t* qdo_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_full = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mtile = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.QH / p.KVH);
+  const int m0 = mtile * 128;
+  const int T = p.T;
+  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int n_tiles = min(mtile + 1, (max(vlen, 1) + 127) / 128);
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_full, 256);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 2) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDS = 256, kColDQ = 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(qdo_full, 2 * FB_TILE);
+      tma_load_4d(smem + FdqSmem::kQ, &tmQ, qdo_full, 0, h, m0, b);
+      tma_load_4d(smem + FdqSmem::kQ + 16384, &tmQ, qdo_full, 64, h, m0, b);
+      tma_load_4d(smem + FdqSmem::kDO, &tmDO, qdo_full, 0, h, m0, b);
+      tma_load_4d(smem + FdqSmem::kDO + 16384, &tmDO, qdo_full, 64, h, m0, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        uint8_t* sK = smem + FdqSmem::kKV + s * 2 * FB_TILE;
+        uint8_t* sV = sK + FB_TILE;
+        mbar_expect_tx(&kv_full[s], 2 * FB_TILE);
+        tma_load_4d(sK, &tmK, &kv_full[s], 0, kvh, j * 128, b);
+        tma_load_4d(sK + 16384, &tmK, &kv_full[s], 64, kvh, j * 128, b);
+        tma_load_4d(sV, &tmV, &kv_full[s], 0, kvh, j * 128, b);
+        tma_load_4d(sV + 16384, &tmV, &kv_full[s], 64, kvh, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);   // both operands K-major
+      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);   // B MN-major
+      const uint32_t aQ = smem_u32(smem + FdqSmem::kQ), aDO = smem_u32(smem + FdqSmem::kDO);
+      auto issue_scores = [&](int j) {
+        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE), aV = aK + FB_TILE;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + kColS, umma_smem_desc(aQ + off, 16, 1024), umma_smem_desc(aK + off, 16, 1024),
+                       idesc_kk, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + kColDP, umma_smem_desc(aDO + off, 16, 1024), umma_smem_desc(aV + off, 16, 1024),
+                       idesc_kk, kk != 0);
+        }
+        umma_commit(sdp_full);
+      };
+      bool ok = mbar_wait(qdo_full, 0, abort_flag);
+      if (ok && n_tiles > 0) {
+        ok = mbar_wait(&kv_full[0], 0, abort_flag);
+        if (ok) { tc_fence_after(); issue_scores(0); }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (!mbar_wait(ds_full, j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(tmem_base + kColDQ, tmem_base + kColDS + kk * 8, umma_smem_desc(aK + kk * 2048, 16384, 1024),
+                       idesc_mn, (j | kk) != 0);
+        umma_commit(&kv_empty[j & 1]);
+        if (j + 1 < n_tiles) {
+          if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(j + 1);
+        } else {
+          umma_commit(sdp_full);      // last dQ MMA done: the math warps may read dQ
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;                   // TMEM lane quarter
+    const int half = (warp - 4) >> 2;         // which 64 key columns of each tile this warpgroup owns
+    const int row = m0 + q * 32 + lane;
+    const uint32_t lane_sel = uint32_t(q * 32) << 16;
+    const float sl2 = p.scale * kFbLog2e;
+    const size_t sidx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
+    const float lse2 = (row < T) ? p.lse[sidx] * kFbLog2e : INFINITY;
+    const float dlt = (row < T) ? p.delta[sidx] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int n0 = j * 128;
+      const bool need_mask = (j == mtile) || (n0 + 128 > vlen);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        const int col = half * 64 + c * 32;
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + col, rs);
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + col, rp);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float d0, d1;
+          {
+            float pe = exp2f(__uint_as_float(rs[e]) * sl2 - lse2);
+            const int key = n0 + col + e;
+            if (need_mask && (key > row || key >= vlen)) pe = 0.f;
+            d0 = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
+          }
+          {
+            float pe = exp2f(__uint_as_float(rs[e + 1]) * sl2 - lse2);
+            const int key = n0 + col + e + 1;
+            if (need_mask && (key > row || key >= vlen)) pe = 0.f;
+            d1 = pe * (__uint_as_float(rp[e + 1]) - dlt) * p.scale;
+          }
+          const bf162 t = __floats2bfloat162_rn(d0, d1);
+          pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+        }
+        tmem_st_32x32b_x16(tmem_base + lane_sel + kColDS + (col >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (ok) {
+      // the commit after the last dQ MMA flips sdp_full once more
+      if (mbar_wait(sdp_full, n_tiles & 1, abort_flag)) {
+        tc_fence_after();
+        bf16* grow = p.dq + b * p.dq_bs + (long long)min(row, T - 1) * p.dq_ts + h * p.dq_hs;
+        store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, int(*abort_flag)) == 0) p.status[1] = 310;
+  }
+}
+
+// =================================================================== dK, dV
+constexpr int FKV_BQ = 64;                       // query rows per iteration
+constexpr int FKV_QTILE = FKV_BQ * FB_D * 2;     // 16 KiB
+struct FdkvSmem {
+  static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;            // stage s: Q_i (16 KiB), dO_i (16 KiB)
+  static constexpr int kStats = kQ + 2 * 2 * FKV_QTILE;                    // stage s: lse2[64], delta[64]
+  static constexpr int kBar = kStats + 2 * 2 * FKV_BQ * 4;
+  // kv_full, q_full[2], q_empty[2], st_full[2] (stats staged), sdp_full, pds_full, acc_done  = 10 barriers
+  static constexpr int kTotal = kBar + 10 * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(FBT_THREADS, 1)
+flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                        const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const FlashBwdTcParams p) {
+  extern __shared__ uint8_t fb_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fb_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FdkvSmem::kBar);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;
+  uint64_t* q_empty = bars + 3;
+  uint64_t* st_full = bars + 5;
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* pds_full = bars + 8;
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntile = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int n0 = ntile * 128;
+  const int T = p.T;
+  const int R = p.QH / p.KVH;
+  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int i_first = n0 / FKV_BQ;                                     // first 64-query tile at / below the diagonal
+  const int n_qt = (T + FKV_BQ - 1) / FKV_BQ - i_first;
+  const int iters = (n0 < vlen) ? R * n_qt : 0;                        // keys past valid_len: zero gradients
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 256);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 2) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColST = 0, kColDPT = 64, kColPT = 128, kColDST = 160, kColDV = 256, kColDK = 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * FB_TILE);
+      tma_load_4d(smem + FdkvSmem::kK, &tmK, kv_full, 0, kvh, n0, b);
+      tma_load_4d(smem + FdkvSmem::kK + 16384, &tmK, kv_full, 64, kvh, n0, b);
+      tma_load_4d(smem + FdkvSmem::kV, &tmV, kv_full, 0, kvh, n0, b);
+      tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, n0, b);
+      for (int it = 0; it < iters; ++it) {
+        const int s = it & 1;
+        const int h = kvh * R + it / n_qt;
+        const int m0 = (i_first + it % n_qt) * FKV_BQ;
+        if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        uint8_t* sQ = smem + FdkvSmem::kQ + s * 2 * FKV_QTILE;
+        uint8_t* sDO = sQ + FKV_QTILE;
+        mbar_expect_tx(&q_full[s], 2 * FKV_QTILE);
+        tma_load_4d(sQ, &tmQ, &q_full[s], 0, h, m0, b);
+        tma_load_4d(sQ + 8192, &tmQ, &q_full[s], 64, h, m0, b);
+        tma_load_4d(sDO, &tmDO, &q_full[s], 0, h, m0, b);
+        tma_load_4d(sDO + 8192, &tmDO, &q_full[s], 64, h, m0, b);
+      }
+    }
+  } else if (warp == 3) {
+    // stages the per-query statistics (lse in log2 units, delta) of each query tile in shared memory
+    for (int it = 0; it < iters; ++it) {
+      const int s = it & 1;
+      const int h = kvh * R + it / n_qt;
+      const int m0 = (i_first + it % n_qt) * FKV_BQ;
+      if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+      float* st = reinterpret_cast<float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
+      for (int r = lane; r < FKV_BQ; r += 32) {
+        const int row = m0 + r;
+        const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
+        st[r] = (row < T) ? p.lse[idx] * kFbLog2e : INFINITY;     // +inf => P = 0 for rows past T
+        st[FKV_BQ + r] = (row < T) ? p.delta[idx] : 0.f;
+      }
+      mbar_arrive(&st_full[s]);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, FKV_BQ, 0, 0);   // [128 keys x 64 q], K-major operands
+      constexpr uint32_t idesc_g = umma_idesc_bf16(128, FB_D, 0, 1);     // [128 keys x 128 d], B MN-major
+      const uint32_t aK = smem_u32(smem + FdkvSmem::kK), aV = smem_u32(smem + FdkvSmem::kV);
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+        // the math warps have consumed the previous S^T / dP^T (pds_full of it - 1 was waited below)
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + s * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;     // 128-row tiles
+          const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;      // 64-row tiles
+          umma_bf16_ss(tmem_base + kColST, umma_smem_desc(aK + offk, 16, 1024), umma_smem_desc(aQ + offq, 16, 1024),
+                       idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;
+          const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + kColDPT, umma_smem_desc(aV + offk, 16, 1024), umma_smem_desc(aDO + offq, 16, 1024),
+                       idesc_s, kk != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // B = dO_i / Q_i read MN-major: 64 query rows (k), 128 d (n); 64-d chunks are 8 KiB apart
+#pragma unroll
+        for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
+          umma_bf16_ts(tmem_base + kColDV, tmem_base + kColPT + kk * 8, umma_smem_desc(aDO + kk * 2048, 8192, 1024),
+                       idesc_g, (it | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
+          umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDST + kk * 8, umma_smem_desc(aQ + kk * 2048, 8192, 1024),
+                       idesc_g, (it | kk) != 0);
+        }
+        umma_commit(&q_empty[s]);
+      }
+      if (ok) umma_commit(acc_done);
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;         // which 32 query columns of each 64-wide tile
+    const int key = n0 + q * 32 + lane;
+    const uint32_t lane_sel = uint32_t(q * 32) << 16;
+    const float sl2 = p.scale * kFbLog2e;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int s = it & 1;
+      const int m0 = (i_first + it % n_qt) * FKV_BQ;
+      if (!mbar_wait(&st_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
+      const int col = half * 32;
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + col, rs);
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + col, rp);
+      tmem_ld_wait();
+      uint32_t pk[16], dk_[16];
+      const bool key_dead = key >= vlen;
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int qc = col + e + u;
+          float pe = exp2f(__uint_as_float(rs[e + u]) * sl2 - st[qc]);
+          if (key_dead || key > m0 + qc) pe = 0.f;
+          pv[u] = pe;
+          dv[u] = pe * (__uint_as_float(rp[e + u]) - st[FKV_BQ + qc]) * p.scale;
+        }
+        const bf162 t0 = __floats2bfloat162_rn(pv[0], pv[1]);
+        const bf162 t1 = __floats2bfloat162_rn(dv[0], dv[1]);
+        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
+        dk_[e >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
+      }
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kColPT + (col >> 1), pk);
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kColDST + (col >> 1), dk_);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    if (ok) {
+      if (iters > 0) ok = mbar_wait(acc_done, 0, abort_flag);
+      tc_fence_after();
+      if (ok) {
+        const bool live = key < T;
+        bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
+        bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
+        if (iters > 0) {
+          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
+          store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * 64, half * 64 + 64, live);
+        } else if (live) {
+          const uint4 z = make_uint4(0, 0, 0, 0);
+          for (int c = half * 64; c < half * 64 + 64; c += 8) {
+            *reinterpret_cast<uint4*>(krow + c) = z;
+            *reinterpret_cast<uint4*>(vrow + c) = z;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, int(*abort_flag)) == 0) p.status[1] = 311;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Gradients w.r.t. (already rotated) q, k and v. delta [B,QH,T] = sum_d dO*O must have been
+// computed (b200_flash_delta). strides: q, k, v, dout, dq, dk, dv (3 each: batch, token, head).
+B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const void* lse,
+                               const void* delta, void* dq, void* dk, void* dv, const void* valid_len,
+                               const long long* s, int B, int T, int QH, int KVH, int D, float scale,
+                               cudaStream_t st) {
+  if (B <= 0 || T <= 0) return 0;
+  if (D != FB_D || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
+  for (int i = 0; i < 21; ++i)
+    if (s[i] % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const CUtensorMap* tq128 = get_tensor_map_bthd(q, B, T, QH, D, s[0], s[1], s[2], 128, 64);
+  const CUtensorMap* tdo128 = get_tensor_map_bthd(dout, B, T, QH, D, s[9], s[10], s[11], 128, 64);
+  const CUtensorMap* tq64 = get_tensor_map_bthd(q, B, T, QH, D, s[0], s[1], s[2], 64, 64);
+  const CUtensorMap* tdo64 = get_tensor_map_bthd(dout, B, T, QH, D, s[9], s[10], s[11], 64, 64);
+  const CUtensorMap* tk = get_tensor_map_bthd(k, B, T, KVH, D, s[3], s[4], s[5], 128, 64);
+  const CUtensorMap* tv = get_tensor_map_bthd(v, B, T, KVH, D, s[6], s[7], s[8], 128, 64);
+  if (!tq128 || !tdo128 || !tq64 || !tdo64 || !tk || !tv) return static_cast<int>(cudaErrorInvalidValue);
+  FlashBwdTcParams p;
+  p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
+  p.lse = static_cast<const float*>(lse); p.delta = static_cast<const float*>(delta);
+  p.valid_len = static_cast<const int*>(valid_len);
+  p.dq_bs = s[12]; p.dq_ts = s[13]; p.dq_hs = s[14];
+  p.dk_bs = s[15]; p.dk_ts = s[16]; p.dk_hs = s[17];
+  p.dv_bs = s[18]; p.dv_ts = s[19]; p.dv_hs = s[20];
+  p.B = B; p.T = T; p.QH = QH; p.KVH = KVH; p.scale = scale; p.status = status_ptr();
+  static bool configured = false;
+  if (!configured) {
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FdqSmem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FdkvSmem::kTotal));
+    configured = true;
+  }
+  const int nt = (T + 127) / 128;
+  flash_bwd_dkv_tc_kernel<<<dim3(nt, KVH, B), FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
+  B200_CHECK(cudaGetLastError());
+  flash_bwd_dq_tc_kernel<<<dim3(nt, QH, B), FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -25,6 +25,31 @@ enum GemmFlags : int {
   GEMM_ADD_C = 2,     // D = alpha * A*B + C
 };
 
+// All-gather fused into the GEMM (one kernel does both): the first `n_copy` CTAs of the grid do no
+// math; they pull every rank's slice of a ZeRO unit out of peer memory into the local unit buffer
+// with bulk TMA copies (peer -> shared -> local global, a ring of 32 KiB buffers per CTA) and
+// publish progress in 1 MiB segment counters. The GEMM CTAs' producer warps wait (bounded) on the
+// segments that hold the rows of the B operand (a weight matrix inside that unit buffer) before
+// they issue the TMA loads for them, so the tensor cores start on the first rows of the weight
+// while later rows - and the rest of the unit - are still crossing NVLink. When the kernel ends
+// the whole unit is local. TMA loads never use cluster multicast.
+constexpr int AG_MAX_W = 8;
+constexpr int AG_CHUNK = 32 * 1024;            // bytes per bulk copy
+constexpr int AG_SEG_SHIFT = 20;               // 1 MiB progress segments
+constexpr int AG_NBUF = 6;
+
+struct AgFusion {
+  const void* src[AG_MAX_W];     // rank q's slice of the unit (peer pointers; src[rank] is local)
+  void* dst;                     // local unit buffer, W * slice_bytes
+  unsigned long long* seg;       // progress counters, one per MiB of dst, monotonically increasing
+  unsigned long long slice_bytes;
+  unsigned long long b_off;      // byte offset of the B matrix inside dst
+  unsigned long long b_row_bytes;
+  unsigned long long first_byte; // copy order starts at the chunk holding this byte (B's first row)
+  unsigned int epoch;            // counters of a complete segment read epoch * segment_bytes
+  int W, n_copy;
+};
+
 struct GemmParams {
   void* D;
   const void* C;
@@ -33,6 +58,7 @@ struct GemmParams {
   int flags;
   float alpha;
   int* status;
+  AgFusion ag;
 };
 
 template <int BN>
@@ -57,13 +83,160 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   nb = r / gsz;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ unsigned long long ag_seg_bytes(const AgFusion& ag, unsigned long long seg) {
+  const unsigned long long total = ag.slice_bytes * ag.W;
+  const unsigned long long lo = seg << AG_SEG_SHIFT;
+  const unsigned long long hi = min(total, lo + (1ull << AG_SEG_SHIFT));
+  return hi - lo;
+}
+
+// Credit a finished chunk [pos, pos + bytes) of the unit buffer to the segment counters.
+__device__ __forceinline__ void ag_publish(const AgFusion& ag, unsigned long long pos, unsigned long long bytes) {
+  fence_proxy_async_all();
+  __threadfence();
+  while (bytes > 0) {
+    const unsigned long long seg = pos >> AG_SEG_SHIFT;
+    const unsigned long long room = ((seg + 1) << AG_SEG_SHIFT) - pos;
+    const unsigned long long part = bytes < room ? bytes : room;
+    atomicAdd(ag.seg + seg, part);
+    pos += part;
+    bytes -= part;
+  }
+}
+
+// Copy role of one CTA (thread 0 drives it): chunks cta, cta + n_copy, ... in rotated order.
+__device__ void ag_copy_role(const AgFusion& ag, uint8_t* smem, uint64_t* bars, volatile int* abort_flag, int* status) {
+  const unsigned long long cps = (ag.slice_bytes + AG_CHUNK - 1) / AG_CHUNK;     // chunks per slice
+  const long long total = (long long)cps * ag.W;
+  const long long j0 = (long long)(ag.first_byte / ag.slice_bytes) * cps + (ag.first_byte % ag.slice_bytes) / AG_CHUNK;
+  const long long mine = (total - blockIdx.x + ag.n_copy - 1) / ag.n_copy;
+  auto chunk_of = [&](long long i, const void*& src, unsigned long long& pos, uint32_t& bytes) {
+    const long long j = (j0 + blockIdx.x + i * ag.n_copy) % total;
+    const int q = int(j / (long long)cps);
+    const unsigned long long c = (unsigned long long)(j % (long long)cps) * AG_CHUNK;
+    const unsigned long long left = ag.slice_bytes - c;
+    bytes = uint32_t(left < AG_CHUNK ? left : AG_CHUNK);
+    src = static_cast<const uint8_t*>(ag.src[q]) + c;
+    pos = (unsigned long long)q * ag.slice_bytes + c;
+  };
+  // Software pipeline driven by one thread: loads run AG_NBUF - 2 chunks ahead of the stores; a
+  // buffer is re-filled once the store that used it has finished READING shared memory; chunks are
+  // credited to the segment counters in batches of 8, after their stores have fully completed.
+  auto issue_load = [&](long long i) {
+    const void* src; unsigned long long pos; uint32_t bytes;
+    chunk_of(i, src, pos, bytes);
+    const int buf = int(i % AG_NBUF);
+    mbar_expect_tx(&bars[buf], bytes);
+    bulk_g2s(smem + buf * AG_CHUNK, src, bytes, &bars[buf]);
+  };
+  auto publish_upto = [&](long long from, long long to) {   // chunks [from, to)
+    if (to <= from) return;
+    fence_proxy_async_all();
+    __threadfence();
+    for (long long i = from; i < to; ++i) {
+      const void* src; unsigned long long pos; uint32_t bytes;
+      chunk_of(i, src, pos, bytes);
+      unsigned long long left = bytes;
+      while (left > 0) {
+        const unsigned long long seg = pos >> AG_SEG_SHIFT;
+        const unsigned long long room = ((seg + 1) << AG_SEG_SHIFT) - pos;
+        const unsigned long long part = left < room ? left : room;
+        atomicAdd(ag.seg + seg, part);
+        pos += part;
+        left -= part;
+      }
+    }
+  };
+  constexpr int kAhead = AG_NBUF - 2;
+  bool ok = true;
+  long long published = 0;
+  for (long long i = 0; i < mine && i < kAhead; ++i) issue_load(i);
+  for (long long i = 0; i < mine; ++i) {
+    const int buf = int(i % AG_NBUF);
+    if (!mbar_wait(&bars[buf], uint32_t((i / AG_NBUF) & 1), abort_flag)) { ok = false; break; }
+    const void* src; unsigned long long pos; uint32_t bytes;
+    chunk_of(i, src, pos, bytes);
+    bulk_s2g(static_cast<uint8_t*>(ag.dst) + pos, smem + buf * AG_CHUNK, bytes);
+    tma_store_commit();
+    tma_store_wait_read<1>();                 // stores up to chunk i - 1 no longer read their buffers
+    if (i + kAhead < mine) issue_load(i + kAhead);   // re-fills the buffer chunk i - 2 used
+    if ((i & 7) == 7) {
+      tma_store_wait<2>();                    // stores up to chunk i - 2 are complete
+      publish_upto(published, i - 1);
+      published = i - 1;
+    }
+  }
+  tma_store_wait<0>();
+  if (ok) {
+    publish_upto(published, mine);
+  } else if (status != nullptr && atomicCAS(status, 0, int(*abort_flag)) == 0) {
+    status[1] = 110;
+  }
+}
+
+// Producer-side wait for the segments that cover bytes [lo, hi) of the unit buffer. `have_lo`,
+// `have_hi` remember the contiguous range of segments already seen complete.
+__device__ __forceinline__ bool ag_wait_bytes(const AgFusion& ag, unsigned long long lo, unsigned long long hi,
+                                              long long& have_lo, long long& have_hi, volatile int* abort_flag) {
+  const long long s_lo = (long long)(lo >> AG_SEG_SHIFT), s_hi = (long long)((hi - 1) >> AG_SEG_SHIFT);
+  if (s_lo >= have_lo && s_hi <= have_hi) return true;
+  for (long long s = s_lo; s <= s_hi; ++s) {
+    if (s >= have_lo && s <= have_hi) continue;
+    const unsigned long long want = (unsigned long long)ag.epoch * ag_seg_bytes(ag, (unsigned long long)s);
+    const uint64_t deadline = globaltimer_ns() + B200_WAIT_NS;
+    uint32_t spins = 0;
+    while (ld_acquire_gpu_u64(ag.seg + s) < want) {
+      if ((++spins & 31) == 0) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() > deadline) { *abort_flag = ERR_PEER_TIMEOUT; return false; }
+      }
+    }
+  }
+  if (have_hi < have_lo || s_lo > have_hi + 1 || s_hi < have_lo - 1) { have_lo = s_lo; have_hi = s_hi; }
+  else { have_lo = min(have_lo, s_lo); have_hi = max(have_hi, s_hi); }
+  fence_proxy_async_all();
+  return true;
+}
+
+template <int BN, bool A_MN, bool B_MN, bool AG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int cta0 = AG ? p.ag.n_copy : 0;             // first GEMM CTA
+  const int gemm_ctas = int(gridDim.x) - cta0;
+  if (AG && int(blockIdx.x) < cta0) {
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AG_NBUF * AG_CHUNK);
+    volatile int* aflag = reinterpret_cast<volatile int*>(bars + AG_NBUF);
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < AG_NBUF; ++i) mbar_init(&bars[i], 1);
+      *aflag = 0;
+      mbar_fence_init();
+      fence_proxy_async_smem();
+      ag_copy_role(p.ag, smem, bars, aflag, p.status);
+    }
+    return;
+  }
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
   uint64_t* empty = full + S::kStages;
   uint64_t* tfull = empty + S::kStages;
@@ -105,11 +278,23 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      long long have_lo = 0, have_hi = -1;
+      for (int t = int(blockIdx.x) - cta0; t < num_tiles && ok; t += gemm_ctas) {
         int mb, nb;
         tile_coords(t, num_m, num_n, mb, nb);
         const int m0 = mb * GEMM_BM, n0 = nb * BN;
+        if (AG && !B_MN) {   // B rows are the n index: this tile needs rows n0 .. n0 + BN
+          const unsigned long long r1 = (unsigned long long)min(n0 + BN, p.N);
+          if (!ag_wait_bytes(p.ag, p.ag.b_off + (unsigned long long)n0 * p.ag.b_row_bytes,
+                             p.ag.b_off + r1 * p.ag.b_row_bytes, have_lo, have_hi, abort_flag)) { ok = false; break; }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
+          if (AG && B_MN) {  // B rows are the k index: this k-block needs rows k0 .. k0 + 64
+            const unsigned long long r0 = (unsigned long long)kb * GEMM_BK;
+            const unsigned long long r1 = (unsigned long long)min((kb + 1) * GEMM_BK, p.K);
+            if (!ag_wait_bytes(p.ag, p.ag.b_off + r0 * p.ag.b_row_bytes, p.ag.b_off + r1 * p.ag.b_row_bytes,
+                               have_lo, have_hi, abort_flag)) { ok = false; break; }
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::kStageBytes;
           uint8_t* sB = sA + S::kABytes;
@@ -140,7 +325,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = int(blockIdx.x) - cta0; t < num_tiles && ok; t += gemm_ctas) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -177,7 +362,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                                 : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 &&
                                    (!add_c || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = int(blockIdx.x) - cta0; t < num_tiles && ok; t += gemm_ctas) {
       int mb, nb;
       tile_coords(t, num_m, num_n, mb, nb);
       const int row = mb * GEMM_BM + q * 32 + lane;
@@ -257,7 +442,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
-    if (atomicCAS(p.status, 0, *abort_flag) == 0) p.status[1] = 100 + BN / 128;
+    if (atomicCAS(p.status, 0, int(*abort_flag)) == 0) p.status[1] = 100 + BN / 128;
   }
 }
 
@@ -295,11 +480,11 @@ __global__ void gemm_fallback_kernel(const bf16* __restrict__ A, const bf16* __r
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool AG = false>
 static int launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const GemmParams& p, cudaStream_t stream,
                      int max_ctas) {
   using S = GemmSmem<BN>;
-  auto kern = gemm_bf16_tc_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_tc_kernel<BN, A_MN, B_MN, AG>;
   static bool configured = false;   // per template instantiation; one device per process
   if (!configured) {
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
@@ -308,7 +493,13 @@ static int launch_tc(const CUtensorMap* tA, const CUtensorMap* tB, const GemmPar
   const int num_tiles = ((p.M + GEMM_BM - 1) / GEMM_BM) * ((p.N + BN - 1) / BN);
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (num_tiles < grid) grid = num_tiles;
+  if (AG) {
+    // copy CTAs + GEMM CTAs, all resident at once (one CTA per SM)
+    const int gemm_ctas = grid - p.ag.n_copy < num_tiles ? grid - p.ag.n_copy : num_tiles;
+    grid = gemm_ctas + p.ag.n_copy;
+  } else if (num_tiles < grid) {
+    grid = num_tiles;
+  }
   kern<<<grid, GEMM_THREADS, S::kTotal, stream>>>(*tA, *tB, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -330,6 +521,7 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, void* D, const void* C
   GemmParams p;
   p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
   p.status = status_ptr();
+  p.ag = AgFusion{};
 
   const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0 &&
                        (lda % 8) == 0 && (ldb % 8) == 0;
@@ -369,4 +561,46 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, void* D, const void* C
   if (bn == 128) { B200_DISPATCH(128) }
   B200_DISPATCH(256)
 #undef B200_DISPATCH
+}
+
+// GEMM with the all-gather of a ZeRO unit fused in (see AgFusion). B must be a weight matrix that
+// lives at byte offset b_off inside the local unit buffer `ag_dst` (row pitch b_row_bytes); the
+// unit's W slices are read from `ag_src[q]` (peer pointers). seg = zero-initialised counters, one
+// per MiB of the unit buffer; epoch = 1, 2, ... per use of that buffer. Returns when launched;
+// when the kernel completes the whole unit buffer is filled.
+B200_API int b200_gemm_bf16_allgather(const void* A, void* D, const void* C, int M, int N, int K, int lda, int ldd,
+                                      int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
+                                      const void* const* ag_src, void* ag_dst, void* seg,
+                                      unsigned long long slice_bytes, unsigned long long b_off, int W, int n_copy,
+                                      unsigned int epoch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > AG_MAX_W || n_copy < 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (slice_bytes % 16 != 0 || b_off % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
+  GemmParams p;
+  p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
+  p.status = status_ptr();
+  p.ag = AgFusion{};
+  for (int q = 0; q < W; ++q) p.ag.src[q] = ag_src[q];
+  p.ag.dst = ag_dst;
+  p.ag.seg = static_cast<unsigned long long*>(seg);
+  p.ag.slice_bytes = slice_bytes;
+  p.ag.b_off = b_off;
+  const int ldb = b_mn_major ? N : K;
+  p.ag.b_row_bytes = (unsigned long long)ldb * 2;
+  p.ag.first_byte = b_off;
+  p.ag.epoch = epoch;
+  p.ag.W = W;
+  p.ag.n_copy = n_copy;
+  const void* B = static_cast<const uint8_t*>(ag_dst) + b_off;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const int bn = 256;
+  const CUtensorMap* tA = a_mn_major ? get_tensor_map_2d(A, K, M, lda, 64, 64, 2, SWIZZLE_128B_)
+                                     : get_tensor_map_2d(A, M, K, lda, GEMM_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = b_mn_major ? get_tensor_map_2d(B, K, N, ldb, 64, 64, 2, SWIZZLE_128B_)
+                                     : get_tensor_map_2d(B, N, K, ldb, bn, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);
+  if (a_mn_major && b_mn_major) return launch_tc<256, true, true, true>(tA, tB, p, stream, 0);
+  if (a_mn_major) return launch_tc<256, true, false, true>(tA, tB, p, stream, 0);
+  if (b_mn_major) return launch_tc<256, false, true, true>(tA, tB, p, stream, 0);
+  return launch_tc<256, false, false, true>(tA, tB, p, stream, 0);
 }

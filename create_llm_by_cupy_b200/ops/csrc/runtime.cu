@@ -1,4 +1,6 @@
 // Process-wide state of the native library: status word, SM count, TMA tensor-map cache.
+#include <string.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -100,6 +102,43 @@ const CUtensorMap* get_tensor_map_2d(const void* base, uint64_t rows, uint64_t c
     for (auto& kv : cache) delete kv.second;
     cache.clear();
   }
+  cache.emplace(key, m);
+  return m;
+}
+
+// 4-D map over a [B, T, heads, D] tensor addressed with element strides (batch, token, head; D
+// contiguous). Dimension order for the copy coordinates is (d, head, t, b); the box is
+// box_d x 1 x box_t x 1 with 128-byte swizzle. Not cached by address alone: keyed on everything.
+const CUtensorMap* get_tensor_map_bthd(const void* base, uint64_t B, uint64_t T, uint64_t heads, uint64_t D,
+                                       uint64_t bs, uint64_t ts, uint64_t hs, uint32_t box_t, uint32_t box_d) {
+  static std::mutex mu;
+  struct K4 { uint64_t v[10]; bool operator==(const K4& o) const { return memcmp(v, o.v, sizeof(v)) == 0; } };
+  struct H4 { size_t operator()(const K4& k) const { uint64_t h = 1469598103934665603ull; for (uint64_t x : k.v) { h ^= x; h *= 1099511628211ull; } return size_t(h); } };
+  static std::unordered_map<K4, CUtensorMap*, H4> cache;
+  K4 key{{reinterpret_cast<uint64_t>(base), B, T, heads, D, bs, ts, hs, box_t, box_d}};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if ((key.v[0] & 15) != 0 || ((bs * 2) & 15) || ((ts * 2) & 15) || ((hs * 2) & 15)) {
+    fprintf(stderr, "[b200] 4-D tensor map: base or a stride is not 16-byte aligned\n");
+    return nullptr;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return nullptr;
+  cuuint64_t dims[4] = {D, heads, T, B};
+  cuuint64_t strides[3] = {hs * 2, ts * 2, bs * 2};
+  cuuint32_t box[4] = {box_d, 1, box_t, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap* m = new CUtensorMap;
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[b200] cuTensorMapEncodeTiled (4-D) failed (%d)\n", (int)r);
+    delete m;
+    return nullptr;
+  }
+  if (cache.size() > 65536) { for (auto& kv : cache) delete kv.second; cache.clear(); }
   cache.emplace(key, m);
   return m;
 }

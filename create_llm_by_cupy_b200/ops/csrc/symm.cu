@@ -107,7 +107,7 @@ __device__ __forceinline__ void adam_apply(float g, float& m, float& v, float& w
   w -= a.lr * (m * a.m_corr) / (sqrtf(v * a.v_corr) + a.eps);
 }
 
-__global__ void __launch_bounds__(512) rs_reduce_kernel(const RsParams p) {
+__global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
   const int vr = blockIdx.y;
   const int rank = p.rank0 + vr;
   const SymmTable& tab = p.tab[vr];
@@ -321,7 +321,7 @@ B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0
   p.do_stats = do_stats; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
   if (blocks < 1) blocks = 1;
   if (blocks > SYMM_MAX_BLOCKS) blocks = SYMM_MAX_BLOCKS;
-  rs_reduce_kernel<<<dim3(blocks, vranks), 512, 0, st>>>(p);
+  rs_reduce_kernel<<<dim3(blocks, vranks), 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -17,6 +17,12 @@ from .gemm import gemm  # noqa: F401  (re-exported)
 
 _f = ctypes.c_float
 
+# head_dim-128 attention forward with un-fused RoPE runs on the tcgen05 kernel; B200_FLASH_TC=0
+# keeps everything on the mma.sync kernels (A/B comparison).
+import os as _os
+FLASH_TC = _os.environ.get("B200_FLASH_TC", "1") != "0"
+FLASH_TC_BWD = _os.environ.get("B200_FLASH_TC_BWD", "1") != "0"
+
 
 def _lib():
     native.status_tensor()
@@ -275,6 +281,14 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     o = torch.empty((B, T, QH, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     strides = _strides3(q) + _strides3(k) + _strides3(v) + _strides3(o)
+    if D == 128 and cos is None and FLASH_TC:
+        # tcgen05 / TMEM kernel (inputs already rotated)
+        arr = (ctypes.c_longlong * 12)(*strides)
+        native.check(_lib().b200_flash_fwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
+                                              native.ptr(lse), native.ptr(valid_len), arr, B, T, QH, KVH, D,
+                                              _f(scale), native.stream_ptr()), "flash_fwd_tc")
+        native.bump()
+        return o, lse
     arr = (ctypes.c_longlong * 24)(*(strides + [0] * 12))
     native.check(_lib().b200_flash_fwd(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o), native.ptr(lse),
                                        native.ptr(valid_len), native.ptr(cos), native.ptr(sin), arr,
@@ -330,6 +344,20 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
     else:
         dq, dk_, dv_ = out
     delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
+    if D == 128 and cos is None and FLASH_TC and FLASH_TC_BWD:
+        # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
+        arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
+        native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
+                                             native.stream_ptr()), "flash_delta")
+        s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
+               _strides3(dv_))
+        arr21 = (ctypes.c_longlong * 21)(*s21)
+        native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
+                                              native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
+                                              native.ptr(dv_), native.ptr(valid_len), arr21, B, T, QH, KVH, D,
+                                              _f(scale), native.stream_ptr()), "flash_bwd_tc")
+        native.bump(3)
+        return dq, dk_, dv_
     strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +
                _strides3(dq) + _strides3(dk_) + _strides3(dv_))
     arr = (ctypes.c_longlong * 24)(*strides)

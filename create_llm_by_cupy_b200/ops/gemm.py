@@ -75,3 +75,43 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     native.check(rc, "b200_gemm_bf16")
     native.bump()
     return out
+
+
+def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_shape: tuple, *, trans_b: bool,
+                   peer_slices, seg: torch.Tensor, epoch: int, n_copy: int = 8, add: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None, trans_a: bool = False) -> torch.Tensor:
+    """``out = op(a) @ op(B) (+ add)`` where B is the weight ``b_shape`` stored at element offset
+    ``b_offset`` of the local ZeRO unit buffer ``unit_buf`` — and the unit buffer is being filled
+    by this same kernel: ``n_copy`` CTAs pull every rank's slice (``peer_slices`` = W device
+    pointers, one per rank, same length) over NVLink while the remaining CTAs run the GEMM, each
+    waiting only for the rows of B it is about to load. When the kernel finishes the whole unit
+    buffer is valid. ``seg`` = this buffer's progress counters (int64 zeros, one per MiB),
+    ``epoch`` = 1, 2, ... per use of the buffer."""
+    W = len(peer_slices)
+    M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    if trans_b:
+        N, Kb = b_shape
+    else:
+        Kb, N = b_shape
+    if K != Kb:
+        raise ValueError(f"gemm_allgather: inner dims differ ({K} vs {Kb})")
+    assert a.is_cuda and a.dtype == torch.bfloat16 and unit_buf.dtype == torch.bfloat16
+    assert unit_buf.numel() % W == 0
+    a, lda = _rowmajor_2d(a)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    flags, ldc = 0, 0
+    if add is not None:
+        assert add.shape == (M, N) and add.stride(1) == 1 and add.dtype == out.dtype
+        ldc = add.stride(0)
+        flags |= GEMM_ADD_C
+    native.status_tensor()
+    src = (ctypes.c_void_p * W)(*[ctypes.c_void_p(int(p)) for p in peer_slices])
+    rc = native.lib().b200_gemm_bf16_allgather(
+        native.ptr(a), native.ptr(out), native.ptr(add), M, N, K, lda, out.stride(0), ldc, int(trans_a),
+        int(not trans_b), flags, ctypes.c_float(1.0), src, native.ptr(unit_buf), native.ptr(seg),
+        ctypes.c_ulonglong(unit_buf.numel() // W * 2), ctypes.c_ulonglong(b_offset * 2), W, n_copy,
+        ctypes.c_uint(epoch), native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_allgather")
+    native.bump()
+    return out

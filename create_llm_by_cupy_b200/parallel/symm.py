@@ -110,7 +110,8 @@ class FusedCollectives:
     gather = True
 
     def __init__(self, comm, device, heap_bytes: int = 8 << 30, rs_blocks: int = 48, ag_blocks: int = 32,
-                 wait_ns: int = _DEFAULT_WAIT_NS, fused_gather: bool = True):
+                 wait_ns: int = _DEFAULT_WAIT_NS, fused_gather: bool = True, gemm_fusion: bool = True,
+                 n_copy: int = 8):
         self.heap = SymmetricHeap(comm, device, heap_bytes)
         self.comm = comm
         self.device = self.heap.device
@@ -121,6 +122,8 @@ class FusedCollectives:
         self.ag_blocks = ag_blocks
         self.wait_ns = int(wait_ns)
         self.gather = fused_gather
+        self.gemm_fusion = gemm_fusion      # pull block units inside their first consuming GEMM
+        self.n_copy = n_copy                # CTAs of that GEMM that copy instead of multiply
         self.rs_epoch = 0
         self.barrier_epoch = 0
         self.launches = 0

@@ -28,13 +28,55 @@ from .layout import FlatLayout, select_replicated_params
 
 
 class _Buf:
-    __slots__ = ("t", "free_event", "ready_event", "uid")
+    __slots__ = ("t", "free_event", "ready_event", "uid", "seg", "epoch")
 
     def __init__(self, t):
         self.t = t
         self.free_event = None
         self.ready_event = None
         self.uid = -1
+        self.seg = None
+        self.epoch = 0
+
+
+class _PendingGather:
+    """A unit whose all-gather has not run yet because it is going to be fused into the first GEMM
+    that reads one of its weights. ``gemm`` launches that fused kernel; ``flush`` falls back to the
+    stand-alone pull when something else touches the unit first."""
+
+    def __init__(self, mgr, uid: int, buf):
+        self.mgr, self.uid, self.buf = mgr, uid, buf
+        self.done = False
+
+    def _peer_slices(self):
+        m = self.mgr
+        lo, _ = m.layout.unit_shard_range(self.uid)
+        off = m.fused.heap.offset_of(m.param_shard_f16) + lo * m.param_shard_f16.element_size()
+        return [b + off for b in m.fused.heap.peer_bases]
+
+    def gemm(self, a, param_index: int, *, trans_b: bool, add=None, out=None):
+        from ..ops.gemm import gemm_allgather
+        m = self.mgr
+        s = m.layout.slots[param_index]
+        assert s.unit == self.uid and not self.done
+        b = self.buf
+        if getattr(b, "seg", None) is None:
+            b.seg = torch.zeros((b.t.numel() * 2 + (1 << 20) - 1) >> 20, dtype=torch.int64, device=m.device)
+            b.epoch = 0
+        b.epoch += 1
+        self.done = True
+        m.bytes_gathered += (b.t.numel() - b.t.numel() // m.world_size) * 2
+        return gemm_allgather(a, b.t, s.offset, tuple(s.shape), trans_b=trans_b, peer_slices=self._peer_slices(),
+                              seg=b.seg, epoch=b.epoch, n_copy=m.fused.n_copy, add=add, out=out)
+
+    def flush(self):
+        if self.done:
+            return
+        m = self.mgr
+        lo, hi = m.layout.unit_shard_range(self.uid)
+        m.fused.all_gather(self.buf.t, m.param_shard_f16[lo:hi], m.compute_stream)
+        m.bytes_gathered += (self.buf.t.numel() - self.buf.t.numel() // m.world_size) * 2
+        self.done = True
 
 
 class _Pool:
@@ -116,6 +158,8 @@ class MemoryZeRO3Manager:
         self.grad_pool = _Pool(self.dtype, self.device, alloc)
         self.live = {}              # uid -> _Buf holding gathered parameters
         self.pending_gather = {}    # uid -> _Buf with an all-gather in flight
+        self.deferred = {}          # uid -> _PendingGather (gather fused into the consuming GEMM)
+        self.phase = "fwd"          # set by the model: which pass is asking for parameters
         self.cur_grad = {}          # uid -> _Buf being written by backward
         self.pending_reduce_handles = collections.deque()
         self.exposed_pairs = []     # (event before wait, event after wait) on the compute stream
@@ -241,6 +285,14 @@ class MemoryZeRO3Manager:
             return
         b = self.gather_pool.get(unit.padded)
         b.uid = uid
+        if self._fuse_gather_into_gemm(uid):
+            # nothing to launch now: the unit is pulled by the first GEMM that consumes it
+            self._wait(self.compute_stream, b.free_event)
+            self._wait(self.compute_stream, self._params_ready_event)
+            b.ready_event = None
+            self.pending_gather[uid] = b
+            self.deferred[uid] = _PendingGather(self, uid, b)
+            return
         with self._comm_ctx():
             self._wait(self.comm_stream, b.free_event)
             self._wait(self.comm_stream, self._params_ready_event)
@@ -272,6 +324,14 @@ class MemoryZeRO3Manager:
                 self._wait(self.compute_stream, b.ready_event)
         self.live[uid] = b
         self._attach(uid, b.t)
+        pg = self.deferred.get(uid)
+        if pg is not None:
+            consumer = self._first_consumer(uid)
+            if consumer is None:
+                pg.flush()
+                del self.deferred[uid]
+            else:
+                consumer.pending_gather = pg
         return b
 
     def _attach(self, uid: int, buf: torch.Tensor):
@@ -302,10 +362,35 @@ class MemoryZeRO3Manager:
                 mod.params[j] = None
             self.model.params[idx] = None
 
+    def _fuse_gather_into_gemm(self, uid: int) -> bool:
+        return (self.fused is not None and self.fused.gather and getattr(self.fused, "gemm_fusion", False)
+                and self.world_size > 1 and self.unit_names[uid].startswith("block"))
+
+    def _first_consumer(self, uid: int):
+        """The layer whose first GEMM reads this unit: the attention projection in forward, the MLP
+        (its down-projection dgrad) in backward."""
+        mods = [m for (m, _, _) in self.unit_modules[self.unit_names[uid]]]
+        want = "SwiGLU" if self.phase == "bwd" else "GroupedQueryAttention"
+        for m in mods:
+            if type(m).__name__ == want:
+                return m
+        return None
+
+    def ensure_gathered(self, module):
+        """Called by a layer that is about to read its parameters outside the fused GEMM."""
+        pg = getattr(module, "pending_gather", None)
+        if pg is not None:
+            pg.flush()
+            module.pending_gather = None
+            self.deferred.pop(pg.uid, None)
+
     def _release_unit(self, uid: int):
         b = self.live.pop(uid, None)
         if b is None:
             return
+        pg = self.deferred.pop(uid, None)
+        if pg is not None and not pg.done:
+            raise RuntimeError(f"unit {self.unit_names[uid]} was released before its fused gather ran")
         self._detach(uid)
         if self.world_size > 1:
             b.free_event = self._record(self.compute_stream)

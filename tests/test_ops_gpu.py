@@ -199,3 +199,28 @@ def test_adamw_and_stats(gdt):
     acc = torch.zeros(n, device=DEV)
     F.accumulate(acc, g.to(DEV), 0.25)
     close(acc, g.float() * 0.25, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
+def test_flash_attention_tcgen05_multi_tile(T, vl):
+    """head_dim 128 without in-kernel RoPE runs the tcgen05/TMEM kernels (forward, dQ, dK/dV)."""
+    B, QH, KVH, D = 2, 8, 2, 128
+    g = torch.Generator().manual_seed(T)
+    q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    do = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    vlt = None if vl is None else torch.tensor(vl, dtype=torch.int32, device=DEV)
+    assert F.FLASH_TC and F.FLASH_TC_BWD
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    dq, dk, dv = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    qc, kc, vc = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    vlc = None if vlt is None else vlt.cpu()
+    o_r, lse_r = F.flash_attn_fwd(qc, kc, vc, valid_len=vlc)
+    r = F.flash_attn_bwd(do.float().cpu(), qc, kc, vc, o_r, lse_r, valid_len=vlc)
+    close(o, o_r)
+    close(lse, lse_r, rtol=1e-2, atol=2e-2)
+    for a, b in zip((dq, dk, dv), r):
+        close(a, b, rtol=3e-2, atol=3e-2)
