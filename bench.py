@@ -60,6 +60,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="1.3b", choices=sorted(CONFIGS))
     ap.add_argument("--fused", type=int, default=-1, help="1: fused peer-memory collectives, 0: NCCL baseline, -1: auto")
+    ap.add_argument("--ag", default="pull", choices=["nccl", "pull", "gemm"],
+                    help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -100,7 +102,7 @@ def main():
     if use_fused:
         try:
             from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
-            fused = FusedCollectives(comm, device)
+            fused = FusedCollectives(comm, device, gather_mode=args.ag)
         except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
             if args.fused == 1:
                 raise
@@ -184,7 +186,8 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": c["name"], "global_batch": B * accum * world, "seq_len": T,
                        "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par,
-                       "collectives": "fused-peer-memory" if fused is not None else ("nccl" if world > 1 else "none"),
+                       "collectives": (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
+                                       else ("nccl" if world > 1 else "none")),
                        "l2": "not flushed: each step streams >10 GB of weights/activations, far above the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "exposed_comm_ms_per_step": exposed,

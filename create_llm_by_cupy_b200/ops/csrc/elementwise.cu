@@ -119,12 +119,13 @@ __global__ void rmsnorm_fwd_scalar_kernel(const bf16* __restrict__ x, const bf16
 // column sums in registers; warps of a CTA are combined in shared memory and each CTA writes one
 // row of `partial` [gridDim.x, H] (coalesced), reduced by rmsnorm_dgamma_reduce_kernel.
 template <int NV>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256, 2)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ gamma,
                    const float* __restrict__ rstd, const bf16* __restrict__ add, bf16* __restrict__ dx,
                    float* __restrict__ partial, int M, int H) {
-  extern __shared__ float sred[];   // [4][H]
+  extern __shared__ float sred[];   // [warps per block][H]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
   const int nchunk = H >> 3;
   const Pack8* gr = reinterpret_cast<const Pack8*>(gamma);
   float dg[NV][8];
@@ -133,13 +134,13 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
 #pragma unroll
     for (int e = 0; e < 8; ++e) dg[i][e] = 0.f;
 
-  for (int row = blockIdx.x * 4 + warp; row < M; row += gridDim.x * 4) {
+  for (int row = blockIdx.x * wpb + warp; row < M; row += gridDim.x * wpb) {
     const Pack8* dyr = reinterpret_cast<const Pack8*>(dy + size_t(row) * H);
     const Pack8* xr = reinterpret_cast<const Pack8*>(x + size_t(row) * H);
     const Pack8* ar = add ? reinterpret_cast<const Pack8*>(add + size_t(row) * H) : nullptr;
     Pack8* dxr = reinterpret_cast<Pack8*>(dx + size_t(row) * H);
     const float r = rstd[row];
-    constexpr bool kCache = NV <= 8;   // wider rows are re-read in the second pass (L1/L2 hits)
+    constexpr bool kCache = NV <= 4;   // wider rows are re-read in the second pass (L1/L2 hits)
     float wdy[kCache ? NV : 1][8], xh[kCache ? NV : 1][8];
     float dot = 0.f;
 #pragma unroll
@@ -186,7 +187,7 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
       }
     }
   }
-  // combine the 4 warps of this CTA
+  // combine the warps of this CTA
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int c = lane + i * 32;
@@ -196,8 +197,11 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     }
   }
   __syncthreads();
-  for (int h = threadIdx.x; h < H; h += blockDim.x)
-    partial[size_t(blockIdx.x) * H + h] = sred[h] + sred[H + h] + sred[2 * H + h] + sred[3 * H + h];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < wpb; ++w) t += sred[w * H + h];
+    partial[size_t(blockIdx.x) * H + h] = t;
+  }
 }
 
 // Generic-H variant: two passes over the row, atomics for dgamma partial rows.
@@ -425,7 +429,7 @@ B200_API int b200_rmsnorm_fwd(const void* x, const void* gamma, void* y, void* r
 
 // Number of partial rows rmsnorm_bwd writes; the caller provides `partial` of [that, H] fp32.
 B200_API int b200_rmsnorm_bwd_partial_rows(int M) {
-  int g = (M + 3) / 4;
+  int g = (M + 7) / 8;
   const int cap = num_sms() * 2;
   return g < cap ? (g < 1 ? 1 : g) : cap;
 }
@@ -442,23 +446,28 @@ B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, 
   const bf16* ap = static_cast<const bf16*>(add);
   bf16* dxp = static_cast<bf16*>(dx);
   float* pp = static_cast<float*>(partial);
-  const size_t smem = size_t(4) * H * sizeof(float);
+  const size_t smem = size_t(8) * H * sizeof(float);   // 8 warps per CTA in the vector kernels
   if (H % 8 != 0 || H > 4096) {
     B200_CHECK(cudaMemsetAsync(pp, 0, size_t(rows) * H * sizeof(float), st));
     rmsnorm_bwd_scalar_kernel<<<rows, 128, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else if (H <= 256) {
-    rmsnorm_bwd_kernel<1><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    rmsnorm_bwd_kernel<1><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else if (H <= 1024) {
-    rmsnorm_bwd_kernel<4><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    rmsnorm_bwd_kernel<4><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else if (H <= 2048) {
-    rmsnorm_bwd_kernel<8><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    static bool configured8 = false;
+    if (!configured8) {
+      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      configured8 = true;
+    }
+    rmsnorm_bwd_kernel<8><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else {
     static bool configured = false;
     if (!configured) {
-      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
       configured = true;
     }
-    rmsnorm_bwd_kernel<16><<<rows, 128, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    rmsnorm_bwd_kernel<16><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   }
   B200_CHECK(cudaGetLastError());
   rmsnorm_dgamma_reduce_kernel<<<(H + 127) / 128, 128, 0, st>>>(pp, static_cast<bf16*>(dgamma), rows, H,

@@ -226,14 +226,22 @@ __global__ void __launch_bounds__(512) ag_pull_kernel(const AgParams p) {
   const int vr = blockIdx.y;
   const int rank = p.rank0 + vr;
   const long long nvec = p.n_slice / 8;
-  const long long total = nvec * p.W;
   uint4* out = static_cast<uint4*>(p.out[vr]);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int q = int(i / nvec);
-    const int peer = (rank + q) % p.W;
-    const long long j = i - (long long)q * nvec;
+  constexpr int U = 4;     // independent 16-byte loads in flight per thread (NVLink latency is ~2 us)
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (int q = 0; q < p.W; ++q) {
+    const int peer = (rank + q) % p.W;     // own slice first, then peers in ring order
     const uint4* s = reinterpret_cast<const uint4*>(static_cast<const char*>(p.tab[vr].base[peer]) + p.shard_off);
-    out[(long long)peer * nvec + j] = s[j];
+    uint4* d = out + (long long)peer * nvec;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < nvec) v[u] = s[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i + u * stride < nvec) d[i + u * stride] = v[u];
+    }
   }
 }
 

@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
 def status_tensor(device=None) -> torch.Tensor:
     """Per-device 4-int status block that kernels write when a bounded wait runs out."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     key = dev.index
     if key not in _status:
         t = torch.zeros(4, dtype=torch.int32, device=dev)

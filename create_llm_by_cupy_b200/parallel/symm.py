@@ -110,8 +110,13 @@ class FusedCollectives:
     gather = True
 
     def __init__(self, comm, device, heap_bytes: int = 8 << 30, rs_blocks: int = 48, ag_blocks: int = 32,
-                 wait_ns: int = _DEFAULT_WAIT_NS, fused_gather: bool = True, gemm_fusion: bool = True,
-                 n_copy: int = 8):
+                 wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "pull", n_copy: int = 8):
+        """``gather_mode`` selects how parameter units are gathered: ``"nccl"`` (ncclAllGather on the
+        communication stream), ``"pull"`` (the P2P pull kernel on the communication stream) or
+        ``"gemm"`` (transformer-block units are pulled inside the first GEMM that consumes them;
+        the other units use the pull kernel). Gradient reduction always uses the fused kernel."""
+        if gather_mode not in ("nccl", "pull", "gemm"):
+            raise ValueError(f"unknown gather_mode {gather_mode!r}")
         self.heap = SymmetricHeap(comm, device, heap_bytes)
         self.comm = comm
         self.device = self.heap.device
@@ -121,8 +126,9 @@ class FusedCollectives:
         self.rs_blocks = rs_blocks
         self.ag_blocks = ag_blocks
         self.wait_ns = int(wait_ns)
-        self.gather = fused_gather
-        self.gemm_fusion = gemm_fusion      # pull block units inside their first consuming GEMM
+        self.gather_mode = gather_mode
+        self.gather = gather_mode != "nccl"
+        self.gemm_fusion = gather_mode == "gemm"   # pull block units inside their first consuming GEMM
         self.n_copy = n_copy                # CTAs of that GEMM that copy instead of multiply
         self.rs_epoch = 0
         self.barrier_epoch = 0
