@@ -1,0 +1,355 @@
+// bf16 GEMM on tcgen05 with CTA pairs (cta_group::2): D[M,N] = alpha * op(A) * op(B) (+ C).
+//
+// Two CTAs of a cluster (two SMs) cooperate on one 256 x 256 output tile. Each CTA stages its own
+// 128 rows of A and HALF of the B tile (128 of the 256 columns) in shared memory; one thread of
+// the leader CTA issues tcgen05.mma.cta_group::2, which reads A and B from both CTAs' shared
+// memory and accumulates each CTA's 128 x 256 half of D in that CTA's TMEM. Compared with the
+// single-CTA kernel every SM pulls 32 KiB instead of 48 KiB per 64-deep k-block from L2 and the
+// ring is 6 stages deep instead of 4, which is what it takes to keep the tensor pipe fed.
+//
+// Synchronisation (all mbarriers live at the same offsets in both CTAs):
+//   full[s]       leader only. The leader's producer arms it with the bytes of BOTH CTAs; the
+//                 follower's TMA loads complete on it too (cp.async.bulk.tensor ... cta_group::2
+//                 with the leader's barrier address). No cluster multicast is used by any load.
+//   empty[s]      one per CTA; the leader's tcgen05.commit arrives on both (multicast commit).
+//   tmem_full[a]  one per CTA; multicast commit after the last k-block of a tile.
+//   tmem_empty[a] leader only, 8 arrivals: the 4 epilogue warps of each CTA (the follower's
+//                 arrive remotely through the cluster shared-memory window).
+// Waits are bounded exactly as in the single-CTA kernel.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int G2_BM = 128;          // rows per CTA (256 per pair)
+constexpr int G2_BN = 256;          // columns per pair; each CTA stages 128 of them
+constexpr int G2_BK = 64;
+constexpr int G2_THREADS = 192;
+constexpr int G2_STAGES = 6;
+constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;          // 16 KiB
+constexpr int G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;    // 16 KiB
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_BAR_OFF = G2_STAGES * G2_STAGE_BYTES;
+constexpr int G2_SMEM = G2_BAR_OFF + (2 * G2_STAGES + 4) * 8 + 16 + 1024;
+
+enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2 };
+
+struct Gemm2Params {
+  void* D;
+  const void* C;
+  int M, N, K;
+  int ldd, ldc;
+  int flags;
+  float alpha;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load whose completion is counted on a barrier that may live in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_out, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this offset in BOTH CTAs once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb) {
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * num_n;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsz = min(num_m - first_m, GROUP_M);
+  const int r = t - g * per_group;
+  mb = first_m + (r % gsz);
+  nb = r / gsz;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw2[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw2) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFF);
+  uint64_t* empty = full + G2_STAGES;
+  uint64_t* tfull = empty + G2_STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();            // 0 = leader of the pair
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
+  const int num_n = (p.N + G2_BN - 1) / G2_BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                  // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int mb, nb;
+        tile_coords2(t, num_m, num_n, mb, nb);
+        const int m0 = mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int n0 = nb * G2_BN + int(rank) * (G2_BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sA = smem + stage * G2_STAGE_BYTES;
+          uint8_t* sB = sA + G2_A_BYTES;
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * G2_STAGE_BYTES);   // bytes of both CTAs
+          const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);           // the leader's barrier
+          const int k0 = kb * G2_BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < G2_BM / 64; ++c) tma_load_2d_pair(sA + c * 8192, &tmA, bar, m0 + c * 64, k0);
+          } else {
+            tma_load_2d_pair(sA, &tmA, bar, k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < (G2_BN / 2) / 64; ++c) tma_load_2d_pair(sB + c * 8192, &tmB, bar, n0 + c * 64, k0);
+          } else {
+            tma_load_2d_pair(sB, &tmB, bar, k0, n0);
+          }
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * G2_BM, G2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * G2_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * G2_STAGE_BYTES);
+          const uint32_t sB = sA + G2_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < G2_BK / 16; ++kk) {
+            const uint64_t adesc = A_MN ? umma_smem_desc(sA + kk * 2048, 8192, 1024)
+                                        : umma_smem_desc(sA + kk * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc(sB + kk * 2048, 8192, 1024)
+                                        : umma_smem_desc(sB + kk * 32, 16, 1024);
+            umma_bf16_ss_pair(tmem_d, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage]);
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = (p.flags & G2_OUT_F32) != 0;
+    const bool add_c = (p.flags & G2_ADD_C) != 0;
+    const bool vec_ok = out_f32 ? ((p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 &&
+                                   (!add_c || ((p.ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)))
+                                : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 &&
+                                   (!add_c || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int mb, nb;
+      tile_coords2(t, num_m, num_n, mb, nb);
+      const int row = mb * 2 * G2_BM + int(rank) * G2_BM + q * 32 + lane;
+      const int n0 = nb * G2_BN;
+      if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
+#pragma unroll 1
+      for (int c = 0; c < G2_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          const bool full_chunk = vec_ok && (col0 + 32 <= p.N);
+          if (out_f32) {
+            float* drow = static_cast<float*>(p.D) + size_t(row) * p.ldd + col0;
+            const float* crow = add_c ? static_cast<const float*>(p.C) + size_t(row) * p.ldc + col0 : nullptr;
+            if (full_chunk) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (add_c) {
+                  const float4 cc = *reinterpret_cast<const float4*>(crow + j);
+                  o.x += cc.x; o.y += cc.y; o.z += cc.z; o.w += cc.w;
+                }
+                *reinterpret_cast<float4*>(drow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) drow[j] = v[j] + (add_c ? crow[j] : 0.f);
+            }
+          } else {
+            bf16* drow = static_cast<bf16*>(p.D) + size_t(row) * p.ldd + col0;
+            const bf16* crow = add_c ? static_cast<const bf16*>(p.C) + size_t(row) * p.ldc + col0 : nullptr;
+            if (full_chunk) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (add_c) {
+                  const uint4 cc = *reinterpret_cast<const uint4*>(crow + j);
+                  const bf162* c2 = reinterpret_cast<const bf162*>(&cc);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(c2[e]);
+                    v[j + 2 * e] += f.x;
+                    v[j + 2 * e + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                *reinterpret_cast<uint4*>(drow + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+                const float cv = add_c ? __bfloat162float(crow[j]) : 0.f;
+                drow[j] = __float2bfloat16(v[j] + cv);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));   // the leader's barrier
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // the leader's MMAs read the follower's shared memory until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, int(*abort_flag)) == 0) p.status[1] = 120;
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2Params& p, cudaStream_t stream) {
+  auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
+    configured = true;
+  }
+  const int num_tiles = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
+  int pairs = num_sms() / 2;
+  if (num_tiles < pairs) pairs = num_tiles;
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Same contract as b200_gemm_bf16 (TMA-legal operands only: 16-byte aligned bases and pitches).
+B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int lda,
+                                 int ldb, int ldd, int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p;
+  p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
+  p.status = status_ptr();
+  const CUtensorMap* tA = a_mn_major ? get_tensor_map_2d(A, K, M, lda, 64, 64, 2, SWIZZLE_128B_)
+                                     : get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = b_mn_major ? get_tensor_map_2d(B, K, N, ldb, 64, 64, 2, SWIZZLE_128B_)
+                                     : get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);
+  if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, p, stream);
+  if (a_mn_major) return launch_tc2<true, false>(tA, tB, p, stream);
+  if (b_mn_major) return launch_tc2<false, true>(tA, tB, p, stream);
+  return launch_tc2<false, false>(tA, tB, p, stream);
+}

@@ -66,6 +66,7 @@ __device__ bool peer_block_barrier(const SymmTable& tab, int rank, int W, int ch
     const uint64_t deadline = globaltimer_ns() + wait_ns;
     uint32_t spins = 0;
     while (int32_t(ld_acquire_sys(mine) - epoch) < 0) {
+      __nanosleep(spins < 64 ? 100 : 1000);     // back off: the SM is shared with compute kernels
       if ((++spins & 63) == 0 && globaltimer_ns() > deadline) {
         s_fail = 1;
         if (status != nullptr && atomicCAS(status, 0, ERR_PEER_TIMEOUT) == 0) {

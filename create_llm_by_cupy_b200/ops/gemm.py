@@ -14,6 +14,11 @@ from . import native
 GEMM_OUT_F32 = 1
 GEMM_ADD_C = 2
 
+import os as _os
+# "1cta": single-CTA 128x256 tiles; "2cta": CTA pairs (cta_group::2) on 256x256 tiles where the
+# problem is large enough, single-CTA otherwise.
+GEMM_IMPL = _os.environ.get("B200_GEMM_IMPL", "2cta")
+
 def _rowmajor_2d(t: torch.Tensor) -> tuple[torch.Tensor, int]:
     """Return (tensor, pitch) for a 2-D view whose last dim is contiguous; copy if it is not."""
     assert t.dim() == 2
@@ -25,7 +30,7 @@ def _rowmajor_2d(t: torch.Tensor) -> tuple[torch.Tensor, int]:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
          out: torch.Tensor | None = None, add: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, alpha: float = 1.0, bn: int = 0,
-         max_ctas: int = 0, force_fallback: bool = False) -> torch.Tensor:
+         max_ctas: int = 0, force_fallback: bool = False, impl: str | None = None) -> torch.Tensor:
     """``out = alpha * op(a) @ op(b) (+ add)``.
 
     ``a`` is ``[M, K]`` (``[K, M]`` with ``trans_a``); ``b`` is ``[K, N]`` (``[N, K]`` with
@@ -68,6 +73,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         ldc = add.stride(0) if M > 1 else max(N, add.stride(0))
         flags |= GEMM_ADD_C
     native.status_tensor()
+    impl = impl or GEMM_IMPL
+    if (impl == "2cta" and not force_fallback and bn == 0 and max_ctas == 0 and M >= 256 and N >= 256
+            and lda % 8 == 0 and ldb % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+        rc = native.lib().b200_gemm_bf16_2cta(
+            native.ptr(a), native.ptr(b), native.ptr(out), native.ptr(add),
+            M, N, K, lda, ldb, ldd, ldc, int(trans_a), int(not trans_b), flags,
+            ctypes.c_float(alpha), native.stream_ptr())
+        native.check(rc, "b200_gemm_bf16_2cta")
+        native.bump()
+        return out
     rc = native.lib().b200_gemm_bf16(
         native.ptr(a), native.ptr(b), native.ptr(out), native.ptr(add),
         M, N, K, lda, ldb, ldd, ldc, int(trans_a), int(not trans_b), flags,

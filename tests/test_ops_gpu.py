@@ -33,7 +33,21 @@ def test_gemm(M, N, K, ta, tb):
     a = bf(*((K, M) if ta else (M, K)), seed=1)
     b = bf(*((N, K) if tb else (K, N)), seed=2)
     ref = F.gemm(a.float(), b.float(), trans_a=ta, trans_b=tb)
-    out = F.gemm(a.to(DEV), b.to(DEV), trans_a=ta, trans_b=tb)
+    for impl in ("1cta", "2cta"):
+        out = F.gemm(a.to(DEV), b.to(DEV), trans_a=ta, trans_b=tb, impl=impl)
+        close(out, ref, rtol=1e-2, atol=1e-2)
+    assert F.native.read_status() == (0, 0)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 264), (1000, 1032, 136), (2048, 768, 512)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_cta_pairs(M, N, K, ta, tb):
+    """cta_group::2 kernel: 256 x 256 tiles over two SMs, ragged edges, accumulate epilogue."""
+    a = bf(*((K, M) if ta else (M, K)), seed=3)
+    b = bf(*((N, K) if tb else (K, N)), seed=4)
+    c = bf(M, N, seed=5)
+    ref = F.gemm(a.float(), b.float(), trans_a=ta, trans_b=tb) + c.float()
+    out = F.gemm(a.to(DEV), b.to(DEV), trans_a=ta, trans_b=tb, add=c.to(DEV), impl="2cta")
     close(out, ref, rtol=1e-2, atol=1e-2)
     assert F.native.read_status() == (0, 0)
 
