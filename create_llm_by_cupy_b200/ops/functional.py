@@ -22,6 +22,7 @@ _f = ctypes.c_float
 import os as _os
 FLASH_TC = _os.environ.get("B200_FLASH_TC", "1") != "0"
 FLASH_TC_BWD = _os.environ.get("B200_FLASH_TC_BWD", "1") != "0"
+FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "2"))   # 2: two softmax warpgroups per tile
 
 
 def _lib():
@@ -284,7 +285,8 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     if D == 128 and cos is None and FLASH_TC:
         # tcgen05 / TMEM kernel (inputs already rotated)
         arr = (ctypes.c_longlong * 12)(*strides)
-        native.check(_lib().b200_flash_fwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
+        fwd_fn = _lib().b200_flash_fwd_tc2 if FLASH_FWD_GEN == 2 else _lib().b200_flash_fwd_tc
+        native.check(fwd_fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
                                               native.ptr(lse), native.ptr(valid_len), arr, B, T, QH, KVH, D,
                                               _f(scale), native.stream_ptr()), "flash_fwd_tc")
         native.bump()
