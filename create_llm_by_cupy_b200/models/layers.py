@@ -106,6 +106,9 @@ class GroupedQueryAttention:
         self.cache_kqv = True            # keep the projection (else re-project from x in backward)
         self.cache_attn = False          # dense path only: keep the [B,QH,T,T] probabilities
         self.flash_backend = "b200"      # "none" selects the dense verification path
+        # Residual-branch dropout (only built when dropout_rate != 0; the reference drops inside
+        # the attention probabilities, which would force the dense path, model/fast_layers.py:93-95)
+        self.drop = TimeDropout(dropout_rate, dtype, generator) if dropout_rate else None
 
     # -- helpers ---------------------------------------------------------------------------
     def _split(self, kqv: torch.Tensor, B: int, T: int):
@@ -146,7 +149,11 @@ class GroupedQueryAttention:
         kqv = self._project(x, T, tabs, True)
         q, k, v = self._split(kqv, B, T)
         o, lse = self._attend(q, k, v, valid_len, tabs)
-        out = F.gemm(o.view(B * T, self.H), self.params[1], add=residual)
+        if self.drop is not None and train_flg:
+            out = self.drop.forward(F.gemm(o.view(B * T, self.H), self.params[1]), True)
+            out = F.add(out, residual) if residual is not None else out
+        else:
+            out = F.gemm(o.view(B * T, self.H), self.params[1], add=residual)
         if train_flg:
             self.cache = (x, B, T, valid_len, kqv if self.cache_kqv else None,
                           o if self.cache_out_value else None, lse)
@@ -156,6 +163,8 @@ class GroupedQueryAttention:
 
     def backward(self, dout: torch.Tensor, grad_out=None) -> torch.Tensor:
         x, B, T, valid_len, kqv, o, lse = self.cache
+        if self.drop is not None:
+            dout = self.drop.backward(dout)
         tabs = self._rope(T, x.device)
         if kqv is None:
             kqv = self._project(x, T, tabs, False)
@@ -247,16 +256,23 @@ class SwiGLU:
         self.cache = None
         self.cache_gate = True
         self.dropout_rate = dropout_rate
+        self.drop = TimeDropout(dropout_rate, dtype, generator) if dropout_rate else None
 
     def forward(self, x: torch.Tensor, residual=None, train_flg: bool = True) -> torch.Tensor:
         gv = F.gemm(x, self.params[0])
         act = F.swiglu_fwd(gv)
-        out = F.gemm(act, self.params[1], add=residual)
+        if self.drop is not None and train_flg:
+            out = self.drop.forward(F.gemm(act, self.params[1]), True)
+            out = F.add(out, residual) if residual is not None else out
+        else:
+            out = F.gemm(act, self.params[1], add=residual)
         self.cache = (x, gv if self.cache_gate else None, act if self.cache_gate else None) if train_flg else None
         return out
 
     def backward(self, dout: torch.Tensor, grad_out=None) -> torch.Tensor:
         x, gv, act = self.cache
+        if self.drop is not None:
+            dout = self.drop.backward(dout)
         if gv is None:
             gv = _weight_gemm(self, x, 0)
             act = F.swiglu_fwd(gv)

@@ -230,14 +230,25 @@ __global__ void rmsnorm_bwd_scalar_kernel(const bf16* __restrict__ dy, const bf1
   }
 }
 
-__global__ void rmsnorm_dgamma_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dgamma, int nrows,
-                                             int H, int accumulate) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
+__global__ void __launch_bounds__(256)
+rmsnorm_dgamma_reduce_kernel(const float* __restrict__ partial, bf16* __restrict__ dgamma, int nrows, int H,
+                             int accumulate) {
+  // block = 32 columns x 8 row-groups: coalesced 128-byte reads, rows split over the warps
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int h = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int r = 0; r < nrows; ++r) s += partial[size_t(r) * H + h];
-  if (accumulate) s += __bfloat162float(dgamma[h]);
-  dgamma[h] = __float2bfloat16(s);
+  if (h < H)
+    for (int r = w; r < nrows; r += 8) s += partial[size_t(r) * H + h];
+  red[w][lane] = s;
+  __syncthreads();
+  if (w == 0 && h < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i][lane];
+    if (accumulate) t += __bfloat162float(dgamma[h]);
+    dgamma[h] = __float2bfloat16(t);
+  }
 }
 
 // ------------------------------------------------------------------ SwiGLU
@@ -327,6 +338,41 @@ __global__ void rope_inplace_kernel(bf16* __restrict__ buf, const float* __restr
     const float c = cs[size_t(pos) * half + j], s = sn[size_t(pos) * half + j] * sign;
     p[0] = __float2bfloat16(x1 * c - x2 * s);
     p[half] = __float2bfloat16(x2 * c + x1 * s);
+  }
+}
+
+// 128-bit version: one thread rotates 8 pairs (two 16-byte chunks). Needs D/2 % 8 == 0 and 16-byte
+// aligned rows / column offset.
+__global__ void rope_inplace_vec_kernel(bf16* __restrict__ buf, const float* __restrict__ cs,
+                                        const float* __restrict__ sn, int M, int T, int nheads, int D, int ld, int col0,
+                                        int pos0, float sign) {
+  const int half = D >> 1;
+  const int cph = half >> 3;                        // 8-element chunks per half head
+  const size_t total = size_t(M) * nheads * cph;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const int jc = int(i % cph);
+    const int h = int((i / cph) % nheads);
+    const int m = int(i / (size_t(cph) * nheads));
+    const int pos = pos0 + (m % T);
+    bf16* p = buf + size_t(m) * ld + col0 + h * D + jc * 8;
+    Pack8 a = *reinterpret_cast<const Pack8*>(p);
+    Pack8 b = *reinterpret_cast<const Pack8*>(p + half);
+    const float4* c4 = reinterpret_cast<const float4*>(cs + size_t(pos) * half + jc * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sn + size_t(pos) * half + jc * 8);
+    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    float x1[8], x2[8], y1[8], y2[8];
+    unpack8(a, x1);
+    unpack8(b, x2);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sg = sv[e] * sign;
+      y1[e] = x1[e] * c[e] - x2[e] * sg;
+      y2[e] = x2[e] * c[e] + x1[e] * sg;
+    }
+    *reinterpret_cast<Pack8*>(p) = pack8(y1);
+    *reinterpret_cast<Pack8*>(p + half) = pack8(y2);
   }
 }
 
@@ -470,7 +516,7 @@ B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, 
     rmsnorm_bwd_kernel<16><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   }
   B200_CHECK(cudaGetLastError());
-  rmsnorm_dgamma_reduce_kernel<<<(H + 127) / 128, 128, 0, st>>>(pp, static_cast<bf16*>(dgamma), rows, H,
+  rmsnorm_dgamma_reduce_kernel<<<(H + 31) / 32, 256, 0, st>>>(pp, static_cast<bf16*>(dgamma), rows, H,
                                                                  accumulate_dgamma);
   return static_cast<int>(cudaGetLastError());
 }
@@ -511,9 +557,16 @@ B200_API int b200_rope_inplace(void* buf, const void* cs, const void* sn, int M,
                                int col0, int pos0, int inverse, cudaStream_t st) {
   const size_t total = size_t(M) * nheads * (D / 2);
   if (total == 0) return 0;
-  rope_inplace_kernel<<<grid_for(total, 256), 256, 0, st>>>(static_cast<bf16*>(buf), static_cast<const float*>(cs),
-                                                            static_cast<const float*>(sn), M, T, nheads, D, ld, col0,
-                                                            pos0, inverse ? -1.f : 1.f);
+  const bool vec = ((D / 2) % 8 == 0) && (ld % 8 == 0) && (col0 % 8 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(buf) & 15) == 0);
+  if (vec)
+    rope_inplace_vec_kernel<<<grid_for(total / 8, 256), 256, 0, st>>>(
+        static_cast<bf16*>(buf), static_cast<const float*>(cs), static_cast<const float*>(sn), M, T, nheads, D, ld,
+        col0, pos0, inverse ? -1.f : 1.f);
+  else
+    rope_inplace_kernel<<<grid_for(total, 256), 256, 0, st>>>(static_cast<bf16*>(buf), static_cast<const float*>(cs),
+                                                              static_cast<const float*>(sn), M, T, nheads, D, ld, col0,
+                                                              pos0, inverse ? -1.f : 1.f);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -127,3 +127,45 @@ def print_memory_status(tag: str = "", device=None, printer=print) -> dict:
     if printer is not None:
         printer(f"[mem] {tag}: allocated {info['allocated_gib']:.2f} GiB, reserved {info['reserved_gib']:.2f} GiB")
     return info
+
+
+def look_list(ids, word_id_path: str = "word_id.pkl.gz", printer=print):
+    """Debug helper: print the words of a list of token ids using a gzip-pickled ``{word: id}``
+    (or ``{id: word}``) dictionary (model/ZeRO3.py:503-515)."""
+    import gzip
+    import pickle
+    with gzip.open(word_id_path, "rb") as f:
+        table = pickle.load(f)
+    if table and not isinstance(next(iter(table)), int):
+        table = {v: k for k, v in table.items()}
+    words = [str(table.get(int(i), f"<{int(i)}>")) for i in ids]
+    if printer is not None:
+        printer(" ".join(words))
+    return words
+
+
+def pad_mask_to_valid_len(mask, T: int):
+    """Accept the pad-mask forms the reference's attention takes (model/fast_layers.py:126-202,
+    model/flash_attention.py:28-41) and return valid key lengths [B] (int32), which is what the
+    attention kernels consume:
+
+      * a 1-D integer vector is taken as the valid lengths themselves;
+      * a boolean mask of shape [B, T], [B, 1, 1, T] or [B, 1, 1, 1, T] with True = padded key;
+      * an additive mask of those shapes with -inf (or a large negative value) at padded keys.
+
+    Padding must be a suffix of each row (keys 0 .. len-1 valid), as produced by make_mask."""
+    m = torch.as_tensor(mask)
+    if m.dim() == 1 and not m.dtype.is_floating_point and m.dtype != torch.bool:
+        return m.to(torch.int32)
+    m = m.reshape(m.shape[0], -1)[:, -T:] if m.dim() > 2 else m
+    if m.dtype == torch.bool:
+        padded = m
+    else:
+        padded = m < -1e4
+    valid = (~padded).to(torch.int32)
+    lens = valid.sum(-1).to(torch.int32)
+    # suffix check: the first `len` keys must be the valid ones
+    idx = torch.arange(T, device=m.device)[None, :]
+    if not bool(((idx < lens[:, None]) == (valid > 0)).all()):
+        raise ValueError("pad mask is not a suffix mask; only right-padded sequences are supported")
+    return lens

@@ -106,3 +106,25 @@ def test_flat_weight_file_roundtrip(tmp_path):
     for a, b in zip(m.params, m2.params):
         torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-3)
     assert m2.layers[0].params[0] is m2.params[0]
+
+
+def test_dropout_branches_and_mask_adapters():
+    from create_llm_by_cupy_b200.utils.functions import pad_mask_to_valid_len
+    d = dict(TINY, dropout_rate=0.25)
+    m = Cupa_ver4(d, device="cpu")
+    x, t, vl = batch(d)
+    X, Tt, V = torch.from_numpy(x), torch.from_numpy(t), torch.from_numpy(vl).int()
+    l1 = float(m.forward(X, Tt, V))
+    m.backward()
+    assert all(torch.isfinite(g).all() for g in m.grads)
+    l_eval = float(m.predict(X, Tt, V))            # no dropout at inference
+    m0 = Cupa_ver4(dict(TINY), device="cpu")
+    assert abs(l_eval - float(m0.predict(X, Tt, V))) < 1e-5 and abs(l1 - l_eval) > 1e-6
+    # pad-mask forms -> valid lengths
+    lens = torch.tensor([16, 11, 5], dtype=torch.int32)
+    add4 = m.make_mask(lens)
+    assert torch.equal(pad_mask_to_valid_len(add4, 16), lens)
+    assert torch.equal(pad_mask_to_valid_len(torch.isinf(add4[:, 0, 0, :]), 16), lens)
+    assert torch.equal(pad_mask_to_valid_len(lens, 16), lens)
+    with pytest.raises(ValueError):
+        pad_mask_to_valid_len(torch.tensor([[False, True, False, False]]), 4)
