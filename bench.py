@@ -97,6 +97,8 @@ def main():
               time_size=c["time_size"], q_head=c["q_head"], kv_head=c["kv_head"], ffn_size=c["ffn_size"],
               padding_id=pad, dropout_rate=0, half_float=True, dtype="bf16", tie_embeddings=True, init_std=0.02,
               seed=0, grad_bucket_elems=25_000_000)
+    if c["zero"] == "2.5":
+        md.update(zero25_replica_ratio=0.5, zero25_replica_policy="largest_first")
     fused = None
     use_fused = world > 1 and args.fused != 0
     if use_fused:

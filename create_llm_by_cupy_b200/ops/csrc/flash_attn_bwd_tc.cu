@@ -69,8 +69,8 @@ __device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, bf16* grow, 
 struct FdqSmem {
   static constexpr int kQ = 0, kDO = FB_TILE, kKV = 2 * FB_TILE;           // KV stage s: K, V
   static constexpr int kBar = kKV + 2 * 2 * FB_TILE;
-  // qdo_full, kv_full[2], kv_empty[2], sdp_full, ds_full   = 7 barriers
-  static constexpr int kTotal = kBar + 7 * 8 + 16 + 1024;
+  // qdo_full, kv_full[2], kv_empty[2], sdp_full[2], ds_full[2], rd_bar[2], dq_done = 12 barriers
+  static constexpr int kTotal = kBar + 12 * 8 + 16 + 1024;
 };
 
 __global__ void __launch_bounds__(FBT_THREADS, 1)
@@ -83,9 +83,11 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* qdo_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = bars + 3;
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* ds_full = bars + 6;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* sdp_full = bars + 5;     // [2]: scores of 64-key sub-tile u live in TMEM buffer u & 1
+  uint64_t* ds_full = bars + 7;      // [2]
+  uint64_t* rd_bar = bars + 9;       // [2]: both math warpgroups have read the scores
+  uint64_t* dq_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -100,8 +102,8 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 256);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 256); mbar_init(&rd_bar[s], 256); }
+    mbar_init(dq_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -111,7 +113,11 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDS = 256, kColDQ = 384;
+  // Every 128-key tile is processed as two 64-key sub-tiles so that S and dP (64 columns each) can
+  // be double-buffered: the tensor core works on sub-tile u + 1 while the math warps are on u.
+  // dS (bf16, 32 packed columns) overwrites the first half of the S buffer it was computed from.
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 384;
+  const int n_sub = 2 * n_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -134,47 +140,51 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);   // both operands K-major
-      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);   // B MN-major
+      constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 64, 0, 0);    // [128 q x 64 keys], K-major operands
+      constexpr uint32_t idesc_mn = umma_idesc_bf16(128, 128, 0, 1);   // [128 q x 128 d], B MN-major
       const uint32_t aQ = smem_u32(smem + FdqSmem::kQ), aDO = smem_u32(smem + FdqSmem::kDO);
-      auto issue_scores = [&](int j) {
-        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE), aV = aK + FB_TILE;
+      auto issue_scores = [&](int u) {
+        const int j = u >> 1, sub = u & 1;
+        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE) + sub * 8192, aV = aK + FB_TILE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16_ss(tmem_base + kColS, umma_smem_desc(aQ + off, 16, 1024), umma_smem_desc(aK + off, 16, 1024),
-                       idesc_kk, kk != 0);
+          umma_bf16_ss(tmem_base + kColS + sub * 64, umma_smem_desc(aQ + off, 16, 1024),
+                       umma_smem_desc(aK + off, 16, 1024), idesc_kk, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16_ss(tmem_base + kColDP, umma_smem_desc(aDO + off, 16, 1024), umma_smem_desc(aV + off, 16, 1024),
-                       idesc_kk, kk != 0);
+          umma_bf16_ss(tmem_base + kColDP + sub * 64, umma_smem_desc(aDO + off, 16, 1024),
+                       umma_smem_desc(aV + off, 16, 1024), idesc_kk, kk != 0);
         }
-        umma_commit(sdp_full);
+        umma_commit(&sdp_full[sub]);
       };
       bool ok = mbar_wait(qdo_full, 0, abort_flag);
-      if (ok && n_tiles > 0) {
+      if (ok && n_sub > 0) {
         ok = mbar_wait(&kv_full[0], 0, abort_flag);
         if (ok) { tc_fence_after(); issue_scores(0); }
       }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (!mbar_wait(ds_full, j & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tmem_base + kColDQ, tmem_base + kColDS + kk * 8, umma_smem_desc(aK + kk * 2048, 16384, 1024),
-                       idesc_mn, (j | kk) != 0);
-        umma_commit(&kv_empty[j & 1]);
-        if (j + 1 < n_tiles) {
-          if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+      for (int u = 0; u < n_sub && ok; ++u) {
+        const int j = u >> 1, sub = u & 1;
+        if (u + 1 < n_sub) {
+          if (((u + 1) & 1) == 0) {       // first sub-tile of the next key tile: its K / V must have landed
+            const int jn = (u + 1) >> 1;
+            if (!mbar_wait(&kv_full[jn & 1], (jn >> 1) & 1, abort_flag)) { ok = false; break; }
+          }
           tc_fence_after();
-          issue_scores(j + 1);
-        } else {
-          umma_commit(sdp_full);      // last dQ MMA done: the math warps may read dQ
+          issue_scores(u + 1);
         }
+        if (!mbar_wait(&ds_full[sub], (u >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(smem + FdqSmem::kKV + (j & 1) * 2 * FB_TILE) + sub * 8192;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16_ts(tmem_base + kColDQ, tmem_base + kColS + sub * 64 + kk * 8,
+                       umma_smem_desc(aK + kk * 2048, 16384, 1024), idesc_mn, (u | kk) != 0);
+        if (sub == 1) umma_commit(&kv_empty[j & 1]);
       }
+      if (ok) umma_commit(dq_done);
     }
   } else if (warp >= 4) {
     const int q = warp & 3;                   // TMEM lane quarter
@@ -186,46 +196,48 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const float lse2 = (row < T) ? p.lse[sidx] * kFbLog2e : INFINITY;
     const float dlt = (row < T) ? p.delta[sidx] : 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
+    for (int u = 0; u < n_sub && ok; ++u) {
+      const int j = u >> 1, sub = u & 1;
+      if (!mbar_wait(&sdp_full[sub], (u >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int n0 = j * 128;
-      const bool need_mask = (j == mtile) || (n0 + 128 > vlen);
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int col = half * 64 + c * 32;
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + col, rs);
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + col, rp);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      const int n0 = j * 128 + sub * 64;
+      const bool need_mask = (j == mtile) || (j * 128 + 128 > vlen);
+      const int col = half * 32;                   // this warpgroup's 32 of the 64 key columns
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + sub * 64 + col, rs);
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + sub * 64 + col, rp);
+      tmem_ld_wait();
+      // dS of warpgroup 1 lands on columns warpgroup 0 reads: wait until both have read
+      tc_fence_before();
+      mbar_arrive(&rd_bar[sub]);
+      if (!mbar_wait(&rd_bar[sub], (u >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float d0, d1;
-          {
-            float pe = exp2f(__uint_as_float(rs[e]) * sl2 - lse2);
-            const int key = n0 + col + e;
-            if (need_mask && (key > row || key >= vlen)) pe = 0.f;
-            d0 = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
-          }
-          {
-            float pe = exp2f(__uint_as_float(rs[e + 1]) * sl2 - lse2);
-            const int key = n0 + col + e + 1;
-            if (need_mask && (key > row || key >= vlen)) pe = 0.f;
-            d1 = pe * (__uint_as_float(rp[e + 1]) - dlt) * p.scale;
-          }
-          const bf162 t = __floats2bfloat162_rn(d0, d1);
-          pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+      for (int e = 0; e < 32; e += 2) {
+        float d0, d1;
+        {
+          float pe = exp2f(__uint_as_float(rs[e]) * sl2 - lse2);
+          const int key = n0 + col + e;
+          if (need_mask && (key > row || key >= vlen)) pe = 0.f;
+          d0 = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
         }
-        tmem_st_32x32b_x16(tmem_base + lane_sel + kColDS + (col >> 1), pk);
+        {
+          float pe = exp2f(__uint_as_float(rs[e + 1]) * sl2 - lse2);
+          const int key = n0 + col + e + 1;
+          if (need_mask && (key > row || key >= vlen)) pe = 0.f;
+          d1 = pe * (__uint_as_float(rp[e + 1]) - dlt) * p.scale;
+        }
+        const bf162 t = __floats2bfloat162_rn(d0, d1);
+        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
       }
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kColS + sub * 64 + (col >> 1), pk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[sub]);
     }
     if (ok) {
-      // the commit after the last dQ MMA flips sdp_full once more
-      if (mbar_wait(sdp_full, n_tiles & 1, abort_flag)) {
+      if (mbar_wait(dq_done, 0, abort_flag)) {
         tc_fence_after();
         bf16* grow = p.dq + b * p.dq_bs + (long long)min(row, T - 1) * p.dq_ts + h * p.dq_hs;
         store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
@@ -251,8 +263,8 @@ struct FdkvSmem {
   static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;            // stage s: Q_i (16 KiB), dO_i (16 KiB)
   static constexpr int kStats = kQ + 2 * 2 * FKV_QTILE;                    // stage s: lse2[64], delta[64]
   static constexpr int kBar = kStats + 2 * 2 * FKV_BQ * 4;
-  // kv_full, q_full[2], q_empty[2], st_full[2] (stats staged), sdp_full, pds_full, acc_done  = 10 barriers
-  static constexpr int kTotal = kBar + 10 * 8 + 16 + 1024;
+  // kv_full, q_full[2], q_empty[2], st_full[2] (stats staged), sdp_full[2], pds_full[2], rd_bar[2], acc_done = 14
+  static constexpr int kTotal = kBar + 14 * 8 + 16 + 1024;
 };
 
 __global__ void __launch_bounds__(FBT_THREADS, 1)
@@ -266,10 +278,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint64_t* q_full = bars + 1;
   uint64_t* q_empty = bars + 3;
   uint64_t* st_full = bars + 5;
-  uint64_t* sdp_full = bars + 7;
-  uint64_t* pds_full = bars + 8;
-  uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* sdp_full = bars + 7;     // [2]: S^T / dP^T of iteration it live in TMEM buffer it & 1
+  uint64_t* pds_full = bars + 9;     // [2]
+  uint64_t* rd_bar = bars + 11;      // [2]: both math warpgroups have read the scores (P^T / dS^T overwrite them)
+  uint64_t* acc_done = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -285,8 +298,7 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 256);
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 256); mbar_init(&rd_bar[s], 256); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -297,7 +309,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kColST = 0, kColDPT = 64, kColPT = 128, kColDST = 160, kColDV = 256, kColDK = 384;
+  // S^T and dP^T are double-buffered (64 columns each per buffer); P^T / dS^T (bf16, 32 packed
+  // columns) overwrite the first half of the S^T / dP^T buffer they were computed from.
+  constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -341,40 +355,52 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, FKV_BQ, 0, 0);   // [128 keys x 64 q], K-major operands
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, FB_D, 0, 1);     // [128 keys x 128 d], B MN-major
       const uint32_t aK = smem_u32(smem + FdkvSmem::kK), aV = smem_u32(smem + FdkvSmem::kV);
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
-      for (int it = 0; it < iters && ok; ++it) {
+      auto issue_scores = [&](int it) {
         const int s = it & 1;
-        if (!mbar_wait(&q_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-        // the math warps have consumed the previous S^T / dP^T (pds_full of it - 1 was waited below)
-        tc_fence_after();
         const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + s * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;     // 128-row tiles
           const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;      // 64-row tiles
-          umma_bf16_ss(tmem_base + kColST, umma_smem_desc(aK + offk, 16, 1024), umma_smem_desc(aQ + offq, 16, 1024),
-                       idesc_s, kk != 0);
+          umma_bf16_ss(tmem_base + kColST + s * 64, umma_smem_desc(aK + offk, 16, 1024),
+                       umma_smem_desc(aQ + offq, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;
-          umma_bf16_ss(tmem_base + kColDPT, umma_smem_desc(aV + offk, 16, 1024), umma_smem_desc(aDO + offq, 16, 1024),
-                       idesc_s, kk != 0);
+          umma_bf16_ss(tmem_base + kColDPT + s * 64, umma_smem_desc(aV + offk, 16, 1024),
+                       umma_smem_desc(aDO + offq, 16, 1024), idesc_s, kk != 0);
         }
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
+        umma_commit(&sdp_full[s]);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      if (ok && iters > 0) {
+        ok = mbar_wait(&q_full[0], 0, abort_flag);
+        if (ok) { tc_fence_after(); issue_scores(0); }
+      }
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        if (it + 1 < iters) {
+          // scores of the next query tile go to the other TMEM buffer while the math warps work on
+          // this one (its previous contents were consumed by the gradient MMAs issued earlier)
+          if (!mbar_wait(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(it + 1);
+        }
+        if (!mbar_wait(&pds_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + s * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
         // B = dO_i / Q_i read MN-major: 64 query rows (k), 128 d (n); 64-d chunks are 8 KiB apart
 #pragma unroll
         for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
-          umma_bf16_ts(tmem_base + kColDV, tmem_base + kColPT + kk * 8, umma_smem_desc(aDO + kk * 2048, 8192, 1024),
-                       idesc_g, (it | kk) != 0);
+          umma_bf16_ts(tmem_base + kColDV, tmem_base + kColST + s * 64 + kk * 8,
+                       umma_smem_desc(aDO + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
-          umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDST + kk * 8, umma_smem_desc(aQ + kk * 2048, 8192, 1024),
-                       idesc_g, (it | kk) != 0);
+          umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDPT + s * 64 + kk * 8,
+                       umma_smem_desc(aQ + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
         }
         umma_commit(&q_empty[s]);
       }
@@ -391,14 +417,19 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const int s = it & 1;
       const int m0 = (i_first + it % n_qt) * FKV_BQ;
       if (!mbar_wait(&st_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
       const int col = half * 32;
       uint32_t rs[32], rp[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + col, rs);
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + col, rp);
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + s * 64 + col, rs);
+      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + s * 64 + col, rp);
       tmem_ld_wait();
+      // P^T / dS^T of warpgroup 1 land on columns warpgroup 0 reads: wait until both have read
+      tc_fence_before();
+      mbar_arrive(&rd_bar[s]);
+      if (!mbar_wait(&rd_bar[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
       uint32_t pk[16], dk_[16];
       const bool key_dead = key >= vlen;
 #pragma unroll
@@ -417,11 +448,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
         dk_[e >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
       }
-      tmem_st_32x32b_x16(tmem_base + lane_sel + kColPT + (col >> 1), pk);
-      tmem_st_32x32b_x16(tmem_base + lane_sel + kColDST + (col >> 1), dk_);
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kColST + s * 64 + (col >> 1), pk);
+      tmem_st_32x32b_x16(tmem_base + lane_sel + kColDPT + s * 64 + (col >> 1), dk_);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      mbar_arrive(&pds_full[s]);
     }
     if (ok) {
       if (iters > 0) ok = mbar_wait(acc_done, 0, abort_flag);

@@ -41,7 +41,7 @@ class Trainer:
                  lr_max: float = 3e-4, lr_mini: float = 3e-5, weight_decay: float = 0.1, warm_up: int = 100,
                  total_steps: int = 1000, beta1: float = 0.9, beta2: float = 0.99, epsilon: float = 1e-6,
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
-                 profile_comm: bool = False, param_path: str | None = None):
+                 profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False):
         self.rank, self.world_size = rank, world_size
         self.comm = comm if comm is not None else SingleProcessComm()
         self.accum_step = int(accum_step)
@@ -66,12 +66,22 @@ class Trainer:
                                 gs.get("Scale_Up_Step"), enabled=bool(gs.get("enabled", False)))
         self.iteration = 0
         self.last = {}
+        # Fully fused gradient path (reduce-scatter + AdamW in one kernel per unit, during backward).
+        # The update of a unit then happens before the global gradient norm exists, so it is only
+        # available without clipping (max_grads <= 0), with a GPU optimizer, one micro-batch per
+        # step, no replicated parameters, and a non-finite step cannot be skipped after the fact.
+        self.fused_adam = bool(fused_adam and fused is not None and self.max_grads <= 0 and self.accum_step == 1
+                               and optimizer_device != "cpu" and self.replica_optimizer is None and world_size > 1)
 
     # ------------------------------------------------------------------ one optimizer step
     def train_step(self, batches) -> dict:
         mgr, model = self.manager, self.model
         scale = float(self.scaler.Scale)
         mgr.zero_grad()
+        if self.fused_adam:
+            lr = self.optimizer._update_learning_rate()
+            mgr.fused_adam = {"opt": self.optimizer, "lr": lr,
+                              "grad_scale": 1.0 / (self.world_size * len(batches) * scale)}
         loss_acc = None
         for (x, t, x_pa) in batches:
             with nvtx_range("forward"):
@@ -98,8 +108,10 @@ class Trainer:
                     self.comm.all_reduce(extra)
                 stats = stats + extra
                 stats[1] = (stats[1] != 0).float()
-            self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
-                                  out_shard=mgr.get_param_shard_view(), stats=stats, max_grad_norm=self.max_grads)
+            if not self.fused_adam:
+                self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
+                                      out_shard=mgr.get_param_shard_view(), stats=stats,
+                                      max_grad_norm=self.max_grads)
             if self.replica_optimizer is not None:
                 self.replica_optimizer.update(rgrad, step_scale, False,
                                               out_shard=mgr.get_replica_optimizer_shard_view(), stats=stats,
@@ -110,7 +122,7 @@ class Trainer:
         host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
         loss_val = host[0] / n_micro
         bad = host[2] != 0.0 or not math.isfinite(host[1])
-        if bad:   # the kernels skipped the update; keep the schedule where it was (reference: `continue`)
+        if bad and not self.fused_adam:   # the kernels skipped the update; keep the schedule where it was
             self.optimizer.t -= 1
             if self.replica_optimizer is not None:
                 self.replica_optimizer.t -= 1

@@ -160,6 +160,7 @@ class MemoryZeRO3Manager:
         self.pending_gather = {}    # uid -> _Buf with an all-gather in flight
         self.deferred = {}          # uid -> _PendingGather (gather fused into the consuming GEMM)
         self.phase = "fwd"          # set by the model: which pass is asking for parameters
+        self.fused_adam = None      # set per step by the trainer: {"opt", "lr", "grad_scale"}
         self.cur_grad = {}          # uid -> _Buf being written by backward
         self.pending_reduce_handles = collections.deque()
         self.exposed_pairs = []     # (event before wait, event after wait) on the compute stream
@@ -531,9 +532,19 @@ class MemoryZeRO3Manager:
             with self._comm_ctx():
                 self._wait(self.comm_stream, ev)
                 if self.fused is not None:
+                    adam = None
+                    if self.fused_adam is not None and self.micro_index == self.accum_steps - 1 and self.direct_grad:
+                        # reduce-scatter -> cast -> scale -> AdamW in ONE kernel: the reduced gradient
+                        # of this unit never goes to memory, the parameter slice is updated in place
+                        fa, opt = self.fused_adam, self.fused_adam["opt"]
+                        adam = dict(m=opt.m[lo:hi], v=opt.v[lo:hi], master=opt.master_weight_shard[lo:hi],
+                                    param=self.param_shard_f16[lo:hi], lr=fa["lr"], beta1=opt.beta1, beta2=opt.beta2,
+                                    eps=opt.epsilon, weight_decay=opt.weight_decay,
+                                    m_corr=1.0 / (1.0 - opt.beta1 ** opt.t), v_corr=1.0 / (1.0 - opt.beta2 ** opt.t),
+                                    grad_scale=fa["grad_scale"])
                     self.fused.reduce_scatter_accumulate(dst, b.t, accumulate=not self.direct_grad,
                                                          stream=self.comm_stream, stats=self._stats,
-                                                         do_stats=self.micro_index == self.accum_steps - 1)
+                                                         do_stats=self.micro_index == self.accum_steps - 1, adam=adam)
                 elif self.direct_grad:
                     self.comm.reduce_scatter(dst, b.t)
                 else:

@@ -141,3 +141,23 @@ def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path):
     for la, lb in zip(a["losses"], b["losses"]):
         assert abs(la - lb) < 3e-2, (a["losses"], b["losses"])
     assert abs(a["param_norm"] - b["param_norm"]) < 1e-2 * a["param_norm"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_fused_reduce_scatter_adam_matches_nccl_baseline(tmp_path):
+    """Reduce-scatter + AdamW in one kernel per unit (no clipping) against NCCL + separate AdamW."""
+    script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
+    outs = {}
+    for mode, extra in (("nccl", {"B200_TEST_NOCLIP": "1"}), ("fused", {"B200_TEST_FUSED_ADAM": "1"})):
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_ACCUM="1",
+                   B200_TEST_GATHER="pull", **extra)
+        out = tmp_path / f"{mode}.pt"
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+               "--master-addr", "127.0.0.1", "--master-port", str(29700 + (os.getpid() % 200) + (mode == "fused")),
+               script, mode, str(out)]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        outs[mode] = torch.load(out)
+    for la, lb in zip(outs["nccl"]["losses"], outs["fused"]["losses"]):
+        assert abs(la - lb) < 3e-2, (outs["nccl"]["losses"], outs["fused"]["losses"])
+    assert abs(outs["nccl"]["param_norm"] - outs["fused"]["param_norm"]) < 1e-2 * outs["nccl"]["param_norm"]
