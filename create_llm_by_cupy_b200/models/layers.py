@@ -172,7 +172,7 @@ class GroupedQueryAttention:
         if o is None:
             o, lse = self._attend(q, k, v, valid_len, tabs)
         go = grad_out if grad_out else (None, None)
-        dW_O = F.gemm(o.view(B * T, self.H), dout, trans_a=True, out=go[1])
+        dW_O = F.wgrad_gemm(o.view(B * T, self.H), dout, out=go[1])
         do = F.gemm(dout, self.params[1], trans_b=True)
         dkqv = torch.empty_like(kqv)
         dq, dk, dv = self._split(dkqv, B, T)
@@ -190,7 +190,7 @@ class GroupedQueryAttention:
         else:
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
                              scale=self.scale, rope=tabs, out=(dq, dk, dv))
-        dW_KQV = F.gemm(x, dkqv, trans_a=True, out=go[0])
+        dW_KQV = F.wgrad_gemm(x, dkqv, out=go[0])
         dx = F.gemm(dkqv, self.params[0], trans_b=True)
         self.grads = [dW_KQV, dW_O]
         self.cache = None
@@ -277,10 +277,10 @@ class SwiGLU:
             gv = _weight_gemm(self, x, 0)
             act = F.swiglu_fwd(gv)
         go = grad_out if grad_out else (None, None)
-        dW_out = F.gemm(act, dout, trans_a=True, out=go[1])
+        dW_out = F.wgrad_gemm(act, dout, out=go[1])
         dact = _weight_gemm(self, dout, 1, trans_b=True)
         dgv = F.swiglu_bwd(dact, gv)
-        dW_gv = F.gemm(x, dgv, trans_a=True, out=go[0])
+        dW_gv = F.wgrad_gemm(x, dgv, out=go[0])
         dx = F.gemm(dgv, self.params[0], trans_b=True)
         self.grads = [dW_gv, dW_out]
         self.cache = None

@@ -375,6 +375,7 @@ class Cupa_ver4:
                 dx = norm2.backward(dn2, add=dx, grad_out=manager.grad_views(norm2))
                 dn1 = gqa.backward(dx, grad_out=manager.grad_views(gqa))
                 dx = norm1.backward(dn1, add=dx, grad_out=manager.grad_views(norm1))
+                F.wgrad_join(dx.device)      # weight-gradient GEMMs of this block (side stream) are in the bucket
                 for m in (feed, norm2, gqa, norm1):
                     manager.add_grads_to_bucket(m.params, m.grads)
                     local_grads[id(m)] = m.grads

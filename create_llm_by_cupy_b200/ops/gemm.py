@@ -130,3 +130,49 @@ def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_sha
     native.check(rc, "b200_gemm_bf16_allgather")
     native.bump()
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Weight-gradient GEMMs on a second stream. Every GEMM here is a persistent kernel that fills the
+# GPU, so two of them never run side by side; but on one stream the next kernel cannot start until
+# the LAST tile of the previous one has finished, and several training shapes end with a
+# part-filled wave (e.g. 2048 x 3072 x 8192 is 1.3 waves of CTA pairs). The weight-gradient GEMMs
+# do not feed the activation-gradient chain, so issuing them on a side stream lets their first
+# CTAs start on SMs the other kernel has already left.
+WGRAD_OVERLAP = _os.environ.get("B200_WGRAD_OVERLAP", "0") != "0"
+_wgrad_streams: dict = {}
+
+
+def _wgrad_stream(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _wgrad_streams.get(key)
+    if st is None:
+        st = _wgrad_streams[key] = torch.cuda.Stream(device=device)
+    return st
+
+
+def wgrad_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a^T @ b`` for a weight gradient; runs on the side stream when overlap is enabled. The
+    caller must call ``wgrad_join()`` before the result is consumed on the main stream."""
+    if not (WGRAD_OVERLAP and a.is_cuda):
+        return gemm(a, b, trans_a=True, out=out)
+    cur = torch.cuda.current_stream(a.device)
+    ws = _wgrad_stream(a.device)
+    ws.wait_stream(cur)
+    with torch.cuda.stream(ws):
+        res = gemm(a, b, trans_a=True, out=out)
+    a.record_stream(ws)
+    b.record_stream(ws)
+    return res
+
+
+def wgrad_join(device=None) -> None:
+    if not WGRAD_OVERLAP or not torch.cuda.is_available():
+        return
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.type != "cuda":
+        return
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    ws = _wgrad_streams.get(key)
+    if ws is not None:
+        torch.cuda.current_stream(dev).wait_stream(ws)
