@@ -204,6 +204,112 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
 }
 
+// Wide rows (1024 < H <= 8192): the whole CTA works on R rows at a time, every thread owning NV
+// fixed 8-column chunks. All loads of the R rows are issued before the first use, the R row dots
+// are combined with one block-wide exchange, and each thread's dgamma columns stay in its own
+// registers for the whole kernel, so no cross-warp combine is needed at the end.
+template <int NV, int R>
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_bwd_cta_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                       const float* __restrict__ rstd, const bf16* __restrict__ add, bf16* __restrict__ dx,
+                       float* __restrict__ partial, int M, int H) {
+  __shared__ float sdot[2][R][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunk = H >> 3;
+  const float inv_h = 1.f / float(H);
+  float g[NV][8], dg[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = tid + i * 256;
+    if (c < nchunk) unpack8(reinterpret_cast<const Pack8*>(gamma)[c], g[i]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dg[i][e] = 0.f;
+      if (c >= nchunk) g[i][e] = 0.f;
+    }
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < M; row0 += gridDim.x * R, ++it) {
+    Pack8 pd[R][NV], px[R][NV], pa[R][NV];
+    float rs[R], dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+      const bool valid = row < M;
+      rs[r] = valid ? rstd[row] : 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = tid + i * 256;
+        if (valid && c < nchunk) {
+          pd[r][i] = reinterpret_cast<const Pack8*>(dy + size_t(row) * H)[c];
+          px[r][i] = reinterpret_cast<const Pack8*>(x + size_t(row) * H)[c];
+          if (add) pa[r][i] = reinterpret_cast<const Pack8*>(add + size_t(row) * H)[c];
+        } else {
+          pd[r][i] = Pack8{};
+          px[r][i] = Pack8{};
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float d[8], xv[8];
+        unpack8(pd[r][i], d);
+        unpack8(px[r][i], xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xhe = xv[e] * rs[r];
+          acc += d[e] * g[i][e] * xhe;
+          dg[i][e] += d[e] * xhe;
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) sdot[it & 1][r][warp] = acc;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += sdot[it & 1][r][w];
+      dot[r] = t * inv_h;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+      if (row >= M) continue;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = tid + i * 256;
+        if (c >= nchunk) continue;
+        float d[8], xv[8], o[8];
+        unpack8(pd[r][i], d);
+        unpack8(px[r][i], xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rs[r] * (d[e] * g[i][e] - xv[e] * rs[r] * dot[r]);
+        if (add) {
+          float a[8];
+          unpack8(pa[r][i], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
+        reinterpret_cast<Pack8*>(dx + size_t(row) * H)[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = tid + i * 256;
+    if (c < nchunk) {
+      float4* dst = reinterpret_cast<float4*>(partial + size_t(blockIdx.x) * H + size_t(c) * 8);
+      dst[0] = make_float4(dg[i][0], dg[i][1], dg[i][2], dg[i][3]);
+      dst[1] = make_float4(dg[i][4], dg[i][5], dg[i][6], dg[i][7]);
+    }
+  }
+}
+
 // Generic-H variant: two passes over the row, atomics for dgamma partial rows.
 __global__ void rmsnorm_bwd_scalar_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                           const bf16* __restrict__ gamma, const float* __restrict__ rstd,
@@ -493,7 +599,7 @@ B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, 
   bf16* dxp = static_cast<bf16*>(dx);
   float* pp = static_cast<float*>(partial);
   const size_t smem = size_t(8) * H * sizeof(float);   // 8 warps per CTA in the vector kernels
-  if (H % 8 != 0 || H > 4096) {
+  if (H % 8 != 0 || H > 8192) {
     B200_CHECK(cudaMemsetAsync(pp, 0, size_t(rows) * H * sizeof(float), st));
     rmsnorm_bwd_scalar_kernel<<<rows, 128, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else if (H <= 256) {
@@ -501,19 +607,11 @@ B200_API int b200_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, 
   } else if (H <= 1024) {
     rmsnorm_bwd_kernel<4><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else if (H <= 2048) {
-    static bool configured8 = false;
-    if (!configured8) {
-      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-      configured8 = true;
-    }
-    rmsnorm_bwd_kernel<8><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    rmsnorm_bwd_cta_kernel<1, 4><<<rows, 256, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+  } else if (H <= 4096) {
+    rmsnorm_bwd_cta_kernel<2, 2><<<rows, 256, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   } else {
-    static bool configured = false;
-    if (!configured) {
-      B200_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024));
-      configured = true;
-    }
-    rmsnorm_bwd_kernel<16><<<rows, 256, smem, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
+    rmsnorm_bwd_cta_kernel<4, 1><<<rows, 256, 0, st>>>(dyp, xp, gp, rp, ap, dxp, pp, M, H);
   }
   B200_CHECK(cudaGetLastError());
   rmsnorm_dgamma_reduce_kernel<<<(H + 31) / 32, 256, 0, st>>>(pp, static_cast<bf16*>(dgamma), rows, H,

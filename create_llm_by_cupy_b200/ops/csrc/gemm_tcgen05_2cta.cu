@@ -15,7 +15,21 @@
 //   tmem_full[a]  one per CTA; multicast commit after the last k-block of a tile.
 //   tmem_empty[a] leader only, 8 arrivals: the 4 epilogue warps of each CTA (the follower's
 //                 arrive remotely through the cluster shared-memory window).
+//   sched_full[i] one per CTA; sched_empty[i] leader only (see "Tile scheduler").
 // Waits are bounded exactly as in the single-CTA kernel.
+//
+// Tile scheduler. Every pair starts on the tile of its own index; all further tiles are handed
+// out dynamically: the leader's producer thread takes the next tile index from a global counter
+// (one tile ahead of the one it is loading), writes it into a
+// 4-slot ring that exists in both CTAs' shared memory and signals sched_full[slot] in both. The
+// follower's producer, the MMA thread and the eight epilogue warps read the ring and each arrive
+// on the leader's sched_empty[slot] (10 arrivals) before the slot is reused. An index beyond the
+// last tile is the stop mark; every pair draws exactly one, and the pair that draws the last one
+// puts the counter back to zero for the launch that reuses it. A pair that starts late (its SMs
+// were still busy with the previous kernel, or with a kernel of another stream) simply draws
+// fewer tiles, which a fixed tile-to-pair assignment cannot do.
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -30,7 +44,9 @@ constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;          // 16 KiB
 constexpr int G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;    // 16 KiB
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_BAR_OFF = G2_STAGES * G2_STAGE_BYTES;
-constexpr int G2_SMEM = G2_BAR_OFF + (2 * G2_STAGES + 4) * 8 + 16 + 1024;
+constexpr int G2_SCHED = 4;         // slots of the tile-index ring
+constexpr int G2_SMEM = G2_BAR_OFF + (2 * G2_STAGES + 4 + 2 * G2_SCHED) * 8 + 16 + G2_SCHED * 4 + 1024;
+constexpr int G2_SCHED_SLOTS = 1024;   // {next tile, finished pairs} counter pairs, used round-robin by launches
 
 enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2 };
 
@@ -42,7 +58,10 @@ struct Gemm2Params {
   int flags;
   float alpha;
   int* status;
+  int* sched;      // [0] next tile index, [1] pairs that have drawn their stop mark; both 0 between launches
 };
+
+static __device__ int g_tile_sched[2 * G2_SCHED_SLOTS];
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -94,6 +113,29 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+
+// Consumer side of the tile-index ring (one instance per consuming thread or warp).
+struct TileRingReader {
+  int slot = 0;
+  uint32_t phase = 0;
+  // Returns the next tile index, or -1 when the wait was abandoned. `arrive` is true for the one
+  // lane that reports the slot as read.
+  __device__ __forceinline__ int next(uint64_t* sched_full, uint64_t* sched_empty, volatile int* ring,
+                                      volatile int* abort_flag, bool whole_warp, bool arrive) {
+    if (!mbar_wait(&sched_full[slot], phase, abort_flag)) return -1;
+    fence_acq_rel_cluster();                 // the index was written by a thread of the leader CTA
+    const int t = ring[slot];
+    if (whole_warp) __syncwarp();
+    if (arrive) mbar_arrive_cluster(mapa_u32(smem_u32(&sched_empty[slot]), 0));
+    if (++slot == G2_SCHED) { slot = 0; phase ^= 1; }
+    return t;
+  }
+};
+
 __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb) {
   constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
@@ -115,8 +157,11 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   uint64_t* empty = full + G2_STAGES;
   uint64_t* tfull = empty + G2_STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* sched_full = tempty + 2;
+  uint64_t* sched_empty = sched_full + G2_SCHED;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + G2_SCHED);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();            // 0 = leader of the pair
@@ -136,6 +181,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 8);
     }
+    for (int i = 0; i < G2_SCHED; ++i) {
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 10);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -154,7 +203,24 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int wslot = 0;                 // leader: ring write position
+      uint32_t wphase = 0;
+      TileRingReader rd;             // follower: ring read position
+      // Leader: hand tile `tile` to every consumer of the pair.
+      auto publish = [&](int tile) -> bool {
+        if (!mbar_wait(&sched_empty[wslot], wphase ^ 1, abort_flag)) return false;
+        tile_ring[wslot] = tile;
+        st_cluster_u32(mapa_u32(smem_u32(const_cast<int*>(&tile_ring[wslot])), 1), uint32_t(tile));
+        mbar_arrive_cluster(mapa_u32(smem_u32(&sched_full[wslot]), 0));
+        mbar_arrive_cluster(mapa_u32(smem_u32(&sched_full[wslot]), 1));
+        if (++wslot == G2_SCHED) { wslot = 0; wphase ^= 1; }
+        return true;
+      };
+      int t = pair, t_next = 0;      // the first tile needs no hand-out
+      const int publish_kb = num_kb > 8 ? 8 : num_kb - 1;
+      while (ok && t < num_tiles) {
+        // the draw is in flight while this tile's first loads are issued
+        if (rank == 0) t_next = num_pairs + atomicAdd(&p.sched[0], 1);
         int mb, nb;
         tile_coords2(t, num_m, num_n, mb, nb);
         const int m0 = mb * 2 * G2_BM + int(rank) * G2_BM;
@@ -179,6 +245,23 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             tma_load_2d_pair(sB, &tmB, bar, k0, n0);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (rank == 0 && kb == publish_kb && !publish(t_next)) { ok = false; break; }
+        }
+        if (!ok) break;
+        if (rank == 0) {
+          t = t_next;
+        } else {
+          t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true);
+          ok = t >= 0;
+        }
+      }
+      if (rank == 0 && ok) {
+        // this pair has drawn its stop mark; the last pair to do so rewinds the counters
+        __threadfence();
+        if (atomicAdd(&p.sched[1], 1) == num_pairs - 1) {
+          p.sched[0] = 0;
+          p.sched[1] = 0;
+          __threadfence();
         }
       }
     }
@@ -191,7 +274,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      TileRingReader rd;
+      for (int t = pair; ok && t >= 0 && t < num_tiles;
+           t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true)) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
@@ -228,7 +313,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                 : ((p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 &&
                                    (!add_c || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+    TileRingReader rd;
+    for (int t = pair; ok && t >= 0 && t < num_tiles;
+         t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0)) {
       int mb, nb;
       tile_coords2(t, num_m, num_n, mb, nb);
       const int row = mb * 2 * G2_BM + int(rank) * G2_BM + q * 32 + lane;
@@ -313,6 +400,23 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
+// Counter pair for one launch. Kernels of different streams may run at the same time, so launches
+// take the slots round-robin; a slot is back to zero when its kernel has finished.
+static int* next_sched_slot() {
+  static std::mutex mu;
+  static int* base[64] = {};
+  static unsigned next = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_tile_sched) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<int*>(ptr);
+  }
+  return base[dev] + 2 * (next++ % G2_SCHED_SLOTS);
+}
+
 template <bool A_MN, bool B_MN>
 static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2Params& p, cudaStream_t stream) {
   auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN>;
@@ -324,7 +428,10 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2P
   const int num_tiles = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
   int pairs = num_sms() / 2;
   if (num_tiles < pairs) pairs = num_tiles;
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, p);
+  Gemm2Params q = p;
+  q.sched = next_sched_slot();
+  if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, q);
   return static_cast<int>(cudaGetLastError());
 }
 

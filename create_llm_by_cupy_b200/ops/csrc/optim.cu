@@ -95,11 +95,53 @@ __global__ void __launch_bounds__(256)
 grad_stats_kernel(const TG* __restrict__ g, size_t n, float* __restrict__ stats) {
   float ss = 0.f;
   int bad = 0;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) {
-    const float x = ld_as_float<TG>(g, i);
+  auto take = [&](float x) {
     if (isfinite(x)) ss += x * x;
     else bad = 1;
+  };
+  // 16-byte loads over the aligned body, scalar loads for the unaligned head and the tail
+  constexpr int PER = 16 / int(sizeof(TG));
+  const size_t mis = (reinterpret_cast<uintptr_t>(g) & 15) / sizeof(TG);
+  size_t head = mis ? size_t(PER) - mis : 0;
+  if (head > n) head = n;
+  const size_t nvec = (n - head) / PER;
+  const uint4* gv = reinterpret_cast<const uint4*>(g + head);
+  const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, nthr = size_t(gridDim.x) * blockDim.x;
+  size_t i = tid;
+  for (; i + 3 * nthr < nvec; i += 4 * nthr) {
+    uint4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] = gv[i + u * nthr];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if constexpr (sizeof(TG) == 4) {
+        take(__uint_as_float(t[u].x)); take(__uint_as_float(t[u].y));
+        take(__uint_as_float(t[u].z)); take(__uint_as_float(t[u].w));
+      } else {
+        const bf162* h = reinterpret_cast<const bf162*>(&t[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          take(f.x); take(f.y);
+        }
+      }
+    }
   }
+  for (; i < nvec; i += nthr) {
+    const uint4 t = gv[i];
+    if constexpr (sizeof(TG) == 4) {
+      take(__uint_as_float(t.x)); take(__uint_as_float(t.y)); take(__uint_as_float(t.z)); take(__uint_as_float(t.w));
+    } else {
+      const bf162* h = reinterpret_cast<const bf162*>(&t);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        take(f.x); take(f.y);
+      }
+    }
+  }
+  for (size_t j = tid; j < head; j += nthr) take(ld_as_float<TG>(g, j));
+  for (size_t j = head + nvec * PER + tid; j < n; j += nthr) take(ld_as_float<TG>(g, j));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ss += __shfl_xor_sync(0xffffffffu, ss, o);

@@ -78,7 +78,8 @@ def test_gemm_canary_bounds():
     close(view, a.float().cpu() @ b.float().cpu(), rtol=1e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("M,H", [(37, 128), (512, 2048), (64, 4096), (9, 100)])
+@pytest.mark.parametrize("M,H", [(37, 128), (512, 2048), (64, 4096), (9, 100), (1203, 2048), (67, 1536), (10, 8192),
+                                 (3001, 3072)])
 def test_rmsnorm(M, H):
     x, g, dy, res = bf(M, H, seed=1), bf(H, seed=2) * 0.1 + 1, bf(M, H, seed=3), bf(M, H, seed=4)
     y_ref, r_ref = F.rmsnorm_fwd(x.float(), g.float())
@@ -213,6 +214,27 @@ def test_adamw_and_stats(gdt):
     acc = torch.zeros(n, device=DEV)
     F.accumulate(acc, g.to(DEV), 0.25)
     close(acc, g.float() * 0.25, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("off,n", [(0, 100_003), (1, 77_777), (3, 5), (5, 1 << 20), (2, 4099)])
+def test_grad_stats_unaligned_slices(dt, off, n):
+    """The vector body starts at the first 16-byte boundary; head and tail are read one by one."""
+    g = (torch.randn(n + 16, generator=torch.Generator().manual_seed(n)) * 3).to(dt)
+    ref = float((g[off:off + n].float() ** 2).sum())
+    st = torch.zeros(2, device=DEV)
+    F.grad_stats(g.to(DEV)[off:off + n], st)
+    assert abs(st[0].item() - ref) <= 2e-3 * ref and st[1].item() == 0.0
+    gb = g.clone()
+    gb[off + n - 1] = float("nan")
+    st.zero_()
+    F.grad_stats(gb.to(DEV)[off:off + n], st)
+    assert st[1].item() == 1.0
+    gb = g.clone()
+    gb[off] = float("inf")
+    st.zero_()
+    F.grad_stats(gb.to(DEV)[off:off + n], st)
+    assert st[1].item() == 1.0
 
 
 @pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
