@@ -69,7 +69,7 @@ __device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, bf16* grow, 
 struct FdqSmem {
   static constexpr int kQ = 0, kDO = FB_TILE, kKV = 2 * FB_TILE;           // KV stage s: K, V
   static constexpr int kBar = kKV + 2 * 2 * FB_TILE;
-  // qdo_full, kv_full[2], kv_empty[2], sdp_full[2], ds_full[2], rd_bar[2], dq_done = 12 barriers
+  // qdo_full, kv_full[2], kv_empty[2], sdp_full[2], ds_full[2], (2 unused), dq_done = 12 barriers
   static constexpr int kTotal = kBar + 12 * 8 + 16 + 1024;
 };
 
@@ -84,8 +84,7 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = bars + 3;
   uint64_t* sdp_full = bars + 5;     // [2]: scores of 64-key sub-tile u live in TMEM buffer u & 1
-  uint64_t* ds_full = bars + 7;      // [2]
-  uint64_t* rd_bar = bars + 9;       // [2]: both math warpgroups have read the scores
+  uint64_t* ds_full = bars + 7;      // [2]: math warpgroup `sub` has written dS of a sub-tile into buffer `sub`
   uint64_t* dq_done = bars + 11;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -102,7 +101,7 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 256); mbar_init(&rd_bar[s], 256); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 128); }
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -114,8 +113,10 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // Every 128-key tile is processed as two 64-key sub-tiles so that S and dP (64 columns each) can
-  // be double-buffered: the tensor core works on sub-tile u + 1 while the math warps are on u.
-  // dS (bf16, 32 packed columns) overwrites the first half of the S buffer it was computed from.
+  // be double-buffered, and each buffer has its own math warpgroup: warpgroup w turns the scores of
+  // sub-tiles u = w, w + 2, ... into dS while the other warpgroup and the tensor core are on u + 1.
+  // A thread owns one query row (one TMEM lane) and walks its 64 key columns in two halves; dS
+  // (bf16, 32 packed columns) overwrites, lane by lane, score columns that thread has already read.
   constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 384;
   const int n_sub = 2 * n_tiles;
 
@@ -188,50 +189,56 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
   } else if (warp >= 4) {
     const int q = warp & 3;                   // TMEM lane quarter
-    const int half = (warp - 4) >> 2;         // which 64 key columns of each tile this warpgroup owns
+    const int wg = (warp - 4) >> 2;           // math warpgroup = score buffer it serves
+    const int half = wg;                      // dQ columns this warpgroup stores at the end
     const int row = m0 + q * 32 + lane;
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
     const float sl2 = p.scale * kFbLog2e;
     const size_t sidx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
     const float lse2 = (row < T) ? p.lse[sidx] * kFbLog2e : INFINITY;
-    const float dlt = (row < T) ? p.delta[sidx] : 0.f;
+    const float dlt_s = (row < T) ? p.delta[sidx] * p.scale : 0.f;
     bool ok = true;
-    for (int u = 0; u < n_sub && ok; ++u) {
-      const int j = u >> 1, sub = u & 1;
+    for (int u = wg; u < n_sub && ok; u += 2) {
+      const int j = u >> 1, sub = wg;
       if (!mbar_wait(&sdp_full[sub], (u >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int n0 = j * 128 + sub * 64;
       const bool need_mask = (j == mtile) || (j * 128 + 128 > vlen);
-      const int col = half * 32;                   // this warpgroup's 32 of the 64 key columns
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + sub * 64 + col, rs);
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + sub * 64 + col, rp);
-      tmem_ld_wait();
-      // dS of warpgroup 1 lands on columns warpgroup 0 reads: wait until both have read
-      tc_fence_before();
-      mbar_arrive(&rd_bar[sub]);
-      if (!mbar_wait(&rd_bar[sub], (u >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t pk[16];
+#pragma unroll 1
+      for (int hc = 0; hc < 2; ++hc) {
+        const int col = hc * 32;
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + sub * 64 + col, rs);
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + sub * 64 + col, rp);
+        tmem_ld_wait();
+        uint32_t pk[16];
+        if (need_mask) {
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float d0, d1;
-        {
-          float pe = exp2f(__uint_as_float(rs[e]) * sl2 - lse2);
-          const int key = n0 + col + e;
-          if (need_mask && (key > row || key >= vlen)) pe = 0.f;
-          d0 = pe * (__uint_as_float(rp[e]) - dlt) * p.scale;
+          for (int e = 0; e < 32; e += 2) {
+            float d[2];
+#pragma unroll
+            for (int w2 = 0; w2 < 2; ++w2) {
+              float pe = exp2f(fmaf(__uint_as_float(rs[e + w2]), sl2, -lse2));
+              const int key = n0 + col + e + w2;
+              if (key > row || key >= vlen) pe = 0.f;
+              d[w2] = pe * fmaf(__uint_as_float(rp[e + w2]), p.scale, -dlt_s);
+            }
+            const bf162 t = __floats2bfloat162_rn(d[0], d[1]);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -lse2));
+            const float d0 = p0 * fmaf(__uint_as_float(rp[e]), p.scale, -dlt_s);
+            const float d1 = p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -dlt_s);
+            const bf162 t = __floats2bfloat162_rn(d0, d1);
+            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+          }
         }
-        {
-          float pe = exp2f(__uint_as_float(rs[e + 1]) * sl2 - lse2);
-          const int key = n0 + col + e + 1;
-          if (need_mask && (key > row || key >= vlen)) pe = 0.f;
-          d1 = pe * (__uint_as_float(rp[e + 1]) - dlt) * p.scale;
-        }
-        const bf162 t = __floats2bfloat162_rn(d0, d1);
-        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+        tmem_st_32x32b_x16(tmem_base + lane_sel + kColS + sub * 64 + (col >> 1), pk);
       }
-      tmem_st_32x32b_x16(tmem_base + lane_sel + kColS + sub * 64 + (col >> 1), pk);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&ds_full[sub]);
@@ -259,12 +266,13 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 // =================================================================== dK, dV
 constexpr int FKV_BQ = 64;                       // query rows per iteration
 constexpr int FKV_QTILE = FKV_BQ * FB_D * 2;     // 16 KiB
+constexpr int FKV_ST = 4;                        // Q / dO / statistics ring depth
 struct FdkvSmem {
   static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;            // stage s: Q_i (16 KiB), dO_i (16 KiB)
-  static constexpr int kStats = kQ + 2 * 2 * FKV_QTILE;                    // stage s: lse2[64], delta[64]
-  static constexpr int kBar = kStats + 2 * 2 * FKV_BQ * 4;
-  // kv_full, q_full[2], q_empty[2], st_full[2] (stats staged), sdp_full[2], pds_full[2], rd_bar[2], acc_done = 14
-  static constexpr int kTotal = kBar + 14 * 8 + 16 + 1024;
+  static constexpr int kStats = kQ + FKV_ST * 2 * FKV_QTILE;               // stage s: lse2[64], delta * scale [64]
+  static constexpr int kBar = kStats + FKV_ST * 2 * FKV_BQ * 4;
+  // kv_full, q_full[4], q_empty[4], st_full[4] (stats staged), sdp_full[2], pds_full[2], acc_done = 18
+  static constexpr int kTotal = kBar + 18 * 8 + 16 + 1024;
 };
 
 __global__ void __launch_bounds__(FBT_THREADS, 1)
@@ -275,14 +283,13 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fb_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FdkvSmem::kBar);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;
-  uint64_t* q_empty = bars + 3;
-  uint64_t* st_full = bars + 5;
-  uint64_t* sdp_full = bars + 7;     // [2]: S^T / dP^T of iteration it live in TMEM buffer it & 1
-  uint64_t* pds_full = bars + 9;     // [2]
-  uint64_t* rd_bar = bars + 11;      // [2]: both math warpgroups have read the scores (P^T / dS^T overwrite them)
-  uint64_t* acc_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* q_full = bars + 1;                    // [FKV_ST]
+  uint64_t* q_empty = q_full + FKV_ST;            // [FKV_ST]
+  uint64_t* st_full = q_empty + FKV_ST;           // [FKV_ST]
+  uint64_t* sdp_full = st_full + FKV_ST;          // [2]: S^T / dP^T of iteration it live in TMEM buffer it & 1
+  uint64_t* pds_full = sdp_full + 2;              // [2]: math warpgroup it & 1 has written P^T / dS^T
+  uint64_t* acc_done = pds_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -297,8 +304,8 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 256); mbar_init(&rd_bar[s], 256); }
+    for (int s = 0; s < FKV_ST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -309,8 +316,12 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // S^T and dP^T are double-buffered (64 columns each per buffer); P^T / dS^T (bf16, 32 packed
-  // columns) overwrite the first half of the S^T / dP^T buffer they were computed from.
+  // S^T and dP^T are double-buffered (64 columns each per buffer) and each buffer has its own math
+  // warpgroup: warpgroup w handles iterations it = w, w + 2, ... while the other warpgroup and the
+  // tensor core are on it + 1. A thread owns one key row (one TMEM lane) and walks the 64 query
+  // columns in two halves; P^T / dS^T (bf16, 32 packed columns) overwrite, lane by lane, columns
+  // of S^T / dP^T that the thread has already read. Q, dO and the row statistics of the next
+  // query tiles are prefetched through a 4-stage ring.
   constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
 
   if (warp == 0) {
@@ -321,10 +332,10 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       tma_load_4d(smem + FdkvSmem::kV, &tmV, kv_full, 0, kvh, n0, b);
       tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, n0, b);
       for (int it = 0; it < iters; ++it) {
-        const int s = it & 1;
+        const int s = it % FKV_ST;
         const int h = kvh * R + it / n_qt;
         const int m0 = (i_first + it % n_qt) * FKV_BQ;
-        if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        if (!mbar_wait(&q_empty[s], ((it / FKV_ST) & 1) ^ 1, abort_flag)) break;
         uint8_t* sQ = smem + FdkvSmem::kQ + s * 2 * FKV_QTILE;
         uint8_t* sDO = sQ + FKV_QTILE;
         mbar_expect_tx(&q_full[s], 2 * FKV_QTILE);
@@ -337,16 +348,16 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   } else if (warp == 3) {
     // stages the per-query statistics (lse in log2 units, delta) of each query tile in shared memory
     for (int it = 0; it < iters; ++it) {
-      const int s = it & 1;
+      const int s = it % FKV_ST;
       const int h = kvh * R + it / n_qt;
       const int m0 = (i_first + it % n_qt) * FKV_BQ;
-      if (!mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) break;
+      if (!mbar_wait(&q_empty[s], ((it / FKV_ST) & 1) ^ 1, abort_flag)) break;
       float* st = reinterpret_cast<float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
       for (int r = lane; r < FKV_BQ; r += 32) {
         const int row = m0 + r;
         const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
         st[r] = (row < T) ? p.lse[idx] * kFbLog2e : INFINITY;     // +inf => P = 0 for rows past T
-        st[FKV_BQ + r] = (row < T) ? p.delta[idx] : 0.f;
+        st[FKV_BQ + r] = (row < T) ? p.delta[idx] * p.scale : 0.f;
       }
       mbar_arrive(&st_full[s]);
     }
@@ -357,7 +368,7 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const uint32_t aK = smem_u32(smem + FdkvSmem::kK), aV = smem_u32(smem + FdkvSmem::kV);
       auto issue_scores = [&](int it) {
         const int s = it & 1;
-        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + s * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
+        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (it % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;     // 128-row tiles
@@ -384,13 +395,13 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (it + 1 < iters) {
           // scores of the next query tile go to the other TMEM buffer while the math warps work on
           // this one (its previous contents were consumed by the gradient MMAs issued earlier)
-          if (!mbar_wait(&q_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&q_full[(it + 1) % FKV_ST], ((it + 1) / FKV_ST) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           issue_scores(it + 1);
         }
         if (!mbar_wait(&pds_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + s * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
+        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (it % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
         // B = dO_i / Q_i read MN-major: 64 query rows (k), 128 d (n); 64-d chunks are 8 KiB apart
 #pragma unroll
         for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
@@ -402,54 +413,59 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDPT + s * 64 + kk * 8,
                        umma_smem_desc(aQ + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
         }
-        umma_commit(&q_empty[s]);
+        umma_commit(&q_empty[it % FKV_ST]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else if (warp >= 4) {
     const int q = warp & 3;
-    const int half = (warp - 4) >> 2;         // which 32 query columns of each 64-wide tile
+    const int wg = (warp - 4) >> 2;           // math warpgroup = score buffer it serves
+    const int half = wg;                      // dK / dV columns this warpgroup stores at the end
     const int key = n0 + q * 32 + lane;
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
     const float sl2 = p.scale * kFbLog2e;
+    const bool key_dead = key >= vlen;
     bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
-      const int s = it & 1;
+    for (int it = wg; it < iters && ok; it += 2) {
+      const int s = wg, s4 = it % FKV_ST;
       const int m0 = (i_first + it % n_qt) * FKV_BQ;
-      if (!mbar_wait(&st_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&st_full[s4], (it / FKV_ST) & 1, abort_flag)) { ok = false; break; }
       if (!mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
-      const int col = half * 32;
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + s * 64 + col, rs);
-      tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + s * 64 + col, rp);
-      tmem_ld_wait();
-      // P^T / dS^T of warpgroup 1 land on columns warpgroup 0 reads: wait until both have read
-      tc_fence_before();
-      mbar_arrive(&rd_bar[s]);
-      if (!mbar_wait(&rd_bar[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t pk[16], dk_[16];
-      const bool key_dead = key >= vlen;
+      const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s4 * 2 * FKV_BQ * 4);
+      const bool need_mask = (m0 < n0 + 128) || (n0 + 128 > vlen);     // the diagonal or the padded tail
+#pragma unroll 1
+      for (int hc = 0; hc < 2; ++hc) {
+        const int col = hc * 32;
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + s * 64 + col, rs);
+        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + s * 64 + col, rp);
+        tmem_ld_wait();
+        uint32_t pk[16], dk_[16];
 #pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        float pv[2], dv[2];
+        for (int e = 0; e < 32; e += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(st + col + e);
+          const float4 d4 = *reinterpret_cast<const float4*>(st + FKV_BQ + col + e);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int qc = col + e + u;
-          float pe = exp2f(__uint_as_float(rs[e + u]) * sl2 - st[qc]);
-          if (key_dead || key > m0 + qc) pe = 0.f;
-          pv[u] = pe;
-          dv[u] = pe * (__uint_as_float(rp[e + u]) - st[FKV_BQ + qc]) * p.scale;
+          for (int w2 = 0; w2 < 4; ++w2) {
+            float pe = exp2f(fmaf(__uint_as_float(rs[e + w2]), sl2, -lv[w2]));
+            if (need_mask && (key_dead || key > m0 + col + e + w2)) pe = 0.f;
+            pv[w2] = pe;
+            dv[w2] = pe * fmaf(__uint_as_float(rp[e + w2]), p.scale, -dl[w2]);
+          }
+#pragma unroll
+          for (int w2 = 0; w2 < 4; w2 += 2) {
+            const bf162 t0 = __floats2bfloat162_rn(pv[w2], pv[w2 + 1]);
+            const bf162 t1 = __floats2bfloat162_rn(dv[w2], dv[w2 + 1]);
+            pk[(e + w2) >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
+            dk_[(e + w2) >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
+          }
         }
-        const bf162 t0 = __floats2bfloat162_rn(pv[0], pv[1]);
-        const bf162 t1 = __floats2bfloat162_rn(dv[0], dv[1]);
-        pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
-        dk_[e >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
+        tmem_st_32x32b_x16(tmem_base + lane_sel + kColST + s * 64 + (col >> 1), pk);
+        tmem_st_32x32b_x16(tmem_base + lane_sel + kColDPT + s * 64 + (col >> 1), dk_);
       }
-      tmem_st_32x32b_x16(tmem_base + lane_sel + kColST + s * 64 + (col >> 1), pk);
-      tmem_st_32x32b_x16(tmem_base + lane_sel + kColDPT + s * 64 + (col >> 1), dk_);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pds_full[s]);

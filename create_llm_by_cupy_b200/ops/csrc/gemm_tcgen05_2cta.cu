@@ -113,10 +113,29 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
-  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+// Write one word into the peer CTA's shared memory and count its 4 bytes on the peer's mbarrier;
+// the word is visible to whoever sees that barrier phase complete. Nothing here waits.
+__device__ __forceinline__ void st_async_u32(uint32_t cluster_addr, uint32_t v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];"
+               ::"r"(cluster_addr), "r"(v), "r"(cluster_bar)
+               : "memory");
 }
-__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx_cluster_relaxed(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;"
+               ::"r"(cluster_bar), "r"(bytes)
+               : "memory");
+}
+// "This slot has been read": a relaxed arrive, issued only once `value` (what was read from the
+// slot) has reached its register. A release here would make the caller wait for everything it
+// has in flight, which for the MMA thread is the whole queue of tensor-core work.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed_after(uint32_t cluster_addr, int value) {
+  asm volatile(
+      "{\n\t.reg .b32 dep;\n\t"
+      "mov.b32 dep, %1;\n\t"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];\n\t}"
+      ::"r"(cluster_addr), "r"(value)
+      : "memory");
+}
 
 // Consumer side of the tile-index ring (one instance per consuming thread or warp).
 struct TileRingReader {
@@ -125,12 +144,14 @@ struct TileRingReader {
   // Returns the next tile index, or -1 when the wait was abandoned. `arrive` is true for the one
   // lane that reports the slot as read.
   __device__ __forceinline__ int next(uint64_t* sched_full, uint64_t* sched_empty, volatile int* ring,
-                                      volatile int* abort_flag, bool whole_warp, bool arrive) {
+                                      volatile int* abort_flag, bool whole_warp, bool arrive, bool remote_writer) {
+    // In the leader the index is an ordinary shared-memory store before an arrive; in the follower
+    // it arrives as an asynchronous store counted on the barrier. Either way a plain wait sees it.
+    (void)remote_writer;
     if (!mbar_wait(&sched_full[slot], phase, abort_flag)) return -1;
-    fence_acq_rel_cluster();                 // the index was written by a thread of the leader CTA
     const int t = ring[slot];
     if (whole_warp) __syncwarp();
-    if (arrive) mbar_arrive_cluster(mapa_u32(smem_u32(&sched_empty[slot]), 0));
+    if (arrive) mbar_arrive_cluster_relaxed_after(mapa_u32(smem_u32(&sched_empty[slot]), 0), t);
     if (++slot == G2_SCHED) { slot = 0; phase ^= 1; }
     return t;
   }
@@ -171,6 +192,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int num_n = (p.N + G2_BN - 1) / G2_BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const bool dyn = p.sched != nullptr;      // null: tile t + k * num_pairs goes to pair t (fixed assignment)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G2_STAGES; ++s) {
@@ -210,9 +232,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       auto publish = [&](int tile) -> bool {
         if (!mbar_wait(&sched_empty[wslot], wphase ^ 1, abort_flag)) return false;
         tile_ring[wslot] = tile;
-        st_cluster_u32(mapa_u32(smem_u32(const_cast<int*>(&tile_ring[wslot])), 1), uint32_t(tile));
-        mbar_arrive_cluster(mapa_u32(smem_u32(&sched_full[wslot]), 0));
-        mbar_arrive_cluster(mapa_u32(smem_u32(&sched_full[wslot]), 1));
+        mbar_arrive(&sched_full[wslot]);                                  // this CTA's readers
+        const uint32_t peer_bar = mapa_u32(smem_u32(&sched_full[wslot]), 1);
+        mbar_expect_tx_cluster_relaxed(peer_bar, 4);                      // the follower's readers
+        st_async_u32(mapa_u32(smem_u32(const_cast<int*>(&tile_ring[wslot])), 1), uint32_t(tile), peer_bar);
         if (++wslot == G2_SCHED) { wslot = 0; wphase ^= 1; }
         return true;
       };
@@ -220,7 +243,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       const int publish_kb = num_kb > 8 ? 8 : num_kb - 1;
       while (ok && t < num_tiles) {
         // the draw is in flight while this tile's first loads are issued
-        if (rank == 0) t_next = num_pairs + atomicAdd(&p.sched[0], 1);
+        if (!dyn) t_next = t + num_pairs;
+        else if (rank == 0) t_next = num_pairs + atomicAdd(&p.sched[0], 1);
         int mb, nb;
         tile_coords2(t, num_m, num_n, mb, nb);
         const int m0 = mb * 2 * G2_BM + int(rank) * G2_BM;
@@ -245,17 +269,17 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             tma_load_2d_pair(sB, &tmB, bar, k0, n0);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
-          if (rank == 0 && kb == publish_kb && !publish(t_next)) { ok = false; break; }
+          if (dyn && rank == 0 && kb == publish_kb && !publish(t_next)) { ok = false; break; }
         }
         if (!ok) break;
-        if (rank == 0) {
+        if (rank == 0 || !dyn) {
           t = t_next;
         } else {
-          t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true);
+          t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true, rank != 0);
           ok = t >= 0;
         }
       }
-      if (rank == 0 && ok) {
+      if (dyn && rank == 0 && ok) {
         // this pair has drawn its stop mark; the last pair to do so rewinds the counters
         __threadfence();
         if (atomicAdd(&p.sched[1], 1) == num_pairs - 1) {
@@ -276,7 +300,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       bool ok = true;
       TileRingReader rd;
       for (int t = pair; ok && t >= 0 && t < num_tiles;
-           t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true)) {
+           t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, false, true, rank != 0) : t + num_pairs) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
@@ -315,7 +339,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     bool ok = true;
     TileRingReader rd;
     for (int t = pair; ok && t >= 0 && t < num_tiles;
-         t = rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0)) {
+         t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0) : t + num_pairs) {
       int mb, nb;
       tile_coords2(t, num_m, num_n, mb, nb);
       const int row = mb * 2 * G2_BM + int(rank) * G2_BM + q * 32 + lane;
@@ -400,6 +424,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   }
 }
 
+static int g_dynamic_tiles = 1;
+
 // Counter pair for one launch. Kernels of different streams may run at the same time, so launches
 // take the slots round-robin; a slot is back to zero when its kernel has finished.
 static int* next_sched_slot() {
@@ -429,8 +455,11 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2P
   int pairs = num_sms() / 2;
   if (num_tiles < pairs) pairs = num_tiles;
   Gemm2Params q = p;
-  q.sched = next_sched_slot();
-  if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  q.sched = nullptr;
+  if (g_dynamic_tiles && num_tiles > pairs) {
+    q.sched = next_sched_slot();
+    if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  }
   kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, q);
   return static_cast<int>(cudaGetLastError());
 }
@@ -438,6 +467,13 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2P
 }  // namespace b200
 
 using namespace b200;
+
+// 1: tiles beyond each pair's first are handed out from a counter; 0: fixed round-robin assignment.
+B200_API int b200_gemm_2cta_dynamic_tiles(int on) {
+  const int old = g_dynamic_tiles;
+  if (on >= 0) g_dynamic_tiles = on != 0;
+  return old;
+}
 
 // Same contract as b200_gemm_bf16 (TMA-legal operands only: 16-byte aligned bases and pitches).
 B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int lda,

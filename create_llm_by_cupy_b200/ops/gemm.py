@@ -18,6 +18,23 @@ import os as _os
 # "1cta": single-CTA 128x256 tiles; "2cta": CTA pairs (cta_group::2) on 256x256 tiles where the
 # problem is large enough, single-CTA otherwise.
 GEMM_IMPL = _os.environ.get("B200_GEMM_IMPL", "2cta")
+# Tile hand-out of the CTA-pair kernel: "1" = tiles beyond each pair's first come from a device
+# counter (pairs that start late draw fewer), "0" = fixed round-robin assignment.
+GEMM_DYNAMIC_TILES = int(_os.environ.get("B200_GEMM_DYNAMIC", "1"))
+_dynamic_applied = None
+
+
+def set_dynamic_tiles(on: bool) -> None:
+    global GEMM_DYNAMIC_TILES
+    GEMM_DYNAMIC_TILES = int(on)
+
+
+def _apply_dynamic():
+    global _dynamic_applied
+    if _dynamic_applied != GEMM_DYNAMIC_TILES:
+        native.lib().b200_gemm_2cta_dynamic_tiles(int(GEMM_DYNAMIC_TILES))
+        _dynamic_applied = GEMM_DYNAMIC_TILES
+
 
 def _rowmajor_2d(t: torch.Tensor) -> tuple[torch.Tensor, int]:
     """Return (tensor, pitch) for a 2-D view whose last dim is contiguous; copy if it is not."""
@@ -76,6 +93,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     impl = impl or GEMM_IMPL
     if (impl == "2cta" and not force_fallback and bn == 0 and max_ctas == 0 and M >= 256 and N >= 256
             and lda % 8 == 0 and ldb % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+        _apply_dynamic()
         rc = native.lib().b200_gemm_bf16_2cta(
             native.ptr(a), native.ptr(b), native.ptr(out), native.ptr(add),
             M, N, K, lda, ldb, ldd, ldc, int(trans_a), int(not trans_b), flags,
