@@ -43,12 +43,14 @@ constexpr int G2_STAGES = 6;
 constexpr int G2_A_BYTES = G2_BM * G2_BK * 2;          // 16 KiB
 constexpr int G2_B_BYTES = (G2_BN / 2) * G2_BK * 2;    // 16 KiB
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_BAR_OFF = G2_STAGES * G2_STAGE_BYTES;
 constexpr int G2_SCHED = 4;         // slots of the tile-index ring
-constexpr int G2_SMEM = G2_BAR_OFF + (2 * G2_STAGES + 4 + 2 * G2_SCHED) * 8 + 16 + G2_SCHED * 4 + 1024;
+constexpr int G2_STG_BYTES = 128 * 128;                 // epilogue staging tile: 128 rows x 128 bytes
+constexpr int G2_STG_OFF = G2_STAGES * G2_STAGE_BYTES;  // two staging tiles follow the operand ring
+constexpr int G2_BAR_OFF2 = G2_STG_OFF + 2 * G2_STG_BYTES;
+constexpr int G2_SMEM = G2_BAR_OFF2 + (2 * G2_STAGES + 4 + 2 * G2_SCHED + 2) * 8 + 16 + G2_SCHED * 4 + 1024;
 constexpr int G2_SCHED_SLOTS = 1024;   // {next tile, finished pairs} counter pairs, used round-robin by launches
 
-enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2 };
+enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4 };
 
 struct Gemm2Params {
   void* D;
@@ -157,6 +159,10 @@ struct TileRingReader {
   }
 };
 
+__device__ __forceinline__ void named_bar_sync_128(int id) {
+  asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+
 __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb) {
   constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
@@ -171,16 +177,18 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmC,
                      const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw2[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw2) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFF);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFF2);
   uint64_t* empty = full + G2_STAGES;
   uint64_t* tfull = empty + G2_STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* sched_full = tempty + 2;
   uint64_t* sched_empty = sched_full + G2_SCHED;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + G2_SCHED);
+  uint64_t* stage_ready = sched_empty + G2_SCHED;      // [2]: epilogue staging tile holds C (or is simply free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_ready + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* tile_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -207,6 +215,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       mbar_init(&sched_full[i], 1);
       mbar_init(&sched_empty[i], 10);
     }
+    mbar_init(&stage_ready[0], 1);
+    mbar_init(&stage_ready[1], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -338,6 +348,117 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                    (!add_c || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
     bool ok = true;
     TileRingReader rd;
+    if (p.flags & G2_TMA_OUT) {
+      // Output through shared memory and TMA. A tile leaves in groups of 128 bytes per row (64 bf16
+      // or 32 fp32 columns): every thread converts its accumulator row and writes it into a
+      // 128-row staging tile in the 128-byte swizzle, one thread stores the tile with
+      // cp.async.bulk.tensor (full 128-byte lines to L2, clipped at the matrix edge). With `add`
+      // the same staging tile is first filled with the C tile by a TMA load. Two staging tiles
+      // alternate, so the store of one group overlaps the conversion of the next.
+      const int gcols = out_f32 ? 32 : 64;
+      const int ngroups = G2_BN / gcols;
+      uint8_t* stg = smem + G2_STG_OFF;
+      const int r = q * 32 + lane;
+      const uint32_t swz = uint32_t(r & 7);
+      const bool elected = (warp == 2 && lane == 0);
+      uint32_t gcount = 0;
+      auto arm = [&](uint32_t gc, int x, int y) {       // make staging tile gc & 1 ready for group gc
+        const uint32_t b = gc & 1;
+        if (add_c) {
+          mbar_expect_tx(&stage_ready[b], G2_STG_BYTES);
+          tma_load_2d(stg + b * G2_STG_BYTES, &tmC, &stage_ready[b], x, y);
+        } else {
+          mbar_arrive(&stage_ready[b]);
+        }
+      };
+      for (int t = pair; ok && t >= 0 && t < num_tiles;
+           t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0)
+                   : t + num_pairs) {
+        int mb, nb;
+        tile_coords2(t, num_m, num_n, mb, nb);
+        const int row0 = mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int n0 = nb * G2_BN;
+        if (elected) {
+          tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
+          arm(gcount, n0, row0);
+        }
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
+#pragma unroll 1
+        for (int g = 0; g < ngroups; ++g) {
+          const uint32_t b = gcount & 1;
+          if (!mbar_wait(&stage_ready[b], (gcount >> 1) & 1, abort_flag)) { ok = false; break; }
+          uint8_t* rowp = stg + b * G2_STG_BYTES + r * 128;
+          if (out_f32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(taddr + g * 32, v);
+            tmem_ld_wait();
+            if (g == ngroups - 1) {                      // accumulator fully read: hand it back to the MMA warp
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float4* dst = reinterpret_cast<float4*>(rowp + ((uint32_t(c) ^ swz) << 4));
+              float4 o = make_float4(__uint_as_float(v[4 * c]) * p.alpha, __uint_as_float(v[4 * c + 1]) * p.alpha,
+                                     __uint_as_float(v[4 * c + 2]) * p.alpha, __uint_as_float(v[4 * c + 3]) * p.alpha);
+              if (add_c) {
+                const float4 cc = *dst;
+                o.x += cc.x; o.y += cc.y; o.z += cc.z; o.w += cc.w;
+              }
+              *dst = o;
+            }
+          } else {
+            uint32_t v[64];
+            tmem_ld_32x32b_x32(taddr + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tmem_ld_32x32b_x32(taddr + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tmem_ld_wait();
+            if (g == ngroups - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint4* dst = reinterpret_cast<uint4*>(rowp + ((uint32_t(c) ^ swz) << 4));
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * c + e]) * p.alpha;
+              if (add_c) {
+                const uint4 cc = *dst;
+                const bf162* c2 = reinterpret_cast<const bf162*>(&cc);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 ff = __bfloat1622float2(c2[e]);
+                  f[2 * e] += ff.x;
+                  f[2 * e + 1] += ff.y;
+                }
+              }
+              uint4 o;
+              bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+              *dst = o;
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync_128(1);
+          if (elected) {
+            tma_store_2d(&tmD, stg + b * G2_STG_BYTES, n0 + g * gcols, row0);
+            tma_store_commit();
+            if (g + 1 < ngroups) {
+              tma_store_wait_read<1>();
+              arm(gcount + 1, n0 + (g + 1) * gcols, row0);
+            }
+          }
+          ++gcount;
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (elected) tma_store_wait<0>();
+    } else
     for (int t = pair; ok && t >= 0 && t < num_tiles;
          t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0) : t + num_pairs) {
       int mb, nb;
@@ -444,7 +565,8 @@ static int* next_sched_slot() {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2Params& p, cudaStream_t stream) {
+static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tD, const CUtensorMap* tC,
+                      const Gemm2Params& p, cudaStream_t stream) {
   auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
@@ -460,7 +582,7 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const Gemm2P
     q.sched = next_sched_slot();
     if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   }
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, q);
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tD, *tC, q);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -491,8 +613,24 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const vo
   const CUtensorMap* tB = b_mn_major ? get_tensor_map_2d(B, K, N, ldb, 64, 64, 2, SWIZZLE_128B_)
                                      : get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
   if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);
-  if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, p, stream);
-  if (a_mn_major) return launch_tc2<true, false>(tA, tB, p, stream);
-  if (b_mn_major) return launch_tc2<false, true>(tA, tB, p, stream);
-  return launch_tc2<false, false>(tA, tB, p, stream);
+  // Output (and C) through TMA when their bases and pitches are 16-byte aligned; otherwise the
+  // epilogue stores straight from registers.
+  const int eb = (flags & G2_OUT_F32) ? 4 : 2;
+  const bool add = (flags & G2_ADD_C) != 0;
+  const CUtensorMap* tD = tA;
+  const CUtensorMap* tC = tA;
+  if ((reinterpret_cast<uintptr_t>(D) & 15) == 0 && (size_t(ldd) * eb) % 16 == 0 &&
+      (!add || ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * eb) % 16 == 0))) {
+    const CUtensorMap* d = get_tensor_map_2d(D, M, N, ldd, 128, 128 / eb, eb, SWIZZLE_128B_);
+    const CUtensorMap* c = add ? get_tensor_map_2d(C, M, N, ldc, 128, 128 / eb, eb, SWIZZLE_128B_) : d;
+    if (d && c) {
+      tD = d;
+      tC = c;
+      p.flags |= G2_TMA_OUT;
+    }
+  }
+  if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, tD, tC, p, stream);
+  if (a_mn_major) return launch_tc2<true, false>(tA, tB, tD, tC, p, stream);
+  if (b_mn_major) return launch_tc2<false, true>(tA, tB, tD, tC, p, stream);
+  return launch_tc2<false, false>(tA, tB, tD, tC, p, stream);
 }

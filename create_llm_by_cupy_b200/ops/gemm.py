@@ -157,7 +157,7 @@ def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_sha
 # part-filled wave (e.g. 2048 x 3072 x 8192 is 1.3 waves of CTA pairs). The weight-gradient GEMMs
 # do not feed the activation-gradient chain, so issuing them on a side stream lets their first
 # CTAs start on SMs the other kernel has already left.
-WGRAD_OVERLAP = _os.environ.get("B200_WGRAD_OVERLAP", "0") != "0"
+WGRAD_OVERLAP = _os.environ.get("B200_WGRAD_OVERLAP", "1") != "0"
 _wgrad_streams: dict = {}
 
 
