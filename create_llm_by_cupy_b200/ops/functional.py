@@ -22,7 +22,9 @@ _f = ctypes.c_float
 import os as _os
 FLASH_TC = _os.environ.get("B200_FLASH_TC", "1") != "0"
 FLASH_TC_BWD = _os.environ.get("B200_FLASH_TC_BWD", "1") != "0"
-FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "2"))   # 2: two softmax warpgroups per tile
+# 1: one softmax warpgroup; 2: two warpgroups split the columns of a tile; 3: two query tiles per CTA,
+# one warpgroup each, output accumulated in TMEM
+FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 
 
 def _lib():
@@ -285,7 +287,7 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     if D == 128 and cos is None and FLASH_TC:
         # tcgen05 / TMEM kernel (inputs already rotated)
         arr = (ctypes.c_longlong * 12)(*strides)
-        fwd_fn = _lib().b200_flash_fwd_tc2 if FLASH_FWD_GEN == 2 else _lib().b200_flash_fwd_tc
+        fwd_fn = {3: _lib().b200_flash_fwd_tc3, 2: _lib().b200_flash_fwd_tc2}.get(FLASH_FWD_GEN, _lib().b200_flash_fwd_tc)
         native.check(fwd_fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
                                               native.ptr(lse), native.ptr(valid_len), arr, B, T, QH, KVH, D,
                                               _f(scale), native.stream_ptr()), "flash_fwd_tc")

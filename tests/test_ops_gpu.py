@@ -260,3 +260,41 @@ def test_flash_attention_tcgen05_multi_tile(T, vl):
     close(lse, lse_r, rtol=1e-2, atol=2e-2)
     for a, b in zip((dq, dk, dv), r):
         close(a, b, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("gen", [1, 2, 3])
+@pytest.mark.parametrize("T,vl", [(128, None), (384, None), (640, [640, 300]), (1000, None)])
+def test_flash_forward_generations(gen, T, vl, monkeypatch):
+    """All three tcgen05 forward kernels against the fp32 reference; T = 384 leaves the second
+    query tile of the last pair empty, T = 1000 ends inside a tile."""
+    B, QH, KVH, D = 2, 4, 2, 128
+    g = torch.Generator().manual_seed(T + gen)
+    q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    vlt = None if vl is None else torch.tensor(vl, dtype=torch.int32, device=DEV)
+    monkeypatch.setattr(F, "FLASH_FWD_GEN", gen)
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    o_r, lse_r = F.flash_attn_fwd(q.float().cpu(), k.float().cpu(), v.float().cpu(),
+                                  valid_len=None if vlt is None else vlt.cpu())
+    close(o, o_r)
+    close(lse, lse_r, rtol=1e-2, atol=2e-2)
+
+
+def test_flash_forward_moving_maximum():
+    """Keys whose norm grows along the sequence push the row maximum up tile after tile, which makes
+    the third-generation kernel rescale its TMEM output accumulator."""
+    B, T, QH, KVH, D = 1, 512, 2, 1, 128
+    g = torch.Generator().manual_seed(1)
+    q = (torch.randn(B, T, QH, D, generator=g) * 3).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g) * torch.linspace(0.2, 4.0, T)[None, :, None, None]
+    k = k.to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    o, lse = F.flash_attn_fwd(q, k, v)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    o_r, lse_r = F.flash_attn_fwd(q.float().cpu(), k.float().cpu(), v.float().cpu())
+    close(o, o_r, rtol=3e-2, atol=3e-2)
+    close(lse, lse_r, rtol=1e-3, atol=1e-2)
