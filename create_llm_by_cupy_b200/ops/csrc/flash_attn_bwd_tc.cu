@@ -65,6 +65,58 @@ __device__ __forceinline__ void store_row_from_tmem(uint32_t taddr, bf16* grow, 
   }
 }
 
+// dS for 16 key columns of one query row: P = exp2(s * sl2 - lse2), dS = P * (dP * scale - delta * scale),
+// packed to bf16 pairs. Masked keys (beyond the diagonal or the valid length) give 0.
+template <bool kMask>
+__device__ __forceinline__ void fb_ds_chunk(const uint32_t (&rs)[16], const uint32_t (&rp)[16], uint32_t (&pk)[8],
+                                            float sl2, float lse2, float scale, float dlt_s, int key_base, int row,
+                                            int vlen) {
+#pragma unroll
+  for (int e = 0; e < 16; e += 2) {
+    float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -lse2));
+    float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -lse2));
+    if (kMask) {
+      const int key = key_base + e;
+      if (key > row || key >= vlen) p0 = 0.f;
+      if (key + 1 > row || key + 1 >= vlen) p1 = 0.f;
+    }
+    const float d0 = p0 * fmaf(__uint_as_float(rp[e]), scale, -dlt_s);
+    const float d1 = p1 * fmaf(__uint_as_float(rp[e + 1]), scale, -dlt_s);
+    const bf162 t = __floats2bfloat162_rn(d0, d1);
+    pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+  }
+}
+
+// P^T and dS^T for 16 query columns of one key row; lse2 / dlt_s point at the 16 per-query values.
+template <bool kMask>
+__device__ __forceinline__ void fb_pds_chunk(const uint32_t (&rs)[16], const uint32_t (&rp)[16], uint32_t (&pk)[8],
+                                             uint32_t (&dk)[8], float sl2, float scale, const float* lse2,
+                                             const float* dlt_s, int q_base, int key, bool key_dead) {
+#pragma unroll
+  for (int e = 0; e < 16; e += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + e);
+    const float4 d4 = *reinterpret_cast<const float4*>(dlt_s + e);
+    const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+    float pv[4], dv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float pe = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -lv[u]));
+      if (kMask) {
+        if (key_dead || key > q_base + e + u) pe = 0.f;
+      }
+      pv[u] = pe;
+      dv[u] = pe * fmaf(__uint_as_float(rp[e + u]), scale, -dl[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      const bf162 t0 = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+      const bf162 t1 = __floats2bfloat162_rn(dv[u], dv[u + 1]);
+      pk[(e + u) >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
+      dk[(e + u) >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
+    }
+  }
+}
+
 // =================================================================== dQ
 struct FdqSmem {
   static constexpr int kQ = 0, kDO = FB_TILE, kKV = 2 * FB_TILE;           // KV stage s: K, V
@@ -204,41 +256,31 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_after();
       const int n0 = j * 128 + sub * 64;
       const bool need_mask = (j == mtile) || (j * 128 + 128 > vlen);
-#pragma unroll 1
-      for (int hc = 0; hc < 2; ++hc) {
-        const int col = hc * 32;
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColS + sub * 64 + col, rs);
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDP + sub * 64 + col, rp);
-        tmem_ld_wait();
-        uint32_t pk[16];
-        if (need_mask) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float d[2];
-#pragma unroll
-            for (int w2 = 0; w2 < 2; ++w2) {
-              float pe = exp2f(fmaf(__uint_as_float(rs[e + w2]), sl2, -lse2));
-              const int key = n0 + col + e + w2;
-              if (key > row || key >= vlen) pe = 0.f;
-              d[w2] = pe * fmaf(__uint_as_float(rp[e + w2]), p.scale, -dlt_s);
-            }
-            const bf162 t = __floats2bfloat162_rn(d[0], d[1]);
-            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(rs[e]), sl2, -lse2));
-            const float p1 = exp2f(fmaf(__uint_as_float(rs[e + 1]), sl2, -lse2));
-            const float d0 = p0 * fmaf(__uint_as_float(rp[e]), p.scale, -dlt_s);
-            const float d1 = p1 * fmaf(__uint_as_float(rp[e + 1]), p.scale, -dlt_s);
-            const bf162 t = __floats2bfloat162_rn(d0, d1);
-            pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
-          }
-        }
-        tmem_st_32x32b_x16(tmem_base + lane_sel + kColS + sub * 64 + (col >> 1), pk);
-      }
+      // 16 key columns at a time, the next 16 already in flight while these are converted
+      const uint32_t tS = tmem_base + lane_sel + kColS + sub * 64, tP = tmem_base + lane_sel + kColDP + sub * 64;
+      uint32_t sa[16], pa[16], sb[16], pb[16];
+      auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
+        uint32_t pk[8];
+        if (need_mask) fb_ds_chunk<true>(rs, rp, pk, sl2, lse2, p.scale, dlt_s, n0 + c * 16, row, vlen);
+        else fb_ds_chunk<false>(rs, rp, pk, sl2, lse2, p.scale, dlt_s, 0, 0, 0);
+        tmem_st_32x32b_x8(tS + c * 8, pk);
+      };
+      tmem_ld_32x32b_x16(tS, sa);
+      tmem_ld_32x32b_x16(tP, pa);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 16, sb);
+      tmem_ld_32x32b_x16(tP + 16, pb);
+      chunk(sa, pa, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 32, sa);
+      tmem_ld_32x32b_x16(tP + 32, pa);
+      chunk(sb, pb, 1);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 48, sb);
+      tmem_ld_32x32b_x16(tP + 48, pb);
+      chunk(sa, pa, 2);
+      tmem_ld_wait();
+      chunk(sb, pb, 3);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&ds_full[sub]);
@@ -434,38 +476,34 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       tc_fence_after();
       const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s4 * 2 * FKV_BQ * 4);
       const bool need_mask = (m0 < n0 + 128) || (n0 + 128 > vlen);     // the diagonal or the padded tail
-#pragma unroll 1
-      for (int hc = 0; hc < 2; ++hc) {
-        const int col = hc * 32;
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColST + s * 64 + col, rs);
-        tmem_ld_32x32b_x32(tmem_base + lane_sel + kColDPT + s * 64 + col, rp);
-        tmem_ld_wait();
-        uint32_t pk[16], dk_[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(st + col + e);
-          const float4 d4 = *reinterpret_cast<const float4*>(st + FKV_BQ + col + e);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], dv[4];
-#pragma unroll
-          for (int w2 = 0; w2 < 4; ++w2) {
-            float pe = exp2f(fmaf(__uint_as_float(rs[e + w2]), sl2, -lv[w2]));
-            if (need_mask && (key_dead || key > m0 + col + e + w2)) pe = 0.f;
-            pv[w2] = pe;
-            dv[w2] = pe * fmaf(__uint_as_float(rp[e + w2]), p.scale, -dl[w2]);
-          }
-#pragma unroll
-          for (int w2 = 0; w2 < 4; w2 += 2) {
-            const bf162 t0 = __floats2bfloat162_rn(pv[w2], pv[w2 + 1]);
-            const bf162 t1 = __floats2bfloat162_rn(dv[w2], dv[w2 + 1]);
-            pk[(e + w2) >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
-            dk_[(e + w2) >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
-          }
-        }
-        tmem_st_32x32b_x16(tmem_base + lane_sel + kColST + s * 64 + (col >> 1), pk);
-        tmem_st_32x32b_x16(tmem_base + lane_sel + kColDPT + s * 64 + (col >> 1), dk_);
-      }
+      // 16 query columns at a time, the next 16 already in flight while these are converted
+      const uint32_t tS = tmem_base + lane_sel + kColST + s * 64, tP = tmem_base + lane_sel + kColDPT + s * 64;
+      uint32_t sa[16], pa[16], sb[16], pb[16];
+      auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
+        uint32_t pk[8], dk_[8];
+        if (need_mask)
+          fb_pds_chunk<true>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, m0 + c * 16, key, key_dead);
+        else
+          fb_pds_chunk<false>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, 0, 0, false);
+        tmem_st_32x32b_x8(tS + c * 8, pk);
+        tmem_st_32x32b_x8(tP + c * 8, dk_);
+      };
+      tmem_ld_32x32b_x16(tS, sa);
+      tmem_ld_32x32b_x16(tP, pa);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 16, sb);
+      tmem_ld_32x32b_x16(tP + 16, pb);
+      chunk(sa, pa, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 32, sa);
+      tmem_ld_32x32b_x16(tP + 32, pa);
+      chunk(sb, pb, 1);
+      tmem_ld_wait();
+      tmem_ld_32x32b_x16(tS + 48, sb);
+      tmem_ld_32x32b_x16(tP + 48, pb);
+      chunk(sa, pa, 2);
+      tmem_ld_wait();
+      chunk(sb, pb, 3);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pds_full[s]);
