@@ -17,6 +17,8 @@
 // caller un-rotates). No atomics and no fp32 scratch; S and dP are recomputed by both kernels.
 //
 // Reference counterpart: cupy_flash_gqa_backward (model/flash_attention.py:109-176).
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -36,6 +38,7 @@ struct FlashBwdTcParams {
   long long dk_bs, dk_ts, dk_hs;
   long long dv_bs, dv_ts, dv_hs;
   int B, T, QH, KVH;
+  int n_tiles;           // 128-row tiles per sequence
   float scale;
   int* status;
 };
@@ -142,8 +145,10 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mtile = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid, longest rows first: all (head, batch) pairs of the last query tile, then the one before, ...
+  const int nhb = p.QH * p.B;
+  const int mtile = p.n_tiles - 1 - int(blockIdx.x) / nhb;
+  const int h = (int(blockIdx.x) % nhb) % p.QH, b = (int(blockIdx.x) % nhb) / p.QH;
   const int kvh = h / (p.QH / p.KVH);
   const int m0 = mtile * 128;
   const int T = p.T;
@@ -335,7 +340,10 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ntile = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // 1-D grid, longest columns first: key tile 0 sees every query tile, the last key tile only two
+  const int nhb = p.KVH * p.B;
+  const int ntile = int(blockIdx.x) / nhb;
+  const int kvh = (int(blockIdx.x) % nhb) % p.KVH, b = (int(blockIdx.x) % nhb) / p.KVH;
   const int n0 = ntile * 128;
   const int T = p.T;
   const int R = p.QH / p.KVH;
@@ -540,6 +548,26 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
 }
 
+// One helper stream (and the two events that tie it to the caller's stream) per device.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+static SideStream* side_stream() {
+  static std::mutex mu;
+  static SideStream per_dev[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  SideStream& s = per_dev[dev];
+  if (s.stream == nullptr) {
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  }
+  return &s;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -578,8 +606,24 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
     configured = true;
   }
   const int nt = (T + 127) / 128;
-  flash_bwd_dkv_tc_kernel<<<dim3(nt, KVH, B), FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
+  p.n_tiles = nt;
+  // The two kernels are independent (both only read delta). dK/dV has few, long CTAs and, when they
+  // number only a few per SM, ends in a ragged tail; dQ has many short ones. Running dQ on a second
+  // stream then lets its CTAs take the SMs the dK/dV kernel leaves idle while its last CTAs finish.
+  // With many dK/dV CTAs per SM there is no tail worth filling and the kernels run back to back.
+  flash_bwd_dkv_tc_kernel<<<nt * KVH * B, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
   B200_CHECK(cudaGetLastError());
-  flash_bwd_dq_tc_kernel<<<dim3(nt, QH, B), FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
-  return static_cast<int>(cudaGetLastError());
+  if (nt * KVH * B >= 3 * num_sms()) {
+    flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
+    return static_cast<int>(cudaGetLastError());
+  }
+  SideStream* side = side_stream();
+  if (side == nullptr) return static_cast<int>(cudaErrorUnknown);
+  B200_CHECK(cudaEventRecord(side->fork, st));
+  B200_CHECK(cudaStreamWaitEvent(side->stream, side->fork, 0));
+  flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, side->stream>>>(*tq128, *tdo128, *tk, *tv, p);
+  B200_CHECK(cudaGetLastError());
+  B200_CHECK(cudaEventRecord(side->join, side->stream));
+  B200_CHECK(cudaStreamWaitEvent(st, side->join, 0));
+  return 0;
 }
