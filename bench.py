@@ -63,6 +63,7 @@ def main():
     ap.add_argument("--ag", default="pull", choices=["nccl", "pull", "gemm"],
                     help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -104,7 +105,8 @@ def main():
     if use_fused:
         try:
             from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
-            fused = FusedCollectives(comm, device, gather_mode=args.ag)
+            kw = dict(rs_blocks=args.comm_blocks, ag_blocks=args.comm_blocks) if args.comm_blocks > 0 else {}
+            fused = FusedCollectives(comm, device, gather_mode=args.ag, **kw)
         except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
             if args.fused == 1:
                 raise

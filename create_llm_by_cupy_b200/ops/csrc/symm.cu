@@ -108,6 +108,107 @@ __device__ __forceinline__ void adam_apply(float g, float& m, float& v, float& w
   w -= a.lr * (m * a.m_corr) / (sqrtf(v * a.v_corr) + a.eps);
 }
 
+// What happens to one reduced vector (8 gradients in fp32): AdamW, store or accumulate, plus the
+// statistics of the global-norm clip.
+__device__ __forceinline__ void rs_consume(const RsParams& p, int vr, long long i, float (&acc)[8], float& ss,
+                                           int& bad) {
+  if (p.mode == RS_ADAM) {
+    const RsAdam& a = p.adam[vr];
+    float4* m4 = reinterpret_cast<float4*>(a.m) + 2 * i;
+    float4* v4 = reinterpret_cast<float4*>(a.v) + 2 * i;
+    float4* w4 = reinterpret_cast<float4*>(a.master) + 2 * i;
+    float mm[8], vv[8], ww[8];
+    *reinterpret_cast<float4*>(mm) = m4[0]; *reinterpret_cast<float4*>(mm + 4) = m4[1];
+    *reinterpret_cast<float4*>(vv) = v4[0]; *reinterpret_cast<float4*>(vv + 4) = v4[1];
+    *reinterpret_cast<float4*>(ww) = w4[0]; *reinterpret_cast<float4*>(ww + 4) = w4[1];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (!isfinite(acc[e])) bad = 1;
+      ss += acc[e] * acc[e];
+      adam_apply(acc[e] * a.grad_scale, mm[e], vv[e], ww[e], a);
+    }
+    m4[0] = *reinterpret_cast<float4*>(mm); m4[1] = *reinterpret_cast<float4*>(mm + 4);
+    v4[0] = *reinterpret_cast<float4*>(vv); v4[1] = *reinterpret_cast<float4*>(vv + 4);
+    w4[0] = *reinterpret_cast<float4*>(ww); w4[1] = *reinterpret_cast<float4*>(ww + 4);
+    uint4 o;
+    bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(ww[2 * e], ww[2 * e + 1]);
+    reinterpret_cast<uint4*>(a.param)[i] = o;
+  } else if (p.dst_fp32) {
+    float4* d4 = reinterpret_cast<float4*>(p.dst[vr]) + 2 * i;
+    if (p.mode == RS_ACCUMULATE) {
+      const float4 o0 = d4[0], o1 = d4[1];
+      acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
+      acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
+    }
+    d4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    d4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (p.do_stats) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (!isfinite(acc[e])) bad = 1; else ss += acc[e] * acc[e];
+      }
+    }
+  } else {
+    uint4 o;
+    bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    reinterpret_cast<uint4*>(p.dst[vr])[i] = o;
+    if (p.do_stats) {
+      // statistics of what is stored (the bf16-rounded value), as the separate pass would see it
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(o2[e]);
+        if (!isfinite(f.x) || !isfinite(f.y)) bad = 1; else ss += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+}
+
+// The pull-and-sum loop. Every thread keeps W x U = 8 16-byte peer loads in flight (an NVLink round
+// trip is a few microseconds, so bandwidth is bought with outstanding loads, not with threads).
+template <int WT, int U>
+__device__ __forceinline__ void rs_loop(const RsParams& p, int vr, const uint4* const (&src)[SYMM_MAX_W], float& ss,
+                                        int& bad) {
+  constexpr int WM = WT > 0 ? WT : SYMM_MAX_W;
+  const int W = WT > 0 ? WT : p.W;
+  const long long nvec = p.n_slice / 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 raw[U][WM];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+#pragma unroll
+        for (int q = 0; q < WM; ++q)
+          if (q < W) raw[u][q] = src[q][i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < WM; ++q) {
+        if (q < W) {
+          const bf162* h = reinterpret_cast<const bf162*>(&raw[u][q]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+      }
+      rs_consume(p, vr, i, acc, ss, bad);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
   const int vr = blockIdx.y;
   const int rank = p.rank0 + vr;
@@ -123,80 +224,13 @@ __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
     src[q] = reinterpret_cast<const uint4*>(static_cast<const char*>(tab.base[q < W ? peer : rank]) + p.bucket_off) +
              size_t(rank) * (p.n_slice / 8);
   }
-  const long long nvec = p.n_slice / 8;
   float ss = 0.f;
   int bad = 0;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
-    uint4 raw[SYMM_MAX_W];
-#pragma unroll
-    for (int q = 0; q < SYMM_MAX_W; ++q)
-      if (q < W) raw[q] = src[q][i];
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int q = 0; q < SYMM_MAX_W; ++q) {
-      if (q < W) {
-        const bf162* h = reinterpret_cast<const bf162*>(&raw[q]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h[e]);
-          acc[2 * e] += f.x;
-          acc[2 * e + 1] += f.y;
-        }
-      }
-    }
-    if (p.mode == RS_ADAM) {
-      const RsAdam& a = p.adam[vr];
-      float4* m4 = reinterpret_cast<float4*>(a.m) + 2 * i;
-      float4* v4 = reinterpret_cast<float4*>(a.v) + 2 * i;
-      float4* w4 = reinterpret_cast<float4*>(a.master) + 2 * i;
-      float mm[8], vv[8], ww[8];
-      *reinterpret_cast<float4*>(mm) = m4[0]; *reinterpret_cast<float4*>(mm + 4) = m4[1];
-      *reinterpret_cast<float4*>(vv) = v4[0]; *reinterpret_cast<float4*>(vv + 4) = v4[1];
-      *reinterpret_cast<float4*>(ww) = w4[0]; *reinterpret_cast<float4*>(ww + 4) = w4[1];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (!isfinite(acc[e])) bad = 1;
-        ss += acc[e] * acc[e];
-        adam_apply(acc[e] * a.grad_scale, mm[e], vv[e], ww[e], a);
-      }
-      m4[0] = *reinterpret_cast<float4*>(mm); m4[1] = *reinterpret_cast<float4*>(mm + 4);
-      v4[0] = *reinterpret_cast<float4*>(vv); v4[1] = *reinterpret_cast<float4*>(vv + 4);
-      w4[0] = *reinterpret_cast<float4*>(ww); w4[1] = *reinterpret_cast<float4*>(ww + 4);
-      uint4 o;
-      bf162* o2 = reinterpret_cast<bf162*>(&o);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(ww[2 * e], ww[2 * e + 1]);
-      reinterpret_cast<uint4*>(a.param)[i] = o;
-    } else if (p.dst_fp32) {
-      float4* d4 = reinterpret_cast<float4*>(p.dst[vr]) + 2 * i;
-      if (p.mode == RS_ACCUMULATE) {
-        const float4 o0 = d4[0], o1 = d4[1];
-        acc[0] += o0.x; acc[1] += o0.y; acc[2] += o0.z; acc[3] += o0.w;
-        acc[4] += o1.x; acc[5] += o1.y; acc[6] += o1.z; acc[7] += o1.w;
-      }
-      d4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      d4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-      if (p.do_stats) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if (!isfinite(acc[e])) bad = 1; else ss += acc[e] * acc[e];
-        }
-      }
-    } else {
-      uint4 o;
-      bf162* o2 = reinterpret_cast<bf162*>(&o);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-      reinterpret_cast<uint4*>(p.dst[vr])[i] = o;
-      if (p.do_stats) {
-        // statistics of what is stored (the bf16-rounded value), as the separate pass would see it
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(o2[e]);
-          if (!isfinite(f.x) || !isfinite(f.y)) bad = 1; else ss += f.x * f.x + f.y * f.y;
-        }
-      }
-    }
+  switch (W) {
+    case 2: rs_loop<2, 4>(p, vr, src, ss, bad); break;
+    case 4: rs_loop<4, 2>(p, vr, src, ss, bad); break;
+    case 8: rs_loop<8, 1>(p, vr, src, ss, bad); break;
+    default: rs_loop<0, 1>(p, vr, src, ss, bad); break;
   }
   if (p.do_stats && p.stats[vr] != nullptr) {
 #pragma unroll

@@ -109,7 +109,7 @@ class FusedCollectives:
 
     gather = True
 
-    def __init__(self, comm, device, heap_bytes: int = 8 << 30, rs_blocks: int = 24, ag_blocks: int = 24,
+    def __init__(self, comm, device, heap_bytes: int = 8 << 30, rs_blocks: int = 64, ag_blocks: int = 64,
                  wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "pull", n_copy: int = 8):
         """``gather_mode`` selects how parameter units are gathered: ``"nccl"`` (ncclAllGather on the
         communication stream), ``"pull"`` (the P2P pull kernel on the communication stream) or
