@@ -63,11 +63,18 @@ def main():
     ap.add_argument("--ag", default="pull", choices=["nccl", "pull", "gemm"],
                     help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1 directly; the contract is
+    # ONE JSON line on stdout, so everything before the final print goes to stderr.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
 
@@ -116,7 +123,7 @@ def main():
     trainer = Trainer(md, rank=rank, world_size=world, comm=comm, device=device, zero_stage=c["zero"],
                       optimizer_device=c["opt"], accum_step=accum, lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1,
                       warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
-                      profile_comm=world > 1)
+                      profile_comm=world > 1, profile_phases=args.phases)
 
     # distinct synthetic batches per rank and per step (seed 0 stream, partitioned by rank)
     n_steps_total = args.warmup + args.steps
@@ -138,6 +145,7 @@ def main():
             run_step(first_index + w)
         barrier_sync()
         native.raise_on_status()
+        trainer.phase_times()                 # drop the warm-up steps' marks
         launches0 = native.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -157,10 +165,12 @@ def main():
     if sampler:
         sampler.start()
     trainer.manager.exposed_comm_ms()
+    trainer.phase_times()
     ms_dev, launches = timed(lambda i: trainer.train_step(dev_batches[i % n_steps_total]), 0)
     exposed = trainer.manager.exposed_comm_ms() / max(args.steps + 0, 1) if world > 1 else 0.0
     clocks = sampler.stop() if sampler else None
     last = dict(trainer.last)
+    phases = trainer.phase_times() if args.phases else None
 
     # ---- end to end through the public API: pinned host ids -> device, loss -> host -------------
     e2e = None
@@ -194,13 +204,16 @@ def main():
                                        else ("nccl" if world > 1 else "none")),
                        "l2": "not flushed: each step streams >10 GB of weights/activations, far above the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "exposed_comm_ms_per_step": exposed,
+            "exposed_comm_ms_per_step": exposed, "phases_ms": phases,
             "model_tflops_per_gpu": flops_tok * tokens / world / (ms_dev / 1e3) / 1e12,
             "mfu_of_measured_sustained": (flops_tok * tokens / world / (ms_dev / 1e3) / 1e12) /
                                          peaks.get("bf16_tflops_sustained", 1401.9),
             "last_loss": last.get("loss"), "last_grad_norm": last.get("grad_norm"),
         }
-        print(json.dumps(out))
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(out), flush=True)
+        os.dup2(2, 1)
     if world > 1:
         comm.barrier()
         shutdown_distributed()

@@ -41,8 +41,11 @@ class Trainer:
                  lr_max: float = 3e-4, lr_mini: float = 3e-5, weight_decay: float = 0.1, warm_up: int = 100,
                  total_steps: int = 1000, beta1: float = 0.9, beta2: float = 0.99, epsilon: float = 1e-6,
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
-                 profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False):
+                 profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False,
+                 profile_phases: bool = False):
         self.rank, self.world_size = rank, world_size
+        self.profile_phases = bool(profile_phases)
+        self._phase_marks = []
         self.comm = comm if comm is not None else SingleProcessComm()
         self.accum_step = int(accum_step)
         self.max_grads = float(max_grads)
@@ -74,9 +77,34 @@ class Trainer:
                                and optimizer_device != "cpu" and self.replica_optimizer is None and world_size > 1)
 
     # ------------------------------------------------------------------ one optimizer step
+    # ------------------------------------------------------------------ phase timing (optional)
+    def _mark(self, name: str):
+        """Record a CUDA event on the compute stream at a phase boundary (``profile_phases``)."""
+        if self.profile_phases and self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(self.device))
+            self._phase_marks.append((name, ev))
+
+    def phase_times(self, reset: bool = True) -> dict:
+        """Mean milliseconds per step between consecutive phase marks since the last call
+        (synchronises the device). Keys: forward, backward, grad_stats, optimizer, tail."""
+        if not self._phase_marks:
+            return {}
+        torch.cuda.synchronize(self.device)
+        tot, steps = {}, 0
+        for (n0, e0), (n1, e1) in zip(self._phase_marks[:-1], self._phase_marks[1:]):
+            if n1 == "start":
+                continue
+            tot[n1] = tot.get(n1, 0.0) + e0.elapsed_time(e1)
+            steps += n1 == "end"
+        if reset:
+            self._phase_marks = []
+        return {k: v / max(steps, 1) for k, v in tot.items()}
+
     def train_step(self, batches) -> dict:
         mgr, model = self.manager, self.model
         scale = float(self.scaler.Scale)
+        self._mark("start")
         mgr.zero_grad()
         if self.fused_adam:
             lr = self.optimizer._update_learning_rate()
@@ -86,9 +114,11 @@ class Trainer:
         for (x, t, x_pa) in batches:
             with nvtx_range("forward"):
                 loss = model.forward(x, t, x_pa, mgr)
+            self._mark("forward")
             with nvtx_range("backward"):
                 model.backward(scale, mgr)
             mgr.end_microbatch()
+            self._mark("backward")
             loss_acc = loss.detach().clone() if loss_acc is None else loss_acc + loss
         n_micro = len(batches)
         if getattr(self, "inject_nan_next", False):      # host-side fault injection (tests)
@@ -97,6 +127,7 @@ class Trainer:
             self.inject_nan_next = False
         with nvtx_range("optimizer"):
             stats = mgr.calculate_global_grad_stats(to_host=False)
+            self._mark("grad_stats")
             step_scale = 1.0 / (self.world_size * n_micro * scale)
             if self.replica_optimizer is not None:
                 rgrad = mgr.prepare_replicated_grads_for_sharded_optimizer()
@@ -118,6 +149,7 @@ class Trainer:
                                               max_grad_norm=self.max_grads)
                 mgr.allgather_replicated_params_from_optimizer_shards()
             mgr.after_optimizer_step()
+        self._mark("end")
         # one host read per step: loss, gradient statistics
         host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
         loss_val = host[0] / n_micro

@@ -80,18 +80,27 @@ class _PendingGather:
 
 
 class _Pool:
-    """Reusable flat buffers keyed by size; zero-filled once so alignment gaps stay zero."""
+    """Reusable flat buffers keyed by size; zero-filled once so alignment gaps stay zero.
 
-    def __init__(self, dtype, device, alloc=None):
+    ``rotate`` > 1 keeps that many buffers per size in rotation (first in, first out): a buffer
+    handed back while a collective is still reading it is then not the next one to be written, so
+    the producer of the next unit does not wait for that collective. The choice depends only on the
+    call sequence, never on timing, so every rank allocates the same buffers in the same order
+    (they live at equal offsets of the symmetric heap)."""
+
+    def __init__(self, dtype, device, alloc=None, rotate: int = 1):
         self.dtype, self.device = dtype, device
         self.free = collections.defaultdict(list)
         self.alloc = alloc
         self.total_bytes = 0
+        self.rotate = max(int(rotate), 1)
+        self.made = collections.defaultdict(int)
 
     def get(self, n: int) -> _Buf:
         lst = self.free[n]
-        if lst:
-            return lst.pop()
+        if lst and self.made[n] >= self.rotate:
+            return lst.pop(0) if self.rotate > 1 else lst.pop()
+        self.made[n] += 1
         t = self.alloc(n, self.dtype) if self.alloc is not None else torch.zeros(n, dtype=self.dtype, device=self.device)
         self.total_bytes += t.numel() * t.element_size()
         return _Buf(t)
@@ -155,7 +164,7 @@ class MemoryZeRO3Manager:
         alloc = fused.alloc if fused is not None else None
         self.gather_pool = _Pool(self.dtype, self.device, None)
         self._params_ready_event = None   # recorded after the optimizer step; gathers wait on it
-        self.grad_pool = _Pool(self.dtype, self.device, alloc)
+        self.grad_pool = _Pool(self.dtype, self.device, alloc, rotate=2 if world_size > 1 else 1)
         self.live = {}              # uid -> _Buf holding gathered parameters
         self.pending_gather = {}    # uid -> _Buf with an all-gather in flight
         self.deferred = {}          # uid -> _PendingGather (gather fused into the consuming GEMM)
