@@ -39,6 +39,7 @@ struct FlashBwdTcParams {
   long long dv_bs, dv_ts, dv_hs;
   int B, T, QH, KVH;
   int n_tiles;           // 128-row tiles per sequence
+  int bchunk;            // batch elements whose Q, dO, K, V stay in L2 together
   float scale;
   int* status;
 };
@@ -145,10 +146,17 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, longest rows first: all (head, batch) pairs of the last query tile, then the one before, ...
-  const int nhb = p.QH * p.B;
-  const int mtile = p.n_tiles - 1 - int(blockIdx.x) / nhb;
-  const int h = (int(blockIdx.x) % nhb) % p.QH, b = (int(blockIdx.x) % nhb) / p.QH;
+  // 1-D grid over chunks of p.bchunk batch elements (what the L2 holds of Q / dO / K / V); inside a
+  // chunk the longest rows come first: every (head, batch) of the last query tile, then the one before
+  int mtile, h, b;
+  {
+    const int per_chunk = p.n_tiles * p.QH * p.bchunk;
+    const int chunk = int(blockIdx.x) / per_chunk, r = int(blockIdx.x) - chunk * per_chunk;
+    const int hb = p.QH * min(p.bchunk, p.B - chunk * p.bchunk);
+    mtile = p.n_tiles - 1 - r / hb;
+    h = (r % hb) % p.QH;
+    b = chunk * p.bchunk + (r % hb) / p.QH;
+  }
   const int kvh = h / (p.QH / p.KVH);
   const int m0 = mtile * 128;
   const int T = p.T;
@@ -340,10 +348,17 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid, longest columns first: key tile 0 sees every query tile, the last key tile only two
-  const int nhb = p.KVH * p.B;
-  const int ntile = int(blockIdx.x) / nhb;
-  const int kvh = (int(blockIdx.x) % nhb) % p.KVH, b = (int(blockIdx.x) % nhb) / p.KVH;
+  // 1-D grid over chunks of p.bchunk batch elements; inside a chunk the longest columns come first
+  // (key tile 0 sees every query tile, the last key tile only two)
+  int ntile, kvh, b;
+  {
+    const int per_chunk = p.n_tiles * p.KVH * p.bchunk;
+    const int chunk = int(blockIdx.x) / per_chunk, r = int(blockIdx.x) - chunk * per_chunk;
+    const int hb = p.KVH * min(p.bchunk, p.B - chunk * p.bchunk);
+    ntile = r / hb;
+    kvh = (r % hb) % p.KVH;
+    b = chunk * p.bchunk + (r % hb) / p.KVH;
+  }
   const int n0 = ntile * 128;
   const int T = p.T;
   const int R = p.QH / p.KVH;
@@ -607,6 +622,12 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   }
   const int nt = (T + 127) / 128;
   p.n_tiles = nt;
+  {
+    // Q and dO of one batch element (bf16) plus its K and V; about two thirds of the L2 is budgeted
+    const double per_batch = 2.0 * T * D * (2.0 * QH + 2.0 * KVH);
+    int bc = int(80.0e6 / per_batch);
+    p.bchunk = bc < 1 ? 1 : (bc > B ? B : bc);
+  }
   // The two kernels are independent (both only read delta). dK/dV has few, long CTAs and, when they
   // number only a few per SM, ends in a ragged tail; dQ has many short ones. Running dQ on a second
   // stream then lets its CTAs take the SMs the dK/dV kernel leaves idle while its last CTAs finish.
