@@ -202,7 +202,8 @@ def main():
                        "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par,
                        "collectives": (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
                                        else ("nccl" if world > 1 else "none")),
-                       "l2": "not flushed: each step streams >10 GB of weights/activations, far above the 126 MB L2"},
+                       "l2": f"not flushed: a step streams more than {28e-9 * n_par / world + 2e-9 * n_par:.1f} GB of weights and "
+                             "optimizer state per GPU, far above the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "exposed_comm_ms_per_step": exposed, "phases_ms": phases,
             "model_tflops_per_gpu": flops_tok * tokens / world / (ms_dev / 1e3) / 1e12,

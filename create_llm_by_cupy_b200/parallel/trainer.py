@@ -59,6 +59,10 @@ class Trainer:
         opt_cls = ZeRO_Adam_Offload if optimizer_device == "cpu" else ZeRO_Adam_ShardedGPU
         okw = dict(lr_max=lr_max, lr_mini=lr_mini, total_steps=total_steps, warm_up=warm_up,
                    weight_decay=weight_decay, beta1=beta1, beta2=beta2, epsilon=epsilon, logger=logger)
+        if optimizer_device == "cpu":
+            # torchrun pins OMP_NUM_THREADS to 1; the host AdamW wants its share of the cores
+            import os
+            okw["threads"] = max(1, (os.cpu_count() or 1) // max(world_size, 1))
         self.optimizer = opt_cls(self.manager.get_param_shard_view(), **okw)
         self.replica_optimizer = None
         if self.manager.replica_param_f16 is not None:
