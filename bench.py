@@ -63,6 +63,8 @@ def main():
     ap.add_argument("--ag", default="pull", choices=["nccl", "pull", "gemm"],
                     help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-adam-overlap", action="store_true", help="AdamW as one kernel after the backward")
+    ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
@@ -123,7 +125,8 @@ def main():
     trainer = Trainer(md, rank=rank, world_size=world, comm=comm, device=device, zero_stage=c["zero"],
                       optimizer_device=c["opt"], accum_step=accum, lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1,
                       warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
-                      profile_comm=world > 1, profile_phases=args.phases)
+                      profile_comm=world > 1, profile_phases=args.phases, cuda_graph=args.graph,
+                      adam_overlap=not args.no_adam_overlap)
 
     # distinct synthetic batches per rank and per step (seed 0 stream, partitioned by rank)
     n_steps_total = args.warmup + args.steps
@@ -151,6 +154,7 @@ def main():
         e0.record()
         for k in range(args.steps):
             run_step(first_index + args.warmup + k)
+        trainer.join_optimizer()              # the last step's pipelined AdamW belongs to the timed region
         e1.record()
         barrier_sync()
         ms = torch.tensor([e0.elapsed_time(e1)], device=device)
@@ -199,7 +203,7 @@ def main():
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": c["name"], "global_batch": B * accum * world, "seq_len": T,
-                       "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par,
+                       "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par, "cuda_graph": bool(trainer.cuda_graph),
                        "collectives": (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
                                        else ("nccl" if world > 1 else "none")),
                        "l2": f"not flushed: a step streams more than {28e-9 * n_par / world + 2e-9 * n_par:.1f} GB of weights and "

@@ -48,7 +48,16 @@ __device__ __forceinline__ void adam_one(float g, float& m, float& v, float& w, 
 template <typename TG>
 __global__ void __launch_bounds__(256)
 adamw_kernel(const TG* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, float* __restrict__ master,
-             bf16* __restrict__ param, size_t n, AdamArgs a, const float* __restrict__ stats, int vec) {
+             bf16* __restrict__ param, size_t n, AdamArgs a, const float* __restrict__ stats, int vec,
+             const float* __restrict__ hyper) {
+  // hyper = {lr, m_corr, v_corr, grad_scale} in device memory: the step-dependent values of a launch
+  // that is replayed from a CUDA graph, where kernel arguments are frozen at capture time
+  if (hyper != nullptr) {
+    a.lr = hyper[0];
+    a.m_corr = hyper[1];
+    a.v_corr = hyper[2];
+    a.grad_scale = hyper[3];
+  }
   float gmul;
   if (!adam_prologue(a, stats, gmul)) return;
   const size_t n4 = vec ? (n >> 2) : 0;   // unaligned shards take the scalar loop for everything
@@ -253,10 +262,12 @@ static inline int grid_cap(size_t items, int block) {
 
 using namespace b200;
 
-B200_API int b200_adamw(const void* grad, int grad_fp32, void* m, void* v, void* master, void* param, long long n,
+static int adamw_launch(const void* grad, int grad_fp32, void* m, void* v, void* master, void* param, long long n,
                         float lr, float beta1, float beta2, float eps, float weight_decay, float m_corr, float v_corr,
-                        float grad_scale, float max_grad_norm, const void* stats, cudaStream_t st) {
+                        float grad_scale, float max_grad_norm, const void* stats, const void* hyper_dev,
+                        cudaStream_t st) {
   if (n <= 0) return 0;
+  const float* hyper = static_cast<const float*>(hyper_dev);
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale, max_grad_norm};
   const int grid = grid_cap(size_t(n) / 4 + 1, 256);
   const uintptr_t all = reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
@@ -267,13 +278,29 @@ B200_API int b200_adamw(const void* grad, int grad_fp32, void* m, void* v, void*
     adamw_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(grad), static_cast<float*>(m),
                                               static_cast<float*>(v), static_cast<float*>(master),
                                               static_cast<bf16*>(param), size_t(n), a,
-                                              static_cast<const float*>(stats), vec);
+                                              static_cast<const float*>(stats), vec, hyper);
   else
     adamw_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(grad), static_cast<float*>(m),
                                              static_cast<float*>(v), static_cast<float*>(master),
                                              static_cast<bf16*>(param), size_t(n), a,
-                                             static_cast<const float*>(stats), vec);
+                                             static_cast<const float*>(stats), vec, hyper);
   return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_adamw(const void* grad, int grad_fp32, void* m, void* v, void* master, void* param, long long n,
+                        float lr, float beta1, float beta2, float eps, float weight_decay, float m_corr, float v_corr,
+                        float grad_scale, float max_grad_norm, const void* stats, cudaStream_t st) {
+  return adamw_launch(grad, grad_fp32, m, v, master, param, n, lr, beta1, beta2, eps, weight_decay, m_corr, v_corr,
+                      grad_scale, max_grad_norm, stats, nullptr, st);
+}
+
+// As b200_adamw, with lr, m_corr, v_corr and grad_scale read from hyper[0..3] in device memory.
+B200_API int b200_adamw_dev(const void* grad, int grad_fp32, void* m, void* v, void* master, void* param, long long n,
+                            float beta1, float beta2, float eps, float weight_decay, float max_grad_norm,
+                            const void* stats, const void* hyper, cudaStream_t st) {
+  if (hyper == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  return adamw_launch(grad, grad_fp32, m, v, master, param, n, 0.f, beta1, beta2, eps, weight_decay, 1.f, 1.f, 1.f,
+                      max_grad_norm, stats, hyper, st);
 }
 
 // Adds into stats[0..1]; the caller zeroes stats once per step.

@@ -460,12 +460,14 @@ def ce_dlogits(logits, targets, rmax, rsum, loss_cnt, col0: int, pad_id: int, gs
 
 # --------------------------------------------------------------------------- optimizer side
 def adamw_step(grad, m, v, master, param, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
-               max_grad_norm=0.0, stats=None):
+               max_grad_norm=0.0, stats=None, hyper=None):
     """In-place AdamW on a flat shard: fp32 master/m/v, bf16 (or same-dtype) param written back.
 
     ``stats`` = device tensor [sum g^2 (unscaled), non-finite flag]: when given, the clip
     coefficient min(1, max_norm / (sqrt(stats[0]) * grad_scale + 1e-6)) is applied and the whole
-    update is skipped if stats[1] != 0, both decided on the device.
+    update is skipped if stats[1] != 0, both decided on the device. ``hyper`` = device tensor
+    [lr, m_corr, v_corr, grad_scale] that overrides the host values of the same names (for launches
+    replayed from a CUDA graph).
     """
     m_corr = 1.0 / (1.0 - beta1 ** step)
     v_corr = 1.0 / (1.0 - beta2 ** step)
@@ -488,6 +490,13 @@ def adamw_step(grad, m, v, master, param, *, lr, beta1, beta2, eps, weight_decay
         return
     assert param.dtype == torch.bfloat16 and grad.dtype in (torch.bfloat16, torch.float32)
     assert all(t.is_contiguous() for t in (grad, m, v, master, param))
+    if hyper is not None:
+        native.check(_lib().b200_adamw_dev(native.ptr(grad), int(grad.dtype == torch.float32), native.ptr(m),
+                                           native.ptr(v), native.ptr(master), native.ptr(param), ctypes.c_longlong(n),
+                                           _f(beta1), _f(beta2), _f(eps), _f(weight_decay), _f(max_grad_norm),
+                                           native.ptr(stats), native.ptr(hyper), native.stream_ptr()), "adamw_dev")
+        native.bump()
+        return
     native.check(_lib().b200_adamw(native.ptr(grad), int(grad.dtype == torch.float32), native.ptr(m), native.ptr(v),
                                    native.ptr(master), native.ptr(param), ctypes.c_longlong(n), _f(lr), _f(beta1),
                                    _f(beta2), _f(eps), _f(weight_decay), _f(m_corr), _f(v_corr), _f(grad_scale),

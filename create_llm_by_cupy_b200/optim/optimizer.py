@@ -83,6 +83,34 @@ class ZeRO_Adam_ShardedGPU(_AdamBase):
         self._log_lr(is_main_device)
         return out_shard
 
+    def hyper_values(self, scale: float):
+        """[lr, m_corr, v_corr, grad_scale] of the step that ``advance()`` has just opened."""
+        return [self.current_lr, 1.0 / (1.0 - self.beta1 ** self.t), 1.0 / (1.0 - self.beta2 ** self.t), float(scale)]
+
+    def advance(self) -> float:
+        """Open the next step on the host (step count, learning-rate schedule)."""
+        return self._update_learning_rate()
+
+    def update_ranges(self, grad_shard, scale: float, ranges, out_shard, stats=None, max_grad_norm: float = 0.0,
+                      after_each=None, is_main_device: bool = True, hyper=None):
+        """The same step as ``update`` issued as one kernel per ``(lo, hi)`` range of the shard, in the
+        given order; ``after_each(i)`` runs after range i has been launched (the caller records an
+        event there, so that whoever needs that part of the parameters waits for it alone). With
+        ``hyper`` (device tensor, see ``hyper_values``) the step-dependent scalars are read on the
+        device and the host schedule is NOT advanced here: the caller calls ``advance()`` once per
+        replay of the captured launches."""
+        lr = self.current_lr if hyper is not None else self._update_learning_rate()
+        for i, (lo, hi) in enumerate(ranges):
+            if hi > lo:
+                F.adamw_step(grad_shard[lo:hi], self.m[lo:hi], self.v[lo:hi], self.master_weight_shard[lo:hi],
+                             out_shard[lo:hi], lr=lr, beta1=self.beta1, beta2=self.beta2, eps=self.epsilon,
+                             weight_decay=self.weight_decay, step=max(self.t, 1), grad_scale=float(scale),
+                             max_grad_norm=float(max_grad_norm), stats=stats, hyper=hyper)
+            if after_each is not None:
+                after_each(i)
+        self._log_lr(is_main_device)
+        return out_shard
+
     def state_dict(self) -> dict:
         return {"m": self.m, "v": self.v, "w_fp32": self.master_weight_shard, "t": self.t}
 

@@ -42,7 +42,7 @@ class Trainer:
                  total_steps: int = 1000, beta1: float = 0.9, beta2: float = 0.99, epsilon: float = 1e-6,
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
                  profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False,
-                 profile_phases: bool = False):
+                 profile_phases: bool = False, adam_overlap: bool = True, cuda_graph: bool = False):
         self.rank, self.world_size = rank, world_size
         self.profile_phases = bool(profile_phases)
         self._phase_marks = []
@@ -73,6 +73,25 @@ class Trainer:
                                 gs.get("Scale_Up_Step"), enabled=bool(gs.get("enabled", False)))
         self.iteration = 0
         self.last = {}
+        # Pipelined optimizer: AdamW runs unit by unit on its own stream in the order the next forward
+        # needs the parameters, and the next step starts while it is still running (AdamW is bound by
+        # HBM, the forward by the tensor cores). Needs the GPU optimizer, one micro-batch per step
+        # (gradients are written in place, nothing is zeroed at the start of a step) and no replica
+        # optimizer.
+        self.adam_overlap = bool(adam_overlap and self.device.type == "cuda" and optimizer_device != "cpu"
+                                 and self.accum_step == 1 and self.replica_optimizer is None and not fused_adam)
+        self._adam_stream = torch.cuda.Stream(device=self.device) if self.adam_overlap else None
+        self._adam_done = None
+        # Whole-step CUDA graph (one GPU): forward, backward, gradient statistics and AdamW are captured
+        # once and replayed; what changes from step to step (token ids, learning rate, bias corrections,
+        # gradient scale) lives in device buffers the graph reads. Pays off when the step is bound by the
+        # host's launch rate (small models); the eager path with the pipelined optimizer is the default.
+        self.cuda_graph = bool(cuda_graph and self.device.type == "cuda" and world_size == 1
+                               and optimizer_device != "cpu" and self.accum_step == 1
+                               and self.replica_optimizer is None and not fused_adam
+                               and not self.scaler.enabled and not self.profile_phases and not profile_comm)
+        self._graph = None
+        self._graph_warm = 0
         # Fully fused gradient path (reduce-scatter + AdamW in one kernel per unit, during backward).
         # The update of a unit then happens before the global gradient norm exists, so it is only
         # available without clipping (max_grads <= 0), with a GPU optimizer, one micro-batch per
@@ -105,9 +124,78 @@ class Trainer:
             self._phase_marks = []
         return {k: v / max(steps, 1) for k, v in tot.items()}
 
+    def _graph_body(self, scale: float):
+        """The device work of one step on static buffers (captured, then replayed)."""
+        mgr = self.manager
+        mgr.zero_grad()
+        loss = self.model.forward(self._gx, self._gt, self._gpa, mgr)
+        self.model.backward(scale, mgr)
+        mgr.end_microbatch()
+        stats = mgr.calculate_global_grad_stats(to_host=False)
+        ranges = [mgr.layout.unit_shard_range(u) for u in mgr.forward_unit_order()]
+        self.optimizer.update_ranges(mgr.grad_shard_f16, 1.0, ranges, mgr.get_param_shard_view(), stats=stats,
+                                     max_grad_norm=self.max_grads, is_main_device=False, hyper=self._hyper)
+        mgr.after_optimizer_step()
+        return loss.detach().float().reshape(1).clone(), stats
+
+    def _graph_step(self, batches, scale: float):
+        """Returns (loss, stats, step_scale) device tensors of a replayed step, or None when this step
+        has to run eagerly (warm-up steps, a batch of another shape)."""
+        from ..ops import native
+        x, t, x_pa = batches[0]
+        if self._graph is None:
+            if self._graph_warm < 2:          # lazy one-time set-up (tensor maps, attributes, streams) happens eagerly
+                self._graph_warm += 1
+                return None
+            self.join_optimizer()
+            self.manager.unit_ready = {}
+            torch.cuda.synchronize(self.device)
+            self._gx, self._gt, self._gpa = x.clone(), t.clone(), x_pa.clone()
+            self._hyper = torch.zeros(4, dtype=torch.float32, device=self.device)
+            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            self._graph_scale = scale
+            graph = torch.cuda.CUDAGraph()
+            n0 = native.launch_count()
+            with torch.cuda.graph(graph):
+                self._g_loss, self._g_stats = self._graph_body(scale)
+            self._graph_launches = native.launch_count() - n0
+            self._graph = graph
+        if x.shape != self._gx.shape or t.shape != self._gt.shape or scale != self._graph_scale:
+            return None
+        self._gx.copy_(x, non_blocking=True)
+        self._gt.copy_(t, non_blocking=True)
+        self._gpa.copy_(x_pa, non_blocking=True)
+        self.optimizer.advance()
+        step_scale = 1.0 / (self.world_size * scale)
+        self._hyper_host.copy_(torch.tensor(self.optimizer.hyper_values(step_scale), dtype=torch.float32))
+        self._hyper.copy_(self._hyper_host, non_blocking=True)
+        self._graph.replay()
+        native.bump(self._graph_launches)
+        return self._g_loss, self._g_stats, step_scale
+
+    def _finish_step(self, loss_acc, stats, n_micro: int, step_scale: float, scale: float) -> dict:
+        """One host read per step (loss, gradient statistics) and the host-side bookkeeping."""
+        host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
+        loss_val = host[0] / n_micro
+        bad = host[2] != 0.0 or not math.isfinite(host[1])
+        if bad and not self.fused_adam:   # the kernels skipped the update; keep the schedule where it was
+            self.optimizer.t -= 1
+            if self.replica_optimizer is not None:
+                self.replica_optimizer.t -= 1
+        self.scaler.UpdateScale(bad)
+        self.iteration += 1
+        gnorm = math.sqrt(max(host[1], 0.0)) * step_scale if not bad else float("nan")
+        self.last = {"loss": loss_val, "grad_norm": gnorm, "skipped": bad, "GradScale": scale,
+                     "lr": self.optimizer.current_lr}
+        return self.last
+
     def train_step(self, batches) -> dict:
         mgr, model = self.manager, self.model
         scale = float(self.scaler.Scale)
+        if self.cuda_graph and len(batches) == 1:
+            out = self._graph_step(batches, scale)
+            if out is not None:
+                return self._finish_step(out[0], out[1], 1, out[2], scale)
         self._mark("start")
         mgr.zero_grad()
         if self.fused_adam:
@@ -119,6 +207,7 @@ class Trainer:
             with nvtx_range("forward"):
                 loss = model.forward(x, t, x_pa, mgr)
             self._mark("forward")
+            self.join_optimizer()          # the gradients are about to be overwritten
             with nvtx_range("backward"):
                 model.backward(scale, mgr)
             mgr.end_microbatch()
@@ -143,7 +232,30 @@ class Trainer:
                     self.comm.all_reduce(extra)
                 stats = stats + extra
                 stats[1] = (stats[1] != 0).float()
-            if not self.fused_adam:
+            pipelined = False
+            if self.adam_overlap and mgr.direct_grad:
+                pipelined = True
+                order = mgr.forward_unit_order()
+                ranges = [mgr.layout.unit_shard_range(u) for u in order]
+                cur = torch.cuda.current_stream(self.device)
+                stats_in = stats.clone()           # the manager reuses its statistics buffer next step
+                self._adam_stream.wait_stream(cur)
+
+                def unit_done(i):
+                    if mgr.fused is not None and self.world_size > 1:
+                        mgr.fused.barrier(self._adam_stream)      # peers pull this slice straight from the shard
+                    ev = torch.cuda.Event()
+                    ev.record(self._adam_stream)
+                    mgr.unit_ready[order[i]] = ev
+
+                with torch.cuda.stream(self._adam_stream):
+                    self.optimizer.update_ranges(mgr.grad_shard_f16, step_scale, ranges, mgr.get_param_shard_view(),
+                                                 stats=stats_in, max_grad_norm=self.max_grads, after_each=unit_done,
+                                                 is_main_device=self.rank == 0)
+                    self._adam_done = torch.cuda.Event()
+                    self._adam_done.record(self._adam_stream)
+                stats_in.record_stream(self._adam_stream)
+            elif not self.fused_adam:
                 self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
                                       out_shard=mgr.get_param_shard_view(), stats=stats,
                                       max_grad_norm=self.max_grads)
@@ -152,22 +264,16 @@ class Trainer:
                                               out_shard=mgr.get_replica_optimizer_shard_view(), stats=stats,
                                               max_grad_norm=self.max_grads)
                 mgr.allgather_replicated_params_from_optimizer_shards()
-            mgr.after_optimizer_step()
+            mgr.after_optimizer_step(pipelined=pipelined)
         self._mark("end")
-        # one host read per step: loss, gradient statistics
-        host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
-        loss_val = host[0] / n_micro
-        bad = host[2] != 0.0 or not math.isfinite(host[1])
-        if bad and not self.fused_adam:   # the kernels skipped the update; keep the schedule where it was
-            self.optimizer.t -= 1
-            if self.replica_optimizer is not None:
-                self.replica_optimizer.t -= 1
-        self.scaler.UpdateScale(bad)
-        self.iteration += 1
-        gnorm = math.sqrt(max(host[1], 0.0)) * step_scale if not bad else float("nan")
-        self.last = {"loss": loss_val, "grad_norm": gnorm, "skipped": bad, "GradScale": scale,
-                     "lr": self.optimizer.current_lr}
-        return self.last
+        return self._finish_step(loss_acc, stats, n_micro, step_scale, scale)
+
+    def join_optimizer(self):
+        """Make the current stream wait for a pipelined optimizer step that may still be running.
+        Called before anything reads optimizer state or overwrites the gradients."""
+        if self._adam_done is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._adam_done)
+            self._adam_done = None
 
     @torch.no_grad()
     def validate(self, batches) -> float:
@@ -183,6 +289,7 @@ class Trainer:
 
     def generate(self, prompt, **kw):
         """Generation on a sharded model: gather everything, decode, release."""
+        self.join_optimizer()
         self.manager.materialize_all()
         try:
             return self.model.generate(prompt, **kw)
@@ -193,12 +300,14 @@ class Trainer:
     def save(self, directory: str, extra: dict | None = None):
         state = {"iteration": self.iteration, "scaler": self.scaler.state_dict(),
                  "torch_rng": torch.get_rng_state(), "numpy_rng": np.random.get_state(), "extra": extra or {}}
+        self.join_optimizer()
         self.manager.synchronize()
         ckpt.save_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer, state)
         if self.world_size > 1:
             self.comm.barrier()
 
     def load(self, directory: str) -> dict | None:
+        self.join_optimizer()
         st = ckpt.load_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer)
         if st is not None:
             self.iteration = int(st.get("iteration", 0))

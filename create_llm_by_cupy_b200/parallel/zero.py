@@ -164,6 +164,7 @@ class MemoryZeRO3Manager:
         alloc = fused.alloc if fused is not None else None
         self.gather_pool = _Pool(self.dtype, self.device, None)
         self._params_ready_event = None   # recorded after the optimizer step; gathers wait on it
+        self.unit_ready = {}              # uid -> event: this unit's shard slice has been updated (pipelined optimizer)
         self.grad_pool = _Pool(self.dtype, self.device, alloc, rotate=2 if world_size > 1 else 1)
         self.live = {}              # uid -> _Buf holding gathered parameters
         self.pending_gather = {}    # uid -> _Buf with an all-gather in flight
@@ -291,6 +292,7 @@ class MemoryZeRO3Manager:
         if self.world_size == 1:
             b = _Buf(self.param_shard_f16[lo:hi])
             b.uid = uid
+            b.ready_event = self.unit_ready.get(uid)     # set while the optimizer of the last step is still running
             self.pending_gather[uid] = b
             return
         b = self.gather_pool.get(unit.padded)
@@ -298,14 +300,14 @@ class MemoryZeRO3Manager:
         if self._fuse_gather_into_gemm(uid):
             # nothing to launch now: the unit is pulled by the first GEMM that consumes it
             self._wait(self.compute_stream, b.free_event)
-            self._wait(self.compute_stream, self._params_ready_event)
+            self._wait(self.compute_stream, self.unit_ready.get(uid, self._params_ready_event))
             b.ready_event = None
             self.pending_gather[uid] = b
             self.deferred[uid] = _PendingGather(self, uid, b)
             return
         with self._comm_ctx():
             self._wait(self.comm_stream, b.free_event)
-            self._wait(self.comm_stream, self._params_ready_event)
+            self._wait(self.comm_stream, self.unit_ready.get(uid, self._params_ready_event))
             if self.fused is not None and self.fused.gather:
                 self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.comm_stream)
             else:
@@ -706,10 +708,29 @@ class MemoryZeRO3Manager:
             self.comm.all_reduce(st)
         return float(st[0]) ** 0.5
 
-    def after_optimizer_step(self):
+    def forward_unit_order(self):
+        """Unit ids in the order the forward pass first needs them (embedding, blocks, final norm,
+        head): the order in which a pipelined optimizer should finish them."""
+        def key(uid):
+            name = self.unit_names[uid]
+            if name == "embedding":
+                return (0, 0)
+            if name.startswith("block"):
+                digits = "".join(ch for ch in name if ch.isdigit())
+                return (1, int(digits) if digits else 0)
+            if name.startswith("final_norm"):
+                return (2, 0)
+            return (3, uid)
+        return sorted((u for u in range(len(self.layout.units)) if not self.layout.units[u].empty), key=key)
+
+    def after_optimizer_step(self, pipelined: bool = False):
         """Order the next gathers after the parameter update: locally with an event the comm stream
         waits on, and across GPUs (fused mode, where peers read this shard directly) with a
-        device-side barrier."""
+        device-side barrier. ``pipelined``: the optimizer has recorded one event per unit in
+        ``unit_ready`` (and issued its own barriers), so there is nothing global to wait for."""
+        if pipelined:
+            return
+        self.unit_ready = {}
         if not self.cuda or self.world_size == 1:
             return
         if self.fused is not None:
