@@ -15,8 +15,10 @@ calls so that nothing is served from L2):
   rs_adam         the same kernel in its AdamW mode (reduced gradient never stored) against
                   ncclReduceScatter + statistics + AdamW kernels;
   all_gather      pull kernel against ncclAllGather;
-  ag_gemm         K|Q|V projection of 8192 tokens with the gather of the unit done inside the GEMM
-                  against ncclAllGather followed by the GEMM.
+  ag_gemm         K|Q|V projection of 8192 tokens with the gather done inside the GEMM - the whole unit,
+                  or (the form the training step uses) only the chunks that hold K|Q|V while the
+                  stand-alone kernel pulls the rest of the unit on another stream - against
+                  ncclAllGather followed by the GEMM.
 
 Every rank receives (W - 1) / W of the unit over NVLink in each of these, so the bound is that many
 bytes over the measured peer-copy bandwidth (770 GB/s per direction); ``of_link`` is achieved / bound.
@@ -33,7 +35,7 @@ import torch
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 from create_llm_by_cupy_b200.ops import functional as F  # noqa: E402
 from create_llm_by_cupy_b200.ops import native  # noqa: E402
-from create_llm_by_cupy_b200.ops.gemm import gemm, gemm_allgather  # noqa: E402
+from create_llm_by_cupy_b200.ops.gemm import ag_region, gemm, gemm_allgather  # noqa: E402
 
 LINK_GBS = 770.0
 H, NKQV, I, M = 2048, 3072, 5504, 8192
@@ -88,6 +90,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--virtual", type=int, default=0)
+    ap.add_argument("--blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
     if args.virtual:
         return run_virtual(args.virtual)
@@ -97,7 +100,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     comm = init_distributed(rank, world, backend="nccl", device_id=local, master_port=int(os.environ["MASTER_PORT"]))
-    fc = FusedCollectives(comm, dev, heap_bytes=2 << 30)
+    kw = dict(rs_blocks=args.blocks, ag_blocks=args.blocks) if args.blocks > 0 else {}
+    fc = FusedCollectives(comm, dev, heap_bytes=2 << 30, **kw)
     total = sum(SIZES)
     pad = (total + world * 128 - 1) // (world * 128) * (world * 128)
     n = pad // world
@@ -173,26 +177,51 @@ def main():
         gemm_allgather(x, unit, 0, (H, NKQV), trans_b=False, peer_slices=peers, seg=seg, epoch=ep[0], n_copy=fc.n_copy,
                        out=out)
 
+    # the split form used by the training step: the GEMM pulls only the chunks of its own weight, the rest
+    # of the unit is pulled by the stand-alone kernel on another stream at the same time
+    side = torch.cuda.Stream(device=dev)
+    region = ag_region(n * 2, world, 0, H * NKQV * 2)
+
+    def split_ag_gemm():
+        cur = torch.cuda.current_stream()
+        side.wait_stream(cur)
+        fc.all_gather(unit, shard, side, skip=region)
+        seg.zero_()
+        gemm_allgather(x, unit, 0, (H, NKQV), trans_b=False, peer_slices=peers, seg=seg, epoch=1, n_copy=fc.n_copy,
+                       out=out, only_b=True)
+        cur.wait_stream(side)
+
     def nccl_ag_gemm():
         torch.distributed.all_gather_into_tensor(full_ref, shard)
         gemm(x, full_ref[:H * NKQV].view(H, NKQV), out=out)
 
     gemm_only = median_ms(lambda: gemm(x, full_ref[:H * NKQV].view(H, NKQV), out=out), flush, sync)
     t_f = torch.tensor([median_ms(fused_ag_gemm, flush, sync)], device=dev)
+    t_s = torch.tensor([median_ms(split_ag_gemm, flush, sync)], device=dev)
     t_n = torch.tensor([median_ms(nccl_ag_gemm, flush, sync)], device=dev)
     comm.all_reduce(t_f, op="max")
+    comm.all_reduce(t_s, op="max")
     comm.all_reduce(t_n, op="max")
+    unit.zero_()
+    sync()
+    split_ag_gemm()
+    torch.distributed.all_gather_into_tensor(full_ref, shard)
+    sync()
+    res["split_ag_gemm_unit_equal_nccl"] = bool(torch.equal(unit, full_ref))
+    res["split_ag_gemm_max_err"] = (out.float() - gemm(x, full_ref[:H * NKQV].view(H, NKQV)).float()).abs().max().item()
     peak = 1590.0
     peaks_file = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(peaks_file):
         peak = float(json.load(open(peaks_file)).get("bf16_tflops", peak))
     gemm_bound = 2.0 * M * NKQV * H / (peak * 1e12) * 1e3
     target = max(gemm_bound, bound_ms)
-    res["ag_gemm"] = {"fused_ms": float(t_f), "nccl_then_gemm_ms": float(t_n), "gemm_alone_ms": gemm_only,
-                      "bound_ms": target, "fused_of_roofline": target / float(t_f),
+    res["ag_gemm"] = {"whole_unit_in_gemm_ms": float(t_f), "own_weight_in_gemm_rest_pulled_ms": float(t_s),
+                      "nccl_then_gemm_ms": float(t_n), "gemm_alone_ms": gemm_only,
+                      "bound_ms": target, "fused_of_roofline": target / float(t_s),
                       "nccl_then_gemm_of_roofline": target / float(t_n)}
     res["status"] = native.read_status()
     res["world"] = world
+    res["blocks"] = fc.rs_blocks
     res["unit_bytes"] = pad * 2
     if rank == 0:
         print(json.dumps(res))

@@ -48,7 +48,29 @@ struct AgFusion {
   unsigned long long first_byte; // copy order starts at the chunk holding this byte (B's first row)
   unsigned int epoch;            // counters of a complete segment read epoch * segment_bytes
   int W, n_copy;
+  // The part of the unit this kernel copies: n_chunks chunks starting at the one that holds
+  // first_byte, i.e. bytes [r_lo, r_hi) of dst. The whole unit, or only the chunks that hold B
+  // (the rest of the unit is then pulled by a separate kernel on the communication stream).
+  long long n_chunks;
+  unsigned long long r_lo, r_hi;
 };
+
+// Chunk grid of the copy: every rank's slice is cut into AG_CHUNK pieces (the last one short).
+struct AgRegion { unsigned long long r_lo, r_hi; long long n_chunks; };
+static AgRegion ag_region(unsigned long long slice_bytes, int W, unsigned long long b_off, unsigned long long b_bytes,
+                          bool only_b) {
+  const unsigned long long cps = (slice_bytes + AG_CHUNK - 1) / AG_CHUNK;
+  if (!only_b || b_bytes == 0) return AgRegion{0ull, slice_bytes * W, (long long)(cps * W)};
+  const unsigned long long last = b_off + b_bytes - 1;
+  const unsigned long long q0 = b_off / slice_bytes, c0 = (b_off % slice_bytes) / AG_CHUNK;
+  const unsigned long long q1 = last / slice_bytes, c1 = (last % slice_bytes) / AG_CHUNK;
+  AgRegion r;
+  r.r_lo = q0 * slice_bytes + c0 * AG_CHUNK;
+  const unsigned long long end1 = q1 * slice_bytes + (c1 + 1) * AG_CHUNK;
+  r.r_hi = end1 < (q1 + 1) * slice_bytes ? end1 : (q1 + 1) * slice_bytes;
+  r.n_chunks = (long long)((q1 * cps + c1) - (q0 * cps + c0) + 1);
+  return r;
+}
 
 struct GemmParams {
   void* D;
@@ -102,10 +124,10 @@ __device__ __forceinline__ unsigned long long ld_acquire_gpu_u64(const unsigned 
 }
 
 __device__ __forceinline__ unsigned long long ag_seg_bytes(const AgFusion& ag, unsigned long long seg) {
-  const unsigned long long total = ag.slice_bytes * ag.W;
-  const unsigned long long lo = seg << AG_SEG_SHIFT;
-  const unsigned long long hi = min(total, lo + (1ull << AG_SEG_SHIFT));
-  return hi - lo;
+  // bytes of this segment that THIS kernel copies and credits
+  const unsigned long long lo = max(seg << AG_SEG_SHIFT, ag.r_lo);
+  const unsigned long long hi = min(ag.r_hi, (seg + 1) << AG_SEG_SHIFT);
+  return hi > lo ? hi - lo : 0ull;
 }
 
 // Credit a finished chunk [pos, pos + bytes) of the unit buffer to the segment counters.
@@ -127,7 +149,7 @@ __device__ void ag_copy_role(const AgFusion& ag, uint8_t* smem, uint64_t* bars, 
   const unsigned long long cps = (ag.slice_bytes + AG_CHUNK - 1) / AG_CHUNK;     // chunks per slice
   const long long total = (long long)cps * ag.W;
   const long long j0 = (long long)(ag.first_byte / ag.slice_bytes) * cps + (ag.first_byte % ag.slice_bytes) / AG_CHUNK;
-  const long long mine = (total - blockIdx.x + ag.n_copy - 1) / ag.n_copy;
+  const long long mine = (ag.n_chunks - blockIdx.x + ag.n_copy - 1) / ag.n_copy;
   auto chunk_of = [&](long long i, const void*& src, unsigned long long& pos, uint32_t& bytes) {
     const long long j = (j0 + blockIdx.x + i * ag.n_copy) % total;
     const int q = int(j / (long long)cps);
@@ -563,7 +585,18 @@ B200_API int b200_gemm_bf16(const void* A, const void* B, void* D, const void* C
 #undef B200_DISPATCH
 }
 
-// GEMM with the all-gather of a ZeRO unit fused in (see AgFusion). B must be a weight matrix that
+// The byte range [out[0], out[1]) of the unit buffer that b200_gemm_bf16_allgather copies itself when
+// called with only_b != 0 for a B matrix of b_bytes at b_off; out[2] = number of chunks.
+B200_API int b200_ag_region(unsigned long long slice_bytes, int W, unsigned long long b_off, unsigned long long b_bytes,
+                            unsigned long long* out) {
+  if (W < 1 || W > AG_MAX_W || slice_bytes == 0 || out == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  const AgRegion r = ag_region(slice_bytes, W, b_off, b_bytes, true);
+  out[0] = r.r_lo; out[1] = r.r_hi; out[2] = (unsigned long long)r.n_chunks;
+  return 0;
+}
+
+// GEMM with the all-gather of a ZeRO unit fused in (see AgFusion). only_b: copy just the chunks that
+// hold B (the caller pulls the rest of the unit with b200_symm_all_gather in its skip mode). B must be a weight matrix that
 // lives at byte offset b_off inside the local unit buffer `ag_dst` (row pitch b_row_bytes); the
 // unit's W slices are read from `ag_src[q]` (peer pointers). seg = zero-initialised counters, one
 // per MiB of the unit buffer; epoch = 1, 2, ... per use of that buffer. Returns when launched;
@@ -572,7 +605,7 @@ B200_API int b200_gemm_bf16_allgather(const void* A, void* D, const void* C, int
                                       int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
                                       const void* const* ag_src, void* ag_dst, void* seg,
                                       unsigned long long slice_bytes, unsigned long long b_off, int W, int n_copy,
-                                      unsigned int epoch, cudaStream_t stream) {
+                                      unsigned int epoch, int only_b, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || W < 1 || W > AG_MAX_W || n_copy < 1) return static_cast<int>(cudaErrorInvalidValue);
   if (slice_bytes % 16 != 0 || b_off % 16 != 0) return static_cast<int>(cudaErrorInvalidValue);
   GemmParams p;
@@ -590,6 +623,11 @@ B200_API int b200_gemm_bf16_allgather(const void* A, void* D, const void* C, int
   p.ag.epoch = epoch;
   p.ag.W = W;
   p.ag.n_copy = n_copy;
+  {
+    const unsigned long long b_rows = b_mn_major ? (unsigned long long)K : (unsigned long long)N;
+    const AgRegion r = ag_region(slice_bytes, W, b_off, b_rows * p.ag.b_row_bytes, only_b != 0);
+    p.ag.r_lo = r.r_lo; p.ag.r_hi = r.r_hi; p.ag.n_chunks = r.n_chunks;
+  }
   const void* B = static_cast<const uint8_t*>(ag_dst) + b_off;
   if ((reinterpret_cast<uintptr_t>(A) & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0)
     return static_cast<int>(cudaErrorInvalidValue);

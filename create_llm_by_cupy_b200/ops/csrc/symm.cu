@@ -32,7 +32,7 @@ namespace b200 {
 
 constexpr int SYMM_MAX_W = 8;
 constexpr int SYMM_PAD_BYTES = 64 * 1024;
-constexpr int SYMM_MAX_BLOCKS = 64;           // blocks (per virtual rank) that take part in a barrier
+constexpr int SYMM_MAX_BLOCKS = 256;          // blocks (per virtual rank) that take part in a barrier
 // signal pad layout (uint32 index): channel c, block b, source rank r -> ((c * MAX_BLOCKS) + b) * MAX_W + r
 constexpr int SYMM_CHANNELS = 8;
 static_assert(SYMM_CHANNELS * SYMM_MAX_BLOCKS * SYMM_MAX_W * 4 <= SYMM_PAD_BYTES, "signal pad too small");
@@ -253,6 +253,10 @@ struct AgParams {
   unsigned long long shard_off;   // byte offset of the unit's slice inside every heap
   long long n_slice;              // elements per rank slice (multiple of 8)
   int rank0, W;
+  // range of the gather buffer in 16-byte vectors and what to do with it:
+  // 0 copy everything, 1 leave [range_lo, range_hi) out (another kernel fills it), 2 copy only that range
+  long long range_lo, range_hi;
+  int range_mode;
 };
 
 // Plain all-gather by pulls: out[q * n_slice + i] = peer q's slice[i]. No barrier inside: parameter
@@ -270,12 +274,18 @@ __global__ void __launch_bounds__(512) ag_pull_kernel(const AgParams p) {
     uint4* d = out + (long long)peer * nvec;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride * U) {
       uint4 v[U];
+      bool take[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long k = i + u * stride;
+        const long long g = (long long)peer * nvec + k;      // position in the gather buffer
+        const bool inside = g >= p.range_lo && g < p.range_hi;
+        take[u] = k < nvec && (p.range_mode == 0 || (p.range_mode == 1 ? !inside : inside));
+        if (take[u]) v[u] = s[k];
+      }
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i + u * stride < nvec) v[u] = s[i + u * stride];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (i + u * stride < nvec) d[i + u * stride] = v[u];
+        if (take[u]) d[i + u * stride] = v[u];
     }
   }
 }
@@ -368,8 +378,9 @@ B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0
   return static_cast<int>(cudaGetLastError());
 }
 
-B200_API int b200_symm_all_gather(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,
-                                  long long n_slice, void* const* out, int blocks, cudaStream_t st) {
+static int symm_all_gather_impl(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,
+                                long long n_slice, void* const* out, int blocks, unsigned long long range_lo_bytes,
+                                unsigned long long range_hi_bytes, int range_mode, cudaStream_t st) {
   if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0)
     return static_cast<int>(cudaErrorInvalidValue);
   if (n_slice == 0) return 0;
@@ -377,9 +388,27 @@ B200_API int b200_symm_all_gather(const void* const* bases, int W, int rank0, in
   fill_tables(p.tab, bases, W, vranks);
   for (int v = 0; v < vranks; ++v) p.out[v] = out[v];
   p.shard_off = shard_off; p.n_slice = n_slice; p.rank0 = rank0; p.W = W;
+  if (range_mode < 0 || range_mode > 2 || (range_lo_bytes | range_hi_bytes) % 16 != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  p.range_lo = (long long)(range_lo_bytes / 16); p.range_hi = (long long)(range_hi_bytes / 16); p.range_mode = range_mode;
   if (blocks < 1) blocks = 1;
   ag_pull_kernel<<<dim3(blocks, vranks), 512, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_symm_all_gather(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,
+                                  long long n_slice, void* const* out, int blocks, cudaStream_t st) {
+  return symm_all_gather_impl(bases, W, rank0, vranks, shard_off, n_slice, out, blocks, 0, 0, 0, st);
+}
+
+// As b200_symm_all_gather, restricted by a byte range of the gather buffer: mode 1 leaves the range
+// out (it is filled by the GEMM that consumes it), mode 2 copies only the range.
+B200_API int b200_symm_all_gather_range(const void* const* bases, int W, int rank0, int vranks,
+                                        unsigned long long shard_off, long long n_slice, void* const* out, int blocks,
+                                        unsigned long long range_lo_bytes, unsigned long long range_hi_bytes,
+                                        int range_mode, cudaStream_t st) {
+  return symm_all_gather_impl(bases, W, rank0, vranks, shard_off, n_slice, out, blocks, range_lo_bytes,
+                              range_hi_bytes, range_mode, st);
 }
 
 B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int vranks, int channel, unsigned int epoch,

@@ -112,14 +112,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
 
 def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_shape: tuple, *, trans_b: bool,
                    peer_slices, seg: torch.Tensor, epoch: int, n_copy: int = 8, add: torch.Tensor | None = None,
-                   out: torch.Tensor | None = None, trans_a: bool = False) -> torch.Tensor:
+                   out: torch.Tensor | None = None, trans_a: bool = False, only_b: bool = False) -> torch.Tensor:
     """``out = op(a) @ op(B) (+ add)`` where B is the weight ``b_shape`` stored at element offset
     ``b_offset`` of the local ZeRO unit buffer ``unit_buf`` — and the unit buffer is being filled
     by this same kernel: ``n_copy`` CTAs pull every rank's slice (``peer_slices`` = W device
     pointers, one per rank, same length) over NVLink while the remaining CTAs run the GEMM, each
     waiting only for the rows of B it is about to load. When the kernel finishes the whole unit
     buffer is valid. ``seg`` = this buffer's progress counters (int64 zeros, one per MiB),
-    ``epoch`` = 1, 2, ... per use of the buffer."""
+    ``epoch`` = 1, 2, ... per use of the buffer. With ``only_b`` the kernel copies just the 32 KiB
+    chunks that hold B (``ag_region`` gives their byte range; the caller gathers the rest of the
+    unit with ``FusedCollectives.all_gather(..., skip=range)``); ``seg`` must then be zeroed and
+    ``epoch`` be 1 for every call, because the range differs from use to use."""
     W = len(peer_slices)
     M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
     if trans_b:
@@ -144,10 +147,18 @@ def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_sha
         native.ptr(a), native.ptr(out), native.ptr(add), M, N, K, lda, out.stride(0), ldc, int(trans_a),
         int(not trans_b), flags, ctypes.c_float(1.0), src, native.ptr(unit_buf), native.ptr(seg),
         ctypes.c_ulonglong(unit_buf.numel() // W * 2), ctypes.c_ulonglong(b_offset * 2), W, n_copy,
-        ctypes.c_uint(epoch), native.stream_ptr())
+        ctypes.c_uint(epoch), int(only_b), native.stream_ptr())
     native.check(rc, "b200_gemm_bf16_allgather")
     native.bump()
     return out
+
+
+def ag_region(slice_bytes: int, world: int, b_offset_bytes: int, b_bytes: int) -> tuple[int, int]:
+    """Byte range of the unit buffer that ``gemm_allgather(..., only_b=True)`` fills itself."""
+    out = (ctypes.c_ulonglong * 3)()
+    native.check(native.lib().b200_ag_region(ctypes.c_ulonglong(slice_bytes), world, ctypes.c_ulonglong(b_offset_bytes),
+                                             ctypes.c_ulonglong(b_bytes), out), "ag_region")
+    return int(out[0]), int(out[1])
 
 
 # ---------------------------------------------------------------------------------------------

@@ -164,14 +164,22 @@ class FusedCollectives:
         native.check(rc, "symm_reduce_scatter")
         native.bump()
 
-    def all_gather(self, out: torch.Tensor, shard_slice: torch.Tensor, stream=None):
-        """out[W * n] <- every rank's shard_slice[n] (shard_slice is a heap tensor)."""
+    def all_gather(self, out: torch.Tensor, shard_slice: torch.Tensor, stream=None, skip=None, only=None):
+        """out[W * n] <- every rank's shard_slice[n] (shard_slice is a heap tensor). ``skip`` /
+        ``only`` = (lo, hi) byte range of ``out`` to leave out / to restrict the copy to."""
         n = shard_slice.numel()
         assert out.numel() == n * self.world_size and n % 8 == 0 and shard_slice.element_size() == 2
         s = native.stream_ptr() if stream is None else ctypes.c_void_p(stream.cuda_stream)
-        rc = self.lib.b200_symm_all_gather(self.heap.table, self.world_size, self.rank, 1,
-                                           ctypes.c_ulonglong(self.heap.offset_of(shard_slice)), ctypes.c_longlong(n),
-                                           _ptr_array([out.data_ptr()]), self.ag_blocks, s)
+        if skip is None and only is None:
+            rc = self.lib.b200_symm_all_gather(self.heap.table, self.world_size, self.rank, 1,
+                                               ctypes.c_ulonglong(self.heap.offset_of(shard_slice)), ctypes.c_longlong(n),
+                                               _ptr_array([out.data_ptr()]), self.ag_blocks, s)
+        else:
+            lo, hi = skip if skip is not None else only
+            rc = self.lib.b200_symm_all_gather_range(
+                self.heap.table, self.world_size, self.rank, 1, ctypes.c_ulonglong(self.heap.offset_of(shard_slice)),
+                ctypes.c_longlong(n), _ptr_array([out.data_ptr()]), self.ag_blocks, ctypes.c_ulonglong(lo),
+                ctypes.c_ulonglong(hi), 1 if skip is not None else 2, s)
         native.check(rc, "symm_all_gather")
         native.bump()
 

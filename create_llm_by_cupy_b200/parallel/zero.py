@@ -44,9 +44,13 @@ class _PendingGather:
     that reads one of its weights. ``gemm`` launches that fused kernel; ``flush`` falls back to the
     stand-alone pull when something else touches the unit first."""
 
-    def __init__(self, mgr, uid: int, buf):
+    def __init__(self, mgr, uid: int, buf, param_index=None, region=None, rest_ready=None):
         self.mgr, self.uid, self.buf = mgr, uid, buf
         self.done = False
+        # The weight the fused GEMM is expected to read, the byte range of the unit buffer that GEMM
+        # will fill itself, and the event after which the rest of the unit (pulled on the
+        # communication stream when the gather was requested) is in place.
+        self.param_index, self.region, self.rest_ready = param_index, region, rest_ready
 
     def _peer_slices(self):
         m = self.mgr
@@ -59,23 +63,40 @@ class _PendingGather:
         m = self.mgr
         s = m.layout.slots[param_index]
         assert s.unit == self.uid and not self.done
+        if self.region is not None and param_index != self.param_index:
+            self.flush()                      # another weight came first: finish the gather the plain way
+            from ..ops import functional as F
+            return F.gemm(a, m.model.params[param_index], trans_b=trans_b, add=add, out=out)
         b = self.buf
         if getattr(b, "seg", None) is None:
             b.seg = torch.zeros((b.t.numel() * 2 + (1 << 20) - 1) >> 20, dtype=torch.int64, device=m.device)
             b.epoch = 0
-        b.epoch += 1
+        only_b = self.region is not None
+        if only_b:
+            b.seg.zero_()                     # the copied range differs from use to use
+            b.epoch = 1
+        else:
+            b.epoch += 1
         self.done = True
-        m.bytes_gathered += (b.t.numel() - b.t.numel() // m.world_size) * 2
-        return gemm_allgather(a, b.t, s.offset, tuple(s.shape), trans_b=trans_b, peer_slices=self._peer_slices(),
-                              seg=b.seg, epoch=b.epoch, n_copy=m.fused.n_copy, add=add, out=out)
+        res = gemm_allgather(a, b.t, s.offset, tuple(s.shape), trans_b=trans_b, peer_slices=self._peer_slices(),
+                             seg=b.seg, epoch=b.epoch, n_copy=m.fused.n_copy, add=add, out=out, only_b=only_b)
+        if only_b:
+            m._wait(m.compute_stream, self.rest_ready)     # the other weights of the unit are needed next
+        else:
+            m.bytes_gathered += (b.t.numel() - b.t.numel() // m.world_size) * 2
+        return res
 
     def flush(self):
         if self.done:
             return
         m = self.mgr
         lo, hi = m.layout.unit_shard_range(self.uid)
-        m.fused.all_gather(self.buf.t, m.param_shard_f16[lo:hi], m.compute_stream)
-        m.bytes_gathered += (self.buf.t.numel() - self.buf.t.numel() // m.world_size) * 2
+        if self.region is not None:
+            m.fused.all_gather(self.buf.t, m.param_shard_f16[lo:hi], m.compute_stream, only=self.region)
+            m._wait(m.compute_stream, self.rest_ready)
+        else:
+            m.fused.all_gather(self.buf.t, m.param_shard_f16[lo:hi], m.compute_stream)
+            m.bytes_gathered += (self.buf.t.numel() - self.buf.t.numel() // m.world_size) * 2
         self.done = True
 
 
@@ -298,12 +319,28 @@ class MemoryZeRO3Manager:
         b = self.gather_pool.get(unit.padded)
         b.uid = uid
         if self._fuse_gather_into_gemm(uid):
-            # nothing to launch now: the unit is pulled by the first GEMM that consumes it
+            # The first GEMM that consumes the unit pulls the chunks that hold ITS weight while it runs;
+            # everything else of the unit is pulled now, on the communication stream.
+            from ..ops.gemm import ag_region
+            ready = self.unit_ready.get(uid, self._params_ready_event)
             self._wait(self.compute_stream, b.free_event)
-            self._wait(self.compute_stream, self.unit_ready.get(uid, self._params_ready_event))
+            self._wait(self.compute_stream, ready)
+            pidx = self._first_weight_index(uid)
+            region = rest_ready = None
+            if pidx is not None:
+                slot = self.layout.slots[pidx]
+                esz = b.t.element_size()
+                region = ag_region((unit.padded // self.world_size) * esz, self.world_size, slot.offset * esz,
+                                   slot.size * esz)
+                with self._comm_ctx():
+                    self._wait(self.comm_stream, b.free_event)
+                    self._wait(self.comm_stream, ready)
+                    self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.comm_stream, skip=region)
+                    rest_ready = self._record(self.comm_stream)
+                self.bytes_gathered += (unit.padded - unit.padded // self.world_size) * esz
             b.ready_event = None
             self.pending_gather[uid] = b
-            self.deferred[uid] = _PendingGather(self, uid, b)
+            self.deferred[uid] = _PendingGather(self, uid, b, pidx, region, rest_ready)
             return
         with self._comm_ctx():
             self._wait(self.comm_stream, b.free_event)
@@ -386,6 +423,18 @@ class MemoryZeRO3Manager:
         for m in mods:
             if type(m).__name__ == want:
                 return m
+        return None
+
+    def _first_weight_index(self, uid: int):
+        """Global parameter index of the weight that the first GEMM on this unit reads: W_KQV of the
+        attention in the forward pass, the down projection of the MLP in the backward pass."""
+        consumer = self._first_consumer(uid)
+        if consumer is None:
+            return None
+        want = 1 if self.phase == "bwd" else 0
+        for mod, j, idx in self.unit_modules[self.unit_names[uid]]:
+            if mod is consumer and j == want and self.layout.slots[idx].unit == uid:
+                return idx
         return None
 
     def ensure_gathered(self, module):
