@@ -143,3 +143,72 @@ def test_validation_and_generation_through_trainer():
     assert math.isfinite(v) and abs(v - math.log(TINY["vocab_size"])) < 1.0
     out = tr.generate([5, 6, 7], greedy=True, max_new_tokens=5)
     assert len(out) == 5
+
+
+def test_gradient_buffer_pool_rotates_two_buffers_deterministically():
+    """With rotate=2 a buffer handed back is not the next one handed out (its collective may still be
+    reading it), and the sequence of allocations depends on the call sequence only."""
+    from create_llm_by_cupy_b200.parallel.zero import _Pool
+    made = []
+
+    def alloc(n, dtype):
+        made.append(n)
+        return torch.zeros(n, dtype=dtype)
+
+    pool = _Pool(torch.float32, "cpu", alloc, rotate=2)
+    a = pool.get(16)
+    pool.put(a)
+    b = pool.get(16)              # second buffer although the first is free again
+    assert b.t.data_ptr() != a.t.data_ptr() and made == [16, 16]
+    pool.put(b)
+    c = pool.get(16)              # first in, first out
+    assert c.t.data_ptr() == a.t.data_ptr()
+    pool.put(c)
+    d = pool.get(16)
+    assert d.t.data_ptr() == b.t.data_ptr() and made == [16, 16]
+    single = _Pool(torch.float32, "cpu", alloc, rotate=1)
+    x = single.get(8)
+    single.put(x)
+    assert single.get(8).t.data_ptr() == x.t.data_ptr()
+
+
+def test_forward_unit_order_and_ranges_cover_the_shard():
+    from create_llm_by_cupy_b200.parallel.trainer import Trainer
+    md = dict(vocab_size=64, hidden_size=32, layer_num=3, time_size=16, q_head=4, kv_head=2, ffn_size=64,
+              padding_id=0, dropout_rate=0, tie_embeddings=True, seed=0)
+    tr = Trainer(md, device="cpu")
+    mgr = tr.manager
+    order = mgr.forward_unit_order()
+    names = [mgr.unit_names[u] for u in order]
+    assert names[0] == "embedding"
+    blocks = [n for n in names if n.startswith("block")]
+    assert blocks == sorted(blocks, key=lambda n: int("".join(c for c in n if c.isdigit())))
+    assert names.index(blocks[-1]) < names.index(next(n for n in names if n.startswith("final_norm")))
+    ranges = sorted(mgr.layout.unit_shard_range(u) for u in order)
+    assert ranges[0][0] == 0 and ranges[-1][1] == mgr.shard_size
+    assert all(a[1] == b[0] for a, b in zip(ranges[:-1], ranges[1:]))
+
+
+def test_fused_gather_region_is_the_chunks_that_hold_the_weight():
+    """Host arithmetic of the all-gather fused into a GEMM: the kernel copies whole 32 KiB chunks of
+    the per-rank slices, starting with the one that holds the first byte of the weight."""
+    import ctypes
+    from create_llm_by_cupy_b200.ops import native
+    try:
+        lib = native.lib()
+    except OSError:
+        pytest.skip("native library not loadable here")
+    out = (ctypes.c_ulonglong * 3)()
+    chunk = 32 * 1024
+    slice_bytes = 5 * chunk + 4096            # the last chunk of every slice is short
+    W = 4
+    # weight inside slice 1, from the middle of its chunk 1 to the middle of its chunk 3
+    b_off = slice_bytes + chunk + 100 * 16
+    b_bytes = 2 * chunk
+    assert lib.b200_ag_region(ctypes.c_ulonglong(slice_bytes), W, ctypes.c_ulonglong(b_off), ctypes.c_ulonglong(b_bytes), out) == 0
+    assert (out[0], out[1], out[2]) == (slice_bytes + chunk, slice_bytes + 4 * chunk, 3)
+    # weight that runs over the short tail of slice 0 into slice 1
+    b_off = 4 * chunk + 16
+    b_bytes = 2 * chunk
+    lib.b200_ag_region(ctypes.c_ulonglong(slice_bytes), W, ctypes.c_ulonglong(b_off), ctypes.c_ulonglong(b_bytes), out)
+    assert out[0] == 4 * chunk and out[1] == slice_bytes + chunk and out[2] == 3     # chunks (0,4), (0,5 short), (1,0)
