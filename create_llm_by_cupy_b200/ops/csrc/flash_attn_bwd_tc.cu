@@ -40,6 +40,8 @@ struct FlashBwdTcParams {
   int B, T, QH, KVH;
   int n_tiles;           // 128-row tiles per sequence
   int bchunk;            // batch elements whose Q, dO, K, V stay in L2 together
+  bf16* ds;              // optional: dS^T written by the dK/dV kernel, [B][QH][ds_tp][ds_tp] (key, query)
+  long long ds_tp;       // its pitch: T rounded up to 128
   float scale;
   int* status;
 };
@@ -502,6 +504,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       // 16 query columns at a time, the next 16 already in flight while these are converted
       const uint32_t tS = tmem_base + lane_sel + kColST + s * 64, tP = tmem_base + lane_sel + kColDPT + s * 64;
       uint32_t sa[16], pa[16], sb[16], pb[16];
+      // dS^T row of this key for the dQ GEMM that follows (16 queries = 32 bytes per chunk)
+      bf16* ds_row = p.ds == nullptr ? nullptr
+                                     : p.ds + (((long long)b * p.QH + (kvh * R + it / n_qt)) * p.ds_tp + key) * p.ds_tp + m0;
       auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
         uint32_t pk[8], dk_[8];
         if (need_mask)
@@ -510,6 +515,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           fb_pds_chunk<false>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, 0, 0, false);
         tmem_st_32x32b_x8(tS + c * 8, pk);
         tmem_st_32x32b_x8(tP + c * 8, dk_);
+        if (ds_row != nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>(ds_row + c * 16);
+          dst[0] = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+          dst[1] = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
+        }
       };
       tmem_ld_32x32b_x16(tS, sa);
       tmem_ld_32x32b_x16(tP, pa);
@@ -583,15 +593,21 @@ static SideStream* side_stream() {
   return &s;
 }
 
+int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
+                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, cudaStream_t st);
+
 }  // namespace b200
 
 using namespace b200;
 
 // Gradients w.r.t. (already rotated) q, k and v. delta [B,QH,T] = sum_d dO*O must have been
 // computed (b200_flash_delta). strides: q, k, v, dout, dq, dk, dv (3 each: batch, token, head).
+// With a workspace `ds_ws` of B * QH * Tp * Tp bf16 (Tp = T rounded up to 128) the dK/dV kernel also
+// writes dS^T there and dQ is computed from it by a GEMM kernel (flash_attn_bwd_dq.cu) instead of the
+// kernel that recomputes S and dP.
 B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const void* lse,
                                const void* delta, void* dq, void* dk, void* dv, const void* valid_len,
-                               const long long* s, int B, int T, int QH, int KVH, int D, float scale,
+                               const long long* s, int B, int T, int QH, int KVH, int D, float scale, void* ds_ws,
                                cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
   if (D != FB_D || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
@@ -632,8 +648,11 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // number only a few per SM, ends in a ragged tail; dQ has many short ones. Running dQ on a second
   // stream then lets its CTAs take the SMs the dK/dV kernel leaves idle while its last CTAs finish.
   // With many dK/dV CTAs per SM there is no tail worth filling and the kernels run back to back.
+  p.ds = static_cast<bf16*>(ds_ws);
+  p.ds_tp = (long long)nt * 128;
   flash_bwd_dkv_tc_kernel<<<nt * KVH * B, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
   B200_CHECK(cudaGetLastError());
+  if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, st);
   if (nt * KVH * B >= 3 * num_sms()) {
     flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
     return static_cast<int>(cudaGetLastError());

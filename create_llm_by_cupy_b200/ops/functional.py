@@ -27,6 +27,26 @@ FLASH_TC_BWD = _os.environ.get("B200_FLASH_TC_BWD", "1") != "0"
 FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 
 
+# dQ from stored dS: the dK/dV kernel writes dS^T (B * QH * Tp^2 bf16, Tp = T rounded up to 128) into a
+# workspace that is kept per shape, and dQ becomes a GEMM over it. Used while the workspace stays small.
+FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
+FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
+_ds_ws_cache: dict = {}
+
+
+def _ds_workspace(device, B: int, QH: int, T: int):
+    tp = (T + 127) // 128 * 128
+    n = B * QH * tp * tp
+    if n * 2 > FLASH_DQ_GEMM_MAX_BYTES:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(), n)
+    ws = _ds_ws_cache.get(key)
+    if ws is None:
+        _ds_ws_cache.clear()           # one shape at a time: a training run has one
+        ws = _ds_ws_cache[key] = torch.empty(n, dtype=torch.bfloat16, device=device)
+    return ws
+
+
 def _lib():
     native.status_tensor()
     return native.lib()
@@ -356,10 +376,11 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
+        ws = _ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None
         native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
                                               native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
                                               native.ptr(dv_), native.ptr(valid_len), arr21, B, T, QH, KVH, D,
-                                              _f(scale), native.stream_ptr()), "flash_bwd_tc")
+                                              _f(scale), native.ptr(ws), native.stream_ptr()), "flash_bwd_tc")
         native.bump(3)
         return dq, dk_, dv_
     strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +
