@@ -40,6 +40,7 @@ struct FlashBwdTcParams {
   int B, T, QH, KVH;
   int n_tiles;           // 128-row tiles per sequence
   int bchunk;            // batch elements whose Q, dO, K, V stay in L2 together
+  int pairing;           // dK/dV kernel: 1 = a CTA owns key tiles i and n_tiles - 1 - i, 0 = one key tile per CTA
   bf16* ds;              // optional: dS^T written by the dK/dV kernel, [B][QH][ds_tp][ds_tp] (key, query)
   long long ds_tp;       // its pitch: T rounded up to 128
   float scale;
@@ -328,9 +329,22 @@ struct FdkvSmem {
   static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;            // stage s: Q_i (16 KiB), dO_i (16 KiB)
   static constexpr int kStats = kQ + FKV_ST * 2 * FKV_QTILE;               // stage s: lse2[64], delta * scale [64]
   static constexpr int kBar = kStats + FKV_ST * 2 * FKV_BQ * 4;
-  // kv_full, q_full[4], q_empty[4], st_full[4] (stats staged), sdp_full[2], pds_full[2], acc_done = 18
-  static constexpr int kTotal = kBar + 18 * 8 + 16 + 1024;
+  // kv_full, q_full[4], q_empty[4], st_full[4] (stats staged), sdp_full[2], pds_full[2], acc_done, acc_free = 19
+  static constexpr int kTotal = kBar + 19 * 8 + 16 + 1024;
 };
+
+// What one pass of the dK/dV kernel works on: a key tile and the query tiles at or below it.
+struct DkvPass {
+  int n0, i_first, n_qt, iters;
+};
+__device__ __forceinline__ DkvPass dkv_pass(int ntile, int T, int R, int vlen) {
+  DkvPass d;
+  d.n0 = ntile * 128;
+  d.i_first = d.n0 / FKV_BQ;                                  // first 64-query tile at / below the diagonal
+  d.n_qt = (T + FKV_BQ - 1) / FKV_BQ - d.i_first;
+  d.iters = (d.n0 < vlen) ? R * d.n_qt : 0;                  // keys past valid_len: zero gradients
+  return d;
+}
 
 __global__ void __launch_bounds__(FBT_THREADS, 1)
 flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
@@ -343,37 +357,42 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint64_t* q_full = bars + 1;                    // [FKV_ST]
   uint64_t* q_empty = q_full + FKV_ST;            // [FKV_ST]
   uint64_t* st_full = q_empty + FKV_ST;           // [FKV_ST]
-  uint64_t* sdp_full = st_full + FKV_ST;          // [2]: S^T / dP^T of iteration it live in TMEM buffer it & 1
-  uint64_t* pds_full = sdp_full + 2;              // [2]: math warpgroup it & 1 has written P^T / dS^T
-  uint64_t* acc_done = pds_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* sdp_full = st_full + FKV_ST;          // [2]: S^T / dP^T of iteration g live in TMEM buffer g & 1
+  uint64_t* pds_full = sdp_full + 2;              // [2]: math warpgroup g & 1 has written P^T / dS^T
+  uint64_t* acc_done = pds_full + 2;              // every MMA of a pass has completed
+  uint64_t* acc_free = acc_done + 1;              // the dK / dV accumulators of a pass have been stored
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // 1-D grid over chunks of p.bchunk batch elements; inside a chunk the longest columns come first
-  // (key tile 0 sees every query tile, the last key tile only two)
-  int ntile, kvh, b;
+  // A CTA owns the key tiles `pair` and `n_tiles - 1 - pair` of one (kv head, batch element), one after
+  // the other: key tile 0 sees every query tile and the last one only two, so each pair adds up to the
+  // same number of iterations and no CTA is left working alone at the end of the kernel. 1-D grid over
+  // chunks of p.bchunk batch elements (what the L2 holds of Q / dO).
+  // With many CTAs per SM (p.pairing == 0) a CTA owns ONE key tile instead and the grid is ordered
+  // longest first.
+  int pair, kvh, b;
   {
-    const int per_chunk = p.n_tiles * p.KVH * p.bchunk;
+    const int n_pairs = p.pairing ? (p.n_tiles + 1) / 2 : p.n_tiles;
+    const int per_chunk = n_pairs * p.KVH * p.bchunk;
     const int chunk = int(blockIdx.x) / per_chunk, r = int(blockIdx.x) - chunk * per_chunk;
     const int hb = p.KVH * min(p.bchunk, p.B - chunk * p.bchunk);
-    ntile = r / hb;
+    pair = r / hb;
     kvh = (r % hb) % p.KVH;
     b = chunk * p.bchunk + (r % hb) / p.KVH;
   }
-  const int n0 = ntile * 128;
   const int T = p.T;
   const int R = p.QH / p.KVH;
   const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
-  const int i_first = n0 / FKV_BQ;                                     // first 64-query tile at / below the diagonal
-  const int n_qt = (T + FKV_BQ - 1) / FKV_BQ - i_first;
-  const int iters = (n0 < vlen) ? R * n_qt : 0;                        // keys past valid_len: zero gradients
+  const int tile_of_pass[2] = {pair, p.pairing ? p.n_tiles - 1 - pair : pair};
+  const int n_pass = tile_of_pass[0] == tile_of_pass[1] ? 1 : 2;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < FKV_ST; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128); }
     mbar_init(acc_done, 1);
+    mbar_init(acc_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -384,58 +403,74 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // S^T and dP^T are double-buffered (64 columns each per buffer) and each buffer has its own math
-  // warpgroup: warpgroup w handles iterations it = w, w + 2, ... while the other warpgroup and the
-  // tensor core are on it + 1. A thread owns one key row (one TMEM lane) and walks the 64 query
-  // columns in two halves; P^T / dS^T (bf16, 32 packed columns) overwrite, lane by lane, columns
-  // of S^T / dP^T that the thread has already read. Q, dO and the row statistics of the next
-  // query tiles are prefetched through a 4-stage ring.
+  // warpgroup: warpgroup w handles iterations g = w, w + 2, ... (g counts on across the two passes)
+  // while the other warpgroup and the tensor core are on g + 1. A thread owns one key row (one TMEM
+  // lane) and walks the 64 query columns in 16-column chunks; P^T / dS^T (bf16, 32 packed columns)
+  // overwrite, lane by lane, columns of S^T / dP^T that the thread has already read. Q, dO and the
+  // row statistics of the next query tiles are prefetched through a 4-stage ring.
   constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * FB_TILE);
-      tma_load_4d(smem + FdkvSmem::kK, &tmK, kv_full, 0, kvh, n0, b);
-      tma_load_4d(smem + FdkvSmem::kK + 16384, &tmK, kv_full, 64, kvh, n0, b);
-      tma_load_4d(smem + FdkvSmem::kV, &tmV, kv_full, 0, kvh, n0, b);
-      tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, n0, b);
-      for (int it = 0; it < iters; ++it) {
-        const int s = it % FKV_ST;
-        const int h = kvh * R + it / n_qt;
-        const int m0 = (i_first + it % n_qt) * FKV_BQ;
-        if (!mbar_wait(&q_empty[s], ((it / FKV_ST) & 1) ^ 1, abort_flag)) break;
-        uint8_t* sQ = smem + FdkvSmem::kQ + s * 2 * FKV_QTILE;
-        uint8_t* sDO = sQ + FKV_QTILE;
-        mbar_expect_tx(&q_full[s], 2 * FKV_QTILE);
-        tma_load_4d(sQ, &tmQ, &q_full[s], 0, h, m0, b);
-        tma_load_4d(sQ + 8192, &tmQ, &q_full[s], 64, h, m0, b);
-        tma_load_4d(sDO, &tmDO, &q_full[s], 0, h, m0, b);
-        tma_load_4d(sDO + 8192, &tmDO, &q_full[s], 64, h, m0, b);
+      int g = 0, kv_loads = 0;
+      bool ok = true;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkvPass d = dkv_pass(tile_of_pass[ps], T, R, vlen);
+        if (d.iters == 0) continue;
+        if (ps > 0) {             // K / V of the previous pass are read by its MMAs until they have all completed
+          if (!mbar_wait(acc_done, (ps - 1) & 1, abort_flag)) break;
+        }
+        mbar_expect_tx(kv_full, 2 * FB_TILE);
+        tma_load_4d(smem + FdkvSmem::kK, &tmK, kv_full, 0, kvh, d.n0, b);
+        tma_load_4d(smem + FdkvSmem::kK + 16384, &tmK, kv_full, 64, kvh, d.n0, b);
+        tma_load_4d(smem + FdkvSmem::kV, &tmV, kv_full, 0, kvh, d.n0, b);
+        tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, d.n0, b);
+        ++kv_loads;
+        for (int it = 0; it < d.iters; ++it, ++g) {
+          const int s = g % FKV_ST;
+          const int h = kvh * R + it / d.n_qt;
+          const int m0 = (d.i_first + it % d.n_qt) * FKV_BQ;
+          if (!mbar_wait(&q_empty[s], ((g / FKV_ST) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sQ = smem + FdkvSmem::kQ + s * 2 * FKV_QTILE;
+          uint8_t* sDO = sQ + FKV_QTILE;
+          mbar_expect_tx(&q_full[s], 2 * FKV_QTILE);
+          tma_load_4d(sQ, &tmQ, &q_full[s], 0, h, m0, b);
+          tma_load_4d(sQ + 8192, &tmQ, &q_full[s], 64, h, m0, b);
+          tma_load_4d(sDO, &tmDO, &q_full[s], 0, h, m0, b);
+          tma_load_4d(sDO + 8192, &tmDO, &q_full[s], 64, h, m0, b);
+        }
       }
+      (void)kv_loads;
     }
   } else if (warp == 3) {
-    // stages the per-query statistics (lse in log2 units, delta) of each query tile in shared memory
-    for (int it = 0; it < iters; ++it) {
-      const int s = it % FKV_ST;
-      const int h = kvh * R + it / n_qt;
-      const int m0 = (i_first + it % n_qt) * FKV_BQ;
-      if (!mbar_wait(&q_empty[s], ((it / FKV_ST) & 1) ^ 1, abort_flag)) break;
-      float* st = reinterpret_cast<float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
-      for (int r = lane; r < FKV_BQ; r += 32) {
-        const int row = m0 + r;
-        const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
-        st[r] = (row < T) ? p.lse[idx] * kFbLog2e : INFINITY;     // +inf => P = 0 for rows past T
-        st[FKV_BQ + r] = (row < T) ? p.delta[idx] * p.scale : 0.f;
+    // stages the per-query statistics (lse in log2 units, delta * scale) of each query tile in shared memory
+    int g = 0;
+    bool ok = true;
+    for (int ps = 0; ps < n_pass && ok; ++ps) {
+      const DkvPass d = dkv_pass(tile_of_pass[ps], T, R, vlen);
+      for (int it = 0; it < d.iters; ++it, ++g) {
+        const int s = g % FKV_ST;
+        const int h = kvh * R + it / d.n_qt;
+        const int m0 = (d.i_first + it % d.n_qt) * FKV_BQ;
+        if (!mbar_wait(&q_empty[s], ((g / FKV_ST) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        float* st = reinterpret_cast<float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
+        for (int r = lane; r < FKV_BQ; r += 32) {
+          const int row = m0 + r;
+          const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
+          st[r] = (row < T) ? p.lse[idx] * kFbLog2e : INFINITY;     // +inf => P = 0 for rows past T
+          st[FKV_BQ + r] = (row < T) ? p.delta[idx] * p.scale : 0.f;
+        }
+        mbar_arrive(&st_full[s]);
       }
-      mbar_arrive(&st_full[s]);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, FKV_BQ, 0, 0);   // [128 keys x 64 q], K-major operands
       constexpr uint32_t idesc_g = umma_idesc_bf16(128, FB_D, 0, 1);     // [128 keys x 128 d], B MN-major
       const uint32_t aK = smem_u32(smem + FdkvSmem::kK), aV = smem_u32(smem + FdkvSmem::kV);
-      auto issue_scores = [&](int it) {
-        const int s = it & 1;
-        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (it % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
+      auto issue_scores = [&](int g) {
+        const int s = g & 1;
+        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (g % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;     // 128-row tiles
@@ -452,113 +487,134 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         umma_commit(&sdp_full[s]);
       };
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
-      if (ok && iters > 0) {
-        ok = mbar_wait(&q_full[0], 0, abort_flag);
-        if (ok) { tc_fence_after(); issue_scores(0); }
-      }
-      for (int it = 0; it < iters && ok; ++it) {
-        const int s = it & 1;
-        if (it + 1 < iters) {
-          // scores of the next query tile go to the other TMEM buffer while the math warps work on
-          // this one (its previous contents were consumed by the gradient MMAs issued earlier)
-          if (!mbar_wait(&q_full[(it + 1) % FKV_ST], ((it + 1) / FKV_ST) & 1, abort_flag)) { ok = false; break; }
+      bool ok = true;
+      int g0 = 0, kv_loads = 0;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkvPass d = dkv_pass(tile_of_pass[ps], T, R, vlen);
+        if (d.iters > 0) {
+          if (!mbar_wait(kv_full, kv_loads & 1, abort_flag)) { ok = false; break; }
+          ++kv_loads;
+          if (!mbar_wait(&q_full[g0 % FKV_ST], (g0 / FKV_ST) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          issue_scores(it + 1);
+          issue_scores(g0);
+          if (ps > 0) {           // the accumulators still hold the previous pass until its rows are stored
+            if (!mbar_wait(acc_free, (ps - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
         }
-        if (!mbar_wait(&pds_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (it % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
-        // B = dO_i / Q_i read MN-major: 64 query rows (k), 128 d (n); 64-d chunks are 8 KiB apart
+        for (int it = 0; it < d.iters && ok; ++it) {
+          const int g = g0 + it, s = g & 1;
+          if (it + 1 < d.iters) {
+            // scores of the next query tile go to the other TMEM buffer while the math warps work on
+            // this one (its previous contents were consumed by the gradient MMAs issued earlier)
+            if (!mbar_wait(&q_full[(g + 1) % FKV_ST], ((g + 1) / FKV_ST) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_scores(g + 1);
+          }
+          if (!mbar_wait(&pds_full[s], (g >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (g % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
+          // B = dO_i / Q_i read MN-major: 64 query rows (k), 128 d (n); 64-d chunks are 8 KiB apart
 #pragma unroll
-        for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
-          umma_bf16_ts(tmem_base + kColDV, tmem_base + kColST + s * 64 + kk * 8,
-                       umma_smem_desc(aDO + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
-        }
+          for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
+            umma_bf16_ts(tmem_base + kColDV, tmem_base + kColST + s * 64 + kk * 8,
+                         umma_smem_desc(aDO + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
+          }
 #pragma unroll
-        for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
-          umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDPT + s * 64 + kk * 8,
-                       umma_smem_desc(aQ + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
+          for (int kk = 0; kk < FKV_BQ / 16; ++kk) {
+            umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDPT + s * 64 + kk * 8,
+                         umma_smem_desc(aQ + kk * 2048, 8192, 1024), idesc_g, (it | kk) != 0);
+          }
+          umma_commit(&q_empty[g % FKV_ST]);
         }
-        umma_commit(&q_empty[it % FKV_ST]);
+        if (ok) umma_commit(acc_done);
+        g0 += d.iters;
       }
-      if (ok) umma_commit(acc_done);
     }
   } else if (warp >= 4) {
     const int q = warp & 3;
     const int wg = (warp - 4) >> 2;           // math warpgroup = score buffer it serves
-    const int half = wg;                      // dK / dV columns this warpgroup stores at the end
-    const int key = n0 + q * 32 + lane;
+    const int half = wg;                      // dK / dV columns this warpgroup stores at the end of a pass
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
     const float sl2 = p.scale * kFbLog2e;
-    const bool key_dead = key >= vlen;
     bool ok = true;
-    for (int it = wg; it < iters && ok; it += 2) {
-      const int s = wg, s4 = it % FKV_ST;
-      const int m0 = (i_first + it % n_qt) * FKV_BQ;
-      if (!mbar_wait(&st_full[s4], (it / FKV_ST) & 1, abort_flag)) { ok = false; break; }
-      if (!mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s4 * 2 * FKV_BQ * 4);
-      const bool need_mask = (m0 < n0 + 128) || (n0 + 128 > vlen);     // the diagonal or the padded tail
-      // 16 query columns at a time, the next 16 already in flight while these are converted
-      const uint32_t tS = tmem_base + lane_sel + kColST + s * 64, tP = tmem_base + lane_sel + kColDPT + s * 64;
-      uint32_t sa[16], pa[16], sb[16], pb[16];
-      // dS^T row of this key for the dQ GEMM that follows (16 queries = 32 bytes per chunk)
-      bf16* ds_row = p.ds == nullptr ? nullptr
-                                     : p.ds + (((long long)b * p.QH + (kvh * R + it / n_qt)) * p.ds_tp + key) * p.ds_tp + m0;
-      auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
-        uint32_t pk[8], dk_[8];
-        if (need_mask)
-          fb_pds_chunk<true>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, m0 + c * 16, key, key_dead);
-        else
-          fb_pds_chunk<false>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, 0, 0, false);
-        tmem_st_32x32b_x8(tS + c * 8, pk);
-        tmem_st_32x32b_x8(tP + c * 8, dk_);
-        if (ds_row != nullptr) {
-          uint4* dst = reinterpret_cast<uint4*>(ds_row + c * 16);
-          dst[0] = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
-          dst[1] = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
-        }
-      };
-      tmem_ld_32x32b_x16(tS, sa);
-      tmem_ld_32x32b_x16(tP, pa);
-      tmem_ld_wait();
-      tmem_ld_32x32b_x16(tS + 16, sb);
-      tmem_ld_32x32b_x16(tP + 16, pb);
-      chunk(sa, pa, 0);
-      tmem_ld_wait();
-      tmem_ld_32x32b_x16(tS + 32, sa);
-      tmem_ld_32x32b_x16(tP + 32, pa);
-      chunk(sb, pb, 1);
-      tmem_ld_wait();
-      tmem_ld_32x32b_x16(tS + 48, sb);
-      tmem_ld_32x32b_x16(tP + 48, pb);
-      chunk(sa, pa, 2);
-      tmem_ld_wait();
-      chunk(sb, pb, 3);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&pds_full[s]);
-    }
-    if (ok) {
-      if (iters > 0) ok = mbar_wait(acc_done, 0, abort_flag);
-      tc_fence_after();
-      if (ok) {
-        const bool live = key < T;
-        bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
-        bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
-        if (iters > 0) {
-          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
-          store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * 64, half * 64 + 64, live);
-        } else if (live) {
-          const uint4 z = make_uint4(0, 0, 0, 0);
-          for (int c = half * 64; c < half * 64 + 64; c += 8) {
-            *reinterpret_cast<uint4*>(krow + c) = z;
-            *reinterpret_cast<uint4*>(vrow + c) = z;
+    int g0 = 0;
+    for (int ps = 0; ps < n_pass && ok; ++ps) {
+      const DkvPass d = dkv_pass(tile_of_pass[ps], T, R, vlen);
+      const int n0 = d.n0;
+      const int key = n0 + q * 32 + lane;
+      const bool key_dead = key >= vlen;
+      for (int it = ((g0 & 1) == wg ? 0 : 1); it < d.iters && ok; it += 2) {
+        const int g = g0 + it;
+        const int s = wg, s4 = g % FKV_ST;
+        const int m0 = (d.i_first + it % d.n_qt) * FKV_BQ;
+        if (!mbar_wait(&st_full[s4], (g / FKV_ST) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&sdp_full[s], (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const float* st = reinterpret_cast<const float*>(smem + FdkvSmem::kStats + s4 * 2 * FKV_BQ * 4);
+        const bool need_mask = (m0 < n0 + 128) || (n0 + 128 > vlen);     // the diagonal or the padded tail
+        // 16 query columns at a time, the next 16 already in flight while these are converted
+        const uint32_t tS = tmem_base + lane_sel + kColST + s * 64, tP = tmem_base + lane_sel + kColDPT + s * 64;
+        uint32_t sa[16], pa[16], sb[16], pb[16];
+        // dS^T row of this key for the dQ GEMM that follows (16 queries = 32 bytes per chunk)
+        bf16* ds_row = p.ds == nullptr
+                           ? nullptr
+                           : p.ds + (((long long)b * p.QH + (kvh * R + it / d.n_qt)) * p.ds_tp + key) * p.ds_tp + m0;
+        auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
+          uint32_t pk[8], dk_[8];
+          if (need_mask)
+            fb_pds_chunk<true>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, m0 + c * 16, key,
+                               key_dead);
+          else
+            fb_pds_chunk<false>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, 0, 0, false);
+          tmem_st_32x32b_x8(tS + c * 8, pk);
+          tmem_st_32x32b_x8(tP + c * 8, dk_);
+          if (ds_row != nullptr) {
+            uint4* dst = reinterpret_cast<uint4*>(ds_row + c * 16);
+            dst[0] = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+            dst[1] = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
           }
+        };
+        tmem_ld_32x32b_x16(tS, sa);
+        tmem_ld_32x32b_x16(tP, pa);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 16, sb);
+        tmem_ld_32x32b_x16(tP + 16, pb);
+        chunk(sa, pa, 0);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 32, sa);
+        tmem_ld_32x32b_x16(tP + 32, pa);
+        chunk(sb, pb, 1);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 48, sb);
+        tmem_ld_32x32b_x16(tP + 48, pb);
+        chunk(sa, pa, 2);
+        tmem_ld_wait();
+        chunk(sb, pb, 3);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&pds_full[s]);
+      }
+      if (!ok) break;
+      g0 += d.iters;
+      // end of the pass: the accumulators of this key tile are complete once every MMA has run
+      if (!mbar_wait(acc_done, ps & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool live = key < T;
+      bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
+      bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
+      if (d.iters > 0) {
+        store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
+        store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * 64, half * 64 + 64, live);
+      } else if (live) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int c = half * 64; c < half * 64 + 64; c += 8) {
+          *reinterpret_cast<uint4*>(krow + c) = z;
+          *reinterpret_cast<uint4*>(vrow + c) = z;
         }
       }
+      tc_fence_before();
+      mbar_arrive(acc_free);
     }
   }
 
@@ -650,10 +706,13 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // With many dK/dV CTAs per SM there is no tail worth filling and the kernels run back to back.
   p.ds = static_cast<bf16*>(ds_ws);
   p.ds_tp = (long long)nt * 128;
-  flash_bwd_dkv_tc_kernel<<<nt * KVH * B, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
+  // few key tiles per SM: pair a long and a short one per CTA (equal work, no tail); many: one per CTA
+  p.pairing = nt * KVH * B < 3 * num_sms() ? 1 : 0;
+  const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
+  flash_bwd_dkv_tc_kernel<<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
   B200_CHECK(cudaGetLastError());
   if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, st);
-  if (nt * KVH * B >= 3 * num_sms()) {
+  if (dkv_ctas >= 3 * num_sms()) {
     flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
     return static_cast<int>(cudaGetLastError());
   }
