@@ -324,14 +324,24 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 // =================================================================== dK, dV
 constexpr int FKV_BQ = 64;                       // query rows per iteration
 constexpr int FKV_QTILE = FKV_BQ * FB_D * 2;     // 16 KiB
-constexpr int FKV_ST = 4;                        // Q / dO / statistics ring depth
+constexpr int FKV_ST = 3;                        // Q / dO / statistics ring depth
+constexpr int FKV_STG = 128 * 128;               // dS^T staging tile of one math warpgroup: 128 keys x 64 queries bf16
 struct FdkvSmem {
   static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;            // stage s: Q_i (16 KiB), dO_i (16 KiB)
   static constexpr int kStats = kQ + FKV_ST * 2 * FKV_QTILE;               // stage s: lse2[64], delta * scale [64]
-  static constexpr int kBar = kStats + FKV_ST * 2 * FKV_BQ * 4;
-  // kv_full, q_full[4], q_empty[4], st_full[4] (stats staged), sdp_full[2], pds_full[2], acc_done, acc_free = 19
-  static constexpr int kTotal = kBar + 19 * 8 + 16 + 1024;
+  static constexpr int kStage = (kStats + FKV_ST * 2 * FKV_BQ * 4 + 1023) / 1024 * 1024;   // [2] dS^T staging tiles
+  static constexpr int kBar = kStage + 2 * FKV_STG;
+  // kv_full, q_full[3], q_empty[3], st_full[3] (stats staged), sdp_full[2], pds_full[2], acc_done, acc_free,
+  // stg_full[2], stg_free[2] = 20
+  static constexpr int kTotal = kBar + 20 * 8 + 16 + 1024;
 };
+
+__device__ __forceinline__ void tma_store_4d_ds(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2,
+                                                int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 
 // What one pass of the dK/dV kernel works on: a key tile and the query tiles at or below it.
 struct DkvPass {
@@ -349,7 +359,7 @@ __device__ __forceinline__ DkvPass dkv_pass(int ntile, int T, int R, int vlen) {
 __global__ void __launch_bounds__(FBT_THREADS, 1)
 flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                        const FlashBwdTcParams p) {
+                        const __grid_constant__ CUtensorMap tmDS, const FlashBwdTcParams p) {
   extern __shared__ uint8_t fb_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fb_smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FdkvSmem::kBar);
@@ -361,7 +371,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint64_t* pds_full = sdp_full + 2;              // [2]: math warpgroup g & 1 has written P^T / dS^T
   uint64_t* acc_done = pds_full + 2;              // every MMA of a pass has completed
   uint64_t* acc_free = acc_done + 1;              // the dK / dV accumulators of a pass have been stored
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+  uint64_t* stg_full = acc_free + 1;              // [2]: warpgroup w has written its dS^T tile into its staging tile
+  uint64_t* stg_free = stg_full + 2;              // [2]: the TMA store of that tile has read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stg_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -393,9 +405,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     for (int s = 0; s < 2; ++s) { mbar_init(&sdp_full[s], 1); mbar_init(&pds_full[s], 128); }
     mbar_init(acc_done, 1);
     mbar_init(acc_free, 256);
+    for (int s = 0; s < 2; ++s) { mbar_init(&stg_full[s], 128); mbar_init(&stg_free[s], 1); }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDS);
   }
   if (warp == 2) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
@@ -527,6 +541,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           }
           umma_commit(&q_empty[g % FKV_ST]);
         }
+        if (ok && d.iters == 0 && ps > 0) {
+          // nothing to do in this pass: still do not complete acc_done a second time before every math
+          // thread has seen its first completion (a waiter two phases behind would never wake up)
+          if (!mbar_wait(acc_free, (ps - 1) & 1, abort_flag)) { ok = false; break; }
+        }
         if (ok) umma_commit(acc_done);
         g0 += d.iters;
       }
@@ -537,6 +556,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int half = wg;                      // dK / dV columns this warpgroup stores at the end of a pass
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
     const float sl2 = p.scale * kFbLog2e;
+    // dS^T goes to global memory through this warpgroup's staging tile (128-byte swizzle) and a TMA store
+    uint8_t* stg_row = smem + FdkvSmem::kStage + wg * FKV_STG + (q * 32 + lane) * 128;
+    const uint32_t swz = uint32_t(lane & 7);
+    const bool ds_on = p.ds != nullptr;
+    uint32_t stg_uses = 0;
     bool ok = true;
     int g0 = 0;
     for (int ps = 0; ps < n_pass && ok; ++ps) {
@@ -556,10 +580,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         // 16 query columns at a time, the next 16 already in flight while these are converted
         const uint32_t tS = tmem_base + lane_sel + kColST + s * 64, tP = tmem_base + lane_sel + kColDPT + s * 64;
         uint32_t sa[16], pa[16], sb[16], pb[16];
-        // dS^T row of this key for the dQ GEMM that follows (16 queries = 32 bytes per chunk)
-        bf16* ds_row = p.ds == nullptr
-                           ? nullptr
-                           : p.ds + (((long long)b * p.QH + (kvh * R + it / d.n_qt)) * p.ds_tp + key) * p.ds_tp + m0;
+        if (ds_on) {              // the store of this warpgroup's previous tile must have read the staging tile
+          if (!mbar_wait(&stg_free[wg], (stg_uses & 1) ^ 1, abort_flag)) { ok = false; break; }
+        }
         auto chunk = [&](const uint32_t (&rs)[16], const uint32_t (&rp)[16], int c) {
           uint32_t pk[8], dk_[8];
           if (need_mask)
@@ -569,10 +592,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             fb_pds_chunk<false>(rs, rp, pk, dk_, sl2, p.scale, st + c * 16, st + FKV_BQ + c * 16, 0, 0, false);
           tmem_st_32x32b_x8(tS + c * 8, pk);
           tmem_st_32x32b_x8(tP + c * 8, dk_);
-          if (ds_row != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(ds_row + c * 16);
-            dst[0] = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
-            dst[1] = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
+          if (ds_on) {            // 16 queries = two 16-byte chunks of this key's 128-byte staging row
+            *reinterpret_cast<uint4*>(stg_row + ((uint32_t(2 * c) ^ swz) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+            *reinterpret_cast<uint4*>(stg_row + ((uint32_t(2 * c + 1) ^ swz) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
           }
         };
         tmem_ld_32x32b_x16(tS, sa);
@@ -594,6 +616,18 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&pds_full[s]);
+        if (ds_on) {
+          fence_proxy_async_smem();
+          mbar_arrive(&stg_full[wg]);
+          if (q == 0 && lane == 0) {
+            if (!mbar_wait(&stg_full[wg], stg_uses & 1, abort_flag)) { ok = false; break; }
+            tma_store_4d_ds(&tmDS, smem + FdkvSmem::kStage + wg * FKV_STG, m0, kvh * R + it / d.n_qt, n0, b);
+            tma_store_commit();
+            tma_store_wait_read<0>();
+            mbar_arrive(&stg_free[wg]);
+          }
+          ++stg_uses;
+        }
       }
       if (!ok) break;
       g0 += d.iters;
@@ -706,10 +740,16 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // With many dK/dV CTAs per SM there is no tail worth filling and the kernels run back to back.
   p.ds = static_cast<bf16*>(ds_ws);
   p.ds_tp = (long long)nt * 128;
+  const CUtensorMap* tds = tk;           // placeholder when no workspace is given (never dereferenced then)
+  if (ds_ws != nullptr) {
+    const unsigned long long Tp = (unsigned long long)nt * 128;
+    tds = get_tensor_map_bthd(ds_ws, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, 128, 64);
+    if (!tds) return static_cast<int>(cudaErrorInvalidValue);
+  }
   // few key tiles per SM: pair a long and a short one per CTA (equal work, no tail); many: one per CTA
   p.pairing = nt * KVH * B < 3 * num_sms() ? 1 : 0;
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
-  flash_bwd_dkv_tc_kernel<<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, p);
+  flash_bwd_dkv_tc_kernel<<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
   B200_CHECK(cudaGetLastError());
   if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, st);
   if (dkv_ctas >= 3 * num_sms()) {
