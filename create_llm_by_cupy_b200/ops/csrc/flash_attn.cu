@@ -382,6 +382,70 @@ __global__ void flash_delta_kernel(const FlashParams p, int D) {
   if (lane == 0) p.delta[(size_t(b) * p.QH + h) * p.T + t] = s;
 }
 
+// The same with 16-byte loads: LPR = D / 8 lanes share a row, a warp covers 32 / LPR rows at a time and
+// every thread keeps U rows in flight. Needs 16-byte aligned rows (strides that are multiples of 8).
+template <int LPR, int U>
+__global__ void __launch_bounds__(256) flash_delta_vec_kernel(const FlashParams p) {
+  constexpr int RPW = 32 / LPR;                      // rows per warp and step
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR, li = lane % LPR;
+  const long long total = (long long)p.B * p.QH * p.T;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r0 = warp0 * RPW * U; r0 < total; r0 += nwarps * RPW * U) {
+    uint4 a[U], c[U];
+    long long row[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      row[u] = r0 + u * RPW + sub;
+      if (row[u] < total) {
+        const int t = int(row[u] % p.T), h = int((row[u] / p.T) % p.QH), b = int(row[u] / ((long long)p.T * p.QH));
+        a[u] = *reinterpret_cast<const uint4*>(p.o + b * p.o_bs + (long long)t * p.o_ts + h * p.o_hs + li * 8);
+        c[u] = *reinterpret_cast<const uint4*>(p.dout + b * p.do_bs + (long long)t * p.do_ts + h * p.do_hs + li * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float s = 0.f;
+      if (row[u] < total) {
+        const bf162* a2 = reinterpret_cast<const bf162*>(&a[u]);
+        const bf162* c2 = reinterpret_cast<const bf162*>(&c[u]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(a2[e]), y = __bfloat1622float2(c2[e]);
+          s += x.x * y.x + x.y * y.y;
+        }
+      }
+#pragma unroll
+      for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      if (li == 0 && row[u] < total) {
+        const int t = int(row[u] % p.T), h = int((row[u] / p.T) % p.QH), b = int(row[u] / ((long long)p.T * p.QH));
+        p.delta[(size_t(b) * p.QH + h) * p.T + t] = s;
+      }
+    }
+  }
+}
+
+static bool launch_delta_vec(const FlashParams& p, int D, cudaStream_t st) {
+  const long long strides[6] = {p.o_bs, p.o_ts, p.o_hs, p.do_bs, p.do_ts, p.do_hs};
+  for (long long v : strides)
+    if (v % 8 != 0) return false;
+  if (((reinterpret_cast<uintptr_t>(p.o) | reinterpret_cast<uintptr_t>(p.dout)) & 15) != 0) return false;
+  const long long total = (long long)p.B * p.QH * p.T;
+  constexpr int U = 4;
+  auto grid_for_rows = [&](int rpw) {
+    const long long warps = (total + rpw * U - 1) / (rpw * U);
+    const long long blocks = (warps + 7) / 8;
+    const long long cap = (long long)num_sms() * 8;
+    return int(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+  };
+  if (D == 128) flash_delta_vec_kernel<16, U><<<grid_for_rows(2), 256, 0, st>>>(p);
+  else if (D == 64) flash_delta_vec_kernel<8, U><<<grid_for_rows(4), 256, 0, st>>>(p);
+  else if (D == 32) flash_delta_vec_kernel<4, U><<<grid_for_rows(8), 256, 0, st>>>(p);
+  else return false;
+  return true;
+}
+
 // ================================================================= backward: dK, dV
 // CTA = 64 keys (4 warps x 16 keys). Works on S^T = K Q^T so that every warp owns key rows.
 constexpr int FB_BN = 64;       // keys per CTA
@@ -760,7 +824,7 @@ static int launch_fwd(const FlashParams& p, bool rope, cudaStream_t st) {
 
 template <int D>
 static int launch_bwd(const FlashParams& p, bool rope, cudaStream_t st) {
-  {
+  if (!launch_delta_vec(p, D, st)) {
     const int total_warps = p.B * p.QH * p.T;
     flash_delta_kernel<<<(total_warps + 7) / 8, 256, 0, st>>>(p, D);
   }
@@ -890,7 +954,9 @@ B200_API int b200_flash_delta(const void* o, const void* dout, void* delta, cons
   p.o_bs = strides[0]; p.o_ts = strides[1]; p.o_hs = strides[2];
   p.do_bs = strides[3]; p.do_ts = strides[4]; p.do_hs = strides[5];
   p.B = B; p.T = T; p.QH = QH;
-  const int total_warps = B * QH * T;
-  flash_delta_kernel<<<(total_warps + 7) / 8, 256, 0, st>>>(p, D);
+  if (!launch_delta_vec(p, D, st)) {
+    const int total_warps = B * QH * T;
+    flash_delta_kernel<<<(total_warps + 7) / 8, 256, 0, st>>>(p, D);
+  }
   return static_cast<int>(cudaGetLastError());
 }
