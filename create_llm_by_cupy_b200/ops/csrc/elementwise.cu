@@ -94,6 +94,73 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, b
   }
 }
 
+// Wide rows (1024 < H <= 8192): the whole CTA works on R rows at a time, every thread owning NV
+// 8-column chunks of each; all loads are issued before the first use and the R sums of squares are
+// combined with one block-wide exchange per step.
+template <int NV, int R>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_cta_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma, bf16* __restrict__ y,
+                       float* __restrict__ rstd, int M, int H, float eps) {
+  __shared__ float sss[2][R][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunk = H >> 3;
+  const float inv_h = 1.f / float(H);
+  float g[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = tid + i * 256;
+    if (c < nchunk) unpack8(reinterpret_cast<const Pack8*>(gamma)[c], g[i]);
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * R; row0 < M; row0 += gridDim.x * R, ++it) {
+    Pack8 px[R][NV];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = tid + i * 256;
+        if (row < M && c < nchunk) px[r][i] = reinterpret_cast<const Pack8*>(x + size_t(row) * H)[c];
+        else px[r][i] = Pack8{};
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        float f[8];
+        unpack8(px[r][i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) sss[it & 1][r][warp] = ss;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row = row0 + r;
+      if (row >= M) continue;
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += sss[it & 1][r][w];
+      const float rs = rsqrtf(t * inv_h + eps);
+      if (tid == 0) rstd[row] = rs;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = tid + i * 256;
+        if (c >= nchunk) continue;
+        float f[8];
+        unpack8(px[r][i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = f[e] * rs * g[i][e];
+        reinterpret_cast<Pack8*>(y + size_t(row) * H)[c] = pack8(f);
+      }
+    }
+  }
+}
+
 // Any H (used when H is not a multiple of 8).
 __global__ void rmsnorm_fwd_scalar_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
                                           bf16* __restrict__ y, float* __restrict__ rstd, int M, int H, float eps) {
@@ -571,8 +638,17 @@ B200_API int b200_rmsnorm_fwd(const void* x, const void* gamma, void* y, void* r
     rmsnorm_fwd_kernel<1><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
   } else if (H <= 1024) {
     rmsnorm_fwd_kernel<4><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
-  } else if (H <= 2048) {
-    rmsnorm_fwd_kernel<8><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+  } else if (H <= 8192) {
+    const int cap = num_sms() * 4;
+    if (H <= 2048) {
+      const int ctas = min((M + 3) / 4, cap);
+      rmsnorm_fwd_cta_kernel<1, 4><<<ctas, 256, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+    } else if (H <= 4096) {
+      const int ctas = min((M + 1) / 2, cap);
+      rmsnorm_fwd_cta_kernel<2, 2><<<ctas, 256, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+    } else {
+      rmsnorm_fwd_cta_kernel<4, 1><<<min(M, cap), 256, 0, st>>>(xp, gp, yp, rp, M, H, eps);
+    }
   } else {
     rmsnorm_fwd_kernel<16><<<grid, block, 0, st>>>(xp, gp, yp, rp, M, H, eps);
   }
