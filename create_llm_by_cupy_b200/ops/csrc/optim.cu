@@ -62,30 +62,32 @@ adamw_kernel(const TG* __restrict__ grad, float* __restrict__ m, float* __restri
   if (!adam_prologue(a, stats, gmul)) return;
   const size_t n4 = vec ? (n >> 2) : 0;   // unaligned shards take the scalar loop for everything
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += size_t(gridDim.x) * blockDim.x) {
+    // Streaming accesses throughout: the optimizer touches every byte once and runs beside the next
+    // forward pass, whose GEMM operands should stay in L2.
     float g[4];
     if constexpr (sizeof(TG) == 4) {
-      const float4 t = reinterpret_cast<const float4*>(grad)[i];
+      const float4 t = __ldcs(reinterpret_cast<const float4*>(grad) + i);
       g[0] = t.x; g[1] = t.y; g[2] = t.z; g[3] = t.w;
     } else {
-      const uint2 t = reinterpret_cast<const uint2*>(grad)[i];
+      const uint2 t = __ldcs(reinterpret_cast<const uint2*>(grad) + i);
       const float2 lo = __bfloat1622float2(*reinterpret_cast<const bf162*>(&t.x));
       const float2 hi = __bfloat1622float2(*reinterpret_cast<const bf162*>(&t.y));
       g[0] = lo.x; g[1] = lo.y; g[2] = hi.x; g[3] = hi.y;
     }
-    float4 mm = reinterpret_cast<float4*>(m)[i];
-    float4 vv = reinterpret_cast<float4*>(v)[i];
-    float4 ww = reinterpret_cast<float4*>(master)[i];
+    float4 mm = __ldcs(reinterpret_cast<const float4*>(m) + i);
+    float4 vv = __ldcs(reinterpret_cast<const float4*>(v) + i);
+    float4 ww = __ldcs(reinterpret_cast<const float4*>(master) + i);
     adam_one(g[0] * gmul, mm.x, vv.x, ww.x, a);
     adam_one(g[1] * gmul, mm.y, vv.y, ww.y, a);
     adam_one(g[2] * gmul, mm.z, vv.z, ww.z, a);
     adam_one(g[3] * gmul, mm.w, vv.w, ww.w, a);
-    reinterpret_cast<float4*>(m)[i] = mm;
-    reinterpret_cast<float4*>(v)[i] = vv;
-    reinterpret_cast<float4*>(master)[i] = ww;
+    __stcs(reinterpret_cast<float4*>(m) + i, mm);
+    __stcs(reinterpret_cast<float4*>(v) + i, vv);
+    __stcs(reinterpret_cast<float4*>(master) + i, ww);
     uint2 o;
     *reinterpret_cast<bf162*>(&o.x) = __floats2bfloat162_rn(ww.x, ww.y);
     *reinterpret_cast<bf162*>(&o.y) = __floats2bfloat162_rn(ww.z, ww.w);
-    reinterpret_cast<uint2*>(param)[i] = o;
+    reinterpret_cast<uint2*>(param)[i] = o;          // the parameters are read again right away: default policy
   }
   {
     for (size_t i = (n4 << 2) + size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -262,6 +264,10 @@ static inline int grid_cap(size_t items, int block) {
 
 using namespace b200;
 
+// Upper bound on the CTAs of one AdamW launch (0 = none). A caller that runs AdamW beside compute
+// kernels keeps it to a couple of CTAs per SM so that those kernels still find thread slots.
+static int g_adam_max_blocks = 0;
+
 static int adamw_launch(const void* grad, int grad_fp32, void* m, void* v, void* master, void* param, long long n,
                         float lr, float beta1, float beta2, float eps, float weight_decay, float m_corr, float v_corr,
                         float grad_scale, float max_grad_norm, const void* stats, const void* hyper_dev,
@@ -269,7 +275,8 @@ static int adamw_launch(const void* grad, int grad_fp32, void* m, void* v, void*
   if (n <= 0) return 0;
   const float* hyper = static_cast<const float*>(hyper_dev);
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale, max_grad_norm};
-  const int grid = grid_cap(size_t(n) / 4 + 1, 256);
+  int grid = grid_cap(size_t(n) / 4 + 1, 256);
+  if (g_adam_max_blocks > 0 && grid > g_adam_max_blocks) grid = g_adam_max_blocks;
   const uintptr_t all = reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
                         reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(master) |
                         (reinterpret_cast<uintptr_t>(param) << 1);
@@ -292,6 +299,12 @@ B200_API int b200_adamw(const void* grad, int grad_fp32, void* m, void* v, void*
                         float grad_scale, float max_grad_norm, const void* stats, cudaStream_t st) {
   return adamw_launch(grad, grad_fp32, m, v, master, param, n, lr, beta1, beta2, eps, weight_decay, m_corr, v_corr,
                       grad_scale, max_grad_norm, stats, nullptr, st);
+}
+
+B200_API int b200_adamw_max_blocks(int n) {
+  const int old = g_adam_max_blocks;
+  if (n >= 0) g_adam_max_blocks = n;
+  return old;
 }
 
 // As b200_adamw, with lr, m_corr, v_corr and grad_scale read from hyper[0..3] in device memory.

@@ -61,7 +61,6 @@ class Trainer:
                    weight_decay=weight_decay, beta1=beta1, beta2=beta2, epsilon=epsilon, logger=logger)
         if optimizer_device == "cpu":
             # torchrun pins OMP_NUM_THREADS to 1; the host AdamW wants its share of the cores
-            import os
             okw["threads"] = max(1, (os.cpu_count() or 1) // max(world_size, 1))
         self.optimizer = opt_cls(self.manager.get_param_shard_view(), **okw)
         self.replica_optimizer = None
@@ -81,6 +80,8 @@ class Trainer:
         self.adam_overlap = bool(adam_overlap and self.device.type == "cuda" and optimizer_device != "cpu"
                                  and self.accum_step == 1 and self.replica_optimizer is None and not fused_adam)
         self._adam_stream = torch.cuda.Stream(device=self.device) if self.adam_overlap else None
+        # AdamW CTAs per SM while it runs beside the forward: few enough that the GEMM CTAs still fit
+        self.adam_overlap_ctas_per_sm = int(os.environ.get("B200_ADAM_OVERLAP_CTAS", "2"))
         self._adam_done = None
         # Whole-step CUDA graph (one GPU): forward, backward, gradient statistics and AdamW are captured
         # once and replayed; what changes from step to step (token ids, learning rate, bias corrections,
@@ -248,12 +249,16 @@ class Trainer:
                     ev.record(self._adam_stream)
                     mgr.unit_ready[order[i]] = ev
 
+                from ..ops import native
+                sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+                prev = native.lib().b200_adamw_max_blocks(self.adam_overlap_ctas_per_sm * sms)
                 with torch.cuda.stream(self._adam_stream):
                     self.optimizer.update_ranges(mgr.grad_shard_f16, step_scale, ranges, mgr.get_param_shard_view(),
                                                  stats=stats_in, max_grad_norm=self.max_grads, after_each=unit_done,
                                                  is_main_device=self.rank == 0)
                     self._adam_done = torch.cuda.Event()
                     self._adam_done.record(self._adam_stream)
+                native.lib().b200_adamw_max_blocks(prev)
                 stats_in.record_stream(self._adam_stream)
             elif not self.fused_adam:
                 self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
