@@ -64,6 +64,7 @@ def main():
                     help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-adam-overlap", action="store_true", help="AdamW as one kernel after the backward")
+    ap.add_argument("--opt", default=None, choices=["gpu", "cpu"], help="override the config's optimizer tier")
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
@@ -101,7 +102,10 @@ def main():
     comm = init_distributed(rank, world, backend="nccl", device_id=local_rank,
                             master_port=int(os.environ.get("MASTER_PORT", 29511)))
 
-    c = CONFIGS[args.config]
+    c = dict(CONFIGS[args.config])
+    if args.opt is not None:
+        c["opt"] = args.opt
+        c["name"] = c["name"] + ("-offload" if args.opt == "cpu" and "offload" not in c["name"] else "")
     pad = 0
     md = dict(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], layer_num=c["layer_num"],
               time_size=c["time_size"], q_head=c["q_head"], kv_head=c["kv_head"], ffn_size=c["ffn_size"],
