@@ -77,31 +77,37 @@ __device__ __forceinline__ float f3_max3(float a, float b, float c) {
   return r;
 }
 
-// 32 raw scores of one row: running raw maximum, and (with_p) P = exp2(s * sl2 - m_ref) packed to
-// bf16 pairs plus their sum. Masked keys (beyond the diagonal or the valid length) count as -inf.
-template <bool kMask, bool with_p>
-__device__ __forceinline__ void f3_chunk(const uint32_t (&r)[32], uint32_t* pk, float sl2, float m_ref, float& mx,
-                                         float& rs, int key_base, int row, int vlen) {
-  float rs1 = 0.f;
+// Raw maximum of the 128 scores of one row; masked keys (beyond the diagonal or the valid length) are
+// set to -inf in place so that the exponential pass needs no mask.
+template <bool kMask>
+__device__ __forceinline__ float f3_row_max(uint32_t (&sc)[128], int key0, int row, int vlen) {
+  float mx = -INFINITY;
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+  for (int e = 0; e < 128; e += 2) {
     if (kMask) {
-      const int key = key_base + e;
-      if (key > row || key >= vlen) s0 = -INFINITY;
-      if (key + 1 > row || key + 1 >= vlen) s1 = -INFINITY;
+      const int key = key0 + e;
+      if (key > row || key >= vlen) sc[e] = 0xff800000u;
+      if (key + 1 > row || key + 1 >= vlen) sc[e + 1] = 0xff800000u;
     }
-    mx = f3_max3(mx, s0, s1);
-    if (with_p) {
-      const float p0 = exp2f(fmaf(s0, sl2, -m_ref));
-      const float p1 = exp2f(fmaf(s1, sl2, -m_ref));
-      rs += p0;
-      rs1 += p1;
-      const bf162 t = __floats2bfloat162_rn(p0, p1);
-      pk[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
-    }
+    mx = f3_max3(mx, __uint_as_float(sc[e]), __uint_as_float(sc[e + 1]));
   }
-  rs += rs1;
+  return mx;
+}
+
+// P = exp2(s * sl2 - m_ref) for the 128 scores of one row, packed to bf16 pairs IN PLACE (pair e / 2 lands in
+// register e / 2, which has been consumed by then); returns the row sum.
+__device__ __forceinline__ float f3_row_p(uint32_t (&sc)[128], float sl2, float m_ref) {
+  float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+  for (int e = 0; e < 128; e += 2) {
+    const float p0 = exp2f(fmaf(__uint_as_float(sc[e]), sl2, -m_ref));
+    const float p1 = exp2f(fmaf(__uint_as_float(sc[e + 1]), sl2, -m_ref));
+    rs0 += p0;
+    rs1 += p1;
+    const bf162 t = __floats2bfloat162_rn(p0, p1);
+    sc[e >> 1] = *reinterpret_cast<const uint32_t*>(&t);
+  }
+  return rs0 + rs1;
 }
 
 __global__ void __launch_bounds__(F3_THREADS, 1)
@@ -265,65 +271,46 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       const bool need_mask = (j == mt) || (j * 128 + 128 > vlen);
       const int key0 = j * 128;
-      uint32_t ra[32], rb[32], pk[64];
-      float mx = -INFINITY, rs = 0.f;
-      // One sweep over the 128 scores of the row, 32 columns at a time with the next load in flight:
-      // the raw maximum, P = exp2(s * scale - m_ref) packed to bf16 (kept in registers) and the row sum.
-      auto sweep = [&](auto mask_tag, auto p_tag) {
-        constexpr bool kMask = decltype(mask_tag)::value;
-        constexpr bool kP = decltype(p_tag)::value;
-        mx = -INFINITY;
-        rs = 0.f;
-        tmem_ld_32x32b_x32(tS, ra);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(tS + 32, rb);
-        f3_chunk<kMask, kP>(ra, &pk[0], sl2, m_ref, mx, rs, key0, row, vlen);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(tS + 64, ra);
-        f3_chunk<kMask, kP>(rb, &pk[16], sl2, m_ref, mx, rs, key0 + 32, row, vlen);
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(tS + 96, rb);
-        f3_chunk<kMask, kP>(ra, &pk[32], sl2, m_ref, mx, rs, key0 + 64, row, vlen);
-        tmem_ld_wait();
-        f3_chunk<kMask, kP>(rb, &pk[48], sl2, m_ref, mx, rs, key0 + 96, row, vlen);
-        mx *= sl2;                             // scale > 0: the maximum commutes with the scaling
-      };
-      auto run_sweep = [&](auto p_tag) {
-        if (need_mask) sweep(TrueTag{}, p_tag);
-        else sweep(FalseTag{}, p_tag);
-      };
-      if (j == 0) {                            // the first tile fixes the reference maximum
-        run_sweep(FalseTag{});
+      // The whole row (128 raw scores) is read in one go: four loads, one wait. A tensor-memory load queues
+      // behind the MMAs the other warpgroup has in flight, so every separate round trip costs that wait again.
+      uint32_t sc[128];
+      tmem_ld_32x32b_x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&sc[0]));
+      tmem_ld_32x32b_x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&sc[32]));
+      tmem_ld_32x32b_x32(tS + 64, *reinterpret_cast<uint32_t(*)[32]>(&sc[64]));
+      tmem_ld_32x32b_x32(tS + 96, *reinterpret_cast<uint32_t(*)[32]>(&sc[96]));
+      tmem_ld_wait();
+      float mx = (need_mask ? f3_row_max<true>(sc, key0, row, vlen) : f3_row_max<false>(sc, key0, row, vlen)) * sl2;
+      // The reference maximum is set by the first tile and afterwards moves only when a tile exceeds it by
+      // more than 2^8; then O_w and the row sum are rescaled by the row's own thread.
+      if (j == 0) {
         m_ref = (mx == -INFINITY) ? 0.f : mx;
-      }
-      run_sweep(TrueTag{});
-      // The reference maximum moves only when a tile exceeds it by more than 2^8; then O_w and the row
-      // sum are rescaled by the row's own thread and P is recomputed (S_w is still intact in TMEM).
-      const bool need = mx > m_ref + kF3RescaleStep;
-      if (__any_sync(0xffffffffu, need)) {
-        if (j > 0) {
+      } else {
+        const bool need = mx > m_ref + kF3RescaleStep;
+        if (__any_sync(0xffffffffu, need)) {
           // O_w holds the key tiles up to j - 1 once their P V has completed
           if (!mbar_wait(&pv_done[w], (j - 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const float corr = need ? exp2f(m_ref - mx) : 1.f;
           l_run *= corr;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            tmem_ld_32x32b_x32(tO + c * 32, ra);
+          for (int c = 0; c < 8; ++c) {
+            uint32_t t[16];
+            tmem_ld_32x32b_x16(tO + c * 16, t);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) ra[e] = __float_as_uint(__uint_as_float(ra[e]) * corr);
-            tmem_st_32x32b_x32(tO + c * 32, ra);
+            for (int e = 0; e < 16; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * corr);
+            tmem_st_32x32b_x16(tO + c * 16, t);
           }
           tmem_st_wait();
+          if (need) m_ref = mx;
         }
-        if (need) m_ref = mx;
-        run_sweep(TrueTag{});
       }
-      // P as bf16 over the first 64 columns of S_w
+      // P = exp2(s * scale - m_ref) as bf16 pairs, packed in place over the first 64 registers, and its row sum
+      const float rs = f3_row_p(sc, sl2, m_ref);
+      // P over the first 64 columns of S_w
 #pragma unroll
       for (int c = 0; c < 4; ++c)
-        tmem_st_32x32b_x16(tS + c * 16, *reinterpret_cast<const uint32_t(*)[16]>(&pk[16 * c]));
+        tmem_st_32x32b_x16(tS + c * 16, *reinterpret_cast<const uint32_t(*)[16]>(&sc[16 * c]));
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[w]);
