@@ -50,7 +50,9 @@ constexpr int G2_BAR_OFF2 = G2_STG_OFF + 2 * G2_STG_BYTES;
 constexpr int G2_SMEM = G2_BAR_OFF2 + (2 * G2_STAGES + 4 + 2 * G2_SCHED + 2) * 8 + 16 + G2_SCHED * 4 + 1024;
 constexpr int G2_SCHED_SLOTS = 1024;   // {next tile, finished pairs} counter pairs, used round-robin by launches
 
-enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4 };
+// G2_WHOLE_TILES (caller): never halve tiles - set for GEMMs that run beside a GEMM of another stream,
+// whose CTAs fill the SMs a part-filled last round leaves idle anyway.
+enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4, G2_WHOLE_TILES = 8 };
 
 struct Gemm2Params {
   void* D;
@@ -61,6 +63,15 @@ struct Gemm2Params {
   float alpha;
   int* status;
   int* sched;      // [0] next tile index, [1] pairs that have drawn their stop mark; both 0 between launches
+  // Work items: the first t_full are whole 256 x 256 tiles; every tile after that is cut into two
+  // 256 x 128 halves (items t_full + 2 i and t_full + 2 i + 1). The launcher halves the tiles of a last,
+  // less than half filled round of CTA pairs, which then takes about half a tile time instead of a whole one.
+  int t_full, n_items;
+};
+
+// A work item: tile coordinates, first column and width.
+struct G2Item {
+  int mb, nb, n0, bn;
 };
 
 static __device__ int g_tile_sched[2 * G2_SCHED_SLOTS];
@@ -163,6 +174,20 @@ __device__ __forceinline__ void named_bar_sync_128(int id) {
   asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
 }
 
+__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb);
+__device__ __forceinline__ G2Item g2_item(int t, int t_full, int num_m, int num_n) {
+  G2Item it;
+  int tile = t, half = -1;
+  if (t >= t_full) {
+    tile = t_full + ((t - t_full) >> 1);
+    half = (t - t_full) & 1;
+  }
+  tile_coords2(tile, num_m, num_n, it.mb, it.nb);
+  it.bn = half < 0 ? 256 : 128;
+  it.n0 = it.nb * 256 + (half == 1 ? 128 : 0);
+  return it;
+}
+
 __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb) {
   constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
@@ -177,8 +202,8 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmC,
-                     const Gemm2Params p) {
+                     const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
+                     const __grid_constant__ CUtensorMap tmC, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw2[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw2) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFF2);
@@ -198,7 +223,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int num_n = (p.N + G2_BN - 1) / G2_BN;
-  const int num_tiles = num_m * num_n;
+  const int num_tiles = p.n_items;          // work items (whole tiles and half tiles)
   const int num_kb = (p.K + G2_BK - 1) / G2_BK;
   const bool dyn = p.sched != nullptr;      // null: tile t + k * num_pairs goes to pair t (fixed assignment)
 
@@ -255,15 +280,15 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         // the draw is in flight while this tile's first loads are issued
         if (!dyn) t_next = t + num_pairs;
         else if (rank == 0) t_next = num_pairs + atomicAdd(&p.sched[0], 1);
-        int mb, nb;
-        tile_coords2(t, num_m, num_n, mb, nb);
-        const int m0 = mb * 2 * G2_BM + int(rank) * G2_BM;
-        const int n0 = nb * G2_BN + int(rank) * (G2_BN / 2);
+        const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+        const int m0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int n0 = wi.n0 + int(rank) * (wi.bn / 2);
+        const uint32_t stage_tx = 2 * (G2_A_BYTES + (wi.bn / 2) * G2_BK * 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sA = smem + stage * G2_STAGE_BYTES;
           uint8_t* sB = sA + G2_A_BYTES;
-          if (rank == 0) mbar_expect_tx(&full[stage], 2 * G2_STAGE_BYTES);   // bytes of both CTAs
+          if (rank == 0) mbar_expect_tx(&full[stage], stage_tx);             // bytes of both CTAs
           const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);           // the leader's barrier
           const int k0 = kb * G2_BK;
           if (A_MN) {
@@ -274,9 +299,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < (G2_BN / 2) / 64; ++c) tma_load_2d_pair(sB + c * 8192, &tmB, bar, n0 + c * 64, k0);
+            for (int c = 0; c < (G2_BN / 2) / 64; ++c)
+              if (c * 64 < wi.bn / 2) tma_load_2d_pair(sB + c * 8192, &tmB, bar, n0 + c * 64, k0);
           } else {
-            tma_load_2d_pair(sB, &tmB, bar, k0, n0);
+            tma_load_2d_pair(sB, wi.bn == G2_BN ? &tmB : &tmBh, bar, k0, n0);      // 128 or 64 rows of B
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
           if (dyn && rank == 0 && kb == publish_kb && !publish(t_next)) { ok = false; break; }
@@ -302,7 +328,8 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * G2_BM, G2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc_full = umma_idesc_bf16(2 * G2_BM, G2_BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc_half = umma_idesc_bf16(2 * G2_BM, G2_BN / 2, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -314,6 +341,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
+        const uint32_t idesc = t < p.t_full ? idesc_full : idesc_half;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -356,7 +384,6 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       // the same staging tile is first filled with the C tile by a TMA load. Two staging tiles
       // alternate, so the store of one group overlaps the conversion of the next.
       const int gcols = out_f32 ? 32 : 64;
-      const int ngroups = G2_BN / gcols;
       uint8_t* stg = smem + G2_STG_OFF;
       const int r = q * 32 + lane;
       const uint32_t swz = uint32_t(r & 7);
@@ -374,10 +401,10 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       for (int t = pair; ok && t >= 0 && t < num_tiles;
            t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0)
                    : t + num_pairs) {
-        int mb, nb;
-        tile_coords2(t, num_m, num_n, mb, nb);
-        const int row0 = mb * 2 * G2_BM + int(rank) * G2_BM;
-        const int n0 = nb * G2_BN;
+        const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+        const int row0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int n0 = wi.n0;
+        const int ngroups = wi.bn / gcols;
         if (elected) {
           tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
           arm(gcount, n0, row0);
@@ -461,15 +488,14 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     } else
     for (int t = pair; ok && t >= 0 && t < num_tiles;
          t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0) : t + num_pairs) {
-      int mb, nb;
-      tile_coords2(t, num_m, num_n, mb, nb);
-      const int row = mb * 2 * G2_BM + int(rank) * G2_BM + q * 32 + lane;
-      const int n0 = nb * G2_BN;
+      const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+      const int row = wi.mb * 2 * G2_BM + int(rank) * G2_BM + q * 32 + lane;
+      const int n0 = wi.n0;
       if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
 #pragma unroll 1
-      for (int c = 0; c < G2_BN / 32; ++c) {
+      for (int c = 0; c < wi.bn / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
@@ -546,6 +572,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 }
 
 static int g_dynamic_tiles = 1;
+static int g_half_tiles = 1;
 
 // Counter pair for one launch. Kernels of different streams may run at the same time, so launches
 // take the slots round-robin; a slot is back to zero when its kernel has finished.
@@ -565,24 +592,34 @@ static int* next_sched_slot() {
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tD, const CUtensorMap* tC,
-                      const Gemm2Params& p, cudaStream_t stream) {
+static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tBh, const CUtensorMap* tD,
+                      const CUtensorMap* tC, const Gemm2Params& p, cudaStream_t stream) {
   auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
     configured = true;
   }
-  const int num_tiles = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
-  int pairs = num_sms() / 2;
+  const int whole = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
+  const int all_pairs = num_sms() / 2;
+  // a last round that fills less than half of the pairs is run on half tiles
+  int halved = 0;
+  if (g_half_tiles && !(p.flags & G2_WHOLE_TILES) && whole > all_pairs) {
+    const int rem = whole % all_pairs;
+    if (rem > 0 && 2 * rem <= all_pairs) halved = rem;
+  }
+  const int num_tiles = whole + halved;
+  int pairs = all_pairs;
   if (num_tiles < pairs) pairs = num_tiles;
   Gemm2Params q = p;
+  q.t_full = whole - halved;
+  q.n_items = num_tiles;
   q.sched = nullptr;
   if (g_dynamic_tiles && num_tiles > pairs) {
     q.sched = next_sched_slot();
     if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   }
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tD, *tC, q);
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tBh, *tD, *tC, q);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -594,6 +631,13 @@ using namespace b200;
 B200_API int b200_gemm_2cta_dynamic_tiles(int on) {
   const int old = g_dynamic_tiles;
   if (on >= 0) g_dynamic_tiles = on != 0;
+  return old;
+}
+
+// 1: the tiles of a last round that fills less than half of the CTA pairs are split into 256 x 128 halves.
+B200_API int b200_gemm_2cta_half_tiles(int on) {
+  const int old = g_half_tiles;
+  if (on >= 0) g_half_tiles = on != 0;
   return old;
 }
 
@@ -612,7 +656,8 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const vo
                                      : get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
   const CUtensorMap* tB = b_mn_major ? get_tensor_map_2d(B, K, N, ldb, 64, 64, 2, SWIZZLE_128B_)
                                      : get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
-  if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);
+  const CUtensorMap* tBh = b_mn_major ? tB : get_tensor_map_2d(B, N, K, ldb, G2_BN / 4, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB || !tBh) return static_cast<int>(cudaErrorInvalidValue);
   // Output (and C) through TMA when their bases and pitches are 16-byte aligned; otherwise the
   // epilogue stores straight from registers.
   const int eb = (flags & G2_OUT_F32) ? 4 : 2;
@@ -629,8 +674,8 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const vo
       p.flags |= G2_TMA_OUT;
     }
   }
-  if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, tD, tC, p, stream);
-  if (a_mn_major) return launch_tc2<true, false>(tA, tB, tD, tC, p, stream);
-  if (b_mn_major) return launch_tc2<false, true>(tA, tB, tD, tC, p, stream);
-  return launch_tc2<false, false>(tA, tB, tD, tC, p, stream);
+  if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, tBh, tD, tC, p, stream);
+  if (a_mn_major) return launch_tc2<true, false>(tA, tB, tBh, tD, tC, p, stream);
+  if (b_mn_major) return launch_tc2<false, true>(tA, tB, tBh, tD, tC, p, stream);
+  return launch_tc2<false, false>(tA, tB, tBh, tD, tC, p, stream);
 }

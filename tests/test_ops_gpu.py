@@ -52,6 +52,34 @@ def test_gemm_cta_pairs(M, N, K, ta, tb):
     assert F.native.read_status() == (0, 0)
 
 
+@pytest.mark.parametrize("M,N,K,ta,tb,mode", [
+    (8192, 2048, 128, False, False, "plain"),      # 256 tiles on 74 pairs: the last 34 are run as 68 half tiles
+    (8192, 2048, 192, False, True, "add"),
+    (2048, 3072, 256, True, False, "plain"),       # 96 tiles: 22 of them halved
+    (2048, 3000, 128, True, False, "fp32"),        # ragged last column tile, fp32 output
+    (4864, 4104, 64, False, True, "add"),          # 19 x 17 = 323 tiles (27 left over), ragged N
+])
+def test_gemm_cta_pairs_half_tiles(M, N, K, ta, tb, mode):
+    """Shapes with more tiles than CTA pairs whose last round is less than half full: those tiles are
+    computed as 256 x 128 halves. Checked against fp32 on the device (the matrices are large)."""
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    a = torch.randn((K, M) if ta else (M, K), device=DEV, generator=g).to(torch.bfloat16)
+    b = torch.randn((N, K) if tb else (K, N), device=DEV, generator=g).to(torch.bfloat16)
+    ref = (a.float().t() if ta else a.float()) @ (b.float().t() if tb else b.float())
+    if mode == "add":
+        c = torch.randn(M, N, device=DEV, generator=g).to(torch.bfloat16)
+        out = F.gemm(a, b, trans_a=ta, trans_b=tb, add=c, impl="2cta")
+        ref = ref + c.float()
+    elif mode == "fp32":
+        out = F.gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32, impl="2cta")
+    else:
+        out = F.gemm(a, b, trans_a=ta, trans_b=tb, impl="2cta")
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_accumulate_and_fp32(bn):
     a, b = bf(300, 264, seed=3), bf(264, 520, seed=4)
