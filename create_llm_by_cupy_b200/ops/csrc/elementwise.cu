@@ -550,15 +550,22 @@ __global__ void rope_inplace_vec_kernel(bf16* __restrict__ buf, const float* __r
 }
 
 // ------------------------------------------------------------------ embedding
+// An id outside [0, V) never touches W: the row is written as zeros (forward) or skipped (backward) and
+// the status word gets error 4 with the kernel id 401 / 402, which the host raises on its next check.
+__device__ __forceinline__ void embedding_bad_id(int* status, int kid) {
+  if (status != nullptr && atomicCAS(status, 0, 4) == 0) status[1] = kid;
+}
+
 __global__ void embedding_fwd_kernel(const bf16* __restrict__ W, const int* __restrict__ idx, bf16* __restrict__ out,
-                                     int M, int H, int pad_id) {
+                                     int M, int H, int pad_id, int V, int* status) {
   const int chunks = H >> 3;
   const size_t total = size_t(M) * chunks;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     const int row = int(i / chunks), c = int(i % chunks);
     const int id = idx[row];
     Pack8 v;
-    if (id == pad_id || id < 0) {
+    if (id >= V && c == 0) embedding_bad_id(status, 401);
+    if (id == pad_id || id < 0 || id >= V) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) v.v[e] = __floats2bfloat162_rn(0.f, 0.f);
     } else {
@@ -568,23 +575,28 @@ __global__ void embedding_fwd_kernel(const bf16* __restrict__ W, const int* __re
   }
 }
 __global__ void embedding_fwd_scalar_kernel(const bf16* __restrict__ W, const int* __restrict__ idx,
-                                            bf16* __restrict__ out, int M, int H, int pad_id) {
+                                            bf16* __restrict__ out, int M, int H, int pad_id, int V, int* status) {
   const size_t total = size_t(M) * H;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     const int row = int(i / H), c = int(i % H);
     const int id = idx[row];
-    out[i] = (id == pad_id || id < 0) ? __float2bfloat16(0.f) : W[size_t(id) * H + c];
+    if (id >= V && c == 0) embedding_bad_id(status, 401);
+    out[i] = (id == pad_id || id < 0 || id >= V) ? __float2bfloat16(0.f) : W[size_t(id) * H + c];
   }
 }
 // dW[idx[m], :] += dout[m, :] for idx != pad. dW is bf16 (packed atomics) or fp32.
 template <typename TW>
 __global__ void embedding_bwd_kernel(TW* __restrict__ dW, const int* __restrict__ idx, const bf16* __restrict__ dout,
-                                     int M, int H, int pad_id) {
+                                     int M, int H, int pad_id, int V, int* status) {
   const int pairs = H >> 1;
   const size_t total = size_t(M) * pairs;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
     const int row = int(i / pairs), c = int(i % pairs);
     const int id = idx[row];
+    if (id >= V) {
+      if (c == 0) embedding_bad_id(status, 402);
+      continue;
+    }
     if (id == pad_id || id < 0) continue;
     const bf162 d = *reinterpret_cast<const bf162*>(dout + size_t(row) * H + 2 * c);
     if constexpr (sizeof(TW) == 2) {
@@ -744,30 +756,35 @@ B200_API int b200_rope_inplace(void* buf, const void* cs, const void* sn, int M,
   return static_cast<int>(cudaGetLastError());
 }
 
-B200_API int b200_embedding_fwd(const void* W, const void* idx, void* out, int M, int H, int pad_id,
+// V: rows of W (vocabulary size).
+B200_API int b200_embedding_fwd(const void* W, const void* idx, void* out, int M, int H, int pad_id, int V,
                                 cudaStream_t st) {
   if (M <= 0) return 0;
   if (H % 8 == 0)
     embedding_fwd_kernel<<<grid_for(size_t(M) * (H / 8), 256), 256, 0, st>>>(
-        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id);
+        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id, V,
+        status_ptr());
   else
     embedding_fwd_scalar_kernel<<<grid_for(size_t(M) * H, 256), 256, 0, st>>>(
-        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id);
+        static_cast<const bf16*>(W), static_cast<const int*>(idx), static_cast<bf16*>(out), M, H, pad_id, V,
+        status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 
 // H must be even. dw_fp32 selects the dtype of dW.
-B200_API int b200_embedding_bwd(void* dW, const void* idx, const void* dout, int M, int H, int pad_id, int dw_fp32,
-                                cudaStream_t st) {
+B200_API int b200_embedding_bwd(void* dW, const void* idx, const void* dout, int M, int H, int pad_id, int V,
+                                int dw_fp32, cudaStream_t st) {
   if (M <= 0) return 0;
   if (H % 2 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const int grid = grid_for(size_t(M) * (H / 2), 256);
   if (dw_fp32)
     embedding_bwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(dW), static_cast<const int*>(idx),
-                                                      static_cast<const bf16*>(dout), M, H, pad_id);
+                                                      static_cast<const bf16*>(dout), M, H, pad_id, V,
+                                                      status_ptr());
   else
     embedding_bwd_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<bf16*>(dW), static_cast<const int*>(idx),
-                                                     static_cast<const bf16*>(dout), M, H, pad_id);
+                                                     static_cast<const bf16*>(dout), M, H, pad_id, V,
+                                                     status_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 

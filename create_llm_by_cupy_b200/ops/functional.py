@@ -201,7 +201,8 @@ def rope_inplace(buf: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, T: int
 
 # --------------------------------------------------------------------------- embedding
 def embedding_fwd(W: torch.Tensor, idx: torch.Tensor, pad_id: int) -> torch.Tensor:
-    """out[m] = W[idx[m]], zeros where idx == pad_id. idx is int32 [M]."""
+    """out[m] = W[idx[m]], zeros where idx == pad_id. idx is int32 [M]. On CUDA an id >= W.shape[0] reads
+    nothing (zeros) and sets native status error 4 (kernel id 401; 402 in the backward)."""
     M = idx.numel()
     H = W.shape[1]
     if not W.is_cuda:
@@ -212,7 +213,7 @@ def embedding_fwd(W: torch.Tensor, idx: torch.Tensor, pad_id: int) -> torch.Tens
     assert idx.dtype == torch.int32 and W.is_contiguous()
     out = torch.empty((M, H), dtype=W.dtype, device=W.device)
     native.check(_lib().b200_embedding_fwd(native.ptr(W), native.ptr(idx), native.ptr(out), M, H, pad_id,
-                                           native.stream_ptr()), "embedding_fwd")
+                                           W.shape[0], native.stream_ptr()), "embedding_fwd")
     native.bump()
     return out
 
@@ -229,7 +230,8 @@ def embedding_bwd(dW: torch.Tensor, idx: torch.Tensor, dout: torch.Tensor, pad_i
     assert idx.dtype == torch.int32 and dW.is_contiguous()
     dout = dout.contiguous()
     native.check(_lib().b200_embedding_bwd(native.ptr(dW), native.ptr(idx), native.ptr(dout), M, H, pad_id,
-                                           int(dW.dtype == torch.float32), native.stream_ptr()), "embedding_bwd")
+                                           dW.shape[0], int(dW.dtype == torch.float32), native.stream_ptr()),
+                 "embedding_bwd")
     native.bump()
     return dW
 

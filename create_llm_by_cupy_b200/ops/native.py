@@ -92,7 +92,8 @@ def raise_on_status() -> None:
     code, kid = read_status()
     if code != 0:
         raise NativeError(f"native kernel {kid} reported error {code} (1: mbarrier wait timed out, "
-                          f"2: peer flag wait timed out, 3: bad argument)")
+                          f"2: peer flag wait timed out, 3: bad argument, 4: index out of range - kernel 401 / 402: "
+                          f"token id >= vocabulary size in the embedding forward / backward)")
 
 
 def check(rc: int, what: str) -> None:

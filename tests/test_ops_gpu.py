@@ -155,6 +155,29 @@ def test_embedding():
         assert (dW[pad] == 0).all()
 
 
+def test_embedding_rejects_ids_beyond_the_vocabulary():
+    """A token id >= V touches no memory: zeros forward, no update backward, status error 4."""
+    V, H, M, pad = 50, 64, 40, 0
+    W = bf(V, H, seed=3).to(DEV)
+    idx = torch.randint(1, V, (M,), dtype=torch.int32)
+    idx[7] = V          # first row past the table
+    idx[19] = 1 << 20
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    out = F.embedding_fwd(W, idx.to(DEV), pad)
+    assert F.native.read_status() == (4, 401)
+    good = idx.clone()
+    good[7] = pad
+    good[19] = pad
+    close(out, F.embedding_fwd(W.float().cpu(), good, pad), rtol=0, atol=0)
+    dW = torch.zeros(V, H, dtype=torch.float32, device=DEV)
+    dout = bf(M, H, seed=4).to(DEV)
+    F.embedding_bwd(dW, idx.to(DEV), dout, pad)
+    assert F.native.read_status() == (4, 402)
+    close(dW, F.embedding_bwd(torch.zeros(V, H), good, dout.float().cpu(), pad), rtol=1e-5, atol=1e-5)
+    assert F.native.read_status() == (0, 0)
+
+
 @pytest.mark.parametrize("D", [32, 64, 128])
 @pytest.mark.parametrize("rope", [False, True])
 def test_flash_attention(D, rope):
