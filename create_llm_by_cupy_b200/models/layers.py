@@ -184,9 +184,11 @@ class GroupedQueryAttention:
             for dst, src in zip((dq, dk, dv), res):
                 dst.copy_(src.to(dst.device, dst.dtype))
         elif self._prerotate(x):
+            fused = F.flash_bwd_can_unrotate(q)          # inverse RoPE in the kernels' epilogues
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
-                             scale=self.scale, rope=None, out=(dq, dk, dv))
-            F.rope_inplace(dkqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0, inverse=True)
+                             scale=self.scale, rope=None, out=(dq, dk, dv), unrotate=tabs if fused else None)
+            if not fused:
+                F.rope_inplace(dkqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0, inverse=True)
         else:
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
                              scale=self.scale, rope=tabs, out=(dq, dk, dv))

@@ -14,6 +14,7 @@
 // is bound by reading dS (T^2 / 2 bf16 per head) from HBM. Every wait is bounded (see ptx.cuh).
 #include "common.cuh"
 #include "ptx.cuh"
+#include "flash_rope_epilogue.cuh"
 
 namespace b200 {
 
@@ -29,6 +30,8 @@ struct DqGemmParams {
   int B, T, QH, KVH;
   int n_tiles;           // 128-row tiles per sequence
   int bchunk;            // batch elements whose K stays in L2 together
+  const float* unrot_cos;   // optional [>= T, 64] fp32 rotary tables: dQ leaves with the inverse rotation applied
+  const float* unrot_sin;
   int* status;
 };
 
@@ -123,7 +126,12 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
     const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16);
     if (mbar_wait(done, 0, abort_flag)) {
       tc_fence_after();
-      bf16* grow = p.dq + b * p.dq_bs + (long long)min(row, T - 1) * p.dq_ts + h * p.dq_hs;
+      const int pos = min(row, T - 1);
+      bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
+      if (p.unrot_cos != nullptr) {
+        store_row_unrot_from_tmem(taddr, grow, 0, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
+        store_row_unrot_from_tmem(taddr, grow, 32, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
+      } else {
 #pragma unroll 1
       for (int c = 0; c < 128; c += 32) {
         uint32_t r[32];
@@ -140,6 +148,7 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
             *reinterpret_cast<uint4*>(grow + c + i) = v;
           }
         }
+      }
       }
     }
   }
@@ -158,7 +167,8 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
 // dq <- dS (as written by the dK/dV kernel into `ds`, [B][QH][Tp][Tp] bf16 with Tp = T rounded up to
 // 128) times K. Strides in elements: k (batch, token, head), dq (batch, token, head).
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
-                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, cudaStream_t st) {
+                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, const float* unrot_cos,
+                         const float* unrot_sin, cudaStream_t st) {
   const int nt = (T + 127) / 128;
   const unsigned long long Tp = (unsigned long long)nt * 128;
   const CUtensorMap* tds = get_tensor_map_bthd(ds, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, 128, 64);
@@ -169,6 +179,7 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
   p.valid_len = static_cast<const int*>(valid_len);
   p.dq_bs = dqs[0]; p.dq_ts = dqs[1]; p.dq_hs = dqs[2];
   p.B = B; p.T = T; p.QH = QH; p.KVH = KVH; p.n_tiles = nt; p.bchunk = bchunk < 1 ? 1 : bchunk;
+  p.unrot_cos = unrot_cos; p.unrot_sin = unrot_sin;
   p.status = status_ptr();
   static bool configured = false;
   if (!configured) {

@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "flash_rope_epilogue.cuh"
 
 namespace b200 {
 
@@ -43,6 +44,8 @@ struct FlashBwdTcParams {
   int pairing;           // dK/dV kernel: 1 = a CTA owns key tiles i and n_tiles - 1 - i, 0 = one key tile per CTA
   bf16* ds;              // optional: dS^T written by the dK/dV kernel, [B][QH][ds_tp][ds_tp] (key, query)
   long long ds_tp;       // its pitch: T rounded up to 128
+  const float* unrot_cos;   // optional [>= T, 64] fp32 tables: dQ and dK leave with the inverse rotary
+  const float* unrot_sin;   // embedding applied (gradients of the un-rotated q and k)
   float scale;
   int* status;
 };
@@ -304,8 +307,13 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (ok) {
       if (mbar_wait(dq_done, 0, abort_flag)) {
         tc_fence_after();
-        bf16* grow = p.dq + b * p.dq_bs + (long long)min(row, T - 1) * p.dq_ts + h * p.dq_hs;
-        store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
+        const int pos = min(row, T - 1);
+        bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
+        if (p.unrot_cos != nullptr)
+          store_row_unrot_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 32, p.unrot_cos + pos * 64,
+                                    p.unrot_sin + pos * 64, row < T);
+        else
+          store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
       }
     }
   }
@@ -638,7 +646,13 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
       bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
       if (d.iters > 0) {
-        store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
+        if (p.unrot_cos != nullptr) {
+          const int pos = min(key, T - 1);
+          store_row_unrot_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 32, p.unrot_cos + pos * 64,
+                                    p.unrot_sin + pos * 64, live);
+        } else {
+          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
+        }
         store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * 64, half * 64 + 64, live);
       } else if (live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
@@ -684,7 +698,8 @@ static SideStream* side_stream() {
 }
 
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
-                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, cudaStream_t st);
+                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, const float* unrot_cos,
+                         const float* unrot_sin, cudaStream_t st);
 
 }  // namespace b200
 
@@ -694,11 +709,13 @@ using namespace b200;
 // computed (b200_flash_delta). strides: q, k, v, dout, dq, dk, dv (3 each: batch, token, head).
 // With a workspace `ds_ws` of B * QH * Tp * Tp bf16 (Tp = T rounded up to 128) the dK/dV kernel also
 // writes dS^T there and dQ is computed from it by a GEMM kernel (flash_attn_bwd_dq.cu) instead of the
-// kernel that recomputes S and dP.
+// kernel that recomputes S and dP. With `unrot_cos` / `unrot_sin` (fp32 tables [>= T][64] of the rotary
+// embedding) dq and dk are written with the inverse rotation applied, i.e. as gradients of the
+// un-rotated q and k.
 B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const void* lse,
                                const void* delta, void* dq, void* dk, void* dv, const void* valid_len,
                                const long long* s, int B, int T, int QH, int KVH, int D, float scale, void* ds_ws,
-                               cudaStream_t st) {
+                               const void* unrot_cos, const void* unrot_sin, cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
   if (D != FB_D || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
   for (int i = 0; i < 21; ++i)
@@ -740,6 +757,11 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // With many dK/dV CTAs per SM there is no tail worth filling and the kernels run back to back.
   p.ds = static_cast<bf16*>(ds_ws);
   p.ds_tp = (long long)nt * 128;
+  p.unrot_cos = static_cast<const float*>(unrot_cos);
+  p.unrot_sin = unrot_cos != nullptr ? static_cast<const float*>(unrot_sin) : nullptr;
+  if (p.unrot_cos != nullptr && (p.unrot_sin == nullptr || ((reinterpret_cast<uintptr_t>(unrot_cos) |
+                                                            reinterpret_cast<uintptr_t>(unrot_sin)) & 15) != 0))
+    return static_cast<int>(cudaErrorInvalidValue);
   const CUtensorMap* tds = tk;           // placeholder when no workspace is given (never dereferenced then)
   if (ds_ws != nullptr) {
     const unsigned long long Tp = (unsigned long long)nt * 128;
@@ -751,7 +773,8 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
   flash_bwd_dkv_tc_kernel<<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
   B200_CHECK(cudaGetLastError());
-  if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, st);
+  if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, p.unrot_cos,
+                                                      p.unrot_sin, st);
   if (dkv_ctas >= 3 * num_sms()) {
     flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
     return static_cast<int>(cudaGetLastError());

@@ -31,6 +31,9 @@ FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 # workspace that is kept per shape, and dQ becomes a GEMM over it. Used while the workspace stays small.
 FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
 FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
+# Inverse rotary embedding of dQ and dK inside the epilogues of the tcgen05 backward kernels (fp32
+# accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns.
+FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
 _ds_ws_cache: dict = {}
 
 
@@ -323,12 +326,22 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     return o, lse
 
 
-def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None):
+def flash_bwd_can_unrotate(q: torch.Tensor) -> bool:
+    """True when ``flash_attn_bwd(..., unrotate=...)`` applies the inverse rotary embedding inside the
+    attention-backward kernels (tcgen05 path, head_dim 128) for this tensor."""
+    return bool(q.is_cuda and q.shape[-1] == 128 and FLASH_TC and FLASH_TC_BWD and FLASH_ROPE_EPILOGUE)
+
+
+def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None, unrotate=None):
     """Gradients (dq, dk, dv) w.r.t. the UN-rotated q, k and v.
 
-    ``out`` may give three preallocated [B,T,heads,D] views (e.g. slices of a packed d(KQV)
-    buffer) to write into.
+    ``rope=(cos, sin)``: q and k are given un-rotated and rotated on the fly. ``unrotate=(cos, sin)``: q and
+    k are given ROTATED (``rope`` must be None) and dq, dk are un-rotated in the kernels' epilogues - only
+    where ``flash_bwd_can_unrotate`` holds (and in the CPU restatement). ``out`` may give three
+    preallocated [B,T,heads,D] views (e.g. slices of a packed d(KQV) buffer) to write into.
     """
+    if unrotate is not None and rope is not None:
+        raise ValueError("flash_attn_bwd: rope and unrotate are exclusive")
     B, T, QH, D = q.shape
     KVH = k.shape[2]
     if scale is None:
@@ -354,6 +367,13 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
                 y1, y2 = x[..., :D // 2], x[..., D // 2:]
                 return torch.cat([y1 * c + y2 * s, y2 * c - y1 * s], -1)
             dqf, dk_ = unrot(dqf), unrot(dk_)
+        if unrotate is not None:
+            uc, us = unrotate[0][:T][None, :, None, :].float(), unrotate[1][:T][None, :, None, :].float()
+
+            def unrot2(x):
+                y1, y2 = x[..., :D // 2], x[..., D // 2:]
+                return torch.cat([y1 * uc + y2 * us, y2 * uc - y1 * us], -1)
+            dqf, dk_ = unrot2(dqf), unrot2(dk_)
         res = (dqf.to(q.dtype), dk_.to(q.dtype), dv_.to(q.dtype))
         if out is not None:
             for dst, src in zip(out, res):
@@ -370,6 +390,8 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
     else:
         dq, dk_, dv_ = out
     delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
+    if unrotate is not None and not flash_bwd_can_unrotate(q):
+        raise ValueError("flash_attn_bwd: unrotate= is only fused on the tcgen05 path (see flash_bwd_can_unrotate)")
     if D == 128 and cos is None and FLASH_TC and FLASH_TC_BWD:
         # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
         arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
@@ -379,10 +401,15 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
         ws = _ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None
+        ucos, usin = unrotate if unrotate is not None else (None, None)
+        if ucos is not None:
+            assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
+                and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == 64
         native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
                                               native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
                                               native.ptr(dv_), native.ptr(valid_len), arr21, B, T, QH, KVH, D,
-                                              _f(scale), native.ptr(ws), native.stream_ptr()), "flash_bwd_tc")
+                                              _f(scale), native.ptr(ws), native.ptr(ucos), native.ptr(usin),
+                                              native.stream_ptr()), "flash_bwd_tc")
         native.bump(3)
         return dq, dk_, dv_
     strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +

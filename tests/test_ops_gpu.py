@@ -313,6 +313,41 @@ def test_flash_attention_tcgen05_multi_tile(T, vl):
         close(a, b, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("dq_gemm", [True, False])
+@pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
+def test_flash_backward_unrotates_in_the_epilogue(T, vl, dq_gemm, monkeypatch):
+    """unrotate=(cos, sin): dQ and dK leave the tcgen05 backward kernels with the inverse rotary embedding
+    applied (both dQ kernels and the dK/dV kernel), equal to the fp32 restatement."""
+    monkeypatch.setattr(F, "FLASH_DQ_GEMM", dq_gemm)
+    B, QH, KVH, D = 2, 8, 2, 128
+    g = torch.Generator().manual_seed(T + 1)
+    q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    do = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    vlt = None if vl is None else torch.tensor(vl, dtype=torch.int32, device=DEV)
+    tabs = F.rope_table(T + 5, D, 10000.0, DEV)
+    assert F.flash_bwd_can_unrotate(q)
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    dq, dk, dv = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt, unrotate=tabs)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    qc, kc, vc = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    vlc = None if vlt is None else vlt.cpu()
+    o_r, lse_r = F.flash_attn_fwd(qc, kc, vc, valid_len=vlc)
+    r = F.flash_attn_bwd(do.float().cpu(), qc, kc, vc, o_r, lse_r, valid_len=vlc,
+                         unrotate=tuple(t.cpu() for t in tabs))
+    for a, b in zip((dq, dk, dv), r):
+        close(a, b, rtol=3e-2, atol=3e-2)
+    # and the two-step form (kernels, then the in-place pass) agrees to bf16 rounding
+    dq2, dk2, dv2 = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)
+    F.rope_inplace(dq2.view(B * T, QH * D), tabs[0], tabs[1], T, QH, D, inverse=True)
+    F.rope_inplace(dk2.view(B * T, KVH * D), tabs[0], tabs[1], T, KVH, D, inverse=True)
+    close(dq, dq2.float().cpu(), rtol=2e-2, atol=2e-2)
+    close(dk, dk2.float().cpu(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(dv, dv2)
+
+
 @pytest.mark.parametrize("gen", [1, 2, 3])
 @pytest.mark.parametrize("T,vl", [(128, None), (384, None), (640, [640, 300]), (1000, None)])
 def test_flash_forward_generations(gen, T, vl, monkeypatch):
