@@ -122,10 +122,11 @@ class GroupedQueryAttention:
         return F.rope_table(max(T, self.T), self.D, self.rope_base, device)
 
     def _prerotate(self, x) -> bool:
-        """head_dim 128 on CUDA runs the tcgen05 attention kernels, which take Q and K already
-        rotated: the rotary embedding is then applied in place to the [K|Q] columns of the packed
-        projection (one pass over 5/6 of it) and undone on d[K|Q] after the backward kernels."""
-        return x.is_cuda and self.D == 128 and self.flash_backend != "none" and F.FLASH_TC
+        """head_dim 128 (and the forward of head_dim 64) on CUDA runs the tcgen05 attention kernels, which
+        take Q and K already rotated: the rotary embedding is then applied in place to the [K|Q] columns of
+        the packed projection (one pass over 5/6 of it) and undone on d[K|Q] in the epilogues of the
+        backward kernels (head_dim 128) or by a pass after them."""
+        return x.is_cuda and self.flash_backend != "none" and F.flash_tc_forward_dim(self.D)
 
     def _project(self, x, T, tabs, first: bool):
         kqv = _weight_gemm(self, x, 0) if first else F.gemm(x, self.params[0])

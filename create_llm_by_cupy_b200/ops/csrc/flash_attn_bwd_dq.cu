@@ -41,6 +41,8 @@ struct DqGemmSmem {
   static constexpr int kTotal = kBar + 7 * 8 + 16 + 1024;
 };
 
+// kD: head dimension (128, or 64: one 64-column box of K per key tile, N = 64, 64 output columns).
+template <int kD>
 __global__ void __launch_bounds__(DQG_THREADS, 1)
 flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_constant__ CUtensorMap tmK,
                          const DqGemmParams p) {
@@ -93,19 +95,19 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
         if (!mbar_wait(&empty[s], ((j / DQG_STAGES) & 1) ^ 1, abort_flag)) break;
         uint8_t* sA = smem + s * DQG_STAGE_BYTES;
         uint8_t* sK = sA + DQG_TILE;
-        mbar_expect_tx(&full[s], DQG_STAGE_BYTES);
+        mbar_expect_tx(&full[s], DQG_TILE + 128 * kD * 2);
         // dS^T tile: key rows j * 128 .., query columns m0 .. (two boxes of 64 queries)
         tma_load_4d(sA, &tmDS, &full[s], m0, h, j * 128, b);
         tma_load_4d(sA + 16384, &tmDS, &full[s], m0 + 64, h, j * 128, b);
         tma_load_4d(sK, &tmK, &full[s], 0, kvh, j * 128, b);
-        tma_load_4d(sK + 16384, &tmK, &full[s], 64, kvh, j * 128, b);
+        if (kD == 128) tma_load_4d(sK + 16384, &tmK, &full[s], 64, kvh, j * 128, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // A = dS^T tile [128 keys (k) x 128 queries (m)], B = K tile [128 keys (k) x 128 d (n)]: both MN-major,
       // 64-element chunks of the contiguous dimension 16 KiB apart, 16 key rows per k-step (2 KiB)
-      constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
+      constexpr uint32_t idesc = umma_idesc_bf16(128, kD, 1, 1);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % DQG_STAGES;
@@ -128,12 +130,12 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
       tc_fence_after();
       const int pos = min(row, T - 1);
       bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
-      if (p.unrot_cos != nullptr) {
+      if (kD == 128 && p.unrot_cos != nullptr) {
         store_row_unrot_from_tmem(taddr, grow, 0, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
         store_row_unrot_from_tmem(taddr, grow, 32, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
       } else {
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
+      for (int c = 0; c < kD; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);     // warp-collective: every lane takes part, rows past T do not store
         tmem_ld_wait();
@@ -167,12 +169,13 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
 // dq <- dS (as written by the dK/dV kernel into `ds`, [B][QH][Tp][Tp] bf16 with Tp = T rounded up to
 // 128) times K. Strides in elements: k (batch, token, head), dq (batch, token, head).
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
-                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, const float* unrot_cos,
-                         const float* unrot_sin, cudaStream_t st) {
+                         const long long* dqs, int B, int T, int QH, int KVH, int D, int bchunk,
+                         const float* unrot_cos, const float* unrot_sin, cudaStream_t st) {
+  if (D != 128 && D != 64) return static_cast<int>(cudaErrorInvalidValue);
   const int nt = (T + 127) / 128;
   const unsigned long long Tp = (unsigned long long)nt * 128;
   const CUtensorMap* tds = get_tensor_map_bthd(ds, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, 128, 64);
-  const CUtensorMap* tk = get_tensor_map_bthd(k, B, T, KVH, 128, ks[0], ks[1], ks[2], 128, 64);
+  const CUtensorMap* tk = get_tensor_map_bthd(k, B, T, KVH, D, ks[0], ks[1], ks[2], 128, 64);
   if (!tds || !tk) return static_cast<int>(cudaErrorInvalidValue);
   DqGemmParams p;
   p.dq = static_cast<bf16*>(dq);
@@ -183,11 +186,16 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
   p.status = status_ptr();
   static bool configured = false;
   if (!configured) {
-    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dq_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dq_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    DqGemmSmem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dq_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     DqGemmSmem::kTotal));
     configured = true;
   }
-  flash_bwd_dq_gemm_kernel<<<nt * QH * B, DQG_THREADS, DqGemmSmem::kTotal, st>>>(*tds, *tk, p);
+  if (D == 128)
+    flash_bwd_dq_gemm_kernel<128><<<nt * QH * B, DQG_THREADS, DqGemmSmem::kTotal, st>>>(*tds, *tk, p);
+  else
+    flash_bwd_dq_gemm_kernel<64><<<nt * QH * B, DQG_THREADS, DqGemmSmem::kTotal, st>>>(*tds, *tk, p);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -364,6 +364,9 @@ __device__ __forceinline__ DkvPass dkv_pass(int ntile, int T, int R, int vlen) {
   return d;
 }
 
+// kD: head dimension (128, or 64: one 64-column box per K / V / Q / dO tile, four k-steps in the score
+// products, N = 64 in the gradient products, 64 live columns in dV and dK).
+template <int kD>
 __global__ void __launch_bounds__(FBT_THREADS, 1)
 flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                         const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -442,11 +445,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (ps > 0) {             // K / V of the previous pass are read by its MMAs until they have all completed
           if (!mbar_wait(acc_done, (ps - 1) & 1, abort_flag)) break;
         }
-        mbar_expect_tx(kv_full, 2 * FB_TILE);
+        mbar_expect_tx(kv_full, 2 * 128 * kD * 2);
         tma_load_4d(smem + FdkvSmem::kK, &tmK, kv_full, 0, kvh, d.n0, b);
-        tma_load_4d(smem + FdkvSmem::kK + 16384, &tmK, kv_full, 64, kvh, d.n0, b);
+        if (kD == 128) tma_load_4d(smem + FdkvSmem::kK + 16384, &tmK, kv_full, 64, kvh, d.n0, b);
         tma_load_4d(smem + FdkvSmem::kV, &tmV, kv_full, 0, kvh, d.n0, b);
-        tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, d.n0, b);
+        if (kD == 128) tma_load_4d(smem + FdkvSmem::kV + 16384, &tmV, kv_full, 64, kvh, d.n0, b);
         ++kv_loads;
         for (int it = 0; it < d.iters; ++it, ++g) {
           const int s = g % FKV_ST;
@@ -455,11 +458,11 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           if (!mbar_wait(&q_empty[s], ((g / FKV_ST) & 1) ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sQ = smem + FdkvSmem::kQ + s * 2 * FKV_QTILE;
           uint8_t* sDO = sQ + FKV_QTILE;
-          mbar_expect_tx(&q_full[s], 2 * FKV_QTILE);
+          mbar_expect_tx(&q_full[s], 2 * FKV_BQ * kD * 2);
           tma_load_4d(sQ, &tmQ, &q_full[s], 0, h, m0, b);
-          tma_load_4d(sQ + 8192, &tmQ, &q_full[s], 64, h, m0, b);
+          if (kD == 128) tma_load_4d(sQ + 8192, &tmQ, &q_full[s], 64, h, m0, b);
           tma_load_4d(sDO, &tmDO, &q_full[s], 0, h, m0, b);
-          tma_load_4d(sDO + 8192, &tmDO, &q_full[s], 64, h, m0, b);
+          if (kD == 128) tma_load_4d(sDO + 8192, &tmDO, &q_full[s], 64, h, m0, b);
         }
       }
       (void)kv_loads;
@@ -488,20 +491,20 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, FKV_BQ, 0, 0);   // [128 keys x 64 q], K-major operands
-      constexpr uint32_t idesc_g = umma_idesc_bf16(128, FB_D, 0, 1);     // [128 keys x 128 d], B MN-major
+      constexpr uint32_t idesc_g = umma_idesc_bf16(128, kD, 0, 1);       // [128 keys x d], B MN-major
       const uint32_t aK = smem_u32(smem + FdkvSmem::kK), aV = smem_u32(smem + FdkvSmem::kV);
       auto issue_scores = [&](int g) {
         const int s = g & 1;
         const uint32_t aQ = smem_u32(smem + FdkvSmem::kQ + (g % FKV_ST) * 2 * FKV_QTILE), aDO = aQ + FKV_QTILE;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;     // 128-row tiles
           const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;      // 64-row tiles
           umma_bf16_ss(tmem_base + kColST + s * 64, umma_smem_desc(aK + offk, 16, 1024),
                        umma_smem_desc(aQ + offq, 16, 1024), idesc_s, kk != 0);
         }
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t offk = (kk >> 2) * 16384 + (kk & 3) * 32;
           const uint32_t offq = (kk >> 2) * 8192 + (kk & 3) * 32;
           umma_bf16_ss(tmem_base + kColDPT + s * 64, umma_smem_desc(aV + offk, 16, 1024),
@@ -645,18 +648,19 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const bool live = key < T;
       bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
       bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
+      constexpr int kHalfCols = kD / 2;          // dK / dV columns each warpgroup stores
       if (d.iters > 0) {
-        if (p.unrot_cos != nullptr) {
+        if (kD == 128 && p.unrot_cos != nullptr) {
           const int pos = min(key, T - 1);
           store_row_unrot_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 32, p.unrot_cos + pos * 64,
                                     p.unrot_sin + pos * 64, live);
         } else {
-          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 64, half * 64 + 64, live);
+          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * kHalfCols, (half + 1) * kHalfCols, live);
         }
-        store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * 64, half * 64 + 64, live);
+        store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * kHalfCols, (half + 1) * kHalfCols, live);
       } else if (live) {
         const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int c = half * 64; c < half * 64 + 64; c += 8) {
+        for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 8) {
           *reinterpret_cast<uint4*>(krow + c) = z;
           *reinterpret_cast<uint4*>(vrow + c) = z;
         }
@@ -698,8 +702,8 @@ static SideStream* side_stream() {
 }
 
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
-                         const long long* dqs, int B, int T, int QH, int KVH, int bchunk, const float* unrot_cos,
-                         const float* unrot_sin, cudaStream_t st);
+                         const long long* dqs, int B, int T, int QH, int KVH, int D, int bchunk,
+                         const float* unrot_cos, const float* unrot_sin, cudaStream_t st);
 
 }  // namespace b200
 
@@ -717,7 +721,9 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
                                const long long* s, int B, int T, int QH, int KVH, int D, float scale, void* ds_ws,
                                const void* unrot_cos, const void* unrot_sin, cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
-  if (D != FB_D || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
+  // head_dim 64 exists only in the form with a dS workspace (dK/dV kernel + dQ GEMM), without the fused un-rotation
+  if ((D != FB_D && D != 64) || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if (D == 64 && (ds_ws == nullptr || unrot_cos != nullptr)) return static_cast<int>(cudaErrorInvalidValue);
   for (int i = 0; i < 21; ++i)
     if (s[i] % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const CUtensorMap* tq128 = get_tensor_map_bthd(q, B, T, QH, D, s[0], s[1], s[2], 128, 64);
@@ -739,7 +745,9 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   if (!configured) {
     B200_CHECK(cudaFuncSetAttribute(flash_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     FdqSmem::kTotal));
-    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FdkvSmem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     FdkvSmem::kTotal));
     configured = true;
   }
@@ -771,10 +779,13 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // few key tiles per SM: pair a long and a short one per CTA (equal work, no tail); many: one per CTA
   p.pairing = nt * KVH * B < 3 * num_sms() ? 1 : 0;
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
-  flash_bwd_dkv_tc_kernel<<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
+  if (D == 128)
+    flash_bwd_dkv_tc_kernel<128><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
+  else
+    flash_bwd_dkv_tc_kernel<64><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
   B200_CHECK(cudaGetLastError());
-  if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, p.bchunk, p.unrot_cos,
-                                                      p.unrot_sin, st);
+  if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, D, p.bchunk,
+                                                      p.unrot_cos, p.unrot_sin, st);
   if (dkv_ctas >= 3 * num_sms()) {
     flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
     return static_cast<int>(cudaGetLastError());

@@ -1,4 +1,4 @@
-// Causal GQA flash-attention forward on tcgen05, third generation (head_dim 128).
+// Causal GQA flash-attention forward on tcgen05, third generation (head_dim 128 or 64).
 //
 // One CTA owns TWO consecutive 128-row query tiles of one (batch, head) and walks the key tiles
 // once for both. Each query tile has its own softmax warpgroup, its own score buffer and its own
@@ -23,6 +23,10 @@
 // S(j) MMAs have run, long before the V slot, so the TMA load of K(j+2) gets a full iteration of
 // lead. The output tile is staged in the (by then unused) Q tile in the 128-byte swizzle and
 // stored with cp.async.bulk.tensor. Every wait is bounded (see ptx.cuh).
+//
+// head_dim 64 (template parameter) uses the same layout with half of everything that depends on it:
+// one 64-column box per Q / K / V / O tile instead of two, four k-steps in S = Q K^T, N = 64 in O += P V,
+// 64 live columns in each O accumulator.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -110,6 +114,7 @@ __device__ __forceinline__ float f3_row_p(uint32_t (&sc)[128], float sl2, float 
   return rs0 + rs1;
 }
 
+template <int kD>
 __global__ void __launch_bounds__(F3_THREADS, 1)
 flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -143,6 +148,7 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     nt[w] = (mt * 128 < T) ? min(mt + 1, kv_tiles) : 0;
   }
   const int nmax = max(nt[0], nt[1]);
+  constexpr uint32_t kTileBytes = 128 * kD * 2;          // live bytes of a Q / K / V tile (its slot stays 32 KiB)
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -173,38 +179,38 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, (nt[1] > 0 ? 2 : 1) * F3_TILE);
+      mbar_expect_tx(q_full, (nt[1] > 0 ? 2 : 1) * kTileBytes);
       for (int w = 0; w < 2; ++w) {
         if (nt[w] == 0) continue;
         uint8_t* sQ = smem + F3Smem::kQ + w * F3_TILE;
         tma_load_4d(sQ, &tmQ, q_full, 0, h, (2 * pt + w) * 128, b);
-        tma_load_4d(sQ + 16384, &tmQ, q_full, 64, h, (2 * pt + w) * 128, b);
+        if (kD == 128) tma_load_4d(sQ + 16384, &tmQ, q_full, 64, h, (2 * pt + w) * 128, b);
       }
       for (int j = 0; j < nmax; ++j) {
         const int s = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
         if (!mbar_wait(&k_empty[s], par, abort_flag)) break;
         uint8_t* sK = smem + F3Smem::kK + s * F3_TILE;
-        mbar_expect_tx(&k_full[s], F3_TILE);
+        mbar_expect_tx(&k_full[s], kTileBytes);
         tma_load_4d(sK, &tmK, &k_full[s], 0, kvh, j * 128, b);
-        tma_load_4d(sK + 16384, &tmK, &k_full[s], 64, kvh, j * 128, b);
+        if (kD == 128) tma_load_4d(sK + 16384, &tmK, &k_full[s], 64, kvh, j * 128, b);
         if (!mbar_wait(&v_empty[s], par, abort_flag)) break;
         uint8_t* sV = smem + F3Smem::kV + s * F3_TILE;
-        mbar_expect_tx(&v_full[s], F3_TILE);
+        mbar_expect_tx(&v_full[s], kTileBytes);
         tma_load_4d(sV, &tmV, &v_full[s], 0, kvh, j * 128, b);
-        tma_load_4d(sV + 16384, &tmV, &v_full[s], 64, kvh, j * 128, b);
+        if (kD == 128) tma_load_4d(sV + 16384, &tmV, &v_full[s], 64, kvh, j * 128, b);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kD, 0, 1);
       auto issue_s = [&](int w, int j) {
         const uint32_t aQ = smem_u32(smem + F3Smem::kQ + w * F3_TILE);
         const uint32_t aK = smem_u32(smem + F3Smem::kK + (j & 1) * F3_TILE);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16_ss(tmem_base + kColS + w * 128, umma_smem_desc(aQ + off, 16, 1024),
                        umma_smem_desc(aK + off, 16, 1024), idesc_s, kk != 0);
@@ -293,7 +299,7 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const float corr = need ? exp2f(m_ref - mx) : 1.f;
           l_run *= corr;
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
+          for (int c = 0; c < kD / 16; ++c) {
             uint32_t t[16];
             tmem_ld_32x32b_x16(tO + c * 16, t);
             tmem_ld_wait();
@@ -325,7 +331,7 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         uint8_t* stg = smem + F3Smem::kQ + w * F3_TILE;
         const uint32_t swz = uint32_t(rloc & 7);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < kD / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tO + c * 32, r);
           tmem_ld_wait();
@@ -349,7 +355,7 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (q == 0 && lane == 0) {
           if (mbar_wait(&stage_bar[w], 0, abort_flag)) {
             tma_store_4d(&tmO, stg, 0, h, mt * 128, b);
-            tma_store_4d(&tmO, stg + 16384, 64, h, mt * 128, b);
+            if (kD == 128) tma_store_4d(&tmO, stg + 16384, 64, h, mt * 128, b);
             tma_store_commit();
             tma_store_wait_read<0>();
           }
@@ -373,13 +379,13 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
 using namespace b200;
 
-// Same contract as b200_flash_fwd_tc (inputs already rotated, head_dim 128); the output must be
+// Same contract as b200_flash_fwd_tc (inputs already rotated) for head_dim 128 or 64; the output must be
 // TMA-addressable (16-byte aligned base, strides that are multiples of 8 elements).
 B200_API int b200_flash_fwd_tc3(const void* q, const void* k, const void* v, void* o, void* lse, const void* valid_len,
                                 const long long* strides, int B, int T, int QH, int KVH, int D, float scale,
                                 cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
-  if (D != 128 || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
+  if ((D != 128 && D != 64) || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
   for (int i = 0; i < 12; ++i)
     if (strides[i] % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(o) & 15) != 0) return static_cast<int>(cudaErrorInvalidValue);
@@ -395,10 +401,16 @@ B200_API int b200_flash_fwd_tc3(const void* q, const void* k, const void* v, voi
   p.status = status_ptr();
   static bool configured = false;
   if (!configured) {
-    B200_CHECK(cudaFuncSetAttribute(flash_fwd_tc3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F3Smem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_fwd_tc3_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    F3Smem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_fwd_tc3_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    F3Smem::kTotal));
     configured = true;
   }
   dim3 grid((T + 255) / 256, QH, B);
-  flash_fwd_tc3_kernel<<<grid, F3_THREADS, F3Smem::kTotal, st>>>(*tq, *tk, *tv, *to, p);
+  if (D == 128)
+    flash_fwd_tc3_kernel<128><<<grid, F3_THREADS, F3Smem::kTotal, st>>>(*tq, *tk, *tv, *to, p);
+  else
+    flash_fwd_tc3_kernel<64><<<grid, F3_THREADS, F3Smem::kTotal, st>>>(*tq, *tk, *tv, *to, p);
   return static_cast<int>(cudaGetLastError());
 }

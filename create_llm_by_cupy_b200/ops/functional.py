@@ -31,6 +31,16 @@ FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 # workspace that is kept per shape, and dQ becomes a GEMM over it. Used while the workspace stays small.
 FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
 FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
+# head_dim 64 on the tcgen05 kernels: the third-generation forward and the dK/dV kernel + dQ GEMM are
+# templates on the head dimension. The un-rotation of dQ / dK is a separate pass for this size.
+FLASH_TC_D64 = _os.environ.get("B200_FLASH_TC_D64", "1") != "0"
+
+
+def flash_tc_forward_dim(D: int) -> bool:
+    """True when the forward for this head_dim runs on the tcgen05 kernels (which take rotated q, k)."""
+    return bool(FLASH_TC and (D == 128 or (D == 64 and FLASH_TC_D64 and FLASH_FWD_GEN == 3)))
+
+
 # Inverse rotary embedding of dQ and dK inside the epilogues of the tcgen05 backward kernels (fp32
 # accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns.
 FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
@@ -309,7 +319,7 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     o = torch.empty((B, T, QH, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     strides = _strides3(q) + _strides3(k) + _strides3(v) + _strides3(o)
-    if D == 128 and cos is None and FLASH_TC:
+    if cos is None and flash_tc_forward_dim(D):
         # tcgen05 / TMEM kernel (inputs already rotated)
         arr = (ctypes.c_longlong * 12)(*strides)
         fwd_fn = {3: _lib().b200_flash_fwd_tc3, 2: _lib().b200_flash_fwd_tc2}.get(FLASH_FWD_GEN, _lib().b200_flash_fwd_tc)
@@ -392,7 +402,11 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
     delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     if unrotate is not None and not flash_bwd_can_unrotate(q):
         raise ValueError("flash_attn_bwd: unrotate= is only fused on the tcgen05 path (see flash_bwd_can_unrotate)")
-    if D == 128 and cos is None and FLASH_TC and FLASH_TC_BWD:
+    # head_dim 64 has the tcgen05 backward only in the form with a dS workspace (dK/dV kernel + dQ GEMM)
+    ws64 = None
+    if D == 64 and cos is None and FLASH_TC and FLASH_TC_BWD and FLASH_TC_D64 and FLASH_DQ_GEMM:
+        ws64 = _ds_workspace(q.device, B, QH, T)
+    if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or ws64 is not None):
         # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
         arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
         native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
@@ -400,10 +414,10 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
-        ws = _ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None
+        ws = ws64 if D == 64 else (_ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None)
         ucos, usin = unrotate if unrotate is not None else (None, None)
         if ucos is not None:
-            assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
+            assert D == 128 and ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
                 and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == 64
         native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
                                               native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),

@@ -313,6 +313,42 @@ def test_flash_attention_tcgen05_multi_tile(T, vl):
         close(a, b, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("T,vl", [(128, None), (333, [333, 100]), (640, [640, 300]), (1000, None)])
+def test_flash_head_dim_64_on_tcgen05(T, vl, monkeypatch):
+    """head_dim 64 runs the same tcgen05 forward and backward kernels (template parameter); checked against
+    fp32 and against the mma.sync kernels they replace."""
+    B, QH, KVH, D = 2, 6, 2, 64
+    g = torch.Generator().manual_seed(T + 64)
+    q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    vlt = None if vl is None else torch.tensor(vl, dtype=torch.int32, device=DEV)
+    assert F.flash_tc_forward_dim(D)
+    n0 = F.native.launch_count()
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0) and F.native.launch_count() == n0 + 1
+    o_r, lse_r = F.flash_attn_fwd(q.float().cpu(), k.float().cpu(), v.float().cpu(),
+                                  valid_len=None if vlt is None else vlt.cpu())
+    close(o, o_r)
+    ok = torch.isfinite(lse_r)
+    close(lse.cpu()[ok], lse_r[ok], rtol=1e-2, atol=2e-2)
+    do = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    n0 = F.native.launch_count()
+    dq, dk, dv = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)     # delta, dK/dV (+ dS^T), dQ GEMM
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0) and F.native.launch_count() == n0 + 3
+    r = F.flash_attn_bwd(do.float().cpu(), q.float().cpu(), k.float().cpu(), v.float().cpu(), o_r, lse_r,
+                         valid_len=None if vlt is None else vlt.cpu())
+    for a, b in zip((dq, dk, dv), r):
+        close(a, b, rtol=3e-2, atol=3e-2)
+    monkeypatch.setattr(F, "FLASH_TC_D64", False)          # the mma.sync kernels this path replaces
+    o2, lse2 = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    close(o, o2)
+    for a, b in zip((dq, dk, dv), F.flash_attn_bwd(do, q, k, v, o2, lse2, valid_len=vlt)):
+        close(a, b, rtol=3e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("dq_gemm", [True, False])
 @pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
 def test_flash_backward_unrotates_in_the_epilogue(T, vl, dq_gemm, monkeypatch):
