@@ -130,9 +130,9 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
       tc_fence_after();
       const int pos = min(row, T - 1);
       bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
-      if (kD == 128 && p.unrot_cos != nullptr) {
-        store_row_unrot_from_tmem(taddr, grow, 0, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
-        store_row_unrot_from_tmem(taddr, grow, 32, p.unrot_cos + pos * 64, p.unrot_sin + pos * 64, row < T);
+      if (p.unrot_cos != nullptr) {
+        store_row_unrot_from_tmem<kD>(taddr, grow, 0, kD / 2, p.unrot_cos + pos * (kD / 2), p.unrot_sin + pos * (kD / 2),
+                                      row < T);
       } else {
 #pragma unroll 1
       for (int c = 0; c < kD; c += 32) {

@@ -310,8 +310,8 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int pos = min(row, T - 1);
         bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
         if (p.unrot_cos != nullptr)
-          store_row_unrot_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 32, p.unrot_cos + pos * 64,
-                                    p.unrot_sin + pos * 64, row < T);
+          store_row_unrot_from_tmem<128>(tmem_base + lane_sel + kColDQ, grow, half * 32, 32, p.unrot_cos + pos * 64,
+                                         p.unrot_sin + pos * 64, row < T);
         else
           store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
       }
@@ -650,10 +650,10 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
       constexpr int kHalfCols = kD / 2;          // dK / dV columns each warpgroup stores
       if (d.iters > 0) {
-        if (kD == 128 && p.unrot_cos != nullptr) {
+        if (p.unrot_cos != nullptr) {
           const int pos = min(key, T - 1);
-          store_row_unrot_from_tmem(tmem_base + lane_sel + kColDK, krow, half * 32, p.unrot_cos + pos * 64,
-                                    p.unrot_sin + pos * 64, live);
+          store_row_unrot_from_tmem<kD>(tmem_base + lane_sel + kColDK, krow, half * (kD / 4), kD / 4,
+                                        p.unrot_cos + pos * (kD / 2), p.unrot_sin + pos * (kD / 2), live);
         } else {
           store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * kHalfCols, (half + 1) * kHalfCols, live);
         }
@@ -713,7 +713,7 @@ using namespace b200;
 // computed (b200_flash_delta). strides: q, k, v, dout, dq, dk, dv (3 each: batch, token, head).
 // With a workspace `ds_ws` of B * QH * Tp * Tp bf16 (Tp = T rounded up to 128) the dK/dV kernel also
 // writes dS^T there and dQ is computed from it by a GEMM kernel (flash_attn_bwd_dq.cu) instead of the
-// kernel that recomputes S and dP. With `unrot_cos` / `unrot_sin` (fp32 tables [>= T][64] of the rotary
+// kernel that recomputes S and dP. With `unrot_cos` / `unrot_sin` (fp32 tables [>= T][D / 2] of the rotary
 // embedding) dq and dk are written with the inverse rotation applied, i.e. as gradients of the
 // un-rotated q and k.
 B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const void* lse,
@@ -721,9 +721,9 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
                                const long long* s, int B, int T, int QH, int KVH, int D, float scale, void* ds_ws,
                                const void* unrot_cos, const void* unrot_sin, cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
-  // head_dim 64 exists only in the form with a dS workspace (dK/dV kernel + dQ GEMM), without the fused un-rotation
+  // head_dim 64 exists only in the form with a dS workspace (dK/dV kernel + dQ GEMM)
   if ((D != FB_D && D != 64) || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
-  if (D == 64 && (ds_ws == nullptr || unrot_cos != nullptr)) return static_cast<int>(cudaErrorInvalidValue);
+  if (D == 64 && ds_ws == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   for (int i = 0; i < 21; ++i)
     if (s[i] % 8 != 0) return static_cast<int>(cudaErrorInvalidValue);
   const CUtensorMap* tq128 = get_tensor_map_bthd(q, B, T, QH, D, s[0], s[1], s[2], 128, 64);

@@ -1,8 +1,8 @@
-// Epilogue shared by the tcgen05 attention-backward kernels (head_dim 128): store one fp32 accumulator
+// Epilogue shared by the tcgen05 attention-backward kernels (head_dim 128 or 64): store one fp32 accumulator
 // row from tensor memory as bf16, applying the inverse rotary embedding on the way.
 //
 // The kernels work on rotated Q and K, so their dQ and dK are gradients of the rotated tensors. The
-// gradient of the un-rotated one is the inverse rotation of the same row (pairs (j, j + 64), angle of
+// gradient of the un-rotated one is the inverse rotation of the same row (pairs (j, j + D/2), angle of
 // the row's position): y1 = x1 c + x2 s, y2 = x2 c - x1 s. Doing it here, on the fp32 accumulator a
 // thread already holds, removes the separate in-place pass over the [dK | dQ] columns.
 #pragma once
@@ -11,17 +11,19 @@
 
 namespace b200 {
 
-// Pairs j in [j0, j0 + 32) of the row at TMEM address `taddr` (column 0 of the 128-wide accumulator).
-// cs_row / sn_row: the 64 cosines / sines of this row's position (fp32, 16-byte aligned). The loads are
-// warp-collective: every lane calls this, `active` only predicates the global stores.
-__device__ __forceinline__ void store_row_unrot_from_tmem(uint32_t taddr, bf16* grow, int j0,
+// Pairs j in [j0, j0 + nj) (nj a multiple of 16) of the row at TMEM address `taddr` (column 0 of the
+// kD-wide accumulator). cs_row / sn_row: the kD / 2 cosines / sines of this row's position (fp32, 16-byte
+// aligned). The loads are warp-collective: every lane calls this, `active` only predicates the global stores.
+template <int kD>
+__device__ __forceinline__ void store_row_unrot_from_tmem(uint32_t taddr, bf16* grow, int j0, int nj,
                                                           const float* __restrict__ cs_row,
                                                           const float* __restrict__ sn_row, bool active) {
 #pragma unroll 1
-  for (int j = j0; j < j0 + 32; j += 16) {
+  constexpr int kHalf = kD / 2;
+  for (int j = j0; j < j0 + nj; j += 16) {
     uint32_t a[16], b[16];
     tmem_ld_32x32b_x16(taddr + j, a);
-    tmem_ld_32x32b_x16(taddr + 64 + j, b);
+    tmem_ld_32x32b_x16(taddr + kHalf + j, b);
     tmem_ld_wait();
     if (!active) continue;
     uint32_t y1[8], y2[8];
@@ -47,8 +49,8 @@ __device__ __forceinline__ void store_row_unrot_from_tmem(uint32_t taddr, bf16* 
     }
     *reinterpret_cast<uint4*>(grow + j) = make_uint4(y1[0], y1[1], y1[2], y1[3]);
     *reinterpret_cast<uint4*>(grow + j + 8) = make_uint4(y1[4], y1[5], y1[6], y1[7]);
-    *reinterpret_cast<uint4*>(grow + 64 + j) = make_uint4(y2[0], y2[1], y2[2], y2[3]);
-    *reinterpret_cast<uint4*>(grow + 64 + j + 8) = make_uint4(y2[4], y2[5], y2[6], y2[7]);
+    *reinterpret_cast<uint4*>(grow + kHalf + j) = make_uint4(y2[0], y2[1], y2[2], y2[3]);
+    *reinterpret_cast<uint4*>(grow + kHalf + j + 8) = make_uint4(y2[4], y2[5], y2[6], y2[7]);
   }
 }
 

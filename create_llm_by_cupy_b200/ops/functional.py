@@ -32,7 +32,7 @@ FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
 FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
 # head_dim 64 on the tcgen05 kernels: the third-generation forward and the dK/dV kernel + dQ GEMM are
-# templates on the head dimension. The un-rotation of dQ / dK is a separate pass for this size.
+# templates on the head dimension.
 FLASH_TC_D64 = _os.environ.get("B200_FLASH_TC_D64", "1") != "0"
 
 
@@ -44,6 +44,9 @@ def flash_tc_forward_dim(D: int) -> bool:
 # Inverse rotary embedding of dQ and dK inside the epilogues of the tcgen05 backward kernels (fp32
 # accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns.
 FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
+# The same for head_dim 64: available, off by default - on the 125 M model the separate pass was faster
+# (11.8 vs 12.1 ms per step), its dK/dV CTAs are short and the table reads sit on their critical path.
+FLASH_ROPE_EPILOGUE_D64 = _os.environ.get("B200_FLASH_ROPE_EPILOGUE_D64", "0") != "0"
 _ds_ws_cache: dict = {}
 
 
@@ -338,8 +341,17 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
 
 def flash_bwd_can_unrotate(q: torch.Tensor) -> bool:
     """True when ``flash_attn_bwd(..., unrotate=...)`` applies the inverse rotary embedding inside the
-    attention-backward kernels (tcgen05 path, head_dim 128) for this tensor."""
-    return bool(q.is_cuda and q.shape[-1] == 128 and FLASH_TC and FLASH_TC_BWD and FLASH_ROPE_EPILOGUE)
+    attention-backward kernels (tcgen05 path: head_dim 128, or head_dim 64 with its dS workspace) for this
+    tensor [B, T, heads, D]."""
+    if not (q.is_cuda and FLASH_TC and FLASH_TC_BWD and FLASH_ROPE_EPILOGUE):
+        return False
+    D = q.shape[-1]
+    if D == 128:
+        return True
+    B, T, QH = q.shape[0], q.shape[1], q.shape[2]
+    tp = (T + 127) // 128 * 128
+    return bool(D == 64 and FLASH_ROPE_EPILOGUE_D64 and FLASH_TC_D64 and FLASH_DQ_GEMM
+                and B * QH * tp * tp * 2 <= FLASH_DQ_GEMM_MAX_BYTES)
 
 
 def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None, unrotate=None):
@@ -417,8 +429,8 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         ws = ws64 if D == 64 else (_ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None)
         ucos, usin = unrotate if unrotate is not None else (None, None)
         if ucos is not None:
-            assert D == 128 and ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
-                and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == 64
+            assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
+                and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == D // 2
         native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
                                               native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
                                               native.ptr(dv_), native.ptr(valid_len), arr21, B, T, QH, KVH, D,

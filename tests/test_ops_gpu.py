@@ -349,13 +349,14 @@ def test_flash_head_dim_64_on_tcgen05(T, vl, monkeypatch):
         close(a, b, rtol=3e-2, atol=3e-2)
 
 
-@pytest.mark.parametrize("dq_gemm", [True, False])
+@pytest.mark.parametrize("D,dq_gemm", [(128, True), (128, False), (64, True)])
 @pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
-def test_flash_backward_unrotates_in_the_epilogue(T, vl, dq_gemm, monkeypatch):
+def test_flash_backward_unrotates_in_the_epilogue(T, vl, D, dq_gemm, monkeypatch):
     """unrotate=(cos, sin): dQ and dK leave the tcgen05 backward kernels with the inverse rotary embedding
     applied (both dQ kernels and the dK/dV kernel), equal to the fp32 restatement."""
     monkeypatch.setattr(F, "FLASH_DQ_GEMM", dq_gemm)
-    B, QH, KVH, D = 2, 8, 2, 128
+    monkeypatch.setattr(F, "FLASH_ROPE_EPILOGUE_D64", True)
+    B, QH, KVH = 2, 8, 2
     g = torch.Generator().manual_seed(T + 1)
     q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
     k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
