@@ -1,18 +1,19 @@
 """Stand-alone causal GQA flash-attention benchmark (forward + backward with RoPE, base 10000).
 
-Shapes: batch 8, 32 query / 8 KV heads, head_dim 128, bf16, seq lengths 1024..16384; Q, K, V, dO
+Shapes: batch 8, 32 query / 8 KV heads, head_dim 128 (or 64: --head-dim), bf16, seq lengths 1024..16384; Q, K, V, dO
 drawn i.i.d. N(0, 1) with seed 0. Two implementations are timed with CUDA events (3 warm-up, then
 the median of 5; inputs of every length exceed the 126 MB L2 from T = 4096 up, below that a 256 MB
 buffer is written between iterations):
 
   tcgen05 : rotary embedding applied in place to Q and K (one elementwise pass, included in the
-            time), tcgen05/TMEM forward, dK/dV and dQ kernels, inverse rotation of dQ and dK;
+            time), tcgen05/TMEM forward, dK/dV and dQ kernels, inverse rotation of dQ and dK (in the
+            kernels' epilogues where that form exists, else one more pass);
   mma     : the mma.sync kernels with the rotation fused into their tile loads.
 
 FLOPs counted: 4*B*H*T^2*D/2 forward, 2.5x that backward (the usual 5-GEMM convention; the
 kernels here recompute S and dP in both backward kernels, which is not counted).
 
-    python bench_flash.py [--seqs 1024,2048,...] [--json out.json]
+    python bench_flash.py [--seqs 1024,2048,...] [--head-dim 128] [--json out.json]
 """
 from __future__ import annotations
 
@@ -49,9 +50,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seqs", default="1024,2048,4096,8192,16384")
     ap.add_argument("--json", default=None)
+    ap.add_argument("--head-dim", type=int, default=128, choices=(64, 128))
     a = ap.parse_args()
     dev = "cuda"
-    B, QH, KVH, D = 8, 32, 8, 128
+    B, QH, KVH, D = 8, 32, 8, a.head_dim
     peak = 1648.3
     try:
         peak = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))["bf16_tflops"]
@@ -90,8 +92,11 @@ def main():
             def bwd():
                 if impl == "tcgen05":
                     F.FLASH_TC = True
-                    F.flash_attn_bwd(do, q, k, v, st["o"], st["lse"], rope=None, out=(dq, dk, dv))
-                    F.rope_inplace(dpacked, tabs[0], tabs[1], T, KVH + QH, D, col0=0, inverse=True)
+                    fused = F.flash_bwd_can_unrotate(q)
+                    F.flash_attn_bwd(do, q, k, v, st["o"], st["lse"], rope=None, out=(dq, dk, dv),
+                                     unrotate=tabs if fused else None)
+                    if not fused:
+                        F.rope_inplace(dpacked, tabs[0], tabs[1], T, KVH + QH, D, col0=0, inverse=True)
                 else:
                     F.FLASH_TC = False
                     F.flash_attn_bwd(do, q, k, v, st["o"], st["lse"], rope=tabs, out=(dq, dk, dv))

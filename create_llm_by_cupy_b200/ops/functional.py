@@ -28,7 +28,8 @@ FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 
 
 # dQ from stored dS: the dK/dV kernel writes dS^T (B * QH * Tp^2 bf16, Tp = T rounded up to 128) into a
-# workspace that is kept per shape, and dQ becomes a GEMM over it. Used while the workspace stays small.
+# workspace that is kept per shape, and dQ becomes a GEMM over it. When the whole batch does not fit the
+# limit the backward runs in chunks of batch elements that do.
 FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
 FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
 # head_dim 64 on the tcgen05 kernels: the third-generation forward and the dK/dV kernel + dQ GEMM are
@@ -48,6 +49,12 @@ FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
 # (11.8 vs 12.1 ms per step), its dK/dV CTAs are short and the table reads sit on their critical path.
 FLASH_ROPE_EPILOGUE_D64 = _os.environ.get("B200_FLASH_ROPE_EPILOGUE_D64", "0") != "0"
 _ds_ws_cache: dict = {}
+
+
+def _ds_batch_chunk(B: int, QH: int, T: int) -> int:
+    """Batch elements whose dS^T (QH * Tp^2 bf16 each) fit the workspace limit together; 0 if not even one."""
+    tp = (T + 127) // 128 * 128
+    return min(B, FLASH_DQ_GEMM_MAX_BYTES // (QH * tp * tp * 2))
 
 
 def _ds_workspace(device, B: int, QH: int, T: int):
@@ -348,10 +355,8 @@ def flash_bwd_can_unrotate(q: torch.Tensor) -> bool:
     D = q.shape[-1]
     if D == 128:
         return True
-    B, T, QH = q.shape[0], q.shape[1], q.shape[2]
-    tp = (T + 127) // 128 * 128
     return bool(D == 64 and FLASH_ROPE_EPILOGUE_D64 and FLASH_TC_D64 and FLASH_DQ_GEMM
-                and B * QH * tp * tp * 2 <= FLASH_DQ_GEMM_MAX_BYTES)
+                and _ds_batch_chunk(q.shape[0], q.shape[2], q.shape[1]) >= 1)
 
 
 def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None, unrotate=None):
@@ -414,11 +419,10 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
     delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     if unrotate is not None and not flash_bwd_can_unrotate(q):
         raise ValueError("flash_attn_bwd: unrotate= is only fused on the tcgen05 path (see flash_bwd_can_unrotate)")
-    # head_dim 64 has the tcgen05 backward only in the form with a dS workspace (dK/dV kernel + dQ GEMM)
-    ws64 = None
-    if D == 64 and cos is None and FLASH_TC and FLASH_TC_BWD and FLASH_TC_D64 and FLASH_DQ_GEMM:
-        ws64 = _ds_workspace(q.device, B, QH, T)
-    if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or ws64 is not None):
+    # Batch elements per call whose dS^T workspace stays within the limit (0: not even one). head_dim 64 has
+    # the tcgen05 backward only in the form with that workspace (dK/dV kernel + dQ GEMM).
+    bc = _ds_batch_chunk(B, QH, T) if (FLASH_DQ_GEMM and (D == 128 or FLASH_TC_D64)) else 0
+    if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or (D == 64 and bc >= 1)):
         # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
         arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
         native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
@@ -426,17 +430,22 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
-        ws = ws64 if D == 64 else (_ds_workspace(q.device, B, QH, T) if FLASH_DQ_GEMM else None)
+        ws = _ds_workspace(q.device, bc, QH, T) if bc >= 1 else None
+        chunks = [(b0, min(b0 + bc, B)) for b0 in range(0, B, bc)] if bc >= 1 else [(0, B)]
         ucos, usin = unrotate if unrotate is not None else (None, None)
         if ucos is not None:
             assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
                 and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == D // 2
-        native.check(_lib().b200_flash_bwd_tc(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(dout),
-                                              native.ptr(lse), native.ptr(delta), native.ptr(dq), native.ptr(dk_),
-                                              native.ptr(dv_), native.ptr(valid_len), arr21, B, T, QH, KVH, D,
-                                              _f(scale), native.ptr(ws), native.ptr(ucos), native.ptr(usin),
-                                              native.stream_ptr()), "flash_bwd_tc")
-        native.bump(3)
+        for b0, b1 in chunks:       # slices along the batch keep every stride
+            vl = None if valid_len is None else valid_len[b0:b1]
+            native.check(_lib().b200_flash_bwd_tc(native.ptr(q[b0:b1]), native.ptr(k[b0:b1]), native.ptr(v[b0:b1]),
+                                                  native.ptr(dout[b0:b1]), native.ptr(lse[b0:b1]),
+                                                  native.ptr(delta[b0:b1]), native.ptr(dq[b0:b1]),
+                                                  native.ptr(dk_[b0:b1]), native.ptr(dv_[b0:b1]), native.ptr(vl),
+                                                  arr21, b1 - b0, T, QH, KVH, D, _f(scale), native.ptr(ws),
+                                                  native.ptr(ucos), native.ptr(usin), native.stream_ptr()),
+                         "flash_bwd_tc")
+        native.bump(1 + 2 * len(chunks))
         return dq, dk_, dv_
     strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +
                _strides3(dq) + _strides3(dk_) + _strides3(dv_))

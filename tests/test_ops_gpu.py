@@ -349,6 +349,28 @@ def test_flash_head_dim_64_on_tcgen05(T, vl, monkeypatch):
         close(a, b, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_flash_backward_in_batch_chunks(D, monkeypatch):
+    """When the dS^T workspace of the whole batch exceeds the limit, the backward runs chunk by chunk."""
+    B, T, QH, KVH = 3, 300, 4, 2
+    g = torch.Generator().manual_seed(D)
+    q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(B, T, KVH, D, generator=g).to(torch.bfloat16).to(DEV)
+    do = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
+    vlt = torch.tensor([300, 17, 200], dtype=torch.int32, device=DEV)
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vlt)
+    whole = [t.clone() for t in F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)]
+    monkeypatch.setattr(F, "FLASH_DQ_GEMM_MAX_BYTES", QH * 384 * 384 * 2)        # room for one batch element
+    assert F._ds_batch_chunk(B, QH, T) == 1
+    n0 = F.native.launch_count()
+    parts = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0) and F.native.launch_count() == n0 + 1 + 2 * B
+    for a, b in zip(parts, whole):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("D,dq_gemm", [(128, True), (128, False), (64, True)])
 @pytest.mark.parametrize("T,vl", [(640, None), (333, [333, 100])])
 def test_flash_backward_unrotates_in_the_epilogue(T, vl, D, dq_gemm, monkeypatch):
