@@ -437,11 +437,15 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
             assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
                 and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == D // 2
         for b0, b1 in chunks:       # slices along the batch keep every stride
-            vl = None if valid_len is None else valid_len[b0:b1]
-            native.check(_lib().b200_flash_bwd_tc(native.ptr(q[b0:b1]), native.ptr(k[b0:b1]), native.ptr(v[b0:b1]),
-                                                  native.ptr(dout[b0:b1]), native.ptr(lse[b0:b1]),
-                                                  native.ptr(delta[b0:b1]), native.ptr(dq[b0:b1]),
-                                                  native.ptr(dk_[b0:b1]), native.ptr(dv_[b0:b1]), native.ptr(vl),
+            whole = b1 - b0 == B
+
+            def part(t):
+                return t if (whole or t is None) else t[b0:b1]
+            native.check(_lib().b200_flash_bwd_tc(native.ptr(part(q)), native.ptr(part(k)), native.ptr(part(v)),
+                                                  native.ptr(part(dout)), native.ptr(part(lse)),
+                                                  native.ptr(part(delta)), native.ptr(part(dq)),
+                                                  native.ptr(part(dk_)), native.ptr(part(dv_)),
+                                                  native.ptr(part(valid_len)),
                                                   arr21, b1 - b0, T, QH, KVH, D, _f(scale), native.ptr(ws),
                                                   native.ptr(ucos), native.ptr(usin), native.stream_ptr()),
                          "flash_bwd_tc")
