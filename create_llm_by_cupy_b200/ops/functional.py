@@ -31,7 +31,7 @@ FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 # workspace that is kept per shape, and dQ becomes a GEMM over it. When the whole batch does not fit the
 # limit the backward runs in chunks of batch elements that do.
 FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
-FLASH_DQ_GEMM_MAX_BYTES = 4 << 30
+FLASH_DQ_GEMM_MAX_BYTES = int(float(_os.environ.get("B200_FLASH_DS_WS_GIB", "4")) * (1 << 30))
 # head_dim 64 on the tcgen05 kernels: the third-generation forward and the dK/dV kernel + dQ GEMM are
 # templates on the head dimension.
 FLASH_TC_D64 = _os.environ.get("B200_FLASH_TC_D64", "1") != "0"
@@ -419,10 +419,14 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
     delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     if unrotate is not None and not flash_bwd_can_unrotate(q):
         raise ValueError("flash_attn_bwd: unrotate= is only fused on the tcgen05 path (see flash_bwd_can_unrotate)")
-    # Batch elements per call whose dS^T workspace stays within the limit (0: not even one). head_dim 64 has
-    # the tcgen05 backward only in the form with that workspace (dK/dV kernel + dQ GEMM).
+    # Batch elements per call whose dS^T workspace stays within the limit; when not even one fits, KV-head
+    # groups of one batch element per call (kc, 0: not even one group). head_dim 64 has the tcgen05
+    # backward only in the form with that workspace (dK/dV kernel + dQ GEMM).
     bc = _ds_batch_chunk(B, QH, T) if (FLASH_DQ_GEMM and (D == 128 or FLASH_TC_D64)) else 0
-    if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or (D == 64 and bc >= 1)):
+    kc = 0
+    if bc == 0 and FLASH_DQ_GEMM and (D == 128 or FLASH_TC_D64):
+        kc = min(KVH, _ds_batch_chunk(KVH, QH // KVH, T))       # a KV-head group holds QH / KVH query heads
+    if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or (D == 64 and (bc >= 1 or kc >= 1))):
         # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
         arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
         native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
@@ -430,23 +434,38 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
-        ws = _ds_workspace(q.device, bc, QH, T) if bc >= 1 else None
-        chunks = [(b0, min(b0 + bc, B)) for b0 in range(0, B, bc)] if bc >= 1 else [(0, B)]
+        R = QH // KVH
+        if bc >= 1:
+            ws = _ds_workspace(q.device, bc, QH, T)
+            chunks = [(b0, min(b0 + bc, B), 0, KVH) for b0 in range(0, B, bc)]
+        elif kc >= 1:
+            ws = _ds_workspace(q.device, 1, kc * R, T)
+            chunks = [(b0, b0 + 1, g0, min(g0 + kc, KVH)) for b0 in range(B) for g0 in range(0, KVH, kc)]
+        else:
+            ws, chunks = None, [(0, B, 0, KVH)]
         ucos, usin = unrotate if unrotate is not None else (None, None)
         if ucos is not None:
             assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
                 and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == D // 2
-        for b0, b1 in chunks:       # slices along the batch keep every stride
-            whole = b1 - b0 == B
+        for b0, b1, g0, g1 in chunks:       # slices along batch and heads keep every stride
+            whole = b1 - b0 == B and g1 - g0 == KVH
 
-            def part(t):
-                return t if (whole or t is None) else t[b0:b1]
-            native.check(_lib().b200_flash_bwd_tc(native.ptr(part(q)), native.ptr(part(k)), native.ptr(part(v)),
-                                                  native.ptr(part(dout)), native.ptr(part(lse)),
-                                                  native.ptr(part(delta)), native.ptr(part(dq)),
-                                                  native.ptr(part(dk_)), native.ptr(part(dv_)),
-                                                  native.ptr(part(valid_len)),
-                                                  arr21, b1 - b0, T, QH, KVH, D, _f(scale), native.ptr(ws),
+            def part(t, kind):      # kind: 0 = [B] vector, 1 = [B, T, kv heads, D], 2 = [B, T, q heads, D], 3 = [B, q heads, T]
+                if whole or t is None:
+                    return t
+                if kind == 0:
+                    return t[b0:b1]
+                if kind == 1:
+                    return t[b0:b1, :, g0:g1]
+                if kind == 2:
+                    return t[b0:b1, :, g0 * R:g1 * R]
+                return t[b0:b1, g0 * R:g1 * R]       # contiguous: head slices only come with one batch element
+            native.check(_lib().b200_flash_bwd_tc(native.ptr(part(q, 2)), native.ptr(part(k, 1)), native.ptr(part(v, 1)),
+                                                  native.ptr(part(dout, 2)), native.ptr(part(lse, 3)),
+                                                  native.ptr(part(delta, 3)), native.ptr(part(dq, 2)),
+                                                  native.ptr(part(dk_, 1)), native.ptr(part(dv_, 1)),
+                                                  native.ptr(part(valid_len, 0)),
+                                                  arr21, b1 - b0, T, (g1 - g0) * R, g1 - g0, D, _f(scale), native.ptr(ws),
                                                   native.ptr(ucos), native.ptr(usin), native.stream_ptr()),
                          "flash_bwd_tc")
         native.bump(1 + 2 * len(chunks))

@@ -369,6 +369,15 @@ def test_flash_backward_in_batch_chunks(D, monkeypatch):
     assert F.native.read_status() == (0, 0) and F.native.launch_count() == n0 + 1 + 2 * B
     for a, b in zip(parts, whole):
         assert torch.equal(a, b)
+    # not even one batch element fits: one KV-head group (QH / KVH query heads) of one batch element per call
+    monkeypatch.setattr(F, "FLASH_DQ_GEMM_MAX_BYTES", (QH // KVH) * 384 * 384 * 2)
+    assert F._ds_batch_chunk(B, QH, T) == 0
+    n0 = F.native.launch_count()
+    parts = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vlt)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0) and F.native.launch_count() == n0 + 1 + 2 * B * KVH
+    for a, b in zip(parts, whole):
+        assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("D,dq_gemm", [(128, True), (128, False), (64, True)])
