@@ -64,6 +64,8 @@ def main():
                     help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-adam-overlap", action="store_true", help="AdamW as one kernel after the backward")
+    ap.add_argument("--keep-params", action="store_true",
+                    help="keep gathered block parameters from the forward until their backward (one gather per step)")
     ap.add_argument("--opt", default=None, choices=["gpu", "cpu"], help="override the config's optimizer tier")
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
@@ -113,6 +115,8 @@ def main():
               seed=0, grad_bucket_elems=25_000_000)
     if c["zero"] == "2.5":
         md.update(zero25_replica_ratio=0.5, zero25_replica_policy="largest_first")
+    if args.keep_params:
+        md.update(keep_params_until_backward=True)
     fused = None
     use_fused = world > 1 and args.fused != 0
     if use_fused:
@@ -208,6 +212,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": c["name"], "global_batch": B * accum * world, "seq_len": T,
                        "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par, "cuda_graph": bool(trainer.cuda_graph),
+                       "keep_params_until_backward": bool(args.keep_params),
                        "collectives": (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
                                        else ("nccl" if world > 1 else "none")),
                        "l2": f"not flushed: a step streams more than {28e-9 * n_par / world + 2e-9 * n_par:.1f} GB of weights and "

@@ -177,6 +177,10 @@ class Cupa_ver4:
         g = d.get
         self.keep_layer_num = max(1, int(g("keep_layer_num", getattr(self, "keep_layer_num", 1))))
         self.keep_embedding_until_backward = bool(g("keep_embedding_until_backward", True))
+        # Keep every block's gathered parameters from the training forward until its backward has used
+        # them (one all-gather per unit and step instead of two; the model's bf16 parameters stay
+        # resident on every rank during the step - 2.3 GB for the 1.3 B model).
+        self.keep_params_until_backward = bool(g("keep_params_until_backward", False))
         # On a 180 GB part keeping activations beats recomputing them; the reference's defaults
         # (False) remain selectable.
         self.gqa_cache_out_value = bool(g("gqa_cache_out_value", True))
@@ -314,7 +318,8 @@ class Cupa_ver4:
                 gqa, feed, norm1, norm2 = mods[s:s + self.one_cycle_num]
                 h = gqa.forward(norm1.forward(h, train_flg), B, T, valid_len, residual=h, train_flg=train_flg)
                 h = feed.forward(norm2.forward(h, train_flg), residual=h, train_flg=train_flg)
-            manager.release_modules(mods)
+            if not (train_flg and self.keep_params_until_backward):
+                manager.release_modules(mods)
         self.x_pa = x_pa
 
         manager.gather_module(self.norm_)

@@ -42,6 +42,19 @@ def test_world_sizes_agree(tmp_path, cfg, tag):
             assert res[0]["gathered"] > 0 and res[0]["reduced"] > 0
 
 
+def test_keep_params_until_backward_gathers_each_block_once(tmp_path):
+    """keep_params_until_backward: same losses and parameters bit for bit, fewer bytes gathered (also with
+    two micro-batches per step, where every forward / backward pair gathers once)."""
+    for accum in (1, 2):
+        l0, p0, r0 = run(2, tmp_path, dict(zero="3", accum=accum), f"regather{accum}")
+        l1, p1, r1 = run(2, tmp_path, dict(zero="3", accum=accum, model=dict(keep_params_until_backward=True)),
+                         f"keep{accum}")
+        np.testing.assert_array_equal(l0, l1)
+        for a, b in zip(p0, p1):
+            np.testing.assert_array_equal(a, b)
+        assert r1[0]["gathered"] < 0.75 * r0[0]["gathered"]
+
+
 def test_accumulation_across_ranks(tmp_path):
     base_l, base_p, _ = run(1, tmp_path, dict(zero="3"), "acc_ref")
     l, p, _ = run(2, tmp_path, dict(zero="3", accum=2), "acc")
