@@ -129,8 +129,15 @@ class GroupedQueryAttention:
         return x.is_cuda and self.flash_backend != "none" and F.flash_tc_forward_dim(self.D)
 
     def _project(self, x, T, tabs, first: bool):
+        """K | Q | V projection; on the pre-rotating path K and Q leave it rotated - inside the GEMM's epilogue
+        where that form exists, else by an in-place pass over the [K|Q] columns."""
+        pre = self._prerotate(x)
+        rope_cols = (self.KVH + self.QH) * self.D
+        if (pre and getattr(self, "pending_gather", None) is None
+                and F.gemm_rope_fusable(x, self.params[0], self.D, rope_cols)):
+            return F.gemm_rope(x, self.params[0], tabs[0], tabs[1], T, self.D, rope_cols)
         kqv = _weight_gemm(self, x, 0) if first else F.gemm(x, self.params[0])
-        if self._prerotate(x):
+        if pre:
             F.rope_inplace(kqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0)
         return kqv
 

@@ -67,6 +67,13 @@ struct Gemm2Params {
   // 256 x 128 halves (items t_full + 2 i and t_full + 2 i + 1). The launcher halves the tiles of a last,
   // less than half filled round of CTA pairs, which then takes about half a tile time instead of a whole one.
   int t_full, n_items;
+  // Rotary embedding in the epilogue (bf16 output through TMA only): the columns below rope_cols are heads of
+  // width rope_dim (128 or 64) whose pairs (j, j + rope_dim / 2) are rotated by the angle of position
+  // row % rope_T. The tables are fp32 and TRANSPOSED, [rope_dim / 2][rope_ld]: a thread owns one row, so the 32
+  // lanes of a warp (consecutive positions) then read consecutive words. Null rope_cos: off.
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_T, rope_cols, rope_dim, rope_ld;
 };
 
 // A work item: tile coordinates, first column and width.
@@ -199,7 +206,7 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
   nb = r / gsz;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool kRope>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
@@ -405,6 +412,14 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int row0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
         const int n0 = wi.n0;
         const int ngroups = wi.bn / gcols;
+        const bool rope_on = kRope && !out_f32 && n0 < p.rope_cols;
+        const float* cs_row = nullptr;      // element j of this row's tables is at [j * rope_ld]
+        const float* sn_row = nullptr;
+        if (rope_on) {
+          const int pos = min(row0 + r, p.M - 1) % p.rope_T;
+          cs_row = p.rope_cos + pos;
+          sn_row = p.rope_sin + pos;
+        }
         if (elected) {
           tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
           arm(gcount, n0, row0);
@@ -441,7 +456,31 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             uint32_t v[64];
             tmem_ld_32x32b_x32(taddr + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
             tmem_ld_32x32b_x32(taddr + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            tmem_ld_wait();
+            const bool rope_g = kRope && rope_on && n0 + g * 64 < p.rope_cols;
+            if (rope_g && p.rope_dim == 128) {
+              // this group is one half of a 128-wide head; the other half is the neighbouring group
+              uint32_t w[64];
+              tmem_ld_32x32b_x32(taddr + (g ^ 1) * 64, *reinterpret_cast<uint32_t(*)[32]>(&w[0]));
+              tmem_ld_32x32b_x32(taddr + (g ^ 1) * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&w[32]));
+              tmem_ld_wait();
+              const float sgn = (g & 1) ? 1.f : -1.f;      // first half: x1 c - x2 s; second half: x2 c + x1 s
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                const float c = __ldg(cs_row + size_t(j) * p.rope_ld), sn = __ldg(sn_row + size_t(j) * p.rope_ld);
+                v[j] = __float_as_uint(fmaf(__uint_as_float(v[j]), c, sgn * __uint_as_float(w[j]) * sn));
+              }
+            } else {
+              tmem_ld_wait();
+              if (rope_g) {                                  // 64-wide head: both halves are in this group
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float c = __ldg(cs_row + size_t(j) * p.rope_ld), sn = __ldg(sn_row + size_t(j) * p.rope_ld);
+                  const float x1 = __uint_as_float(v[j]), x2 = __uint_as_float(v[j + 32]);
+                  v[j] = __float_as_uint(fmaf(x1, c, -x2 * sn));
+                  v[j + 32] = __float_as_uint(fmaf(x2, c, x1 * sn));
+                }
+              }
+            }
             if (g == ngroups - 1) {
               tc_fence_before();
               __syncwarp();
@@ -591,10 +630,10 @@ static int* next_sched_slot() {
   return base[dev] + 2 * (next++ % G2_SCHED_SLOTS);
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool kRope = false>
 static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tBh, const CUtensorMap* tD,
                       const CUtensorMap* tC, const Gemm2Params& p, cudaStream_t stream) {
-  auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN, kRope>;
   static bool configured = false;
   if (!configured) {
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
@@ -641,10 +680,40 @@ B200_API int b200_gemm_2cta_half_tiles(int on) {
   return old;
 }
 
+static int gemm_2cta_run(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int lda, int ldb,
+                         int ldd, int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
+                         const float* rope_cos, const float* rope_sin, int rope_T, int rope_ld, int rope_cols,
+                         int rope_dim, cudaStream_t stream);
+
 // Same contract as b200_gemm_bf16 (TMA-legal operands only: 16-byte aligned bases and pitches).
 B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int lda,
                                  int ldb, int ldd, int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
                                  cudaStream_t stream) {
+  return gemm_2cta_run(A, B, D, C, M, N, K, lda, ldb, ldd, ldc, a_mn_major, b_mn_major, flags, alpha, nullptr, nullptr,
+                       0, 0, 0, 0, stream);
+}
+
+// D = rope(A B): the first `rope_cols` columns of the bf16 result are heads of width `rope_dim` (128 or 64,
+// rope_cols a multiple of it) that leave the epilogue rotated by the angle of position row % rope_T (fp32 tables,
+// transposed: [rope_dim / 2][rope_ld], rope_ld >= rope_T). No C operand; D must be TMA-addressable (16-byte
+// aligned base and pitch).
+B200_API int b200_gemm_bf16_2cta_rope(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,
+                                      int ldd, int a_mn_major, int b_mn_major, int flags, const void* rope_cos,
+                                      const void* rope_sin, int rope_T, int rope_ld, int rope_cols, int rope_dim,
+                                      cudaStream_t stream) {
+  if ((rope_dim != 128 && rope_dim != 64) || rope_T <= 0 || rope_ld < rope_T || rope_cols <= 0 ||
+      rope_cols % rope_dim != 0 || rope_cols > N || rope_cos == nullptr || rope_sin == nullptr ||
+      (flags & (G2_OUT_F32 | G2_ADD_C)) != 0 || (reinterpret_cast<uintptr_t>(D) & 15) != 0 || (ldd % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  return gemm_2cta_run(A, B, D, nullptr, M, N, K, lda, ldb, ldd, 0, a_mn_major, b_mn_major, flags, 1.0f,
+                       static_cast<const float*>(rope_cos), static_cast<const float*>(rope_sin), rope_T, rope_ld,
+                       rope_cols, rope_dim, stream);
+}
+
+static int gemm_2cta_run(const void* A, const void* B, void* D, const void* C, int M, int N, int K, int lda, int ldb,
+                         int ldd, int ldc, int a_mn_major, int b_mn_major, int flags, float alpha,
+                         const float* rope_cos, const float* rope_sin, int rope_T, int rope_ld, int rope_cols,
+                         int rope_dim, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0)
@@ -652,6 +721,8 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const vo
   Gemm2Params p;
   p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
   p.status = status_ptr();
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T; p.rope_cols = rope_cols; p.rope_dim = rope_dim;
+  p.rope_ld = rope_ld;
   const CUtensorMap* tA = a_mn_major ? get_tensor_map_2d(A, K, M, lda, 64, 64, 2, SWIZZLE_128B_)
                                      : get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
   const CUtensorMap* tB = b_mn_major ? get_tensor_map_2d(B, K, N, ldb, 64, 64, 2, SWIZZLE_128B_)
@@ -673,6 +744,11 @@ B200_API int b200_gemm_bf16_2cta(const void* A, const void* B, void* D, const vo
       tC = c;
       p.flags |= G2_TMA_OUT;
     }
+  }
+  if (p.rope_cos != nullptr) {       // the rotating epilogue exists for row-major A (x W) and TMA output
+    if (!(p.flags & G2_TMA_OUT) || a_mn_major) return static_cast<int>(cudaErrorInvalidValue);
+    if (b_mn_major) return launch_tc2<false, true, true>(tA, tB, tBh, tD, tC, p, stream);
+    return launch_tc2<false, false, true>(tA, tB, tBh, tD, tC, p, stream);
   }
   if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, tBh, tD, tC, p, stream);
   if (a_mn_major) return launch_tc2<true, false>(tA, tB, tBh, tD, tC, p, stream);

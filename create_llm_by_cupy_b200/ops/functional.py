@@ -13,7 +13,7 @@ import math
 import torch
 
 from . import native
-from .gemm import gemm, wgrad_gemm, wgrad_join  # noqa: F401  (re-exported)
+from .gemm import gemm, gemm_rope, gemm_rope_fusable, wgrad_gemm, wgrad_join  # noqa: F401  (re-exported)
 
 _f = ctypes.c_float
 

@@ -128,6 +128,55 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     return out
 
 
+# Rotary embedding in the epilogue of the CTA-pair kernel instead of an in-place pass over the output.
+GEMM_ROPE_EPILOGUE = _os.environ.get("B200_GEMM_ROPE_EPILOGUE", "1") != "0"
+
+
+_rope_t_cache: dict = {}
+
+
+def gemm_rope_fusable(a: torch.Tensor, b: torch.Tensor, head_dim: int, rope_cols: int) -> bool:
+    """True when ``gemm_rope(a, b, ...)`` (``a`` [M, K], ``b`` [K, N], both row-major bf16) runs with the
+    rotation fused into the GEMM epilogue."""
+    if not (GEMM_ROPE_EPILOGUE and a.is_cuda and GEMM_IMPL == "2cta" and head_dim in (64, 128)):
+        return False
+    M, N = a.shape[0], b.shape[1]
+    return bool(a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and M >= 256 and N >= 256 and N % 8 == 0
+                and rope_cols % head_dim == 0 and 0 < rope_cols <= N
+                and a.stride(1) == 1 and b.stride(1) == 1 and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0
+                and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
+def gemm_rope(a: torch.Tensor, b: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, T: int, head_dim: int,
+              rope_cols: int) -> torch.Tensor:
+    """``a @ b`` whose first ``rope_cols`` output columns are heads of width ``head_dim`` rotated by the
+    rotary embedding of position ``row % T`` (half-split pairing, tables fp32 [>= T, head_dim / 2]).
+    Only where ``gemm_rope_fusable`` holds."""
+    M, K = a.shape
+    N = b.shape[1]
+    assert gemm_rope_fusable(a, b, head_dim, rope_cols)
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    assert cos.shape[0] >= T and cos.shape[1] == head_dim // 2
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    native.status_tensor()
+    _apply_dynamic()
+    flags = GEMM_WHOLE_TILES if _wgrad_pending.get(a.device.index, False) else 0
+    # the epilogue reads the tables transposed ([head_dim / 2][positions]): a thread owns a row, so a warp
+    # then reads consecutive words
+    key = (cos.data_ptr(), sin.data_ptr(), tuple(cos.shape))
+    tt = _rope_t_cache.get(key)
+    if tt is None:
+        if len(_rope_t_cache) > 16:
+            _rope_t_cache.clear()
+        tt = _rope_t_cache[key] = (cos.t().contiguous(), sin.t().contiguous(), cos, sin)   # keeps the sources alive
+    rc = native.lib().b200_gemm_bf16_2cta_rope(
+        native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0), b.stride(0), N, 0, 1, flags,
+        native.ptr(tt[0]), native.ptr(tt[1]), T, tt[0].shape[1], rope_cols, head_dim, native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_rope")
+    native.bump()
+    return out
+
+
 def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_shape: tuple, *, trans_b: bool,
                    peer_slices, seg: torch.Tensor, epoch: int, n_copy: int = 8, add: torch.Tensor | None = None,
                    out: torch.Tensor | None = None, trans_a: bool = False, only_b: bool = False) -> torch.Tensor:

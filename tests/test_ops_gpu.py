@@ -80,6 +80,31 @@ def test_gemm_cta_pairs_half_tiles(M, N, K, ta, tb, mode):
     assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
 
 
+@pytest.mark.parametrize("M,N,K,T,D,rope_cols", [
+    (1000, 768, 136, 250, 128, 640),          # ragged M, rotation ends inside a tile
+    (8192, 3072, 128, 2048, 128, 2560),       # the 1.3 B projection shape (part of its tiles run as halves)
+    (2048, 1280, 192, 1024, 64, 1024),        # 64-wide heads
+    (512, 512, 64, 512, 64, 512),
+])
+def test_gemm_with_rotary_epilogue(M, N, K, T, D, rope_cols):
+    """gemm_rope = GEMM followed by the in-place rotary pass over the first rope_cols columns."""
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    a = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    b = (torch.randn(K, N, device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    cos, sin = F.rope_table(T, D, 10000.0, DEV)
+    assert F.gemm_rope_fusable(a, b, D, rope_cols)
+    out = F.gemm_rope(a, b, cos, sin, T, D, rope_cols)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    ref = (a.float() @ b.float()).cpu()
+    F.rope_inplace(ref, cos.cpu(), sin.cpu(), T, rope_cols // D, D, col0=0)
+    close(out, ref, rtol=1e-2, atol=2e-2)
+    two_step = F.gemm(a, b)
+    F.rope_inplace(two_step, cos, sin, T, rope_cols // D, D, col0=0)
+    close(out, two_step, rtol=1e-2, atol=2e-2)
+    assert torch.equal(out[:, rope_cols:], F.gemm(a, b)[:, rope_cols:])
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_accumulate_and_fp32(bn):
     a, b = bf(300, 264, seed=3), bf(264, 520, seed=4)
