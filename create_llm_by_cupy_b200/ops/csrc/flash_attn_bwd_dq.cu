@@ -30,8 +30,9 @@ struct DqGemmParams {
   int B, T, QH, KVH;
   int n_tiles;           // 128-row tiles per sequence
   int bchunk;            // batch elements whose K stays in L2 together
-  const float* unrot_cos;   // optional [>= T, 64] fp32 rotary tables: dQ leaves with the inverse rotation applied
-  const float* unrot_sin;
+  const float* unrot_cos;   // optional fp32 rotary tables, transposed [kD / 2][unrot_ld]: dQ leaves with the
+  const float* unrot_sin;   // inverse rotation applied
+  int unrot_ld;
   int* status;
 };
 
@@ -131,8 +132,7 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
       const int pos = min(row, T - 1);
       bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
       if (p.unrot_cos != nullptr) {
-        store_row_unrot_from_tmem<kD>(taddr, grow, 0, kD / 2, p.unrot_cos + pos * (kD / 2), p.unrot_sin + pos * (kD / 2),
-                                      row < T);
+        store_row_unrot_from_tmem<kD>(taddr, grow, 0, kD / 2, p.unrot_cos + pos, p.unrot_sin + pos, p.unrot_ld, row < T);
       } else {
 #pragma unroll 1
       for (int c = 0; c < kD; c += 32) {
@@ -170,7 +170,7 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
 // 128) times K. Strides in elements: k (batch, token, head), dq (batch, token, head).
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
                          const long long* dqs, int B, int T, int QH, int KVH, int D, int bchunk,
-                         const float* unrot_cos, const float* unrot_sin, cudaStream_t st) {
+                         const float* unrot_cos, const float* unrot_sin, int unrot_ld, cudaStream_t st) {
   if (D != 128 && D != 64) return static_cast<int>(cudaErrorInvalidValue);
   const int nt = (T + 127) / 128;
   const unsigned long long Tp = (unsigned long long)nt * 128;
@@ -182,7 +182,7 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
   p.valid_len = static_cast<const int*>(valid_len);
   p.dq_bs = dqs[0]; p.dq_ts = dqs[1]; p.dq_hs = dqs[2];
   p.B = B; p.T = T; p.QH = QH; p.KVH = KVH; p.n_tiles = nt; p.bchunk = bchunk < 1 ? 1 : bchunk;
-  p.unrot_cos = unrot_cos; p.unrot_sin = unrot_sin;
+  p.unrot_cos = unrot_cos; p.unrot_sin = unrot_sin; p.unrot_ld = unrot_ld;
   p.status = status_ptr();
   static bool configured = false;
   if (!configured) {

@@ -44,8 +44,9 @@ struct FlashBwdTcParams {
   int pairing;           // dK/dV kernel: 1 = a CTA owns key tiles i and n_tiles - 1 - i, 0 = one key tile per CTA
   bf16* ds;              // optional: dS^T written by the dK/dV kernel, [B][QH][ds_tp][ds_tp] (key, query)
   long long ds_tp;       // its pitch: T rounded up to 128
-  const float* unrot_cos;   // optional [>= T, 64] fp32 tables: dQ and dK leave with the inverse rotary
-  const float* unrot_sin;   // embedding applied (gradients of the un-rotated q and k)
+  const float* unrot_cos;   // optional fp32 tables, transposed [D / 2][unrot_ld >= T]: dQ and dK leave with the
+  const float* unrot_sin;   // inverse rotary embedding applied (gradients of the un-rotated q and k)
+  int unrot_ld;
   float scale;
   int* status;
 };
@@ -310,8 +311,8 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int pos = min(row, T - 1);
         bf16* grow = p.dq + b * p.dq_bs + (long long)pos * p.dq_ts + h * p.dq_hs;
         if (p.unrot_cos != nullptr)
-          store_row_unrot_from_tmem<128>(tmem_base + lane_sel + kColDQ, grow, half * 32, 32, p.unrot_cos + pos * 64,
-                                         p.unrot_sin + pos * 64, row < T);
+          store_row_unrot_from_tmem<128>(tmem_base + lane_sel + kColDQ, grow, half * 32, 32, p.unrot_cos + pos,
+                                         p.unrot_sin + pos, p.unrot_ld, row < T);
         else
           store_row_from_tmem(tmem_base + lane_sel + kColDQ, grow, half * 64, half * 64 + 64, row < T);
       }
@@ -653,7 +654,7 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (p.unrot_cos != nullptr) {
           const int pos = min(key, T - 1);
           store_row_unrot_from_tmem<kD>(tmem_base + lane_sel + kColDK, krow, half * (kD / 4), kD / 4,
-                                        p.unrot_cos + pos * (kD / 2), p.unrot_sin + pos * (kD / 2), live);
+                                        p.unrot_cos + pos, p.unrot_sin + pos, p.unrot_ld, live);
         } else {
           store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * kHalfCols, (half + 1) * kHalfCols, live);
         }
@@ -703,7 +704,7 @@ static SideStream* side_stream() {
 
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
                          const long long* dqs, int B, int T, int QH, int KVH, int D, int bchunk,
-                         const float* unrot_cos, const float* unrot_sin, cudaStream_t st);
+                         const float* unrot_cos, const float* unrot_sin, int unrot_ld, cudaStream_t st);
 
 }  // namespace b200
 
@@ -713,13 +714,13 @@ using namespace b200;
 // computed (b200_flash_delta). strides: q, k, v, dout, dq, dk, dv (3 each: batch, token, head).
 // With a workspace `ds_ws` of B * QH * Tp * Tp bf16 (Tp = T rounded up to 128) the dK/dV kernel also
 // writes dS^T there and dQ is computed from it by a GEMM kernel (flash_attn_bwd_dq.cu) instead of the
-// kernel that recomputes S and dP. With `unrot_cos` / `unrot_sin` (fp32 tables [>= T][D / 2] of the rotary
-// embedding) dq and dk are written with the inverse rotation applied, i.e. as gradients of the
-// un-rotated q and k.
+// kernel that recomputes S and dP. With `unrot_cos` / `unrot_sin` (fp32 tables of the rotary embedding,
+// transposed: [D / 2][unrot_ld], unrot_ld >= T) dq and dk are written with the inverse rotation applied, i.e.
+// as gradients of the un-rotated q and k.
 B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const void* lse,
                                const void* delta, void* dq, void* dk, void* dv, const void* valid_len,
                                const long long* s, int B, int T, int QH, int KVH, int D, float scale, void* ds_ws,
-                               const void* unrot_cos, const void* unrot_sin, cudaStream_t st) {
+                               const void* unrot_cos, const void* unrot_sin, int unrot_ld, cudaStream_t st) {
   if (B <= 0 || T <= 0) return 0;
   // head_dim 64 exists only in the form with a dS workspace (dK/dV kernel + dQ GEMM)
   if ((D != FB_D && D != 64) || QH % KVH != 0) return static_cast<int>(cudaErrorInvalidValue);
@@ -767,9 +768,8 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   p.ds_tp = (long long)nt * 128;
   p.unrot_cos = static_cast<const float*>(unrot_cos);
   p.unrot_sin = unrot_cos != nullptr ? static_cast<const float*>(unrot_sin) : nullptr;
-  if (p.unrot_cos != nullptr && (p.unrot_sin == nullptr || ((reinterpret_cast<uintptr_t>(unrot_cos) |
-                                                            reinterpret_cast<uintptr_t>(unrot_sin)) & 15) != 0))
-    return static_cast<int>(cudaErrorInvalidValue);
+  p.unrot_ld = unrot_ld;
+  if (p.unrot_cos != nullptr && (p.unrot_sin == nullptr || unrot_ld < T)) return static_cast<int>(cudaErrorInvalidValue);
   const CUtensorMap* tds = tk;           // placeholder when no workspace is given (never dereferenced then)
   if (ds_ws != nullptr) {
     const unsigned long long Tp = (unsigned long long)nt * 128;
@@ -785,7 +785,7 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
     flash_bwd_dkv_tc_kernel<64><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
   B200_CHECK(cudaGetLastError());
   if (ds_ws != nullptr) return flash_bwd_dq_from_ds(ds_ws, k, dq, valid_len, s + 3, s + 12, B, T, QH, KVH, D, p.bchunk,
-                                                      p.unrot_cos, p.unrot_sin, st);
+                                                      p.unrot_cos, p.unrot_sin, p.unrot_ld, st);
   if (dkv_ctas >= 3 * num_sms()) {
     flash_bwd_dq_tc_kernel<<<nt * QH * B, FBT_THREADS, FdqSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, p);
     return static_cast<int>(cudaGetLastError());

@@ -12,12 +12,14 @@
 namespace b200 {
 
 // Pairs j in [j0, j0 + nj) (nj a multiple of 16) of the row at TMEM address `taddr` (column 0 of the
-// kD-wide accumulator). cs_row / sn_row: the kD / 2 cosines / sines of this row's position (fp32, 16-byte
-// aligned). The loads are warp-collective: every lane calls this, `active` only predicates the global stores.
+// kD-wide accumulator). The tables are fp32 and TRANSPOSED, [kD / 2][ld]: cs_row / sn_row point at this row's
+// position in line 0 and element j is at [j * ld], so the lanes of a warp (consecutive positions) read
+// consecutive words. The TMEM loads are warp-collective: every lane calls this, `active` only predicates
+// the global stores.
 template <int kD>
 __device__ __forceinline__ void store_row_unrot_from_tmem(uint32_t taddr, bf16* grow, int j0, int nj,
                                                           const float* __restrict__ cs_row,
-                                                          const float* __restrict__ sn_row, bool active) {
+                                                          const float* __restrict__ sn_row, int ld, bool active) {
 #pragma unroll 1
   constexpr int kHalf = kD / 2;
   for (int j = j0; j < j0 + nj; j += 16) {
@@ -29,9 +31,12 @@ __device__ __forceinline__ void store_row_unrot_from_tmem(uint32_t taddr, bf16* 
     uint32_t y1[8], y2[8];
 #pragma unroll
     for (int i = 0; i < 16; i += 4) {
-      const float4 c = *reinterpret_cast<const float4*>(cs_row + j + i);
-      const float4 s = *reinterpret_cast<const float4*>(sn_row + j + i);
-      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+      float cc[4], ss[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        cc[e] = __ldg(cs_row + size_t(j + i + e) * ld);
+        ss[e] = __ldg(sn_row + size_t(j + i + e) * ld);
+      }
       float o1[4], o2[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {

@@ -45,9 +45,10 @@ def flash_tc_forward_dim(D: int) -> bool:
 # Inverse rotary embedding of dQ and dK inside the epilogues of the tcgen05 backward kernels (fp32
 # accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns.
 FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
-# The same for head_dim 64: available, off by default - on the 125 M model the separate pass was faster
-# (11.8 vs 12.1 ms per step), its dK/dV CTAs are short and the table reads sit on their critical path.
-FLASH_ROPE_EPILOGUE_D64 = _os.environ.get("B200_FLASH_ROPE_EPILOGUE_D64", "0") != "0"
+# The same for head_dim 64. (With the tables read row by row this form was slower than the separate pass
+# on the 125 M model, 12.1 vs 11.8 ms per step; with the transposed tables the two are level and the
+# epilogue form saves a launch per layer.)
+FLASH_ROPE_EPILOGUE_D64 = _os.environ.get("B200_FLASH_ROPE_EPILOGUE_D64", "1") != "0"
 _ds_ws_cache: dict = {}
 
 
@@ -447,6 +448,9 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         if ucos is not None:
             assert ucos.dtype == torch.float32 and usin.dtype == torch.float32 and ucos.is_contiguous() \
                 and usin.is_contiguous() and ucos.shape[0] >= T and ucos.shape[1] == D // 2
+            from .gemm import rope_tables_transposed
+            ucos, usin = rope_tables_transposed(ucos, usin)[:2]
+        uld = ucos.shape[1] if ucos is not None else 0
         for b0, b1, g0, g1 in chunks:       # slices along batch and heads keep every stride
             whole = b1 - b0 == B and g1 - g0 == KVH
 
@@ -466,7 +470,7 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
                                                   native.ptr(part(dk_, 1)), native.ptr(part(dv_, 1)),
                                                   native.ptr(part(valid_len, 0)),
                                                   arr21, b1 - b0, T, (g1 - g0) * R, g1 - g0, D, _f(scale), native.ptr(ws),
-                                                  native.ptr(ucos), native.ptr(usin), native.stream_ptr()),
+                                                  native.ptr(ucos), native.ptr(usin), uld, native.stream_ptr()),
                          "flash_bwd_tc")
         native.bump(1 + 2 * len(chunks))
         return dq, dk_, dv_

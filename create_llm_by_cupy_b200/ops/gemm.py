@@ -135,6 +135,18 @@ GEMM_ROPE_EPILOGUE = _os.environ.get("B200_GEMM_ROPE_EPILOGUE", "1") != "0"
 _rope_t_cache: dict = {}
 
 
+def rope_tables_transposed(cos: torch.Tensor, sin: torch.Tensor):
+    """([D/2, T] cos, [D/2, T] sin) copies of the [T, D/2] rotary tables, cached per table. The kernels'
+    epilogues own one row (position) per thread, so a warp reads consecutive words from this layout."""
+    key = (cos.data_ptr(), sin.data_ptr(), tuple(cos.shape))
+    tt = _rope_t_cache.get(key)
+    if tt is None:
+        if len(_rope_t_cache) > 16:
+            _rope_t_cache.clear()
+        tt = _rope_t_cache[key] = (cos.t().contiguous(), sin.t().contiguous(), cos, sin)   # keeps the sources alive
+    return tt
+
+
 def gemm_rope_fusable(a: torch.Tensor, b: torch.Tensor, head_dim: int, rope_cols: int) -> bool:
     """True when ``gemm_rope(a, b, ...)`` (``a`` [M, K], ``b`` [K, N], both row-major bf16) runs with the
     rotation fused into the GEMM epilogue."""
@@ -163,12 +175,7 @@ def gemm_rope(a: torch.Tensor, b: torch.Tensor, cos: torch.Tensor, sin: torch.Te
     flags = GEMM_WHOLE_TILES if _wgrad_pending.get(a.device.index, False) else 0
     # the epilogue reads the tables transposed ([head_dim / 2][positions]): a thread owns a row, so a warp
     # then reads consecutive words
-    key = (cos.data_ptr(), sin.data_ptr(), tuple(cos.shape))
-    tt = _rope_t_cache.get(key)
-    if tt is None:
-        if len(_rope_t_cache) > 16:
-            _rope_t_cache.clear()
-        tt = _rope_t_cache[key] = (cos.t().contiguous(), sin.t().contiguous(), cos, sin)   # keeps the sources alive
+    tt = rope_tables_transposed(cos, sin)
     rc = native.lib().b200_gemm_bf16_2cta_rope(
         native.ptr(a), native.ptr(b), native.ptr(out), M, N, K, a.stride(0), b.stride(0), N, 0, 1, flags,
         native.ptr(tt[0]), native.ptr(tt[1]), T, tt[0].shape[1], rope_cols, head_dim, native.stream_ptr())
