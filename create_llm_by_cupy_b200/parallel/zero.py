@@ -124,7 +124,15 @@ class _Pool:
         self.made[n] += 1
         t = self.alloc(n, self.dtype) if self.alloc is not None else torch.zeros(n, dtype=self.dtype, device=self.device)
         self.total_bytes += t.numel() * t.element_size()
-        return _Buf(t)
+        b = _Buf(t)
+        if t.is_cuda:
+            # The block may have been handed back by a tensor of the allocating stream whose kernels are still
+            # queued, and the zero fill itself runs on that stream: whoever uses the buffer first on ANOTHER
+            # stream (the communication stream gathers into it) has to wait for this point, exactly as for a
+            # buffer that comes back from a release.
+            b.free_event = torch.cuda.Event()
+            b.free_event.record(torch.cuda.current_stream(t.device))
+        return b
 
     def put(self, b: _Buf):
         self.free[b.t.numel()].append(b)

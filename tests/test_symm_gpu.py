@@ -161,3 +161,26 @@ def test_two_gpu_fused_reduce_scatter_adam_matches_nccl_baseline(tmp_path):
     for la, lb in zip(outs["nccl"]["losses"], outs["fused"]["losses"]):
         assert abs(la - lb) < 3e-2, (outs["nccl"]["losses"], outs["fused"]["losses"])
     assert abs(outs["nccl"]["param_norm"] - outs["fused"]["param_norm"]) < 1e-2 * outs["nccl"]["param_norm"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_keep_params_until_backward_follows_the_regathering_run(tmp_path):
+    """Parameters kept gathered from the forward to their backward: same first loss to the last digit
+    (nothing but the forward has run), same curve within bf16 atomics noise."""
+    script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
+    outs = {}
+    for keep in ("0", "1"):
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_ACCUM="1",
+                   B200_TEST_GATHER="pull", B200_TEST_KEEP=keep)
+        out = tmp_path / f"keep{keep}.pt"
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+               "--master-addr", "127.0.0.1", "--master-port", str(29900 + (os.getpid() % 90) + int(keep)),
+               script, "fused", str(out)]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        outs[keep] = torch.load(out)
+    a, b = outs["0"], outs["1"]
+    assert abs(a["losses"][0] - b["losses"][0]) < 1e-6, (a["losses"], b["losses"])
+    for la, lb in zip(a["losses"], b["losses"]):
+        assert abs(la - lb) < 2e-3, (a["losses"], b["losses"])
+    assert abs(a["param_norm"] - b["param_norm"]) < 1e-4 * a["param_norm"]
