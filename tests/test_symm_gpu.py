@@ -163,7 +163,8 @@ def test_two_gpu_fused_reduce_scatter_adam_matches_nccl_baseline(tmp_path):
     assert abs(outs["nccl"]["param_norm"] - outs["fused"]["param_norm"]) < 1e-2 * outs["nccl"]["param_norm"]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.skipif(torch.cuda.device_count() < 2 or os.environ.get("B200_TEST_KEEP_PARAMS") != "1",
+                    reason="needs 2 GPUs; opt-in (B200_TEST_KEEP_PARAMS=1): the option is experimental")
 def test_two_gpu_keep_params_until_backward_follows_the_regathering_run(tmp_path):
     """Parameters kept gathered from the forward to their backward: same first loss to the last digit
     (nothing but the forward has run), same curve within bf16 atomics noise."""
@@ -176,7 +177,7 @@ def test_two_gpu_keep_params_until_backward_follows_the_regathering_run(tmp_path
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                "--master-addr", "127.0.0.1", "--master-port", str(29900 + (os.getpid() % 90) + int(keep)),
                script, "fused", str(out)]
-        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=180)
         assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
         outs[keep] = torch.load(out)
     a, b = outs["0"], outs["1"]
