@@ -65,7 +65,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-adam-overlap", action="store_true", help="AdamW as one kernel after the backward")
     ap.add_argument("--keep-params", action="store_true",
-                    help="keep gathered block parameters from the forward until their backward (one gather per step)")
+                    help="experimental: keep gathered block parameters from the forward until their backward "
+                         "(one gather per unit and step)")
     ap.add_argument("--opt", default=None, choices=["gpu", "cpu"], help="override the config's optimizer tier")
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
