@@ -128,3 +128,38 @@ def test_dropout_branches_and_mask_adapters():
     assert torch.equal(pad_mask_to_valid_len(lens, 16), lens)
     with pytest.raises(ValueError):
         pad_mask_to_valid_len(torch.tensor([[False, True, False, False]]), 4)
+
+
+def test_attention_backward_unrotate_equals_in_kernel_rope():
+    """Two ways to the same gradients: (a) q, k un-rotated and ``rope=`` (rotation inside), (b) q, k rotated
+    beforehand and ``unrotate=`` (inverse rotation of dq, dk on the way out) - the contract of the epilogue
+    form on the GPU, checked here on the fp32 restatement; and the chunk sizes of the dS^T workspace."""
+    import torch
+    from create_llm_by_cupy_b200.ops import functional as F
+    B, T, QH, KVH, D = 2, 24, 4, 2, 16
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(B, T, h, D, generator=g) for h in (QH, KVH, KVH))
+    do = torch.randn(B, T, QH, D, generator=g)
+    vl = torch.tensor([24, 9], dtype=torch.int32)
+    tabs = F.rope_table(T, D, 10000.0, "cpu")
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=vl, rope=tabs)
+    ref = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=vl, rope=tabs)
+    packed = torch.cat([k.reshape(B * T, -1), q.reshape(B * T, -1)], 1).clone()
+    F.rope_inplace(packed, tabs[0], tabs[1], T, KVH + QH, D)
+    kr = packed[:, :KVH * D].reshape(B, T, KVH, D)
+    qr = packed[:, KVH * D:].reshape(B, T, QH, D)
+    o2, lse2 = F.flash_attn_fwd(qr, kr, v, valid_len=vl)
+    torch.testing.assert_close(o2, o, rtol=1e-5, atol=1e-5)
+    got = F.flash_attn_bwd(do, qr, kr, v, o2, lse2, valid_len=vl, unrotate=tabs)
+    for a, b in zip(got, ref):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    try:
+        F.flash_attn_bwd(do, q, k, v, o, lse, rope=tabs, unrotate=tabs)
+        raise AssertionError("rope= and unrotate= together must be refused")
+    except ValueError:
+        pass
+    # batch elements (or, below one, KV-head groups) per call under the workspace cap
+    cap = F.FLASH_DQ_GEMM_MAX_BYTES
+    assert F._ds_batch_chunk(4, 16, 2048) == 4
+    assert F._ds_batch_chunk(8, 32, 4096) == cap // (32 * 4096 * 4096 * 2)
+    assert F._ds_batch_chunk(8, 32, 16384) == (1 if cap >= 32 * 16384 * 16384 * 2 else 0)
