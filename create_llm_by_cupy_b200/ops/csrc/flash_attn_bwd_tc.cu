@@ -1,4 +1,4 @@
-// Causal GQA flash-attention BACKWARD on the 5th-generation tensor cores (head_dim 128).
+// Causal GQA flash-attention BACKWARD on the 5th-generation tensor cores (head_dim 128; dK/dV also 64).
 //
 // Two kernels, both TMA-fed with accumulators in TMEM and the element-wise softmax-gradient math
 // done by two warpgroups that split the columns of each score tile:
@@ -13,8 +13,12 @@
 //        S^T = K Q_i^T (SS)    dP^T = V dO_i^T (SS)   P^T, dS^T -> bf16 into TMEM
 //        dV += P^T dO_i        dK += dS^T Q_i      (A from TMEM, B = the same Q_i / dO_i tiles read
 //                                                   MN-major), accumulated in TMEM over all i
-// Q and K are expected already rotated; dQ and dK are gradients w.r.t. the rotated tensors (the
-// caller un-rotates). No atomics and no fp32 scratch; S and dP are recomputed by both kernels.
+// Q and K are expected already rotated; dQ and dK are gradients w.r.t. the rotated tensors unless the
+// caller passes the rotary tables, in which case the epilogues apply the inverse rotation
+// (flash_rope_epilogue.cuh). No atomics and no fp32 scratch. When the caller gives a workspace the
+// dK/dV kernel also stores its dS^T tiles there and dQ is computed from them by a GEMM kernel
+// (flash_attn_bwd_dq.cu) instead of flash_bwd_dq_tc, which recomputes S and dP. The dK/dV kernel and
+// that GEMM are templates on the head dimension (128 or 64).
 //
 // Reference counterpart: cupy_flash_gqa_backward (model/flash_attention.py:109-176).
 #include <mutex>
@@ -433,7 +437,7 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   // while the other warpgroup and the tensor core are on g + 1. A thread owns one key row (one TMEM
   // lane) and walks the 64 query columns in 16-column chunks; P^T / dS^T (bf16, 32 packed columns)
   // overwrite, lane by lane, columns of S^T / dP^T that the thread has already read. Q, dO and the
-  // row statistics of the next query tiles are prefetched through a 4-stage ring.
+  // row statistics of the next query tiles are prefetched through a 3-stage ring.
   constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
 
   if (warp == 0) {
