@@ -40,6 +40,13 @@ def parse():
     ap.add_argument("--resume-dir", default=None)
     ap.add_argument("--backend", default=None)
     ap.add_argument("--wandb", action="store_true")
+    ap.add_argument("--collectives", default="fused", choices=["fused", "nccl"],
+                    help="multi-GPU data plane: peer-memory kernels / copy engines over NVLink (default) or NCCL")
+    ap.add_argument("--gather", default="copy", choices=["copy", "pull", "gemm", "nccl"],
+                    help="parameter gather with --collectives fused: copy engines, P2P pull kernel, inside the "
+                         "consuming GEMM, or ncclAllGather")
+    ap.add_argument("--validate-every", type=int, default=0,
+                    help="validation loss and a generation sample every N iterations (0: off)")
     ap.add_argument("--replica-ratio", type=float, default=0.25, help="fraction of parameter elements kept replicated")
     ap.add_argument("--replica-policy", default="largest_first",
                     choices=["largest_first", "first", "last", "embedding_first"])
@@ -64,6 +71,7 @@ if __name__ == "__main__":
         "zero3_param_prefetch": True, "zero3_grad_bucket": True, "zero3_max_pending_reduces": 8,
         "zero25_replica_ratio": a.replica_ratio, "zero25_replica_policy": a.replica_policy,
         "grad_bucket_elems": 25_000_000, "zero3_sync_gather": False, "flash_backend": "b200",
+        "zero3_fused_collectives": a.collectives == "fused", "zero3_gather_mode": a.gather,
     }
     if a.backend == "gloo":
         model_dic.update(dtype="fp32", half_float=False)
@@ -71,7 +79,7 @@ if __name__ == "__main__":
     trainer = TrainMultiGPU(
         model_dic, GradScale_dic, use_devices=use_devices, batch_size=a.batch, max_epoch=a.epochs,
         lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1, warm_up=1000, max_grads=1.0, accum_step=a.accum,
-        save=a.save_dir is not None, save_step=2000, vali=False, vali_step=600, wand=a.wandb,
+        save=a.save_dir is not None, save_step=2000, vali=a.validate_every > 0, vali_step=max(a.validate_every, 1), wand=a.wandb,
         optimizer_device=a.optimizer_device, train_continue_path=None, data_dir=a.data_dir, save_dir=a.save_dir,
         resume_dir=a.resume_dir, backend=a.backend, beta1=0.9, beta2=0.95)
     trainer.fit(a.data_size)

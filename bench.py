@@ -9,11 +9,16 @@ heads, head_dim 128, SwiGLU FFN 5504, seq 2048, micro-batch 4 per GPU, bf16 comp
 master weights and AdamW state sharded; synthetic uniform-random token ids (seed 0), random-init
 N(0, 0.02) weights. A step = forward + backward + gradient reduction + global-norm clip + AdamW.
 
-Two numbers are measured, each over exactly K steps after W warm-up steps, bracketed by a barrier
+Three numbers are measured, each over exactly K steps after W warm-up steps, bracketed by a barrier
 and a device synchronise, timed with CUDA events, max over ranks:
-  value : the step with its inputs already resident on the device;
-  e2e   : the same step driven through the public ``Trainer.train_step`` API with every step's
-          token ids copied from pinned host memory and the loss read back to the host.
+  value    : the step with its inputs already resident on the device;
+  e2e      : the same step driven through the public ``Trainer.train_step`` API with every step's
+             token ids copied from pinned host memory and every step's loss read back to the host;
+  baseline : this framework's own plain path on the same box, in the same process, after the two
+             above: NCCL all-gather / reduce-scatter instead of the peer-memory collectives, AdamW as
+             one kernel after the backward, rotary embedding / SwiGLU / loss statistics as separate
+             kernels, weight gradients on the main stream. ``vs_baseline`` = value / baseline value (the
+             reference itself cannot run here: it needs CuPy, see ``--impl reference``).
 Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
@@ -60,16 +65,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="1.3b", choices=sorted(CONFIGS))
     ap.add_argument("--fused", type=int, default=-1, help="1: fused peer-memory collectives, 0: NCCL baseline, -1: auto")
-    ap.add_argument("--ag", default="pull", choices=["nccl", "pull", "gemm"],
-                    help="parameter gather with --fused: NCCL all-gather, P2P pull kernel, or pulled inside the consuming GEMM")
+    ap.add_argument("--ag", default="copy", choices=["nccl", "pull", "gemm", "copy"],
+                    help="parameter gather with --fused: copy engines (cudaMemcpyAsync per peer slice), P2P pull "
+                         "kernel, NCCL all-gather, or pulled inside the consuming GEMM")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the plain-path arm (vs_baseline stays null)")
+    ap.add_argument("--sync-read", action="store_true", help="read the loss of every step before the next one starts")
     ap.add_argument("--no-adam-overlap", action="store_true", help="AdamW as one kernel after the backward")
     ap.add_argument("--keep-params", action="store_true",
-                    help="experimental: keep gathered block parameters from the forward until their backward "
-                         "(one gather per unit and step)")
+                    help="keep gathered block parameters from the forward until their backward (one GPU only)")
     ap.add_argument("--opt", default=None, choices=["gpu", "cpu"], help="override the config's optimizer tier")
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
-    ap.add_argument("--phases", action="store_true", help="report mean ms per phase (CUDA events on the compute stream)")
+    ap.add_argument("--no-phases", action="store_true", help="do not record the per-phase CUDA events")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -85,6 +92,7 @@ def main():
     import torch
 
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from create_llm_by_cupy_b200.ops import functional as F
     from create_llm_by_cupy_b200.ops import native
     from create_llm_by_cupy_b200.parallel.comm import init_distributed, shutdown_distributed
     from create_llm_by_cupy_b200.parallel.trainer import Trainer
@@ -117,28 +125,15 @@ def main():
     if c["zero"] == "2.5":
         md.update(zero25_replica_ratio=0.5, zero25_replica_policy="largest_first")
     if args.keep_params:
+        if world > 1:
+            raise SystemExit("--keep-params is a one-GPU option: on multi-GPU runs it is refused (one such run "
+                             "did not finish and the cause is not established)")
         md.update(keep_params_until_backward=True)
-    fused = None
-    use_fused = world > 1 and args.fused != 0
-    if use_fused:
-        try:
-            from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
-            kw = dict(rs_blocks=args.comm_blocks, ag_blocks=args.comm_blocks) if args.comm_blocks > 0 else {}
-            fused = FusedCollectives(comm, device, gather_mode=args.ag, **kw)
-        except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
-            if args.fused == 1:
-                raise
-            if rank == 0:
-                print(f"[bench] fused collectives unavailable ({e}); using NCCL", file=sys.stderr)
     B, T, accum = c["micro_batch"], c["time_size"], c["accum"]
-    trainer = Trainer(md, rank=rank, world_size=world, comm=comm, device=device, zero_stage=c["zero"],
-                      optimizer_device=c["opt"], accum_step=accum, lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1,
-                      warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
-                      profile_comm=world > 1, profile_phases=args.phases, cuda_graph=args.graph,
-                      adam_overlap=not args.no_adam_overlap)
+    n_steps_total = args.warmup + args.steps
+    tokens = B * T * accum * world
 
     # distinct synthetic batches per rank and per step (seed 0 stream, partitioned by rank)
-    n_steps_total = args.warmup + args.steps
     ids = synthetic_token_stream(n_steps_total * accum * B * world, T, c["vocab_size"], "train", pad, low=1)
     ids = ids[rank::world]
     stager = BatchStager(B, T, device)
@@ -152,52 +147,104 @@ def main():
             comm.barrier()
         torch.cuda.synchronize()
 
-    def timed(run_step, first_index):
+    dev_batches = [[stager.stage(host_batch(i * accum + a), vl, pad) for a in range(accum)] for i in range(n_steps_total)]
+    torch.cuda.synchronize()
+
+    def make_trainer(plain: bool):
+        """The product configuration, or (``plain``) the framework's own baseline path."""
+        fused = None
+        if world > 1 and args.fused != 0 and not plain:
+            try:
+                from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
+                kw = dict(rs_blocks=args.comm_blocks, ag_blocks=args.comm_blocks) if args.comm_blocks > 0 else {}
+                fused = FusedCollectives(comm, device, gather_mode=args.ag, **kw)
+            except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
+                if args.fused == 1:
+                    raise
+                if rank == 0:
+                    print(f"[bench] fused collectives unavailable ({e}); using NCCL", file=sys.stderr)
+        F.set_unfused_baseline(plain)
+        tr = Trainer(md, rank=rank, world_size=world, comm=comm, device=device, zero_stage=c["zero"],
+                     optimizer_device=c["opt"], accum_step=accum, lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1,
+                     warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
+                     profile_comm=world > 1, profile_phases=not (args.no_phases or args.graph),
+                     cuda_graph=args.graph and not plain, adam_overlap=not (args.no_adam_overlap or plain),
+                     defer_host_read=not (args.sync_read or plain))
+        return tr, fused
+
+    def timed(trainer, run_step):
         for w in range(args.warmup):
-            run_step(first_index + w)
+            run_step(w)
+        trainer.flush_host_read()
         barrier_sync()
         native.raise_on_status()
         trainer.phase_times()                 # drop the warm-up steps' marks
+        trainer.manager.exposed_comm_ms()
         launches0 = native.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for k in range(args.steps):
-            run_step(first_index + args.warmup + k)
+            run_step(args.warmup + k)
+        trainer.flush_host_read()             # the last step's scalars are read inside the timed region
         trainer.join_optimizer()              # the last step's pipelined AdamW belongs to the timed region
         e1.record()
         barrier_sync()
         ms = torch.tensor([e0.elapsed_time(e1)], device=device)
         if world > 1:
             comm.all_reduce(ms, op="max")
-        return float(ms) / args.steps, (native.launch_count() - launches0) // args.steps
+        exposed = trainer.manager.exposed_comm_ms() / max(args.steps, 1) if world > 1 else 0.0
+        return float(ms) / args.steps, (native.launch_count() - launches0) // args.steps, exposed, trainer.phase_times()
 
-    # ---- device-resident inputs --------------------------------------------------------------
-    dev_batches = [[stager.stage(host_batch(i * accum + a), vl, pad) for a in range(accum)] for i in range(n_steps_total)]
-    torch.cuda.synchronize()
+    def dev_step(trainer):
+        return lambda i: trainer.train_step(dev_batches[i % n_steps_total])
+
+    def e2e_step(trainer):
+        def step(i):
+            batches = [stager.stage(host_batch((i % n_steps_total) * accum + a), vl, pad) for a in range(accum)]
+            return trainer.train_step(batches)["loss"]
+        return step
+
+    # ---- product arm: device-resident inputs, then end to end through the public API ------------------------
+    trainer, fused = make_trainer(plain=False)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    trainer.manager.exposed_comm_ms()
-    trainer.phase_times()
-    ms_dev, launches = timed(lambda i: trainer.train_step(dev_batches[i % n_steps_total]), 0)
-    exposed = trainer.manager.exposed_comm_ms() / max(args.steps + 0, 1) if world > 1 else 0.0
+    ms_dev, launches, exposed, phases = timed(trainer, dev_step(trainer))
     clocks = sampler.stop() if sampler else None
     last = dict(trainer.last)
-    phases = trainer.phase_times() if args.phases else None
-
-    # ---- end to end through the public API: pinned host ids -> device, loss -> host -------------
     e2e = None
     if not args.no_e2e:
-        def e2e_step(i):
-            batches = [stager.stage(host_batch((i % n_steps_total) * accum + a), vl, pad) for a in range(accum)]
-            return trainer.train_step(batches)["loss"]
-        ms_e2e, _ = timed(e2e_step, 0)
-        tokens = B * T * accum * world
+        ms_e2e, _, _, _ = timed(trainer, e2e_step(trainer))
         e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": stager.h2d_bytes * accum, "d2h_bytes_per_step": 12}
+               "h2d_bytes_per_step": stager.h2d_bytes * accum, "d2h_bytes_per_step": 12,
+               "host_read": "deferred by one step" if trainer.defer_host_read else "every step before the next"}
     native.raise_on_status()
+    n_par = trainer.n_params
+    cuda_graph = bool(trainer.cuda_graph)
+    collectives = (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
+                   else ("nccl" if world > 1 else "none"))
+    copies = fused.copies if fused is not None else 0
+    trainer.close()
+    del trainer, fused
 
-    tokens = B * T * accum * world
+    # ---- baseline arm: the framework's own plain path on the same box ---------------------------------------
+    baseline = None
+    if not args.no_baseline:
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        btr, _ = make_trainer(plain=True)
+        ms_b, launches_b, exposed_b, phases_b = timed(btr, dev_step(btr))
+        native.raise_on_status()
+        baseline = {"value": tokens / (ms_b / 1e3), "unit": "tokens/s", "ms_per_step": ms_b, "gpu_launches": launches_b,
+                    "exposed_comm_ms_per_step": exposed_b, "phases_ms": phases_b,
+                    "what": ("NCCL all-gather / reduce-scatter, " if world > 1 else "") +
+                            "AdamW after the backward, separate RoPE / SwiGLU / loss-statistics kernels, "
+                            "weight gradients on the main stream; same process, after the product arm"}
+        btr.close()
+        del btr
+        F.set_unfused_baseline(False)
+
     value = tokens / (ms_dev / 1e3)
     if rank == 0:
         peaks = {}
@@ -205,25 +252,24 @@ def main():
             peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
         except Exception:
             pass
-        n_par = trainer.n_params
         flops_tok = 6.0 * n_par + 6.0 * c["layer_num"] * c["hidden_size"] * T
         out = {
             "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / baseline["value"]) if baseline else None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": c["name"], "global_batch": B * accum * world, "seq_len": T,
-                       "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par, "cuda_graph": bool(trainer.cuda_graph),
-                       "keep_params_until_backward": bool(args.keep_params),
-                       "collectives": (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
-                                       else ("nccl" if world > 1 else "none")),
+                       "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par, "cuda_graph": cuda_graph,
+                       "keep_params_until_backward": bool(args.keep_params), "collectives": collectives,
                        "l2": f"not flushed: a step streams more than {28e-9 * n_par / world + 2e-9 * n_par:.1f} GB of weights and "
                              "optimizer state per GPU, far above the 126 MB L2"},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "exposed_comm_ms_per_step": exposed, "phases_ms": phases,
+            "e2e": e2e, "gpu_launches": launches, "copy_engine_transfers_total": copies, "clocks": clocks,
+            "exposed_comm_ms_per_step": exposed, "phases_ms": phases, "baseline": baseline,
             "model_tflops_per_gpu": flops_tok * tokens / world / (ms_dev / 1e3) / 1e12,
             "mfu_of_measured_sustained": (flops_tok * tokens / world / (ms_dev / 1e3) / 1e12) /
                                          peaks.get("bf16_tflops_sustained", 1401.9),
             "last_loss": last.get("loss"), "last_grad_norm": last.get("grad_norm"),
+            "native_digest": native.source_digest(),
         }
         sys.stdout.flush()
         os.dup2(real_stdout, 1)

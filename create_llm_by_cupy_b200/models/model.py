@@ -200,7 +200,9 @@ class Cupa_ver4:
         self.zero3_embedding_grad_bucket_max_bytes = int(g("zero3_embedding_grad_bucket_max_bytes", 64 * 1024 * 1024))
         self.zero3_sync_gather = bool(g("zero3_sync_gather", False))
         self.zero3_sync_after_each_microbatch = bool(g("zero3_sync_after_each_microbatch", False))
-        self.zero3_fused_collectives = bool(g("zero3_fused_collectives", False))
+        # multi-GPU data plane of the training worker: peer-memory kernels / copy engines (default) or NCCL
+        self.zero3_fused_collectives = bool(g("zero3_fused_collectives", True))
+        self.zero3_gather_mode = str(g("zero3_gather_mode", "copy"))
         self.grad_bucket_elems = int(g("grad_bucket_elems", 25_000_000))
         backend = str(g("flash_backend", "b200"))
         for layer in self.layers:

@@ -22,10 +22,27 @@ LIB_NAME = "libb200llm.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
     "--expt-relaxed-constexpr",
 ]
+# Approximate division / exp / rsqrt only where the arithmetic feeds bf16 tensor-core operands anyway (the
+# attention and GEMM units). The optimizer, the normalisation and the loss kernels keep IEEE division and
+# square roots: their results go into fp32 state.
+FAST_MATH_PREFIXES = ("flash_", "gemm_")
+# ``B200_BOUNDS_CHECK=1``: debug build in which the kernels that take indices or offsets from their
+# arguments check them (and report through the status word instead of touching memory) - the stand-in for
+# a memory checker. Objects of the two builds are kept apart by the flag's part in the digest.
+BOUNDS_CHECK = os.environ.get("B200_BOUNDS_CHECK") == "1"
+
+
+def flags_for(src: Path) -> list[str]:
+    fl = list(NVCC_FLAGS)
+    if src.name.startswith(FAST_MATH_PREFIXES):
+        fl.append("--use_fast_math")
+    if BOUNDS_CHECK:
+        fl.append("-DB200_BOUNDS_CHECK=1")
+    return fl
 
 
 def _nvcc() -> str:
@@ -44,7 +61,7 @@ def _digest(src: Path) -> str:
     h.update(src.read_bytes())
     for hdr in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
         h.update(hdr.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags_for(src)).encode())
     return h.hexdigest()
 
 
@@ -52,11 +69,43 @@ def lib_path() -> Path:
     return OUT_DIR / LIB_NAME
 
 
+def source_digest() -> str:
+    """One digest over every source, header and the compiler flags: names the code a library was built from."""
+    h = hashlib.sha1()
+    for src in sources():
+        h.update(_digest(src).encode())
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    """True when the library exists and every object's stamp matches its source as it is now."""
+    if not lib_path().exists():
+        return False
+    obj_dir = OUT_DIR / "build"
+    for src in sources():
+        stamp = obj_dir / (src.stem + ".sha1")
+        if not stamp.exists() or stamp.read_text() != _digest(src):
+            return False
+    return True
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source under ``csrc/`` that changed and link ``libb200llm.so``."""
+    """Compile every source under ``csrc/`` that changed and link ``libb200llm.so``. Processes that
+    build at the same time (one per GPU at start-up) take turns on a lock file; the second one then finds
+    everything up to date."""
     nvcc = _nvcc()
     obj_dir = OUT_DIR / "build"
     obj_dir.mkdir(exist_ok=True)
+    import fcntl
+    with open(obj_dir / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(nvcc, obj_dir, force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(nvcc: str, obj_dir: Path, force: bool, verbose: bool) -> Path:
     jobs = []
     objs = []
     for src in sources():
@@ -66,7 +115,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         dig = _digest(src)
         if not force and obj.exists() and stamp.exists() and stamp.read_text() == dig:
             continue
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *flags_for(src), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if src.suffix == ".cpp":
             cmd = [nvcc, "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fopenmp,-march=x86-64-v3,-fvisibility=hidden",
                    "-I", str(CSRC), "-c", str(src), "-o", str(obj)]

@@ -16,8 +16,10 @@
  *   - hidden sizes above B200_NOALLOC_RMS_MAX_H are refused (cudaErrorInvalidValue and a message
  *     on stderr), as is a device with so many SMs that the partial rows would not fit;
  *   - the first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress, with that device current). Make that first call outside of any
- *     stream capture; later calls on the same device do no set-up;
+ *     (cudaGetSymbolAddress, with that device current). Under lazy module loading that look-up may
+ *     also be the moment the driver loads the module that holds the array, i.e. when the 4.75 MiB are
+ *     actually taken from the device. Make that first call at start-up and outside of any stream
+ *     capture; later calls on the same device do no set-up and change no memory accounting;
  *   - it calls no cudaMalloc / cudaFree and no allocating library routine. Inputs and outputs are
  *     the caller's;
  *   - all calls on one device share the array and it keeps the previous call's contents. The

@@ -411,6 +411,28 @@ B200_API int b200_symm_all_gather_range(const void* const* bases, int W, int ran
                               range_hi_bytes, range_mode, st);
 }
 
+// All-gather by the copy engines: one cudaMemcpyAsync per rank slice (peer heap -> local gather buffer) on
+// `st`, peers taken in ring order starting after this rank so that at any moment the ranks read from
+// different sources. No SM takes part, which is the point: the parameter prefetch of a ZeRO unit runs beside
+// persistent GEMMs that are tuned for all SMs. `out` may contain the local slice itself (an in-place gather
+// of a replicated buffer): the copy of a slice onto itself is skipped. Ordering against the owners' updates
+// is the caller's (stream events plus symm_barrier_kernel), exactly as for ag_pull_kernel.
+B200_API int b200_symm_all_gather_copy(const void* const* bases, int W, int rank, unsigned long long shard_off,
+                                       long long n_slice, int elem_bytes, void* out, cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || rank < 0 || rank >= W || n_slice < 0 || elem_bytes < 1)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const size_t bytes = size_t(n_slice) * size_t(elem_bytes);
+  if (bytes == 0) return 0;
+  for (int q = 1; q <= W; ++q) {
+    const int peer = (rank + q) % W;          // the local slice comes last
+    const char* src = static_cast<const char*>(bases[peer]) + shard_off;
+    char* dst = static_cast<char*>(out) + size_t(peer) * bytes;
+    if (src == dst) continue;
+    B200_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st));
+  }
+  return 0;
+}
+
 B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int vranks, int channel, unsigned int epoch,
                                unsigned long long wait_ns, cudaStream_t st) {
   if (W < 1 || W > SYMM_MAX_W || channel < 1 || channel >= SYMM_CHANNELS) return static_cast<int>(cudaErrorInvalidValue);

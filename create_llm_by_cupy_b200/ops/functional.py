@@ -71,6 +71,35 @@ def _ds_workspace(device, B: int, QH: int, T: int):
     return ws
 
 
+_fusion_defaults: dict = {}
+
+
+def set_unfused_baseline(on: bool) -> None:
+    """Switch the epilogue fusions and stream overlaps off (``on``) or back to their defaults: rotary
+    embedding in the K|Q|V GEMM epilogue and in the attention-backward epilogues, SwiGLU in the gate|value
+    GEMM epilogue, loss statistics / logit gradients in the LM-head GEMM epilogues, weight-gradient GEMMs on
+    a side stream. With all of them off every one of these steps is a separate kernel on one stream: the
+    plain path the benchmark measures the product against."""
+    from . import gemm as _g
+    global FLASH_ROPE_EPILOGUE, FLASH_ROPE_EPILOGUE_D64, SWIGLU_EPILOGUE, CE_EPILOGUE
+    if not _fusion_defaults:
+        _fusion_defaults.update(rope=_g.GEMM_ROPE_EPILOGUE, wgrad=_g.WGRAD_OVERLAP, frope=FLASH_ROPE_EPILOGUE,
+                                frope64=FLASH_ROPE_EPILOGUE_D64, swiglu=SWIGLU_EPILOGUE, ce=CE_EPILOGUE)
+    d = _fusion_defaults
+    _g.GEMM_ROPE_EPILOGUE = False if on else d["rope"]
+    _g.WGRAD_OVERLAP = False if on else d["wgrad"]
+    FLASH_ROPE_EPILOGUE = False if on else d["frope"]
+    FLASH_ROPE_EPILOGUE_D64 = False if on else d["frope64"]
+    SWIGLU_EPILOGUE = False if on else d["swiglu"]
+    CE_EPILOGUE = False if on else d["ce"]
+
+
+# SwiGLU inside the epilogue of the gate|value projection, and the loss statistics / logit gradients inside
+# the epilogues of the LM-head GEMMs (see ``gemm.gemm_swiglu`` / ``gemm.gemm_ce_stats`` / ``gemm.gemm_ce_dlogits``).
+SWIGLU_EPILOGUE = _os.environ.get("B200_SWIGLU_EPILOGUE", "1") != "0"
+CE_EPILOGUE = _os.environ.get("B200_CE_EPILOGUE", "1") != "0"
+
+
 def _lib():
     native.status_tensor()
     return native.lib()

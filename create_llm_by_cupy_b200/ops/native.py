@@ -55,15 +55,30 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
+        # The library is rebuilt whenever a source, a header or the flags changed since it was made (the
+        # build is incremental: with nothing changed it only compares digests). A machine without nvcc
+        # can only load a library whose stamps match the sources; a stale one is an error, never a
+        # silent mismatch between the code that is read and the code that runs.
         path = _build.lib_path()
-        if not path.exists() or os.environ.get("B200_REBUILD") == "1":
-            path = _build.build()
+        try:
+            path = _build.build(force=os.environ.get("B200_REBUILD") == "1")
+        except RuntimeError as e:
+            if "nvcc not found" not in str(e):
+                raise NativeError(str(e)) from e
+            if not _build.is_current():
+                raise NativeError(f"{path} is missing or older than the sources under csrc/ and nvcc is not "
+                                  f"available to rebuild it") from e
         try:
             _lib = ctypes.CDLL(str(path))
         except OSError as e:  # pragma: no cover
             raise NativeError(f"cannot load {path}: {e}") from e
         _lib.b200_abi_version.restype = c_int
         return _lib
+
+
+def source_digest() -> str:
+    """Digest of the sources the loaded library was built from (recorded by the benchmark)."""
+    return _build.source_digest()
 
 
 def status_tensor(device=None) -> torch.Tensor:

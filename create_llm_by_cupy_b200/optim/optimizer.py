@@ -111,6 +111,14 @@ class ZeRO_Adam_ShardedGPU(_AdamBase):
         self._log_lr(is_main_device)
         return out_shard
 
+    def reseed_from_params(self, param_shard: torch.Tensor):
+        """Start a fresh optimizer state from (newly loaded) parameters: fp32 master = the shard, m = v = 0,
+        step 0. Used when a checkpoint carries weights but no optimizer file."""
+        self.master_weight_shard.copy_(param_shard.detach().float())
+        self.m.zero_()
+        self.v.zero_()
+        self.t = 0
+
     def state_dict(self) -> dict:
         return {"m": self.m, "v": self.v, "w_fp32": self.master_weight_shard, "t": self.t}
 
@@ -218,6 +226,13 @@ class ZeRO_Adam_Offload(_AdamBase):
         torch.cuda.current_stream(self.device).wait_stream(side)
         self._log_lr(is_main_device)
         return out_shard
+
+    def reseed_from_params(self, param_shard: torch.Tensor):
+        """As ``ZeRO_Adam_ShardedGPU.reseed_from_params``, on the host-resident state."""
+        self.master_weight_shard.copy_(param_shard.detach().float().cpu())
+        self.m.zero_()
+        self.v.zero_()
+        self.t = 0
 
     def state_dict(self) -> dict:
         return {"m": self.m, "v": self.v, "w_fp32": self.master_weight_shard, "t": self.t}

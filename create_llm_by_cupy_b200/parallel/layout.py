@@ -166,8 +166,11 @@ class FlatLayout:
 def select_replicated_params(sizes, unit_of_embedding_params, ratio: float, policy: str = "largest_first"):
     """Choose parameters to replicate until ``ratio`` of all elements is covered.
 
-    Policies as in the reference (model/ZeRO2_5.py:863-892): ``largest_first`` (default),
-    ``first``, ``last``, ``embedding_first``. ``ratio`` >= 1 replicates everything (ZeRO-2).
+    Policies and stopping rule as in the reference (model/ZeRO2_5.py:863-892): ``largest_first``
+    (default), ``first``, ``last``, ``embedding_first``; parameters are taken in the policy's order
+    until the running total has REACHED ``ratio * total``, so the last one taken may overshoot the
+    target and any ``ratio`` > 0 replicates at least one parameter. ``ratio`` >= 1 replicates
+    everything (ZeRO-2).
     """
     n = len(sizes)
     total = sum(sizes)
@@ -175,7 +178,6 @@ def select_replicated_params(sizes, unit_of_embedding_params, ratio: float, poli
         return []
     if ratio >= 1.0:
         return list(range(n))
-    budget = ratio * total
     if policy == "largest_first":
         order = sorted(range(n), key=lambda i: (-sizes[i], i))
     elif policy == "first":
@@ -188,11 +190,10 @@ def select_replicated_params(sizes, unit_of_embedding_params, ratio: float, poli
         order = emb + rest
     else:
         raise ValueError(f"unknown zero25_replica_policy {policy!r}")
+    target = int(total * ratio)
     chosen, acc = [], 0
     for i in order:
-        if acc + sizes[i] > budget and chosen:
-            continue
-        if acc + sizes[i] > budget and not chosen:
+        if acc >= target:
             break
         chosen.append(i)
         acc += sizes[i]

@@ -8,9 +8,14 @@ The first 64 KiB hold the signal flags the kernels use for their cross-GPU barri
 ``FusedCollectives`` is what a ZeRO manager takes as ``fused=``:
   * ``reduce_scatter_accumulate`` — one kernel: barrier, P2P pull of this rank's slice of every
     peer's gradient bucket, fp32 sum, store / accumulate (or AdamW), gradient statistics, barrier;
-  * ``all_gather`` — P2P pull of every peer's parameter slice into the local unit buffer;
+  * ``all_gather`` — every peer's parameter slice into the local unit buffer, by the copy engines
+    (one ``cudaMemcpyAsync`` per peer slice, no SM involved; the default) or by the P2P pull kernel;
   * ``barrier`` — device-side barrier fencing the optimizer step.
 The NCCL path of ``comm.py`` is the baseline these are measured against.
+
+Every heap allocation sits between two 256-byte guard blocks filled with a known pattern;
+``check_canaries()`` (also run by ``close()``) reports any allocation whose guards were overwritten —
+the stand-in for a memory checker on buffers that other GPUs write and read through peer pointers.
 
 Virtual ranks: ``LocalVirtualRanks`` builds W heaps on ONE device and drives the same kernels with
 ``gridDim.y = W`` (all ranks inside one launch), which is how the protocol is tested on a single
@@ -24,7 +29,13 @@ import torch
 
 from ..ops import native
 
-_DEFAULT_WAIT_NS = 20_000_000_000   # 20 s: a peer that never arrives ends in an error status, not a hang
+# Budget of one cross-GPU wait (barrier flags): a peer that never arrives ends in an error status, not a
+# hang. Ranks legitimately drift apart by far less than this (first-step lazy loading, a checkpoint write on
+# one rank is fenced by a host barrier); the waits on local mbarriers inside the compute kernels use 2 s.
+_DEFAULT_WAIT_NS = 10_000_000_000
+_GUARD_BYTES = 256
+_GUARD_BYTE = 0xA5
+_DEFAULT_HEAP_BYTES = 8 << 30
 
 
 class _RawCuda:
@@ -56,6 +67,7 @@ class SymmetricHeap:
         self.pad_bytes = int(self.lib.b200_symm_pad_bytes())
         self.cursor = self.pad_bytes
         self.bytes_view = _wrap(self.base, self.heap_bytes, self.device)
+        self.guards = []          # (byte offset of the data, data bytes) of every allocation
         self.peer_bases = [0] * self.world_size
         self.peer_bases[self.rank] = self.base
         self._imported = []
@@ -76,14 +88,32 @@ class SymmetricHeap:
         self.table = _ptr_array(self.peer_bases)
 
     def alloc(self, n: int, dtype) -> torch.Tensor:
-        """Zero-initialised tensor of ``n`` elements at the next 256-byte aligned heap offset."""
+        """Zero-initialised tensor of ``n`` elements at the next 256-byte aligned heap offset, with a
+        256-byte guard block on either side."""
         esz = torch.empty((), dtype=dtype).element_size()
-        off = (self.cursor + 255) // 256 * 256
+        g0 = (self.cursor + 255) // 256 * 256
+        off = g0 + _GUARD_BYTES
         nbytes = n * esz
-        if off + nbytes > self.heap_bytes:
-            raise MemoryError(f"symmetric heap exhausted: need {off + nbytes} of {self.heap_bytes} bytes")
-        self.cursor = off + nbytes
+        g1 = (off + nbytes + 255) // 256 * 256
+        if g1 + _GUARD_BYTES > self.heap_bytes:
+            raise MemoryError(f"symmetric heap exhausted: need {g1 + _GUARD_BYTES} of {self.heap_bytes} bytes")
+        self.cursor = g1 + _GUARD_BYTES
+        self.bytes_view[g0:off].fill_(_GUARD_BYTE)
+        self.bytes_view[off + nbytes:g1 + _GUARD_BYTES].fill_(_GUARD_BYTE)
+        self.guards.append((off, nbytes))
         return self.bytes_view[off:off + nbytes].view(dtype)
+
+    def check_canaries(self) -> list:
+        """Indices (allocation order) of the allocations whose guard blocks no longer hold the pattern,
+        i.e. something wrote outside a neighbouring buffer. Synchronises the device."""
+        bad = []
+        for i, (off, nbytes) in enumerate(self.guards):
+            end = (off + nbytes + 255) // 256 * 256 + _GUARD_BYTES
+            lo = self.bytes_view[off - _GUARD_BYTES:off]
+            hi = self.bytes_view[off + nbytes:end]
+            if bool((lo != _GUARD_BYTE).any()) or bool((hi != _GUARD_BYTE).any()):
+                bad.append(i)
+        return bad
 
     def offset_of(self, t: torch.Tensor) -> int:
         off = t.data_ptr() - self.base
@@ -95,13 +125,23 @@ class SymmetricHeap:
         return 0 <= t.data_ptr() - self.base < self.heap_bytes
 
     def close(self):
-        for p in self._imported:
-            self.lib.b200_symm_unimport(ctypes.c_void_p(p))
-        self._imported = []
+        """Unmap the peers, free the heap; raises afterwards if a guard block was overwritten."""
+        bad = []
         if self.base:
             torch.cuda.synchronize(self.device)
+            bad = self.check_canaries()
+        for p in self._imported:
+            self.lib.b200_symm_unimport(ctypes.c_void_p(p))
+        if self._imported and self.world_size > 1:
+            self.comm.barrier()           # nobody frees a heap a peer still has mapped
+        self._imported = []
+        if self.base:
+            self.bytes_view = None
             self.lib.b200_symm_free(ctypes.c_void_p(self.base))
             self.base = 0
+        if bad:
+            raise RuntimeError(f"symmetric heap: guard blocks of allocation(s) {bad} were overwritten "
+                               f"(sizes {[self.guards[i][1] for i in bad]} bytes)")
 
 
 class FusedCollectives:
@@ -109,30 +149,53 @@ class FusedCollectives:
 
     gather = True
 
-    def __init__(self, comm, device, heap_bytes: int = 8 << 30, rs_blocks: int = 64, ag_blocks: int = 64,
-                 wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "pull", n_copy: int = 8):
-        """``gather_mode`` selects how parameter units are gathered: ``"nccl"`` (ncclAllGather on the
-        communication stream), ``"pull"`` (the P2P pull kernel on the communication stream) or
-        ``"gemm"`` (transformer-block units are pulled inside the first GEMM that consumes them;
-        the other units use the pull kernel). Gradient reduction always uses the fused kernel."""
-        if gather_mode not in ("nccl", "pull", "gemm"):
+    def __init__(self, comm, device, heap_bytes: int | None = None, rs_blocks: int = 64, ag_blocks: int = 64,
+                 wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "copy", n_copy: int = 8,
+                 copy_min_bytes: int = 1 << 20):
+        """``gather_mode`` selects how parameter units are gathered: ``"copy"`` (one ``cudaMemcpyAsync``
+        per peer slice on the communication stream: the copy engines move the unit and no SM is taken
+        from the GEMMs; slices below ``copy_min_bytes`` use the pull kernel), ``"pull"`` (the P2P pull
+        kernel), ``"nccl"`` (ncclAllGather) or ``"gemm"`` (transformer-block units are pulled inside the
+        first GEMM that consumes them; the other units use the pull kernel). Gradient reduction always
+        uses the fused kernel. ``heap_bytes`` None: the heap is created on the first ``reserve`` /
+        ``alloc`` (the ZeRO manager reserves what its layout needs)."""
+        if gather_mode not in ("nccl", "pull", "gemm", "copy"):
             raise ValueError(f"unknown gather_mode {gather_mode!r}")
-        self.heap = SymmetricHeap(comm, device, heap_bytes)
         self.comm = comm
-        self.device = self.heap.device
+        self.device = torch.device(device)
         self.world_size = comm.world_size
         self.rank = comm.rank
-        self.lib = self.heap.lib
+        self.lib = native.lib()
+        self._heap = None
+        if heap_bytes is not None:
+            self._heap = SymmetricHeap(comm, device, heap_bytes)
         self.rs_blocks = rs_blocks
         self.ag_blocks = ag_blocks
         self.wait_ns = int(wait_ns)
         self.gather_mode = gather_mode
         self.gather = gather_mode != "nccl"
         self.gemm_fusion = gather_mode == "gemm"   # pull block units inside their first consuming GEMM
+        self.copy_engine = gather_mode == "copy"
+        self.copy_min_bytes = int(copy_min_bytes)
         self.n_copy = n_copy                # CTAs of that GEMM that copy instead of multiply
         self.rs_epoch = 0
         self.barrier_epoch = 0
-        self.launches = 0
+        self.launches = 0                   # kernels of this module launched so far
+        self.copies = 0                     # copy-engine transfers issued so far
+
+    @property
+    def heap(self) -> SymmetricHeap:
+        if self._heap is None:
+            self._heap = SymmetricHeap(self.comm, self.device, _DEFAULT_HEAP_BYTES)
+        return self._heap
+
+    def reserve(self, nbytes: int):
+        """Create the heap with room for ``nbytes`` of allocations (plus signal pad and guards) if it
+        does not exist yet. Every rank must ask for the same size."""
+        if self._heap is None:
+            total = int(nbytes) + (64 << 20)
+            self._heap = SymmetricHeap(self.comm, self.device, (total + (1 << 21) - 1) >> 21 << 21)
+        return self._heap
 
     def alloc(self, n: int, dtype) -> torch.Tensor:
         return self.heap.alloc(n, dtype)
@@ -163,6 +226,7 @@ class FusedCollectives:
             ctypes.c_uint(self.rs_epoch), ctypes.c_ulonglong(self.wait_ns), self.rs_blocks, s)
         native.check(rc, "symm_reduce_scatter")
         native.bump()
+        self.launches += 1
 
     def all_gather(self, out: torch.Tensor, shard_slice: torch.Tensor, stream=None, skip=None, only=None):
         """out[W * n] <- every rank's shard_slice[n] (shard_slice is a heap tensor). ``skip`` /
@@ -170,6 +234,13 @@ class FusedCollectives:
         n = shard_slice.numel()
         assert out.numel() == n * self.world_size and n % 8 == 0 and shard_slice.element_size() == 2
         s = native.stream_ptr() if stream is None else ctypes.c_void_p(stream.cuda_stream)
+        if self.copy_engine and skip is None and only is None and n * 2 >= self.copy_min_bytes:
+            rc = self.lib.b200_symm_all_gather_copy(self.heap.table, self.world_size, self.rank,
+                                                    ctypes.c_ulonglong(self.heap.offset_of(shard_slice)),
+                                                    ctypes.c_longlong(n), 2, ctypes.c_void_p(out.data_ptr()), s)
+            native.check(rc, "symm_all_gather_copy")
+            self.copies += self.world_size - 1
+            return
         if skip is None and only is None:
             rc = self.lib.b200_symm_all_gather(self.heap.table, self.world_size, self.rank, 1,
                                                ctypes.c_ulonglong(self.heap.offset_of(shard_slice)), ctypes.c_longlong(n),
@@ -182,6 +253,7 @@ class FusedCollectives:
                 ctypes.c_ulonglong(hi), 1 if skip is not None else 2, s)
         native.check(rc, "symm_all_gather")
         native.bump()
+        self.launches += 1
 
     def barrier(self, stream=None, channel: int = 1):
         self.barrier_epoch += 1
@@ -190,9 +262,14 @@ class FusedCollectives:
                                         ctypes.c_uint(self.barrier_epoch), ctypes.c_ulonglong(self.wait_ns), s)
         native.check(rc, "symm_barrier")
         native.bump()
+        self.launches += 1
+
+    def check_canaries(self) -> list:
+        return self._heap.check_canaries() if self._heap is not None else []
 
     def close(self):
-        self.heap.close()
+        if self._heap is not None:
+            self._heap.close()
 
 
 class LocalVirtualRanks:
@@ -251,6 +328,32 @@ class LocalVirtualRanks:
                                            ctypes.c_ulonglong(shard_off), ctypes.c_longlong(n_slice),
                                            _ptr_array([o.data_ptr() for o in outs]), blocks, native.stream_ptr())
         native.check(rc, "symm_all_gather")
+
+    def gemm_allgather(self, a, shard_off: int, n_slice: int, unit_buf, b_offset: int, b_shape, *, trans_b: bool,
+                       only_b: bool = False, n_copy: int = 4, add=None):
+        """The GEMM with the all-gather fused in, as ONE rank sees it, with every "peer" slice on this
+        device: ``unit_buf`` (W * n_slice bf16, local) is filled from the W heaps' slices at ``shard_off``
+        by the copy CTAs of the same launch that multiplies ``a`` with the weight stored at element
+        ``b_offset`` of ``unit_buf``. With ``only_b`` the kernel copies just the chunks that hold that
+        weight and the rest of the unit is gathered here by the pull kernel (range mode), as the ZeRO
+        manager does on its communication stream. Returns the product."""
+        from ..ops.gemm import ag_region, gemm_allgather
+        W = self.world_size
+        assert unit_buf.numel() == W * n_slice and unit_buf.dtype == torch.bfloat16
+        peer = [b + shard_off for b in self.bases]
+        seg = torch.zeros((unit_buf.numel() * 2 + (1 << 20) - 1) >> 20, dtype=torch.int64, device=self.device)
+        if only_b:
+            n_b = 1
+            for d in b_shape:
+                n_b *= int(d)
+            lo, hi = ag_region(n_slice * 2, W, b_offset * 2, n_b * 2)
+            rc = self.lib.b200_symm_all_gather_range(
+                _ptr_array(self.bases), W, 0, 1, ctypes.c_ulonglong(shard_off), ctypes.c_longlong(n_slice),
+                _ptr_array([unit_buf.data_ptr()]), 4, ctypes.c_ulonglong(lo), ctypes.c_ulonglong(hi), 1,
+                native.stream_ptr())
+            native.check(rc, "symm_all_gather_range")
+        return gemm_allgather(a, unit_buf, b_offset, tuple(b_shape), trans_b=trans_b, peer_slices=peer, seg=seg,
+                              epoch=1, n_copy=n_copy, add=add, only_b=only_b)
 
     def barrier(self, channel: int = 1):
         self.barrier_epoch += 1

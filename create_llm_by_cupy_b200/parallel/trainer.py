@@ -42,7 +42,8 @@ class Trainer:
                  total_steps: int = 1000, beta1: float = 0.9, beta2: float = 0.99, epsilon: float = 1e-6,
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
                  profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False,
-                 profile_phases: bool = False, adam_overlap: bool = True, cuda_graph: bool = False):
+                 profile_phases: bool = False, adam_overlap: bool = True, cuda_graph: bool = False,
+                 defer_host_read: bool = False):
         self.rank, self.world_size = rank, world_size
         self.profile_phases = bool(profile_phases)
         self._phase_marks = []
@@ -72,6 +73,16 @@ class Trainer:
                                 gs.get("Scale_Up_Step"), enabled=bool(gs.get("enabled", False)))
         self.iteration = 0
         self.last = {}
+        # Deferred host read: the loss and the gradient statistics of step k are copied to pinned host
+        # memory at the end of step k and read while step k + 1 is already queued, so the host never
+        # waits for the device between steps (``train_step`` then returns the scalars of the step before;
+        # ``flush_host_read`` returns the last one). The skip-on-non-finite decision stays on the device;
+        # only the host's bookkeeping (schedule step count, logging) lags by one step. Not with loss
+        # scaling: the scale of the next step depends on this step's overflow flag.
+        self.defer_host_read = bool(defer_host_read and self.device.type == "cuda" and not self.scaler.enabled)
+        self._pending_read = None
+        self._host_slots = None
+        self._host_slot_i = 0
         # Pipelined optimizer: AdamW runs unit by unit on its own stream in the order the next forward
         # needs the parameters, and the next step starts while it is still running (AdamW is bound by
         # HBM, the forward by the tensor cores). Needs the GPU optimizer, one micro-batch per step
@@ -174,9 +185,8 @@ class Trainer:
         native.bump(self._graph_launches)
         return self._g_loss, self._g_stats, step_scale
 
-    def _finish_step(self, loss_acc, stats, n_micro: int, step_scale: float, scale: float) -> dict:
-        """One host read per step (loss, gradient statistics) and the host-side bookkeeping."""
-        host = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)]).tolist()
+    def _account(self, host, n_micro: int, step_scale: float, scale: float, iteration: int) -> dict:
+        """Host-side bookkeeping of one finished step from its scalars [loss sum, sum g^2, non-finite flag]."""
         loss_val = host[0] / n_micro
         bad = host[2] != 0.0 or not math.isfinite(host[1])
         if bad and not self.fused_adam:   # the kernels skipped the update; keep the schedule where it was
@@ -184,10 +194,42 @@ class Trainer:
             if self.replica_optimizer is not None:
                 self.replica_optimizer.t -= 1
         self.scaler.UpdateScale(bad)
-        self.iteration += 1
         gnorm = math.sqrt(max(host[1], 0.0)) * step_scale if not bad else float("nan")
         self.last = {"loss": loss_val, "grad_norm": gnorm, "skipped": bad, "GradScale": scale,
-                     "lr": self.optimizer.current_lr}
+                     "lr": self.optimizer.current_lr, "iteration": iteration}
+        return self.last
+
+    def _finish_step(self, loss_acc, stats, n_micro: int, step_scale: float, scale: float) -> dict:
+        """One host read per step (loss, gradient statistics) and the host-side bookkeeping. With
+        ``defer_host_read`` the read is of the PREVIOUS step (see the constructor); the first call then
+        returns a placeholder with ``pending`` set."""
+        dev = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)])
+        self.iteration += 1
+        if not self.defer_host_read:
+            return self._account(dev.tolist(), n_micro, step_scale, scale, self.iteration)
+        if self._host_slots is None:
+            self._host_slots = [torch.zeros(3, dtype=torch.float32).pin_memory() for _ in range(2)]
+        slot = self._host_slots[self._host_slot_i]
+        self._host_slot_i ^= 1
+        slot.copy_(dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        prev, self._pending_read = self._pending_read, (slot, ev, n_micro, step_scale, scale, self.iteration)
+        if prev is None:
+            return {"loss": float("nan"), "grad_norm": float("nan"), "skipped": False, "GradScale": scale,
+                    "lr": self.optimizer.current_lr, "iteration": 0, "pending": True}
+        return self._read_pending(prev)
+
+    def _read_pending(self, rec) -> dict:
+        slot, ev, n_micro, step_scale, scale, it = rec
+        ev.synchronize()
+        return self._account(slot.tolist(), n_micro, step_scale, scale, it)
+
+    def flush_host_read(self) -> dict:
+        """Scalars of the most recent step (waits for it when the read was deferred)."""
+        if self._pending_read is not None:
+            rec, self._pending_read = self._pending_read, None
+            return self._read_pending(rec)
         return self.last
 
     def train_step(self, batches) -> dict:
@@ -220,19 +262,13 @@ class Trainer:
             mgr.grad_shard_f16[:1] = float("nan")
             self.inject_nan_next = False
         with nvtx_range("optimizer"):
+            rgrad = None
+            if self.replica_optimizer is not None:
+                # first, so that the replica slices join the one statistics pass / all-reduce below
+                rgrad = mgr.prepare_replicated_grads_for_sharded_optimizer()
             stats = mgr.calculate_global_grad_stats(to_host=False)
             self._mark("grad_stats")
             step_scale = 1.0 / (self.world_size * n_micro * scale)
-            if self.replica_optimizer is not None:
-                rgrad = mgr.prepare_replicated_grads_for_sharded_optimizer()
-                # the replica slices join the same global norm
-                from ..ops import functional as F
-                extra = torch.zeros_like(stats)
-                F.grad_stats(rgrad, extra)
-                if self.world_size > 1:
-                    self.comm.all_reduce(extra)
-                stats = stats + extra
-                stats[1] = (stats[1] != 0).float()
             pipelined = False
             if self.adam_overlap and mgr.direct_grad:
                 pipelined = True
@@ -303,8 +339,11 @@ class Trainer:
 
     # ------------------------------------------------------------------ checkpoint
     def save(self, directory: str, extra: dict | None = None):
+        self.flush_host_read()
+        gen = getattr(self.model, "_gen", None)
         state = {"iteration": self.iteration, "scaler": self.scaler.state_dict(),
-                 "torch_rng": torch.get_rng_state(), "numpy_rng": np.random.get_state(), "extra": extra or {}}
+                 "torch_rng": torch.get_rng_state(), "numpy_rng": np.random.get_state(),
+                 "model_rng": gen.get_state().cpu() if gen is not None else None, "extra": extra or {}}
         self.join_optimizer()
         self.manager.synchronize()
         ckpt.save_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer, state)
@@ -312,12 +351,41 @@ class Trainer:
             self.comm.barrier()
 
     def load(self, directory: str) -> dict | None:
+        """Restore shard, optimizer state (re-seeded from the weights when the checkpoint has none),
+        iteration, loss scale and the random-number states. Ends with a device synchronise and a barrier
+        across ranks: in fused mode peers read this rank's shard directly, so nobody may start a step
+        before every rank has finished loading."""
+        self.flush_host_read()
         self.join_optimizer()
+        self.manager.synchronize()
         st = ckpt.load_checkpoint(directory, self.manager, self.optimizer, self.replica_optimizer)
         if st is not None:
             self.iteration = int(st.get("iteration", 0))
             self.scaler.load_state_dict(st.get("scaler", self.scaler.state_dict()))
+            if st.get("torch_rng") is not None:
+                torch.set_rng_state(torch.as_tensor(st["torch_rng"], dtype=torch.uint8))
+            if st.get("numpy_rng") is not None:
+                np.random.set_state(st["numpy_rng"])
+            gen = getattr(self.model, "_gen", None)
+            if gen is not None and st.get("model_rng") is not None:
+                gen.set_state(torch.as_tensor(st["model_rng"], dtype=torch.uint8))
+        self.manager.unit_ready = {}
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if self.world_size > 1:
+            self.comm.barrier()
         return st
+
+    def close(self):
+        """Release what outlives the Python objects: the symmetric heap of the fused collectives
+        (checked for overwritten guard blocks on the way out)."""
+        self.flush_host_read()
+        self.join_optimizer()
+        self.manager.synchronize()
+        if self.world_size > 1:
+            self.comm.barrier()
+        if self.manager.fused is not None:
+            self.manager.fused.close()
 
 
 # ------------------------------------------------------------------------------- worker
@@ -364,10 +432,21 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
     logger = MetricsLogger(rank, wand=bool(a.get("wand", False)), config=a.get("model_dic"),
                            jsonl_path=a.get("metrics_path"), console=bool(a.get("console", True)))
     result = {}
+    trainer = None
     try:
         md = a["model_dic"]
         B, T, accum = int(a["batch_size"]), int(md["time_size"]), int(a.get("accum_step", 1))
         max_iters = int(a["max_iters"])
+        # Peer-memory collectives (fused reduce-scatter + statistics, copy-engine / pull gathers) are what a
+        # multi-GPU job runs by default; ``zero3_fused_collectives=False`` selects the NCCL path.
+        fused = None
+        if on_gpu and world_size > 1 and bool(md.get("zero3_fused_collectives", True)) \
+                and getattr(comm, "backend", "") == "nccl":
+            from .symm import FusedCollectives
+            fkw = {}
+            if a.get("peer_wait_s") is not None:
+                fkw["wait_ns"] = int(float(a["peer_wait_s"]) * 1e9)
+            fused = FusedCollectives(comm, device, gather_mode=str(md.get("zero3_gather_mode", "copy")), **fkw)
         trainer = Trainer(md, rank=rank, world_size=world_size, comm=comm, device=device,
                           zero_stage=a.get("zero_stage", "3"), optimizer_device=a.get("optimizer_device", "gpu"),
                           accum_step=accum, lr_max=a.get("lr_max", 3e-4), lr_mini=a.get("lr_mini", 3e-5),
@@ -375,12 +454,14 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
                           total_steps=max_iters * int(a.get("max_epoch", 1)), beta1=a.get("beta1", 0.9),
                           beta2=a.get("beta2", 0.99), epsilon=a.get("epsilon", 1e-6), max_grads=a.get("max_grads", 1.0),
                           GradScale_dic=a.get("GradScale_dic"), logger=logger, param_path=a.get("train_continue_path"),
-                          profile_comm=bool(a.get("profile_timing", False)))
+                          profile_comm=bool(a.get("profile_timing", False)), fused=fused,
+                          defer_host_read=bool(a.get("defer_host_read", True)))
         if a.get("resume_dir") and os.path.exists(ckpt.model_shard_path(a["resume_dir"], rank)):
             trainer.load(a["resume_dir"])
         if rank == 0:
             logger.line(f"parameters: {trainer.n_params:,}; shard {trainer.manager.shard_size * 2 / 2**30:.3f} GiB/rank; "
-                        f"world {world_size}; ZeRO-{a.get('zero_stage', '3')}")
+                        f"world {world_size}; ZeRO-{a.get('zero_stage', '3')}; collectives: "
+                        + ("nccl" if fused is None else f"peer memory (gather: {fused.gather_mode})"))
             print_memory_status("after init", printer=logger.line)
 
         pad = int(md["padding_id"])
@@ -395,44 +476,82 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
                                         int(a.get("n_gen", 4)), pad)
         tr_ids, tr_vl = shard_for_rank(*ds.train, rank, world_size)
         va_ids, va_vl = shard_for_rank(*ds.val, rank, world_size)
+        gen_ids, gen_vl = ds.gen
         stager = BatchStager(B, T, device)
         val_batches = None
         tokens_per_step = B * T * accum * world_size
-        losses = []
-        time_idx = 0
+        losses = {}
+        samples = []
+        # a resumed job continues where the saved one stopped: same epoch, same position in the data
+        start_epoch, start_it = divmod(trainer.iteration, max_iters)
+        time_idx = trainer.iteration * accum
         hb = a.get("heartbeat_dir")
         t_last = time.perf_counter()
-        for epoch in range(int(a.get("max_epoch", 1))):
-            for it in range(trainer.iteration % max_iters if epoch == 0 else 0, max_iters):
+
+        def report(out):
+            nonlocal t_last
+            if out.get("pending"):
+                return
+            losses[out["iteration"]] = out["loss"]
+            now = time.perf_counter()
+            tok_s = tokens_per_step / max(now - t_last, 1e-9)
+            t_last = now
+            logger.log({"loss": out["loss"], "Perplexity": math.exp(min(out["loss"], 30.0)),
+                        "Grad Norm": out["grad_norm"], "GradScale": out["GradScale"],
+                        "tokens_per_s": tok_s}, step=out["iteration"])
+            e, i = divmod(out["iteration"] - 1, max_iters)
+            logger.step_line(e, i + 1, max_iters, out["loss"],
+                             {"gnorm": out["grad_norm"], "tok/s": tok_s, "skipped": out["skipped"]})
+
+        stop_after = int(a.get("stop_after") or 0)      # leave after this many iterations in total (0: run to the end)
+        for epoch in range(start_epoch, int(a.get("max_epoch", 1))):
+            for it in range(start_it if epoch == start_epoch else 0, max_iters):
+                if stop_after and trainer.iteration >= stop_after:
+                    break
                 _heartbeat(hb, rank, it)
                 _maybe_inject(a.get("fault"), rank, it, trainer)
                 batches = []
                 for _ in range(accum):
                     xb, vb, time_idx = get_batch(tr_ids, tr_vl, B, time_idx)
                     batches.append(stager.stage(xb, vb, pad))
-                out = trainer.train_step(batches)
-                losses.append(out["loss"])
-                now = time.perf_counter()
-                tok_s = tokens_per_step / max(now - t_last, 1e-9)
-                t_last = now
-                logger.log({"loss": out["loss"], "Perplexity": math.exp(min(out["loss"], 30.0)),
-                            "Grad Norm": out["grad_norm"], "GradScale": out["GradScale"],
-                            "tokens_per_s": tok_s}, step=trainer.iteration)
-                logger.step_line(epoch, it + 1, max_iters, out["loss"],
-                                 {"gnorm": out["grad_norm"], "tok/s": tok_s, "skipped": out["skipped"]})
-                if a.get("vali") and (it + 1) % int(a.get("vali_step", 600)) == 0 and len(va_ids) >= B:
-                    if val_batches is None:
-                        val_batches = [stager.stage(va_ids[i:i + B], va_vl[i:i + B], pad)
-                                       for i in range(0, len(va_ids) - B + 1, B)]
-                    v = trainer.validate(val_batches)
-                    logger.log({"validation": v}, step=trainer.iteration)
-                    logger.line(f"validation loss {v:.4f}")
+                report(trainer.train_step(batches))
+                if a.get("vali") and (it + 1) % int(a.get("vali_step", 600)) == 0:
+                    report(trainer.flush_host_read())
+                    if len(va_ids) >= B:
+                        if val_batches is None:
+                            val_batches = [stager.stage(va_ids[i:i + B], va_vl[i:i + B], pad)
+                                           for i in range(0, len(va_ids) - B + 1, B)]
+                        v = trainer.validate(val_batches)
+                        logger.log({"validation": v}, step=trainer.iteration)
+                        logger.line(f"validation loss {v:.4f}")
+                    # Generation split (the third part of the reference's "Train, Validation, Generation"):
+                    # every rank takes part in the gathers, the samples are logged once.
+                    n_prompt = int(a.get("gen_prompt_tokens", 16))
+                    for g in range(min(len(gen_ids), int(a.get("gen_samples", 1)))):
+                        prompt = [int(v) for v in gen_ids[g][:min(n_prompt, int(gen_vl[g]), T - 2)] if int(v) != pad]
+                        if not prompt:
+                            continue
+                        toks = trainer.generate(prompt, max_new_tokens=int(a.get("gen_tokens", 32)),
+                                                greedy=bool(a.get("gen_greedy", True)), padding_id=pad)
+                        samples.append({"iteration": trainer.iteration, "prompt": prompt, "tokens": toks})
+                        logger.log({"generated_tokens": len(toks)}, step=trainer.iteration)
+                        logger.line(f"generation sample {g}: prompt {prompt} -> {toks}")
                 if a.get("save") and a.get("save_dir") and (it + 1) % int(a.get("save_step", 2000)) == 0:
+                    report(trainer.flush_host_read())
                     trainer.save(a["save_dir"])
+        report(trainer.flush_host_read())
         trainer.manager.synchronize()
-        result = {"losses": losses, "iteration": trainer.iteration}
+        from ..ops import native
+        if on_gpu:
+            native.raise_on_status()
+        result = {"losses": [losses[k] for k in sorted(losses)], "iteration": trainer.iteration,
+                  "generation": samples, "native_launches": native.launch_count(),
+                  "fused_launches": fused.launches if fused is not None else 0,
+                  "copy_engine_transfers": fused.copies if fused is not None else 0,
+                  "collectives": "nccl" if fused is None else f"fused:{fused.gather_mode}"}
         if a.get("result_dir"):
             ckpt.atomic_pickle_gzip(result, os.path.join(a["result_dir"], f"result_rank{rank}.pkl.gz"))
+        trainer.close()
     except BaseException:
         traceback.print_exc()
         logger.close()

@@ -176,6 +176,12 @@ class MemoryZeRO3Manager:
 
         self._tag_model_param_indices()
         self._build_layout()
+        if self.cuda and self.world_size > 1 and getattr(model, "keep_params_until_backward", False):
+            # One multi-GPU run with this option never finished and its cause was not established; until it
+            # is, the option is accepted on CPU ranks (where it is tested) and on a single GPU only.
+            raise ValueError("keep_params_until_backward is not available on multi-GPU runs")
+        if fused is not None:
+            fused.reserve(self._heap_bytes_needed())
         # Gradients accumulate in fp32 across micro-batches (the reference accumulates in fp16,
         # model/ZeRO3.py:1396); with a single micro-batch the reduced bf16 gradient is used as is.
         self.grad_dtype = self.dtype if (self.accum_steps == 1) else torch.float32
@@ -207,6 +213,33 @@ class MemoryZeRO3Manager:
         self.bytes_reduced = 0
         self.micro_index = 0        # micro-batch inside the current optimizer step
         self._stats = torch.zeros(2, dtype=torch.float32, device=self.device)
+        if self.cuda and self.world_size > 1:
+            self._prewarm_pools()
+
+    def _heap_bytes_needed(self) -> int:
+        """Bytes of symmetric heap this manager allocates: the parameter shard, two gradient buckets per
+        distinct unit size (see ``_Pool.rotate``), the replicated parameters and their gradient bucket
+        (ZeRO-2.5), each with its guard blocks."""
+        esz = 2
+        sizes = sorted({u.padded for u in self.layout.units if not u.empty})
+        total = max(self.shard_size, 8) * esz + sum(2 * n * esz for n in sizes)
+        total += 2 * self.layout.replica_padded_total * esz
+        return total + 1024 * (2 * len(sizes) + 4)
+
+    def _prewarm_pools(self):
+        """Create the pooled buffers the steady state needs before the first collective runs, so that no
+        device allocation (a ``cudaMalloc`` inside the caching allocator, which can serialise with kernels
+        that wait for a peer) happens while such kernels are in flight: per distinct unit size two gradient
+        buckets (the rotation) and as many gather buffers as are live at once (two where several units
+        share the size: the unit in use and the prefetched one)."""
+        count = collections.Counter(u.padded for u in self.layout.units if not u.empty)
+        for n in sorted(count):
+            bufs = [self.grad_pool.get(n) for _ in range(self.grad_pool.rotate)]
+            for b in bufs:
+                self.grad_pool.put(b)
+            bufs = [self.gather_pool.get(n) for _ in range(2 if count[n] > 1 else 1)]
+            for b in bufs:
+                self.gather_pool.put(b)
 
     # ------------------------------------------------------------------ layout
     def _tag_model_param_indices(self):
@@ -242,9 +275,22 @@ class MemoryZeRO3Manager:
 
     def _init_replica_buffers(self):
         n = self.replica_padded_total
-        self.replica_param_f16 = torch.zeros(n, dtype=self.dtype, device=self.device) if n else None
-        self.replica_grad_f16 = torch.zeros(n, dtype=torch.float32 if self.accum_steps > 1 else self.dtype,
-                                            device=self.device) if n else None
+        gdt = torch.float32 if self.accum_steps > 1 else self.dtype
+        self._replica_bucket = None         # bf16 heap copy of an fp32 replica gradient (fused reduce-scatter input)
+        self._replica_shard_buf = None      # reduced slice the replica optimizer reads (allocated once)
+        self._replica_stats_fused = False
+        if n and self.fused is not None and self.world_size > 1:
+            # peers pull the updated slices / the gradient slices straight out of these buffers
+            self.replica_param_f16 = self.fused.alloc(n, self.dtype)
+            bucket = self.fused.alloc(n, self.dtype)
+            if gdt == self.dtype:
+                self.replica_grad_f16 = bucket
+            else:
+                self.replica_grad_f16 = torch.zeros(n, dtype=gdt, device=self.device)
+                self._replica_bucket = bucket
+        else:
+            self.replica_param_f16 = torch.zeros(n, dtype=self.dtype, device=self.device) if n else None
+            self.replica_grad_f16 = torch.zeros(n, dtype=gdt, device=self.device) if n else None
         self.replica_grad_shard = None
         self.replica_views = {}
         self.replica_grad_views = {}
@@ -740,7 +786,7 @@ class MemoryZeRO3Manager:
         if self.fused is None or self.world_size == 1:
             st.zero_()
             F.grad_stats(self.grad_shard_f16, st)
-        if self.replica_grad_shard is not None:
+        if self.replica_grad_shard is not None and not self._replica_stats_fused:
             F.grad_stats(self.replica_grad_shard, st)
         if self.world_size > 1:
             self.comm.all_reduce(st)
@@ -816,13 +862,27 @@ class MemoryZeRO3Manager:
     def prepare_replicated_grads_for_sharded_optimizer(self):
         """Reduce-scatter the locally accumulated replica gradients so each rank holds the summed
         slice its replica optimizer owns (the reference all-reduces the whole buffer and slices,
-        model/ZeRO2_5.py:1240-1265)."""
+        model/ZeRO2_5.py:1240-1265). Call it BEFORE ``calculate_global_grad_stats``: the slices join
+        the same global norm - in fused mode the reduce-scatter kernel adds their sum of squares and
+        non-finite flag to the statistics itself, otherwise the statistics pass reads the slice."""
         if self.replica_grad_f16 is None:
             return None
         n = self.replica_opt_shard_size
-        out = torch.empty(n, dtype=self.replica_grad_f16.dtype, device=self.device)
+        if self._replica_shard_buf is None:
+            self._replica_shard_buf = torch.empty(n, dtype=self.replica_grad_f16.dtype, device=self.device)
+        out = self._replica_shard_buf
+        self._replica_stats_fused = False
         if self.world_size == 1:
             out.copy_(self.replica_grad_f16[:n])
+        elif self.fused is not None:
+            bucket = self.replica_grad_f16
+            if self._replica_bucket is not None:
+                self._replica_bucket.copy_(self.replica_grad_f16)        # fp32 accumulation -> bf16 bucket
+                bucket = self._replica_bucket
+            self.fused.reduce_scatter_accumulate(out, bucket, accumulate=False, stream=self.compute_stream,
+                                                 stats=self._stats, do_stats=True)
+            self._replica_stats_fused = True
+            self.bytes_reduced += (bucket.numel() - n) * bucket.element_size()
         else:
             self.comm.reduce_scatter(out, self.replica_grad_f16)
         self.replica_grad_shard = out
@@ -830,10 +890,18 @@ class MemoryZeRO3Manager:
 
     def allgather_replicated_params_from_optimizer_shards(self):
         """Rebuild the full replica from the slices the replica optimizers just updated
-        (model/ZeRO2_5.py:1272-1291)."""
+        (model/ZeRO2_5.py:1272-1291), in place: every rank's slice already sits at its position."""
         if self.replica_param_f16 is None or self.world_size == 1:
             return
-        self.comm.all_gather_into(self.replica_param_f16, self.get_replica_optimizer_shard_view().clone())
+        mine = self.get_replica_optimizer_shard_view()
+        if self.fused is not None and self.fused.gather:
+            self.fused.barrier(self.compute_stream)       # every rank has finished writing its slice
+            self.fused.all_gather(self.replica_param_f16, mine, self.compute_stream)
+        elif getattr(self.comm, "backend", "") == "gloo":
+            self.comm.all_gather_into(self.replica_param_f16, mine.clone())
+        else:
+            self.comm.all_gather_into(self.replica_param_f16, mine)
+        self.bytes_gathered += (self.replica_param_f16.numel() - mine.numel()) * mine.element_size()
 
     # ------------------------------------------------------------------ accounting
     def exposed_comm_ms(self, reset: bool = True) -> float:

@@ -133,15 +133,25 @@ def load_checkpoint(directory: str, manager, optimizer=None, replica_optimizer=N
     manager.param_shard_f16.copy_(_from_np(shard["param_shard_f16"], shard.get("dtype", "fp16")).to(manager.dtype))
     if manager.replica_param_f16 is not None and "replica_param_f16" in shard:
         manager.replica_param_f16.copy_(_from_np(shard["replica_param_f16"], shard.get("dtype", "fp16")).to(manager.dtype))
-    if optimizer is not None and os.path.exists(optimizer_path(directory, manager.rank)):
-        opt = read_pickle_gzip(optimizer_path(directory, manager.rank))
-        optimizer.load_state_dict({k: torch.from_numpy(np.asarray(opt[k])) if k != "t" else opt[k]
-                                   for k in ("m", "v", "w_fp32", "t")})
-        if replica_optimizer is not None and "replica_m" in opt:
-            replica_optimizer.load_state_dict({"m": torch.from_numpy(opt["replica_m"]),
-                                               "v": torch.from_numpy(opt["replica_v"]),
-                                               "w_fp32": torch.from_numpy(opt["replica_w_fp32"]),
+    have_opt = os.path.exists(optimizer_path(directory, manager.rank))
+    opt = read_pickle_gzip(optimizer_path(directory, manager.rank)) if have_opt else {}
+    if optimizer is not None:
+        if have_opt:
+            optimizer.load_state_dict({k: torch.from_numpy(np.asarray(opt[k])) if k != "t" else opt[k]
+                                       for k in ("m", "v", "w_fp32", "t")})
+        else:
+            # Weights without optimizer state (flat_to_shards, reshard_checkpoint(with_optimizer=False)): the
+            # fp32 master must follow the loaded shard, or the first AdamW step would write back values
+            # derived from the master of the randomly initialised model.
+            optimizer.reseed_from_params(manager.param_shard_f16)
+    if replica_optimizer is not None:
+        if "replica_m" in opt:
+            replica_optimizer.load_state_dict({"m": torch.from_numpy(np.asarray(opt["replica_m"])),
+                                               "v": torch.from_numpy(np.asarray(opt["replica_v"])),
+                                               "w_fp32": torch.from_numpy(np.asarray(opt["replica_w_fp32"])),
                                                "t": opt["replica_t"]})
+        else:
+            replica_optimizer.reseed_from_params(manager.get_replica_optimizer_shard_view())
     p = trainer_state_path(directory)
     return read_pickle_gzip(p) if os.path.exists(p) else None
 

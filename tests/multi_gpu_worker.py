@@ -25,11 +25,10 @@ def main():
     if mode == "fused":
         from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
         fused = FusedCollectives(comm, dev, heap_bytes=512 << 20, wait_ns=5_000_000_000,
-                                 gather_mode=os.environ.get("B200_TEST_GATHER", "gemm"))
+                                 gather_mode=os.environ.get("B200_TEST_GATHER", "copy"))
     accum = int(os.environ.get("B200_TEST_ACCUM", "2"))
     md = dict(vocab_size=2048, hidden_size=256, layer_num=3, time_size=256, q_head=4, kv_head=2, ffn_size=688,
-              padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=1,
-              keep_params_until_backward=os.environ.get("B200_TEST_KEEP", "0") == "1")
+              padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=1)
     fused_adam = os.environ.get("B200_TEST_FUSED_ADAM", "0") == "1"
     tr = Trainer(md, rank=rank, world_size=world, comm=comm, device=dev, accum_step=accum, lr_max=1e-3, warm_up=1,
                  total_steps=6, beta2=0.95, fused=fused, profile_comm=True, fused_adam=fused_adam,
@@ -53,8 +52,7 @@ def main():
         torch.save({"losses": (loss_t / world).tolist(), "param_norm": pn,
                     "exposed_ms": tr.manager.exposed_comm_ms()}, out_path)
     comm.barrier()
-    if fused is not None:
-        fused.close()
+    tr.close()                      # frees the heap; raises if a guard block around an allocation was overwritten
     shutdown_distributed()
 
 

@@ -106,3 +106,33 @@ def test_launcher_runs_clean_job(tmp_path):
     assert (tmp_path / "ck" / "model_shard_rank1.pkl.gz").exists()
     lines = open(tmp_path / "metrics.jsonl").read().strip().splitlines()
     assert any("validation" in ln for ln in lines) and any("tokens_per_s" in ln for ln in lines)
+    # the generation split is used: every validation point decodes from a prompt of that split
+    from create_llm_by_cupy_b200.utils import checkpoint as ckpt
+    res = ckpt.read_pickle_gzip(str(tmp_path / "result_rank0.pkl.gz"))
+    assert len(res["losses"]) == 4 and res["iteration"] == 4
+    assert len(res["generation"]) == 2 and all(len(g["tokens"]) > 0 for g in res["generation"])
+    assert any("generated_tokens" in ln for ln in lines)
+
+
+def test_launcher_resumes_at_the_saved_iteration_and_data_position(tmp_path):
+    """A job stopped after 3 of 6 iterations and resumed produces the losses of the uninterrupted job."""
+    from create_llm_by_cupy_b200.parallel.trainer import TrainMultiGPU
+    from create_llm_by_cupy_b200.utils import checkpoint as ckpt
+    from tests.dist_helpers import TINY
+
+    common = dict(use_devices=[0], batch_size=2, accum_step=1, backend="gloo", console=False, synthetic_samples=32,
+                  warm_up=2)
+    whole = tmp_path / "whole"
+    TrainMultiGPU(TINY, result_dir=str(whole), **common).fit(2 * 6)
+    ref = ckpt.read_pickle_gzip(str(whole / "result_rank0.pkl.gz"))["losses"]
+    assert len(ref) == 6
+    ck = tmp_path / "ck"
+    first = tmp_path / "first"
+    a = TrainMultiGPU(TINY, result_dir=str(first), save=True, save_step=3, save_dir=str(ck), **common)
+    a.args["stop_after"] = 3
+    a.fit(2 * 6)
+    second = tmp_path / "second"
+    TrainMultiGPU(TINY, result_dir=str(second), resume_dir=str(ck), **common).fit(2 * 6)
+    got = ckpt.read_pickle_gzip(str(second / "result_rank0.pkl.gz"))
+    assert got["iteration"] == 6
+    np.testing.assert_allclose(got["losses"], ref[3:], rtol=1e-5, atol=1e-6)

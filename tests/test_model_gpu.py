@@ -41,6 +41,37 @@ def test_forward_backward_matches_cpu_fp32_path():
         assert (a - b).abs().max().item() / denom < 6e-2, f"param {i}"
 
 
+@pytest.mark.parametrize("head_dim,T,B", [(128, 256, 2), (64, 256, 2), (128, 384, 1)])
+def test_forward_backward_on_the_tcgen05_attention_path_matches_cpu_fp32(head_dim, T, B):
+    """Model-level gradient check where everything fused runs together: rotary embedding in the K|Q|V GEMM
+    epilogue, tcgen05 attention forward, dK/dV kernel + dQ GEMM with the un-rotating epilogues, SwiGLU and
+    loss epilogues. Every gradient is compared with the fp32 CPU path in the maximum norm and in the
+    relative Frobenius norm (a wrong low-magnitude tile fails the second)."""
+    q_head, kv_head = 4, 2
+    cfg = dict(vocab_size=1024, hidden_size=head_dim * q_head, layer_num=2, time_size=T, q_head=q_head,
+               kv_head=kv_head, ffn_size=3 * 256, padding_id=0, dropout_rate=0, tie_embeddings=True, init_std=0.02,
+               seed=3, rope_base=10000.0)
+    gpu = Cupa_ver4(dict(cfg, dtype="bf16", half_float=True), device="cuda")
+    cpu = Cupa_ver4(dict(cfg, dtype="fp32", half_float=False), device="cpu")
+    cpu.load_flat(gpu.flat_params().float().cpu())
+    ids = synthetic_token_stream(B, T, 1024, "train", 0, low=1)
+    x, t, pa = padding_proceccing(ids, np.full(B, T), 0)
+    pa[0] = T - 57                                   # one ragged sequence
+    lg = gpu.forward(x.cuda(), t.cuda(), pa.cuda())
+    lc = cpu.forward(x, t, pa)
+    assert abs(float(lg) - float(lc)) < 2e-2
+    gpu.backward(1.0)
+    cpu.backward(1.0)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for i, (a, b) in enumerate(zip(gpu.grads, cpu.grads)):
+        a, b = a.float().cpu(), b.float()
+        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-8) < 6e-2, f"param {i} (max norm)"
+        rel = ((a - b).norm() / (b.norm() + 1e-12)).item()
+        # bf16 activations and bf16 gradient storage put ~1e-2 of relative noise on a weight gradient
+        assert rel < 3e-2, f"param {i}: relative Frobenius error {rel}"
+
+
 def test_config1_ten_steps_follow_the_oracle_and_greedy_decode():
     hp = dict(lr_max=3e-4, lr_mini=3e-5, weight_decay=0.1, warm_up=0, total_steps=10, beta1=0.9, beta2=0.95,
               epsilon=1e-6, max_grads=1.0)

@@ -107,6 +107,53 @@ def test_virtual_ranks_all_gather_and_barrier():
     vr.close()
 
 
+@pytest.mark.parametrize("W,only_b", [(2, False), (4, False), (4, True), (8, True)])
+def test_virtual_ranks_gemm_with_the_all_gather_fused_in(W, only_b):
+    """One rank's fused all-gather GEMM with all "peer" slices on this device: the unit buffer ends up equal
+    to the concatenation of the slices and the product equals the GEMM on the gathered weight - for the form
+    that copies the whole unit and the one that copies only the chunks of its own weight."""
+    from create_llm_by_cupy_b200.ops import functional as F
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    H, N2, M = 512, 768, 384                          # weight [H, N2] at the start of the unit, then other parameters
+    extra = 40_000
+    n_unit = ((H * N2 + extra + W * 128 - 1) // (W * 128)) * (W * 128)
+    n_slice = n_unit // W
+    vr = LocalVirtualRanks(W, heap_bytes=32 << 20)
+    off, shards = vr.alloc(n_slice, torch.bfloat16)
+    full = (torch.randn(n_unit, generator=torch.Generator().manual_seed(W)) * 0.5).to(torch.bfloat16)
+    for r, sh in enumerate(shards):
+        sh.copy_(full[r * n_slice:(r + 1) * n_slice])
+    a = (torch.randn(M, H, generator=torch.Generator().manual_seed(7)) * 0.5).to(torch.bfloat16).cuda()
+    unit_buf = torch.zeros(n_unit, dtype=torch.bfloat16, device="cuda")
+    out = vr.gemm_allgather(a, off, n_slice, unit_buf, 0, (H, N2), trans_b=False, only_b=only_b)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    assert torch.equal(unit_buf.cpu(), full)
+    ref = F.gemm(a, full[:H * N2].view(H, N2).cuda())
+    assert torch.equal(out, ref)
+    vr.close()
+
+
+def test_heap_guard_blocks_report_a_write_past_the_end_of_an_allocation():
+    from create_llm_by_cupy_b200.parallel.comm import SingleProcessComm
+    from create_llm_by_cupy_b200.parallel.symm import SymmetricHeap
+
+    heap = SymmetricHeap(SingleProcessComm(), "cuda", heap_bytes=8 << 20)
+    a = heap.alloc(1000, torch.bfloat16)
+    b = heap.alloc(4096, torch.float32)
+    a.fill_(1.0)
+    b.fill_(2.0)
+    assert heap.check_canaries() == []
+    off_b, nbytes_b = heap.guards[1]
+    heap.bytes_view[off_b + nbytes_b + 3] = 0          # one byte behind the second allocation
+    assert heap.check_canaries() == [1]
+    heap.bytes_view[off_b - 1] = 7                     # and one in front of it
+    assert heap.check_canaries() == [1]
+    with pytest.raises(RuntimeError, match="guard blocks"):
+        heap.close()
+
+
 def test_wait_on_a_flag_nobody_sets_times_out_with_an_error_status():
     """Failure detection on the device: the wait gives up after its (short) budget, records
     ERR_PEER_TIMEOUT and returns; the context stays usable."""
@@ -125,8 +172,11 @@ def test_wait_on_a_flag_nobody_sets_times_out_with_an_error_status():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+@pytest.mark.parametrize("gather", ["copy", "gemm"])
+def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path, gather):
+    """Gradient accumulation over two micro-batches; parameters gathered by the copy engines or inside
+    the first consuming GEMM."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_GATHER=gather)
     script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
     outs = {}
     for mode in ("nccl", "fused"):
@@ -163,25 +213,33 @@ def test_two_gpu_fused_reduce_scatter_adam_matches_nccl_baseline(tmp_path):
     assert abs(outs["nccl"]["param_norm"] - outs["fused"]["param_norm"]) < 1e-2 * outs["nccl"]["param_norm"]
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2 or os.environ.get("B200_TEST_KEEP_PARAMS") != "1",
-                    reason="needs 2 GPUs; opt-in (B200_TEST_KEEP_PARAMS=1): the option is experimental")
-def test_two_gpu_keep_params_until_backward_follows_the_regathering_run(tmp_path):
-    """Parameters kept gathered from the forward to their backward: same first loss to the last digit
-    (nothing but the forward has run), same curve within bf16 atomics noise."""
-    script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
-    outs = {}
-    for keep in ("0", "1"):
-        env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_ACCUM="1",
-                   B200_TEST_GATHER="pull", B200_TEST_KEEP=keep)
-        out = tmp_path / f"keep{keep}.pt"
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-               "--master-addr", "127.0.0.1", "--master-port", str(29900 + (os.getpid() % 90) + int(keep)),
-               script, "fused", str(out)]
-        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=180)
-        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
-        outs[keep] = torch.load(out)
-    a, b = outs["0"], outs["1"]
-    assert abs(a["losses"][0] - b["losses"][0]) < 1e-6, (a["losses"], b["losses"])
-    for la, lb in zip(a["losses"], b["losses"]):
-        assert abs(la - lb) < 2e-3, (a["losses"], b["losses"])
-    assert abs(a["param_norm"] - b["param_norm"]) < 1e-4 * a["param_norm"]
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("zero,ratio", [("3", 0.0), ("2.5", 0.5)])
+def test_launcher_trains_on_the_fused_collectives_by_default_and_matches_nccl(tmp_path, zero, ratio):
+    """``TrainMultiGPU`` (the product entry path) on 2 GPUs: by default the peer-memory collectives carry the
+    data plane (their launch and copy-engine counters move), and the loss curve equals that of the NCCL
+    run. ZeRO-2.5: the replica gradients and the replica rebuild take the same kernels."""
+    from create_llm_by_cupy_b200.parallel.trainer import TrainMultiGPU, TrainMultiGPU_ZeRO25
+    from create_llm_by_cupy_b200.utils import checkpoint as ckpt
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    md = dict(vocab_size=2048, hidden_size=256, layer_num=3, time_size=256, q_head=4, kv_head=2, ffn_size=768,
+              padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=1,
+              zero3_gather_mode="copy")
+    cls = TrainMultiGPU_ZeRO25 if zero == "2.5" else TrainMultiGPU
+    res = {}
+    for k, mode in enumerate(("fused", "nccl")):
+        out = tmp_path / mode
+        kw = dict(zero25_replica_ratio=ratio) if zero == "2.5" else {}
+        launcher = cls(dict(md, zero3_fused_collectives=mode == "fused"), use_devices=[0, 1], batch_size=2,
+                       accum_step=1, console=False, result_dir=str(out), synthetic_samples=64, lr_max=1e-3, warm_up=1,
+                       beta2=0.95, peer_wait_s=5.0, collective_timeout_s=120.0, heartbeat_timeout_s=300.0,
+                       master_port=24000 + (os.getpid() % 2000) + 7 * k + (50 if zero == "2.5" else 0), **kw)
+        assert launcher.fit(2 * 2 * 6) == [0, 0]
+        res[mode] = ckpt.read_pickle_gzip(str(out / "result_rank0.pkl.gz"))
+    f, n = res["fused"], res["nccl"]
+    assert f["collectives"] == "fused:copy" and n["collectives"] == "nccl"
+    assert f["fused_launches"] > 0 and f["copy_engine_transfers"] > 0 and n["fused_launches"] == 0
+    assert len(f["losses"]) == 6
+    for la, lb in zip(f["losses"], n["losses"]):
+        assert abs(la - lb) < 3e-2, (f["losses"], n["losses"])

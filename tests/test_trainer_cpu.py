@@ -137,6 +137,77 @@ def test_checkpoint_roundtrip_resume_flat_and_reshard(tmp_path):
         np.testing.assert_allclose(p.numpy(), q.numpy(), rtol=2e-3, atol=2e-3)
 
 
+def test_weights_without_optimizer_file_reseed_the_master_copy(tmp_path):
+    """flat -> shards writes no optimizer file. Loading it must make the fp32 master follow the loaded
+    weights: the first AdamW step then moves the parameters by about one learning-rate step instead of
+    replacing them with values derived from the randomly initialised master."""
+    src = Trainer(TINY, device="cpu", **HP)
+    for b in batches(3):
+        src.train_step([b])
+    flat = str(tmp_path / "flat.pkl.gz")
+    src.manager.materialize_all()
+    src.model.save_weights_to_flat_file(flat)
+    shapes = [tuple(p.shape) for p in src.model.params]
+    src.manager.release_all()
+    d = str(tmp_path / "shards")
+    ckpt.flat_to_shards(flat, d, shapes, src.model.unit_defs(), 1, dtype_name="fp32")
+    assert not os.path.exists(ckpt.optimizer_path(d, 0))
+    tr = Trainer(dict(TINY, seed=123), device="cpu", **HP)
+    tr.load(d)
+    loaded = full_params(tr)
+    np.testing.assert_array_equal(tr.optimizer.master_weight_shard.numpy(), tr.manager.param_shard_f16.float().numpy())
+    assert tr.optimizer.t == 0 and float(tr.optimizer.m.abs().max()) == 0.0
+    tr.train_step([batches(1)[0]])
+    for a, b in zip(full_params(tr), loaded):
+        assert np.abs(a - b).max() <= 3 * HP["lr_max"] * (1 + np.abs(b).max())
+
+
+def test_resume_restores_rng_states_and_iteration(tmp_path):
+    tr = Trainer(TINY, device="cpu", **HP)
+    tr.train_step([batches(1)[0]])
+    d = str(tmp_path / "ck")
+    torch.manual_seed(1234)
+    np.random.seed(99)
+    tr.save(d)
+    want_t, want_n = torch.rand(3), np.random.rand(3)
+    torch.manual_seed(1)
+    np.random.seed(1)
+    tr2 = Trainer(dict(TINY, seed=5), device="cpu", **HP)
+    tr2.load(d)
+    assert tr2.iteration == 1
+    assert torch.equal(torch.rand(3), want_t)
+    np.testing.assert_array_equal(np.random.rand(3), want_n)
+
+
+def test_replica_selection_stops_once_the_target_is_reached():
+    """Same rule as the reference (model/ZeRO2_5.py:863-892): take parameters in the policy's order until
+    the running total has reached int(total * ratio); the last one may overshoot, at least one is taken."""
+    from create_llm_by_cupy_b200.parallel.layout import select_replicated_params
+
+    sizes = [50, 10, 30, 5, 40, 15]          # total 150
+
+    def restated(order, ratio):
+        target, acc, out = int(sum(sizes) * ratio), 0, []
+        for i in order:
+            if acc >= target:
+                break
+            out.append(i)
+            acc += sizes[i]
+        return sorted(out)
+
+    by_size = sorted(range(6), key=lambda i: (-sizes[i], i))
+    for ratio in (0.01, 0.3, 0.34, 0.5, 0.9):
+        assert select_replicated_params(sizes, [2], ratio, "largest_first") == restated(by_size, ratio)
+        assert select_replicated_params(sizes, [2], ratio, "first") == restated(list(range(6)), ratio)
+        assert select_replicated_params(sizes, [2], ratio, "last") == restated(list(range(5, -1, -1)), ratio)
+        emb_first = [2] + [i for i in by_size if i != 2]
+        assert select_replicated_params(sizes, [2], ratio, "embedding_first") == restated(emb_first, ratio)
+    # a ratio below the embedding's share still replicates the embedding (never silently plain ZeRO-3)
+    assert select_replicated_params(sizes, [2], 0.05, "embedding_first") == [2]
+    assert select_replicated_params(sizes, [2], 0.0, "first") == []
+    assert select_replicated_params(sizes, [2], 1.0, "last") == list(range(6))
+
+
 def test_validation_and_generation_through_trainer():
     tr = Trainer(TINY, device="cpu", **HP)
     v = tr.validate(batches(2, seed_split="validation"))

@@ -41,23 +41,36 @@ def test_noalloc_matches_regular_entry_point_twice(M, H, with_add):
     partial = torch.empty(rows, H, dtype=torch.float32, device=dev)
     ref_dx, ref_dg = torch.empty(M, H, dtype=torch.bfloat16, device=dev), torch.empty(H, dtype=torch.bfloat16, device=dev)
     out_dx, out_dg = torch.empty_like(ref_dx), torch.empty_like(ref_dg)
+    kept = [tuple(torch.empty_like(t) for t in (ref_dx, ref_dg, out_dx, out_dg)) for _ in sets]
     import gc
     gc.collect()                              # garbage of earlier tests must not be freed in the middle of the measurement
+    # Warm the entry point once: under lazy module loading the first call on a device may load the module
+    # that holds the built-in scratch array (that is when the driver materialises its 4.75 MiB).
+    x0, dy0, add0, rstd0 = sets[0]
+    assert fn(_ptr(dy0), _ptr(x0), _ptr(gamma), _ptr(rstd0), _ptr(add0), _ptr(out_dx), _ptr(out_dg), M, H, 0, stream) == 0
+    assert lib.b200_rmsnorm_bwd(_ptr(dy0), _ptr(x0), _ptr(gamma), _ptr(rstd0), _ptr(add0), _ptr(ref_dx), _ptr(ref_dg),
+                                _ptr(partial), M, H, 0, stream) == 0
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
-    for (x, dy, add, rstd) in sets:          # two calls in a row share the built-in scratch
+    # torch's counter only sees torch's own allocator; the driver's free-byte count also sees a raw
+    # cudaMalloc made inside the library
+    free_before = torch.cuda.mem_get_info()[0]
+    for i, (x, dy, add, rstd) in enumerate(sets):      # two calls in a row share the built-in scratch
         rc = lib.b200_rmsnorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(rstd), _ptr(add), _ptr(ref_dx), _ptr(ref_dg),
                                   _ptr(partial), M, H, 0, stream)
         assert rc == 0
         rc = fn(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(rstd), _ptr(add), _ptr(out_dx), _ptr(out_dg), M, H, 0, stream)
         assert rc == 0
-        torch.cuda.synchronize()
-        scale = ref_dx.float().abs().max().item()
-        assert (out_dx.float() - ref_dx.float()).abs().max().item() <= 2e-2 + 2e-2 * scale
-        gscale = ref_dg.float().abs().max().item()
-        assert (out_dg.float() - ref_dg.float()).abs().max().item() <= 2e-2 + 2e-2 * gscale
-    gc.collect()
+        for dst, src in zip(kept[i], (ref_dx, ref_dg, out_dx, out_dg)):
+            dst.copy_(src)                    # into buffers made beforehand: nothing is allocated in this loop
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated or freed during the calls"
     assert torch.cuda.memory_allocated() == before
+    for r_dx, r_dg, o_dx, o_dg in kept:
+        scale = r_dx.float().abs().max().item()
+        assert (o_dx.float() - r_dx.float()).abs().max().item() <= 2e-2 + 2e-2 * scale
+        gscale = r_dg.float().abs().max().item()
+        assert (o_dg.float() - r_dg.float()).abs().max().item() <= 2e-2 + 2e-2 * gscale
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch():
