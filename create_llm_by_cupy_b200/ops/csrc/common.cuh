@@ -23,6 +23,20 @@
     }                                                                                         \
   } while (0)
 
+// Kernels that are meant to run BESIDE the persistent GEMM / attention CTAs (collectives, AdamW pipelined with
+// the next forward) ask for the same shared-memory carve-out as those CTAs, the maximum. An SM holds one
+// carve-out configuration at a time: a small kernel left on the driver's default (a small shared-memory
+// partition) and a 225 KiB GEMM CTA cannot be resident on one SM together, so each waits for the other to
+// drain - and a persistent GEMM cannot finish before every one of its CTAs has had its turn.
+#define B200_PREFER_MAX_SMEM(kernel)                                                                            \
+  do {                                                                                                          \
+    static bool _done = false;                                                                                  \
+    if (!_done) {                                                                                               \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared); \
+      _done = true;                                                                                             \
+    }                                                                                                           \
+  } while (0)
+
 namespace b200 {
 
 typedef __nv_bfloat16 bf16;

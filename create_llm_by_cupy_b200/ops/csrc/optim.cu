@@ -281,16 +281,20 @@ static int adamw_launch(const void* grad, int grad_fp32, void* m, void* v, void*
                         reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(master) |
                         (reinterpret_cast<uintptr_t>(param) << 1);
   const int vec = (all & 15) == 0;
-  if (grad_fp32)
+  // AdamW runs beside the next forward's GEMMs (pipelined optimizer): same carve-out as their CTAs
+  if (grad_fp32) {
+    B200_PREFER_MAX_SMEM(adamw_kernel<float>);
     adamw_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(grad), static_cast<float*>(m),
                                               static_cast<float*>(v), static_cast<float*>(master),
                                               static_cast<bf16*>(param), size_t(n), a,
                                               static_cast<const float*>(stats), vec, hyper);
-  else
+  } else {
+    B200_PREFER_MAX_SMEM(adamw_kernel<bf16>);
     adamw_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(grad), static_cast<float*>(m),
                                              static_cast<float*>(v), static_cast<float*>(master),
                                              static_cast<bf16*>(param), size_t(n), a,
                                              static_cast<const float*>(stats), vec, hyper);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -54,9 +54,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // for rank p's signal. Returns false (for the whole block) when a wait ran out of time.
 __device__ bool peer_block_barrier(const SymmTable& tab, int rank, int W, int channel, uint32_t epoch,
                                    unsigned long long wait_ns, int* status, int kernel_id) {
-  __shared__ int s_fail;
-  if (threadIdx.x == 0) s_fail = 0;
-  __syncthreads();
+  int fail = 0;          // combined over the block with a barrier-reduction: no shared memory is used
   if (threadIdx.x < W) {
     const int p = threadIdx.x;
     const int slot = (channel * SYMM_MAX_BLOCKS + int(blockIdx.x)) * SYMM_MAX_W;
@@ -68,7 +66,7 @@ __device__ bool peer_block_barrier(const SymmTable& tab, int rank, int W, int ch
     while (int32_t(ld_acquire_sys(mine) - epoch) < 0) {
       __nanosleep(spins < 64 ? 100 : 1000);     // back off: the SM is shared with compute kernels
       if ((++spins & 63) == 0 && globaltimer_ns() > deadline) {
-        s_fail = 1;
+        fail = 1;
         if (status != nullptr && atomicCAS(status, 0, ERR_PEER_TIMEOUT) == 0) {
           status[1] = kernel_id;
           status[2] = p;
@@ -77,8 +75,7 @@ __device__ bool peer_block_barrier(const SymmTable& tab, int rank, int W, int ch
       }
     }
   }
-  __syncthreads();
-  return s_fail == 0;
+  return __syncthreads_or(fail) == 0;
 }
 
 enum RsMode : int { RS_STORE = 0, RS_ACCUMULATE = 1, RS_ADAM = 2 };
@@ -374,6 +371,7 @@ B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0
   p.do_stats = do_stats; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
   if (blocks < 1) blocks = 1;
   if (blocks > SYMM_MAX_BLOCKS) blocks = SYMM_MAX_BLOCKS;
+  B200_PREFER_MAX_SMEM(rs_reduce_kernel);
   rs_reduce_kernel<<<dim3(blocks, vranks), 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -392,6 +390,7 @@ static int symm_all_gather_impl(const void* const* bases, int W, int rank0, int 
     return static_cast<int>(cudaErrorInvalidValue);
   p.range_lo = (long long)(range_lo_bytes / 16); p.range_hi = (long long)(range_hi_bytes / 16); p.range_mode = range_mode;
   if (blocks < 1) blocks = 1;
+  B200_PREFER_MAX_SMEM(ag_pull_kernel);
   ag_pull_kernel<<<dim3(blocks, vranks), 512, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -439,6 +438,7 @@ B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int v
   BarrierParams p = {};
   fill_tables(p.tab, bases, W, vranks);
   p.rank0 = rank0; p.W = W; p.channel = channel; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
+  B200_PREFER_MAX_SMEM(symm_barrier_kernel);
   symm_barrier_kernel<<<dim3(1, vranks), 32, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -446,6 +446,8 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
             fkw = {}
             if a.get("peer_wait_s") is not None:
                 fkw["wait_ns"] = int(float(a["peer_wait_s"]) * 1e9)
+            if md.get("zero3_copy_min_bytes") is not None:       # smaller slices use the pull kernel
+                fkw["copy_min_bytes"] = int(md["zero3_copy_min_bytes"])
             fused = FusedCollectives(comm, device, gather_mode=str(md.get("zero3_gather_mode", "copy")), **fkw)
         trainer = Trainer(md, rank=rank, world_size=world_size, comm=comm, device=device,
                           zero_stage=a.get("zero_stage", "3"), optimizer_device=a.get("optimizer_device", "gpu"),

@@ -225,7 +225,7 @@ def test_launcher_trains_on_the_fused_collectives_by_default_and_matches_nccl(tm
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     md = dict(vocab_size=2048, hidden_size=256, layer_num=3, time_size=256, q_head=4, kv_head=2, ffn_size=768,
               padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=1,
-              zero3_gather_mode="copy")
+              zero3_gather_mode="copy", zero3_copy_min_bytes=0)
     cls = TrainMultiGPU_ZeRO25 if zero == "2.5" else TrainMultiGPU
     res = {}
     for k, mode in enumerate(("fused", "nccl")):
