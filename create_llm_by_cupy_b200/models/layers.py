@@ -268,15 +268,25 @@ class SwiGLU:
         self.dropout_rate = dropout_rate
         self.drop = TimeDropout(dropout_rate, dtype, generator) if dropout_rate else None
 
+    def _gate_act(self, x: torch.Tensor, keep_gv: bool):
+        """(gv or None, act): the gate|value projection with the activation applied in the GEMM's epilogue
+        where that form exists (one kernel, the projection is only written when the backward will read it),
+        else the GEMM followed by the activation kernel."""
+        if (F.SWIGLU_EPILOGUE and getattr(self, "pending_gather", None) is None
+                and F.gemm_swiglu_fusable(x, self.params[0])):
+            return F.gemm_swiglu(x, self.params[0], keep_gv=keep_gv)
+        gv = _weight_gemm(self, x, 0)
+        return gv, F.swiglu_fwd(gv)
+
     def forward(self, x: torch.Tensor, residual=None, train_flg: bool = True) -> torch.Tensor:
-        gv = F.gemm(x, self.params[0])
-        act = F.swiglu_fwd(gv)
+        keep = train_flg and self.cache_gate
+        gv, act = self._gate_act(x, keep)
         if self.drop is not None and train_flg:
             out = self.drop.forward(F.gemm(act, self.params[1]), True)
             out = F.add(out, residual) if residual is not None else out
         else:
             out = F.gemm(act, self.params[1], add=residual)
-        self.cache = (x, gv if self.cache_gate else None, act if self.cache_gate else None) if train_flg else None
+        self.cache = (x, gv if keep else None, act if keep else None) if train_flg else None
         return out
 
     def backward(self, dout: torch.Tensor, grad_out=None) -> torch.Tensor:
@@ -284,8 +294,7 @@ class SwiGLU:
         if self.drop is not None:
             dout = self.drop.backward(dout)
         if gv is None:
-            gv = _weight_gemm(self, x, 0)
-            act = F.swiglu_fwd(gv)
+            gv, act = self._gate_act(x, True)
         go = grad_out if grad_out else (None, None)
         dW_out = F.wgrad_gemm(act, dout, out=go[1])
         dact = _weight_gemm(self, dout, 1, trans_b=True)
@@ -318,17 +327,22 @@ class TimeEmbedding_shard:
 
 
 class ChunkedCrossEntropy_Share:
-    """LM head + mean cross-entropy over non-pad targets without an ``[M, V]`` tensor.
+    """LM head + mean cross-entropy over non-pad targets without an ``[M, V]`` tensor
+    (reference: model/fast_layers.py:1280-1488, which makes two chunked passes forward and one backward).
 
-    Forward walks the vocabulary in chunks of ``chunk_size``: one fp32 logits GEMM per chunk folded
-    into running (max, sum-exp, target-logit) row statistics — a single pass, where the reference
-    makes two (model/fast_layers.py:1322-1367). Backward re-forms the logits chunk (or reuses the
-    kept ones when ``cache_logits``), turns it into ``(softmax - onehot) * GradScale / n_valid`` in
-    bf16 and feeds the two gradient GEMMs; ``dW`` rows go to ``grad_writer(row_start, row_end)``
-    -> destination view, so they land directly in the gradient bucket.
+    On CUDA the logits never reach memory. Forward: ONE GEMM over the whole vocabulary whose epilogue folds
+    each 256-column tile of the fp32 accumulator into per-row (max, sum-exp, target logit); a small merge gives
+    the row's log-sum-exp. Backward walks the vocabulary in chunks of ``chunk_size``: the logits of a chunk are
+    recomputed by a GEMM whose epilogue turns them into ``(softmax - onehot) * GradScale / n_valid`` in bf16 (the
+    only [M, chunk] tensor that exists), which feeds the two gradient GEMMs; ``dW`` rows go to
+    ``grad_writer(row_start, row_end)`` -> destination view, so they land directly in the gradient bucket.
+
+    Where the fused GEMMs do not apply (CPU tensors, tiny shapes, ``cache_logits`` asked for explicitly) the
+    chunked form with fp32 logits per chunk is used: one pass forward, logits kept for the backward only when
+    ``cache_logits``.
     """
 
-    def __init__(self, padding_id: int, chunk_size: int = 8192, dtype=torch.bfloat16, cache_logits: bool = True):
+    def __init__(self, padding_id: int, chunk_size: int = 8192, dtype=torch.bfloat16, cache_logits: bool = False):
         self.padding_id = padding_id
         self.chunk_size = int(chunk_size)
         self.cache_logits = cache_logits
@@ -338,22 +352,30 @@ class ChunkedCrossEntropy_Share:
         c = self.chunk_size if self.chunk_size > 0 else V
         return [(s, min(s + c, V)) for s in range(0, V, c)]
 
+    def _fused(self, x: torch.Tensor, W: torch.Tensor) -> bool:
+        return bool(F.CE_EPILOGUE and not self.cache_logits and F.gemm_ce_fusable(x, W))
+
     def forward(self, x: torch.Tensor, t: torch.Tensor, W: torch.Tensor, train_flg: bool = True) -> torch.Tensor:
         """x [M, H], t [M] int32 targets, W [V, H]. Returns the scalar mean loss (device tensor)."""
         M = x.shape[0]
         t = t.reshape(-1).to(torch.int32)
-        rmax = torch.empty(M, dtype=torch.float32, device=x.device)
-        rsum = torch.empty_like(rmax)
-        tlogit = torch.zeros_like(rmax)
-        kept = []
-        for i, (s, e) in enumerate(self._chunks(W.shape[0])):
-            logits = F.gemm(x, W[s:e], trans_b=True, out_dtype=torch.float32)
-            F.ce_stats(logits, t, rmax, rsum, tlogit, s, i == 0)
-            if train_flg and self.cache_logits:
-                kept.append(logits)
+        tlogit = torch.zeros(M, dtype=torch.float32, device=x.device)
+        kept = None
+        if self._fused(x, W):
+            pmax, psum = F.gemm_ce_stats(x, W, t, tlogit)
+            rmax, rsum = F.ce_merge(pmax, psum)
+        else:
+            rmax = torch.empty(M, dtype=torch.float32, device=x.device)
+            rsum = torch.empty_like(rmax)
+            kept = [] if (train_flg and self.cache_logits) else None
+            for i, (s, e) in enumerate(self._chunks(W.shape[0])):
+                logits = F.gemm(x, W[s:e], trans_b=True, out_dtype=torch.float32)
+                F.ce_stats(logits, t, rmax, rsum, tlogit, s, i == 0)
+                if kept is not None:
+                    kept.append(logits)
         loss_cnt = F.ce_loss(rmax, rsum, tlogit, t, self.padding_id)
         if train_flg:
-            self.cache = (x, t, rmax, rsum, loss_cnt, kept if self.cache_logits else None)
+            self.cache = (x, t, rmax, rsum, loss_cnt, kept)
         self.loss_cnt = loss_cnt
         return loss_cnt[0] / loss_cnt[1].clamp_min(1.0)
 
@@ -365,11 +387,17 @@ class ChunkedCrossEntropy_Share:
         self.dW = None
         if grad_writer is None:
             self.dW = torch.empty_like(W)
+        fused = kept is None and self._fused(x, W)
+        if fused:
+            lse, coef = F.ce_row_coef(rmax, rsum, t, loss_cnt, self.padding_id, float(GradScale))
         for i, (s, e) in enumerate(self._chunks(W.shape[0])):
-            logits = kept[i] if kept is not None else F.gemm(x, W[s:e], trans_b=True, out_dtype=torch.float32)
-            dlog = F.ce_dlogits(logits, t, rmax, rsum, loss_cnt, s, self.padding_id, float(GradScale), x.dtype)
-            if kept is not None:
-                kept[i] = None
+            if fused and (e - s) % 8 == 0 and e - s >= 256:
+                dlog = F.gemm_ce_dlogits(x, W[s:e], t, lse, coef, col0=s)
+            else:
+                logits = kept[i] if kept is not None else F.gemm(x, W[s:e], trans_b=True, out_dtype=torch.float32)
+                dlog = F.ce_dlogits(logits, t, rmax, rsum, loss_cnt, s, self.padding_id, float(GradScale), x.dtype)
+                if kept is not None:
+                    kept[i] = None
             dst = grad_writer(s, e) if grad_writer is not None else self.dW[s:e]
             F.gemm(dlog, x, trans_a=True, out=dst)
             dx = F.gemm(dlog, W[s:e], out=dx, add=dx) if dx is not None else F.gemm(dlog, W[s:e])

@@ -136,7 +136,7 @@ class Cupa_ver4:
 
         chunk = int(d.get("ce_chunk_size", 8192))
         self.AF_Cross_loss = ChunkedCrossEntropy_Share(self.padding_id, chunk, self.dtype,
-                                                      cache_logits=bool(d.get("ce_cache_logits", True)))
+                                                      cache_logits=bool(d.get("ce_cache_logits", False)))
         self.embed = TimeEmbedding_shard(self.padding_id, self.dtype)
         self.params = []
         self._initialize_layers()

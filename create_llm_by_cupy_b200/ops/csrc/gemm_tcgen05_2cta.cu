@@ -54,6 +54,15 @@ constexpr int G2_SCHED_SLOTS = 1024;   // {next tile, finished pairs} counter pa
 // whose CTAs fill the SMs a part-filled last round leaves idle anyway.
 enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4, G2_WHOLE_TILES = 8 };
 
+// What the epilogue does with the accumulator (a template parameter: the plain instantiations keep their
+// register count).
+//   EPI_ROPE       rotary embedding on the leading columns (K|Q|V projection)
+//   EPI_SWIGLU     B = [gate | value]; a work item holds 128 gate columns beside the 128 value columns of the
+//                  same index and leaves silu(gate) * value (and, on request, the raw projection)
+//   EPI_CE_STATS   LM head: nothing is stored but per-row (max, sum of exp, target logit) of the tile's columns
+//   EPI_CE_DLOGITS LM head again: (exp(logit - lse) - onehot) * coef leaves as bf16
+enum Gemm2Epi : int { EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_CE_STATS = 3, EPI_CE_DLOGITS = 4 };
+
 struct Gemm2Params {
   void* D;
   const void* C;
@@ -74,6 +83,18 @@ struct Gemm2Params {
   const float* rope_cos;
   const float* rope_sin;
   int rope_T, rope_cols, rope_dim, rope_ld;
+  // EPI_SWIGLU: N = 2 * sw_I. The leader CTA stages gate columns [g0, g0 + 128), the follower value columns
+  // [sw_I + g0, sw_I + g0 + 128); the activation goes out through the map in the tmBh slot (no half tiles in this
+  // mode), the raw gate / value halves through tmD / tmC when sw_store_gv is set.
+  int sw_I, sw_store_gv;
+  // EPI_CE_*: rows are tokens, column j is vocabulary id ce_col0 + j. Targets outside [0, vocabulary) match no column.
+  const int* ce_targets;     // [M]
+  float* ce_pmax;            // [tile columns][M] row maximum over one 256-column tile (EPI_CE_STATS)
+  float* ce_psum;            // [tile columns][M] sum of exp(logit - that maximum)
+  float* ce_tlogit;          // [M] logit of the target, written by the tile that holds it
+  const float* ce_lse;       // [M] log-sum-exp of the whole row (EPI_CE_DLOGITS)
+  const float* ce_coef;      // [M] valid * gradient scale / number of valid rows
+  int ce_col0, ce_nt0;       // vocabulary id of column 0; tile-column index of this call's first tile in pmax / psum
 };
 
 // A work item: tile coordinates, first column and width.
@@ -206,7 +227,7 @@ __device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& m
   nb = r / gsz;
 }
 
-template <bool A_MN, bool B_MN, bool kRope>
+template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
@@ -229,7 +250,9 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (p.M + 2 * G2_BM - 1) / (2 * G2_BM);
-  const int num_n = (p.N + G2_BN - 1) / G2_BN;
+  constexpr bool kRope = EPI == EPI_ROPE;
+  // SwiGLU: one tile column per 128 activation columns (its accumulator is 128 gate + 128 value columns)
+  const int num_n = EPI == EPI_SWIGLU ? (p.sw_I + G2_BN / 2 - 1) / (G2_BN / 2) : (p.N + G2_BN - 1) / G2_BN;
   const int num_tiles = p.n_items;          // work items (whole tiles and half tiles)
   const int num_kb = (p.K + G2_BK - 1) / G2_BK;
   const bool dyn = p.sched != nullptr;      // null: tile t + k * num_pairs goes to pair t (fixed assignment)
@@ -289,7 +312,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         else if (rank == 0) t_next = num_pairs + atomicAdd(&p.sched[0], 1);
         const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
         const int m0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
-        const int n0 = wi.n0 + int(rank) * (wi.bn / 2);
+        const int n0 = EPI == EPI_SWIGLU ? wi.nb * (G2_BN / 2) + int(rank) * p.sw_I : wi.n0 + int(rank) * (wi.bn / 2);
         const uint32_t stage_tx = 2 * (G2_A_BYTES + (wi.bn / 2) * G2_BK * 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
@@ -383,6 +406,135 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                                    (!add_c || ((p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0)));
     bool ok = true;
     TileRingReader rd;
+    if constexpr (EPI == EPI_CE_STATS) {
+      // LM-head logits that never leave the SM: every thread folds its row of the accumulator into
+      // (max, sum of exp, target logit) over the tile's valid columns and writes three floats.
+      const int r = q * 32 + lane;
+      for (int t = pair; ok && t >= 0 && t < num_tiles;
+           t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0)
+                   : t + num_pairs) {
+        const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+        const int row = wi.mb * 2 * G2_BM + int(rank) * G2_BM + r;
+        const int ncols = min(wi.bn, p.N - wi.n0);                       // valid columns of this tile
+        const int tcol = row < p.M ? __ldg(p.ce_targets + row) - p.ce_col0 - wi.n0 : -1;
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
+        float mx = -INFINITY, sum = 0.f, tl = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < wi.bn / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (c == wi.bn / 32 - 1) {                     // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+          }
+          const int left = ncols - c * 32;
+          if (left > 0) {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < left) cm = fmaxf(cm, __uint_as_float(v[j]));
+            const float nm = fmaxf(mx, cm);
+            float part = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < left) part += __expf(__uint_as_float(v[j]) - nm);
+              if (c * 32 + j == tcol) tl = __uint_as_float(v[j]);
+            }
+            sum = sum * __expf(mx - nm) + part;
+            mx = nm;
+          }
+        }
+        if (row < p.M) {
+          const size_t at = size_t(p.ce_nt0 + wi.nb) * size_t(p.M) + size_t(row);
+          p.ce_pmax[at] = mx;
+          p.ce_psum[at] = sum;
+          if (tcol >= 0 && tcol < ncols) p.ce_tlogit[row] = tl;
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    } else if constexpr (EPI == EPI_SWIGLU) {
+      // 256 rows x 128 activation columns per item: accumulator columns [0, 128) are the gate, [128, 256)
+      // the value. Per 64-column group the thread's row leaves as up to three 128-byte staging rows (raw
+      // gate, raw value, activation), each stored by TMA; two staging tiles alternate as in the plain path.
+      uint8_t* stg = smem + G2_STG_OFF;
+      const int r = q * 32 + lane;
+      const uint32_t swz = uint32_t(r & 7);
+      const bool elected = (warp == 2 && lane == 0);
+      uint32_t gcount = 0;
+      // One group: this thread's 64 fp32 values -> bf16 -> staging row; one thread stores the tile. `more`: another
+      // group of the same item follows (its staging tile is released here; an item's first one at the item's start).
+      auto put = [&](const uint32_t (&v)[64], const CUtensorMap* map, int x, int y, bool more) -> bool {
+        const uint32_t b = gcount & 1;
+        if (!mbar_wait(&stage_ready[b], (gcount >> 1) & 1, abort_flag)) return false;
+        uint8_t* rowp = stg + b * G2_STG_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 o;
+          bf162* o2 = reinterpret_cast<bf162*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            o2[e] = __floats2bfloat162_rn(__uint_as_float(v[8 * c + 2 * e]), __uint_as_float(v[8 * c + 2 * e + 1]));
+          *reinterpret_cast<uint4*>(rowp + ((uint32_t(c) ^ swz) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        named_bar_sync_128(1);
+        if (elected) {
+          if (x < p.sw_I) tma_store_2d(map, stg + b * G2_STG_BYTES, x, y);      // a group wholly past the edge is dropped
+          tma_store_commit();
+          if (more) {
+            tma_store_wait_read<1>();
+            mbar_arrive(&stage_ready[(gcount + 1) & 1]);
+          }
+        }
+        ++gcount;
+        return true;
+      };
+      for (int t = pair; ok && t >= 0 && t < num_tiles;
+           t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0)
+                   : t + num_pairs) {
+        const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+        const int row0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int g0 = wi.nb * (G2_BN / 2);
+        if (elected) {
+          tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
+          mbar_arrive(&stage_ready[gcount & 1]);
+        }
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
+#pragma unroll 1
+        for (int g = 0; g < 2 && ok; ++g) {
+          uint32_t ga[64], va[64];
+          tmem_ld_32x32b_x32(taddr + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&ga[0]));
+          tmem_ld_32x32b_x32(taddr + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&ga[32]));
+          tmem_ld_32x32b_x32(taddr + G2_BN / 2 + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&va[0]));
+          tmem_ld_32x32b_x32(taddr + G2_BN / 2 + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&va[32]));
+          tmem_ld_wait();
+          if (g == 1) {                                  // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+          }
+          const int x = g0 + g * 64;
+          if (p.sw_store_gv) {
+            if (!put(ga, &tmD, x, row0, true)) { ok = false; break; }
+            if (!put(va, &tmC, x, row0, true)) { ok = false; break; }
+          }
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const float gt = __uint_as_float(ga[j]);
+            ga[j] = __float_as_uint(gt / (1.f + __expf(-gt)) * __uint_as_float(va[j]));
+          }
+          if (!put(ga, &tmBh, x, row0, g == 0)) { ok = false; break; }
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (elected) tma_store_wait<0>();
+    } else
     if (p.flags & G2_TMA_OUT) {
       // Output through shared memory and TMA. A tile leaves in groups of 128 bytes per row (64 bf16
       // or 32 fp32 columns): every thread converts its accumulator row and writes it into a
@@ -419,6 +571,14 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           const int pos = min(row0 + r, p.M - 1) % p.rope_T;
           cs_row = p.rope_cos + pos;
           sn_row = p.rope_sin + pos;
+        }
+        float ce_lse = 0.f, ce_coef = 0.f;
+        int ce_t = -1;                          // target as a column of this call (vocabulary id - ce_col0)
+        if constexpr (EPI == EPI_CE_DLOGITS) {
+          const int row = min(row0 + r, p.M - 1);
+          ce_lse = __ldg(p.ce_lse + row);
+          ce_coef = __ldg(p.ce_coef + row);
+          ce_t = __ldg(p.ce_targets + row) - p.ce_col0;
         }
         if (elected) {
           tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
@@ -471,6 +631,16 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               }
             } else {
               tmem_ld_wait();
+              if constexpr (EPI == EPI_CE_DLOGITS) {
+                // logits -> (softmax - onehot) * coef with the row's log-sum-exp from the forward pass
+                const int tcol = ce_t - (n0 + g * 64);
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                  float x = __expf(__uint_as_float(v[j]) - ce_lse);
+                  if (j == tcol) x -= 1.f;
+                  v[j] = __float_as_uint(x * ce_coef);
+                }
+              }
               if (rope_g) {                                  // 64-wide head: both halves are in this group
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -630,20 +800,21 @@ static int* next_sched_slot() {
   return base[dev] + 2 * (next++ % G2_SCHED_SLOTS);
 }
 
-template <bool A_MN, bool B_MN, bool kRope = false>
+template <bool A_MN, bool B_MN, int EPI = EPI_PLAIN>
 static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tBh, const CUtensorMap* tD,
                       const CUtensorMap* tC, const Gemm2Params& p, cudaStream_t stream) {
-  auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN, kRope>;
+  auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
     B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
     configured = true;
   }
-  const int whole = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((p.N + G2_BN - 1) / G2_BN);
+  const int tile_cols = EPI == EPI_SWIGLU ? (p.sw_I + G2_BN / 2 - 1) / (G2_BN / 2) : (p.N + G2_BN - 1) / G2_BN;
+  const int whole = ((p.M + 2 * G2_BM - 1) / (2 * G2_BM)) * tile_cols;
   const int all_pairs = num_sms() / 2;
-  // a last round that fills less than half of the pairs is run on half tiles
+  // a last round that fills less than half of the pairs is run on half tiles (plain and rotary epilogues only)
   int halved = 0;
-  if (g_half_tiles && !(p.flags & G2_WHOLE_TILES) && whole > all_pairs) {
+  if (g_half_tiles && EPI <= EPI_ROPE && !(p.flags & G2_WHOLE_TILES) && whole > all_pairs) {
     const int rem = whole % all_pairs;
     if (rem > 0 && 2 * rem <= all_pairs) halved = rem;
   }
@@ -660,6 +831,13 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
   }
   kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tBh, *tD, *tC, q);
   return static_cast<int>(cudaGetLastError());
+}
+
+static Gemm2Params base_params(void* D, const void* C, int M, int N, int K, int ldd, int ldc, int flags, float alpha) {
+  Gemm2Params p = {};
+  p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
+  p.status = status_ptr();
+  return p;
 }
 
 }  // namespace b200
@@ -718,9 +896,7 @@ static int gemm_2cta_run(const void* A, const void* B, void* D, const void* C, i
   if (K <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0)
     return static_cast<int>(cudaErrorInvalidValue);
-  Gemm2Params p;
-  p.D = D; p.C = C; p.M = M; p.N = N; p.K = K; p.ldd = ldd; p.ldc = ldc; p.flags = flags; p.alpha = alpha;
-  p.status = status_ptr();
+  Gemm2Params p = base_params(D, C, M, N, K, ldd, ldc, flags, alpha);
   p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_T = rope_T; p.rope_cols = rope_cols; p.rope_dim = rope_dim;
   p.rope_ld = rope_ld;
   const CUtensorMap* tA = a_mn_major ? get_tensor_map_2d(A, K, M, lda, 64, 64, 2, SWIZZLE_128B_)
@@ -747,11 +923,86 @@ static int gemm_2cta_run(const void* A, const void* B, void* D, const void* C, i
   }
   if (p.rope_cos != nullptr) {       // the rotating epilogue exists for row-major A (x W) and TMA output
     if (!(p.flags & G2_TMA_OUT) || a_mn_major) return static_cast<int>(cudaErrorInvalidValue);
-    if (b_mn_major) return launch_tc2<false, true, true>(tA, tB, tBh, tD, tC, p, stream);
-    return launch_tc2<false, false, true>(tA, tB, tBh, tD, tC, p, stream);
+    if (b_mn_major) return launch_tc2<false, true, EPI_ROPE>(tA, tB, tBh, tD, tC, p, stream);
+    return launch_tc2<false, false, EPI_ROPE>(tA, tB, tBh, tD, tC, p, stream);
   }
   if (a_mn_major && b_mn_major) return launch_tc2<true, true>(tA, tB, tBh, tD, tC, p, stream);
   if (a_mn_major) return launch_tc2<true, false>(tA, tB, tBh, tD, tC, p, stream);
   if (b_mn_major) return launch_tc2<false, true>(tA, tB, tBh, tD, tC, p, stream);
   return launch_tc2<false, false>(tA, tB, tBh, tD, tC, p, stream);
+}
+
+// act[M, I] = silu(A W_gate) * (A W_value) for B = [W_gate | W_value] ([K, 2 I] row-major), A [M, K] row-major,
+// in the epilogue of ONE GEMM: a work item's accumulator holds 128 gate columns (the leader CTA's half of B)
+// beside the 128 value columns of the same index (the follower's half). GV ([M, 2 I], pitch ldgv), when not null,
+// also receives the raw projection (the backward needs it). I must be a multiple of 8 (16-byte column offset of
+// the value half); every base 16-byte aligned, every pitch a multiple of 8 elements.
+B200_API int b200_gemm_bf16_2cta_swiglu(const void* A, const void* B, void* GV, void* ACT, int M, int I, int K, int lda,
+                                        int ldb, int ldgv, int ldact, int flags, cudaStream_t stream) {
+  if (M <= 0 || I <= 0) return 0;
+  if (K <= 0 || (I % 8) != 0 || ACT == nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  const uintptr_t all = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(GV) |
+                        reinterpret_cast<uintptr_t>(ACT);
+  if ((all & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldact % 8) != 0 || (GV != nullptr && (ldgv % 8) != 0))
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p = base_params(ACT, nullptr, M, 2 * I, K, ldact, 0, (flags & G2_WHOLE_TILES) | G2_TMA_OUT, 1.0f);
+  p.sw_I = I;
+  p.sw_store_gv = GV != nullptr;
+  const CUtensorMap* tA = get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = get_tensor_map_2d(B, K, 2 * I, ldb, 64, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tAct = get_tensor_map_2d(ACT, M, I, ldact, 128, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tG = tA;
+  const CUtensorMap* tV = tA;
+  if (GV != nullptr) {
+    tG = get_tensor_map_2d(GV, M, I, ldgv, 128, 64, 2, SWIZZLE_128B_);
+    tV = get_tensor_map_2d(static_cast<const bf16*>(GV) + I, M, I, ldgv, 128, 64, 2, SWIZZLE_128B_);
+  }
+  if (!tA || !tB || !tAct || !tG || !tV) return static_cast<int>(cudaErrorInvalidValue);
+  return launch_tc2<false, true, EPI_SWIGLU>(tA, tB, tAct, tG, tV, p, stream);
+}
+
+// LM-head forward without logits in memory: for A [M, K] (tokens) and B [N, K] (vocabulary rows col0 .. col0 + N,
+// K-major) every 256-column tile leaves, per row, the maximum and the sum of exp(logit - maximum) of its valid
+// columns in pmax / psum ([tile columns][M], this call's first tile column at index nt0) and the tile that holds
+// the row's target writes that logit to tlogit[row]. A merge over the tile columns gives the row's log-sum-exp.
+B200_API int b200_gemm_bf16_2cta_ce_stats(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
+                                          const void* targets, void* pmax, void* psum, void* tlogit, int col0, int nt0,
+                                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0 || (lda % 8) != 0 ||
+      (ldb % 8) != 0 || !targets || !pmax || !psum || !tlogit)
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p = base_params(nullptr, nullptr, M, N, K, 0, 0, G2_WHOLE_TILES, 1.0f);
+  p.ce_targets = static_cast<const int*>(targets);
+  p.ce_pmax = static_cast<float*>(pmax);
+  p.ce_psum = static_cast<float*>(psum);
+  p.ce_tlogit = static_cast<float*>(tlogit);
+  p.ce_col0 = col0;
+  p.ce_nt0 = nt0;
+  const CUtensorMap* tA = get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);
+  return launch_tc2<false, false, EPI_CE_STATS>(tA, tB, tB, tA, tA, p, stream);
+}
+
+// LM-head backward, first GEMM: D[M, N] (bf16) = (exp(A B^T - lse[row]) - [column == target]) * coef[row], the
+// gradient of the mean cross-entropy w.r.t. the logits of vocabulary rows col0 .. col0 + N, formed on the
+// accumulator (the logits themselves are never stored). D must be TMA-addressable.
+B200_API int b200_gemm_bf16_2cta_ce_dlogits(const void* A, const void* B, void* D, int M, int N, int K, int lda, int ldb,
+                                            int ldd, const void* targets, const void* lse, const void* coef, int col0,
+                                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(D);
+  if (K <= 0 || (all & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 || (ldd % 8) != 0 || !targets || !lse || !coef)
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p = base_params(D, nullptr, M, N, K, ldd, 0, G2_WHOLE_TILES | G2_TMA_OUT, 1.0f);
+  p.ce_targets = static_cast<const int*>(targets);
+  p.ce_lse = static_cast<const float*>(lse);
+  p.ce_coef = static_cast<const float*>(coef);
+  p.ce_col0 = col0;
+  const CUtensorMap* tA = get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tD = get_tensor_map_2d(D, M, N, ldd, 128, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB || !tD) return static_cast<int>(cudaErrorInvalidValue);
+  return launch_tc2<false, false, EPI_CE_DLOGITS>(tA, tB, tB, tD, tD, p, stream);
 }

@@ -254,6 +254,34 @@ ce_dlogits_kernel(const float* __restrict__ logits, const int* __restrict__ targ
   }
 }
 
+// Rows of the fused LM-head path. The logits GEMM leaves, per 256-column tile, the row maximum and the sum
+// of exp(logit - maximum) ([nt][M]); this kernel merges the nt partials of a row into (rmax, rsum).
+__global__ void __launch_bounds__(256)
+ce_merge_kernel(const float* __restrict__ pmax, const float* __restrict__ psum, float* __restrict__ rmax,
+                float* __restrict__ rsum, int M, int nt) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float mx = -INFINITY;
+  for (int t = 0; t < nt; ++t) mx = fmaxf(mx, pmax[size_t(t) * M + row]);
+  float s = 0.f;
+  for (int t = 0; t < nt; ++t) s += psum[size_t(t) * M + row] * __expf(pmax[size_t(t) * M + row] - mx);
+  rmax[row] = mx;
+  rsum[row] = s;
+}
+
+// What the logit-gradient epilogue needs per row: lse = rmax + log(rsum) and
+// coef = valid(row) * gscale / max(number of valid rows, 1) (the count is read on the device).
+__global__ void __launch_bounds__(256)
+ce_row_coef_kernel(const float* __restrict__ rmax, const float* __restrict__ rsum, const int* __restrict__ targets,
+                   const float* __restrict__ loss_cnt, float* __restrict__ lse, float* __restrict__ coef, int M,
+                   int pad_id, float gscale) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  const int t = targets[row];
+  lse[row] = rmax[row] + logf(rsum[row]);
+  coef[row] = (t != pad_id && t >= 0) ? gscale / fmaxf(loss_cnt[1], 1.f) : 0.f;
+}
+
 static inline int grid_cap(size_t items, int block) {
   size_t g = (items + block - 1) / block;
   const size_t cap = size_t(num_sms()) * 8;
@@ -370,5 +398,22 @@ B200_API int b200_ce_dlogits(const void* logits, const void* targets, const void
                                                  static_cast<const float*>(rmax), static_cast<const float*>(rsum),
                                                  static_cast<const float*>(loss_cnt), static_cast<bf16*>(dlogits), M, C,
                                                  ld, ldd, col0, pad_id, gscale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_ce_merge(const void* pmax, const void* psum, void* rmax, void* rsum, int M, int nt, cudaStream_t st) {
+  if (M <= 0 || nt <= 0) return 0;
+  ce_merge_kernel<<<(M + 255) / 256, 256, 0, st>>>(static_cast<const float*>(pmax), static_cast<const float*>(psum),
+                                                   static_cast<float*>(rmax), static_cast<float*>(rsum), M, nt);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_ce_row_coef(const void* rmax, const void* rsum, const void* targets, const void* loss_cnt, void* lse,
+                              void* coef, int M, int pad_id, float gscale, cudaStream_t st) {
+  if (M <= 0) return 0;
+  ce_row_coef_kernel<<<(M + 255) / 256, 256, 0, st>>>(static_cast<const float*>(rmax), static_cast<const float*>(rsum),
+                                                      static_cast<const int*>(targets),
+                                                      static_cast<const float*>(loss_cnt), static_cast<float*>(lse),
+                                                      static_cast<float*>(coef), M, pad_id, gscale);
   return static_cast<int>(cudaGetLastError());
 }

@@ -13,7 +13,8 @@ import math
 import torch
 
 from . import native
-from .gemm import gemm, gemm_rope, gemm_rope_fusable, wgrad_gemm, wgrad_join  # noqa: F401  (re-exported)
+from .gemm import (gemm, gemm_ce_dlogits, gemm_ce_fusable, gemm_ce_stats, gemm_rope, gemm_rope_fusable,  # noqa: F401
+                   gemm_swiglu, gemm_swiglu_fusable, wgrad_gemm, wgrad_join)
 
 _f = ctypes.c_float
 
@@ -597,6 +598,35 @@ def ce_dlogits(logits, targets, rmax, rsum, loss_cnt, col0: int, pad_id: int, gs
                                         pad_id, _f(gscale), native.stream_ptr()), "ce_dlogits")
     native.bump()
     return out
+
+
+def ce_merge(pmax: torch.Tensor, psum: torch.Tensor):
+    """Merge per-tile row statistics [nt, M] (see ``gemm_ce_stats``) into (rmax [M], rsum [M])."""
+    nt, M = pmax.shape
+    if not pmax.is_cuda:
+        mx = pmax.max(0).values
+        return mx, (psum * torch.exp(pmax - mx[None, :])).sum(0)
+    rmax = torch.empty(M, dtype=torch.float32, device=pmax.device)
+    rsum = torch.empty_like(rmax)
+    native.check(_lib().b200_ce_merge(native.ptr(pmax), native.ptr(psum), native.ptr(rmax), native.ptr(rsum), M, nt,
+                                      native.stream_ptr()), "ce_merge")
+    native.bump()
+    return rmax, rsum
+
+
+def ce_row_coef(rmax, rsum, targets, loss_cnt, pad_id: int, gscale: float):
+    """(lse [M], coef [M]) for the logit-gradient epilogue: lse = rmax + log(rsum), coef = valid * gscale / n_valid."""
+    M = rmax.numel()
+    if not rmax.is_cuda:
+        valid = ((targets != pad_id) & (targets >= 0)).float()
+        return rmax + torch.log(rsum), valid * gscale / loss_cnt[1].clamp_min(1.0)
+    lse = torch.empty(M, dtype=torch.float32, device=rmax.device)
+    coef = torch.empty_like(lse)
+    native.check(_lib().b200_ce_row_coef(native.ptr(rmax), native.ptr(rsum), native.ptr(targets), native.ptr(loss_cnt),
+                                         native.ptr(lse), native.ptr(coef), M, pad_id, _f(gscale), native.stream_ptr()),
+                 "ce_row_coef")
+    native.bump()
+    return lse, coef
 
 
 # --------------------------------------------------------------------------- optimizer side

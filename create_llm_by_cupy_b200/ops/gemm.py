@@ -184,6 +184,86 @@ def gemm_rope(a: torch.Tensor, b: torch.Tensor, cos: torch.Tensor, sin: torch.Te
     return out
 
 
+def _tma_ok(*ts) -> bool:
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+               and t.data_ptr() % 16 == 0 for t in ts)
+
+
+def _whole_tiles_flag(device) -> int:
+    return GEMM_WHOLE_TILES if _wgrad_pending.get(device.index, False) else 0
+
+
+def gemm_swiglu_fusable(x: torch.Tensor, w_gate_val: torch.Tensor) -> bool:
+    """True when ``gemm_swiglu(x, w_gate_val)`` runs as one kernel (``x`` [M, K], ``w_gate_val`` [K, 2 I], bf16)."""
+    if not (x.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(x, w_gate_val)):
+        return False
+    I = w_gate_val.shape[1] // 2
+    return x.shape[0] >= 256 and I >= 128 and w_gate_val.shape[1] == 2 * I and I % 8 == 0
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate_val: torch.Tensor, keep_gv: bool = True):
+    """``gv = x @ [W_gate | W_value]`` and ``act = silu(gate) * value`` from ONE GEMM whose epilogue applies the
+    activation to the fp32 accumulator (a tile holds 128 gate columns beside the matching 128 value columns).
+    Returns ``(gv [M, 2 I] or None, act [M, I])``; ``gv`` is only written when ``keep_gv`` (the backward reads it).
+    Only where ``gemm_swiglu_fusable`` holds."""
+    M, K = x.shape
+    I = w_gate_val.shape[1] // 2
+    assert gemm_swiglu_fusable(x, w_gate_val)
+    act = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+    gv = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=x.device) if keep_gv else None
+    native.status_tensor()
+    _apply_dynamic()
+    rc = native.lib().b200_gemm_bf16_2cta_swiglu(
+        native.ptr(x), native.ptr(w_gate_val), native.ptr(gv), native.ptr(act), M, I, K, x.stride(0),
+        w_gate_val.stride(0), 2 * I, I, _whole_tiles_flag(x.device), native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_swiglu")
+    native.bump()
+    return gv, act
+
+
+def gemm_ce_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """True when the LM-head GEMMs with the loss epilogues run for ``x`` [M, K] and ``w`` [V, K] (bf16)."""
+    return bool(x.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(x, w) and x.shape[0] >= 256 and w.shape[0] >= 256)
+
+
+def gemm_ce_stats(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, tlogit: torch.Tensor, col0: int = 0):
+    """Logits ``x @ w^T`` that are never stored: returns per-tile row statistics ``(pmax, psum)``, each
+    ``[ceil(V / 256), M]`` fp32 (maximum and sum of exp(logit - maximum) over the tile's columns), and writes the
+    target's logit of every row whose target lies in ``[col0, col0 + V)`` into ``tlogit`` [M] fp32."""
+    M, K = x.shape
+    V = w.shape[0]
+    assert gemm_ce_fusable(x, w) and targets.dtype == torch.int32 and targets.numel() == M
+    nt = (V + 255) // 256
+    pmax = torch.empty((nt, M), dtype=torch.float32, device=x.device)
+    psum = torch.empty((nt, M), dtype=torch.float32, device=x.device)
+    native.status_tensor()
+    _apply_dynamic()
+    rc = native.lib().b200_gemm_bf16_2cta_ce_stats(
+        native.ptr(x), native.ptr(w), M, V, K, x.stride(0), w.stride(0), native.ptr(targets), native.ptr(pmax),
+        native.ptr(psum), native.ptr(tlogit), col0, 0, native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_ce_stats")
+    native.bump()
+    return pmax, psum
+
+
+def gemm_ce_dlogits(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, coef: torch.Tensor,
+                    col0: int = 0) -> torch.Tensor:
+    """``(exp(x @ w^T - lse[row]) - onehot(target)) * coef[row]`` as bf16 [M, V_chunk]: the gradient of the loss
+    w.r.t. the logits of vocabulary rows ``col0 .. col0 + V_chunk``, formed in the GEMM epilogue."""
+    M, K = x.shape
+    C = w.shape[0]
+    assert gemm_ce_fusable(x, w) and C % 8 == 0
+    out = torch.empty((M, C), dtype=torch.bfloat16, device=x.device)
+    native.status_tensor()
+    _apply_dynamic()
+    rc = native.lib().b200_gemm_bf16_2cta_ce_dlogits(
+        native.ptr(x), native.ptr(w), native.ptr(out), M, C, K, x.stride(0), w.stride(0), C, native.ptr(targets),
+        native.ptr(lse), native.ptr(coef), col0, native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_ce_dlogits")
+    native.bump()
+    return out
+
+
 def gemm_allgather(a: torch.Tensor, unit_buf: torch.Tensor, b_offset: int, b_shape: tuple, *, trans_b: bool,
                    peer_slices, seg: torch.Tensor, epoch: int, n_copy: int = 8, add: torch.Tensor | None = None,
                    out: torch.Tensor | None = None, trans_a: bool = False, only_b: bool = False) -> torch.Tensor:

@@ -93,6 +93,34 @@ def test_config1_ten_steps_follow_the_oracle_and_greedy_decode():
     assert len(toks) == 32 and all(0 < v < 512 for v in toks)
 
 
+def test_fused_epilogues_agree_with_the_separate_kernels_at_model_level():
+    """The same model stepped with and without the epilogue fusions (SwiGLU, loss statistics / logit gradients,
+    rotary embedding, side-stream weight gradients): same losses and gradient norms up to bf16 rounding."""
+    from create_llm_by_cupy_b200.ops import functional as F
+
+    md = dict(vocab_size=2048, hidden_size=512, layer_num=2, time_size=256, q_head=4, kv_head=2, ffn_size=1376,
+              padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=4)
+    ids = synthetic_token_stream(8, 256, 2048, "train", 0, low=1)
+    bs = [tuple(v.cuda() for v in padding_proceccing(ids[i * 4:(i + 1) * 4], np.full(4, 256), 0)) for i in range(2)]
+    runs = []
+    for plain in (False, True):
+        F.set_unfused_baseline(plain)
+        try:
+            tr = Trainer(md, device="cuda", lr_max=1e-3, warm_up=1, total_steps=8, adam_overlap=False)
+            n0 = native.launch_count()
+            outs = [tr.train_step([bs[i % 2]]) for i in range(4)]
+            runs.append((outs, native.launch_count() - n0))
+        finally:
+            F.set_unfused_baseline(False)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    (fused, n_fused), (plain, n_plain) = runs
+    assert n_fused < n_plain                       # the fused run launches fewer kernels
+    for a, b in zip(fused, plain):
+        assert abs(a["loss"] - b["loss"]) < 2e-2, (a, b)
+        assert abs(a["grad_norm"] - b["grad_norm"]) < 3e-2 * b["grad_norm"], (a, b)
+
+
 def test_decode_with_kv_cache_matches_full_forward_logits():
     m = Cupa_ver4(dict(CFG1, dtype="bf16", half_float=True), device="cuda")
     prompt = [int(v) for v in synthetic_token_stream(1, 24, 512, "generation", 0, low=1)[0]]

@@ -113,6 +113,71 @@ def test_gemm_with_rotary_epilogue(M, N, K, T, D, rope_cols):
     assert torch.equal(out[:, rope_cols:], F.gemm(a, b)[:, rope_cols:])
 
 
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 688, 264), (1000, 1376, 136), (2048, 5504, 256), (512, 200, 72)])
+@pytest.mark.parametrize("keep_gv", [True, False])
+def test_gemm_with_swiglu_epilogue(M, I, K, keep_gv):
+    """gate|value projection with the activation in the GEMM epilogue (ragged I: the last tile's gate columns run
+    into the value half and must be clipped; I = 200 puts a whole 64-column group past the edge)."""
+    x = bf(M, K, seed=21)
+    w = bf(K, 2 * I, scale=0.3, seed=22)
+    assert F.gemm_swiglu_fusable(x.to(DEV), w.to(DEV))
+    gv_ref = x.float() @ w.float()
+    act_ref = torch.nn.functional.silu(gv_ref[:, :I]) * gv_ref[:, I:]
+    canary = torch.full((M + 2, 2 * I), 7.0, dtype=torch.bfloat16, device=DEV)
+    gv, act = F.gemm_swiglu(x.to(DEV), w.to(DEV), keep_gv=keep_gv)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    assert (gv is None) == (not keep_gv)
+    close(act, act_ref, rtol=1e-2, atol=1e-2)
+    if keep_gv:
+        close(gv, gv_ref, rtol=1e-2, atol=1e-2)
+        # the separate activation kernel on the stored projection agrees up to the bf16 rounding of gv
+        close(act, F.swiglu_fwd(gv), rtol=2e-2, atol=2e-2)
+    del canary
+
+
+@pytest.mark.parametrize("M,V,K", [(256, 256, 64), (300, 1000, 136), (1024, 4096, 256), (520, 2000, 72)])
+def test_lm_head_gemms_with_loss_epilogues(M, V, K):
+    """Forward: logits never stored, per-tile row statistics merged into the row's log-sum-exp and the target's
+    logit. Backward: (softmax - onehot) * coef formed on the recomputed accumulator, chunk by chunk."""
+    x = bf(M, K, seed=31)
+    w = bf(V, K, scale=0.5, seed=32)
+    g = torch.Generator().manual_seed(33)
+    t = torch.randint(0, V, (M,), generator=g, dtype=torch.int32)
+    t[::7] = 0                                        # pad id: no loss, no gradient
+    t[3] = V - 1
+    logits = x.float() @ w.float().t()
+    xd, wd, td = x.to(DEV), w.to(DEV), t.to(DEV)
+    assert F.gemm_ce_fusable(xd, wd)
+    tlogit = torch.zeros(M, device=DEV)
+    pmax, psum = F.gemm_ce_stats(xd, wd, td, tlogit)
+    rmax, rsum = F.ce_merge(pmax, psum)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    lse_ref = torch.logsumexp(logits, -1)
+    close(rmax + torch.log(rsum), lse_ref, rtol=1e-3, atol=2e-2)
+    close(tlogit, logits[torch.arange(M), t.long()], rtol=1e-3, atol=2e-2)
+    loss_cnt = F.ce_loss(rmax, rsum, tlogit, td, 0)
+    valid = t != 0
+    ref_loss = (lse_ref - logits[torch.arange(M), t.long()])[valid].sum()
+    assert abs(loss_cnt[0].item() - ref_loss.item()) <= 2e-3 * abs(ref_loss.item()) + 1e-2
+    assert loss_cnt[1].item() == float(valid.sum())
+    gscale = 3.0
+    lse, coef = F.ce_row_coef(rmax, rsum, td, loss_cnt, 0, gscale)
+    p = torch.softmax(logits, -1)
+    p[torch.arange(M), t.long()] -= 1.0
+    ref = p * (valid.float() * gscale / valid.sum())[:, None]
+    chunk = 512 if V > 512 else V
+    for s0 in range(0, V, chunk):
+        e0 = min(s0 + chunk, V)
+        if (e0 - s0) % 8 or e0 - s0 < 256:
+            continue
+        d = F.gemm_ce_dlogits(xd, wd[s0:e0], td, lse, coef, col0=s0)
+        torch.cuda.synchronize()
+        assert F.native.read_status() == (0, 0)
+        close(d, ref[:, s0:e0], rtol=2e-2, atol=1e-6, frob=2e-2)
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_accumulate_and_fp32(bn):
     a, b = bf(300, 264, seed=3), bf(264, 520, seed=4)
