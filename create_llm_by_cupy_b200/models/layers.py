@@ -297,8 +297,12 @@ class SwiGLU:
             gv, act = self._gate_act(x, True)
         go = grad_out if grad_out else (None, None)
         dW_out = F.wgrad_gemm(act, dout, out=go[1])
-        dact = _weight_gemm(self, dout, 1, trans_b=True)
-        dgv = F.swiglu_bwd(dact, gv)
+        if (F.SWIGLU_EPILOGUE and getattr(self, "pending_gather", None) is None
+                and F.gemm_swiglu_bwd_fusable(dout, self.params[1], gv)):
+            dgv = F.gemm_swiglu_bwd(dout, self.params[1], gv)      # d(act) never leaves tensor memory
+        else:
+            dact = _weight_gemm(self, dout, 1, trans_b=True)
+            dgv = F.swiglu_bwd(dact, gv)
         dW_gv = F.wgrad_gemm(x, dgv, out=go[0])
         dx = F.gemm(dgv, self.params[0], trans_b=True)
         self.grads = [dW_gv, dW_out]

@@ -61,7 +61,11 @@ enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4, G2_WHOLE_T
 //                  same index and leaves silu(gate) * value (and, on request, the raw projection)
 //   EPI_CE_STATS   LM head: nothing is stored but per-row (max, sum of exp, target logit) of the tile's columns
 //   EPI_CE_DLOGITS LM head again: (exp(logit - lse) - onehot) * coef leaves as bf16
-enum Gemm2Epi : int { EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_CE_STATS = 3, EPI_CE_DLOGITS = 4 };
+//   EPI_SWIGLU_BWD D = A B^T is d(activation); the epilogue fetches the stored gate / value tiles by TMA and
+//                  leaves d(gate), d(value) (the backward of silu(gate) * value), d(activation) is never stored
+enum Gemm2Epi : int {
+  EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_CE_STATS = 3, EPI_CE_DLOGITS = 4, EPI_SWIGLU_BWD = 5
+};
 
 struct Gemm2Params {
   void* D;
@@ -231,17 +235,24 @@ template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
-                     const __grid_constant__ CUtensorMap tmC, const Gemm2Params p) {
+                     const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmE,
+                     const Gemm2Params p) {
+  // The SwiGLU-backward epilogue works on two fetched tiles per group and prefetches the next pair: it trades
+  // one stage of the operand ring for two more staging tiles (5 x 32 KiB + 4 x 16 KiB instead of 6 + 2).
+  constexpr int kStages = EPI == EPI_SWIGLU_BWD ? G2_STAGES - 1 : G2_STAGES;
+  constexpr int kStg = EPI == EPI_SWIGLU_BWD ? 4 : 2;
+  constexpr int kStgOff = kStages * G2_STAGE_BYTES;
+  static_assert(kStgOff + kStg * G2_STG_BYTES == G2_BAR_OFF2 && 2 * kStages + kStg == 2 * G2_STAGES + 2, "smem layout");
   extern __shared__ uint8_t smem_raw2[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw2) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFF2);
-  uint64_t* empty = full + G2_STAGES;
-  uint64_t* tfull = empty + G2_STAGES;
+  uint64_t* empty = full + kStages;
+  uint64_t* tfull = empty + kStages;
   uint64_t* tempty = tfull + 2;
   uint64_t* sched_full = tempty + 2;
   uint64_t* sched_empty = sched_full + G2_SCHED;
-  uint64_t* stage_ready = sched_empty + G2_SCHED;      // [2]: epilogue staging tile holds C (or is simply free)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_ready + 2);
+  uint64_t* stage_ready = sched_empty + G2_SCHED;      // [kStg]: epilogue staging tile holds its input (or is simply free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stage_ready + kStg);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* tile_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
@@ -258,7 +269,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   const bool dyn = p.sched != nullptr;      // null: tile t + k * num_pairs goes to pair t (fixed assignment)
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < G2_STAGES; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -270,8 +281,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       mbar_init(&sched_full[i], 1);
       mbar_init(&sched_empty[i], 10);
     }
-    mbar_init(&stage_ready[0], 1);
-    mbar_init(&stage_ready[1], 1);
+    for (int i = 0; i < kStg; ++i) mbar_init(&stage_ready[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -334,7 +344,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           } else {
             tma_load_2d_pair(sB, wi.bn == G2_BN ? &tmB : &tmBh, bar, k0, n0);      // 128 or 64 rows of B
           }
-          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
           if (dyn && rank == 0 && kb == publish_kb && !publish(t_next)) { ok = false; break; }
         }
         if (!ok) break;
@@ -386,7 +396,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             umma_bf16_ss_pair(tmem_d, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           umma_commit_pair(&empty[stage]);
-          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit_pair(&tfull[acc]);
@@ -460,7 +470,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       // 256 rows x 128 activation columns per item: accumulator columns [0, 128) are the gate, [128, 256)
       // the value. Per 64-column group the thread's row leaves as up to three 128-byte staging rows (raw
       // gate, raw value, activation), each stored by TMA; two staging tiles alternate as in the plain path.
-      uint8_t* stg = smem + G2_STG_OFF;
+      uint8_t* stg = smem + kStgOff;
       const int r = q * 32 + lane;
       const uint32_t swz = uint32_t(r & 7);
       const bool elected = (warp == 2 && lane == 0);
@@ -534,6 +544,99 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (elected) tma_store_wait<0>();
+    } else if constexpr (EPI == EPI_SWIGLU_BWD) {
+      // The accumulator is d(act) for 256 rows x 256 columns. Per 64-column group the stored gate and value tiles
+      // (bf16, the two halves of the forward projection; maps tmBh / tmE) are fetched by TMA into a pair of staging
+      // tiles, turned in place into d(gate) and d(value) and stored (maps tmD / tmC). Two pairs alternate: the next
+      // group's pair is fetched while this one is computed.
+      uint8_t* stg = smem + kStgOff;
+      const int r = q * 32 + lane;
+      const uint32_t swz = uint32_t(r & 7);
+      const bool elected = (warp == 2 && lane == 0);
+      uint32_t ucount = 0;                               // groups handled so far; pair = ucount & 1
+      auto fetch = [&](uint32_t uc, int x, int y) {      // by the elected thread: fill pair uc & 1 for a group
+        const uint32_t b = (uc & 1) * 2;
+        if (x < p.sw_I) {
+          mbar_expect_tx(&stage_ready[b], G2_STG_BYTES);
+          tma_load_2d(stg + b * G2_STG_BYTES, &tmBh, &stage_ready[b], x, y);
+          mbar_expect_tx(&stage_ready[b + 1], G2_STG_BYTES);
+          tma_load_2d(stg + (b + 1) * G2_STG_BYTES, &tmE, &stage_ready[b + 1], x, y);
+        } else {                                         // wholly past the edge: nothing to fetch, nothing is stored
+          mbar_arrive(&stage_ready[b]);
+          mbar_arrive(&stage_ready[b + 1]);
+        }
+      };
+      for (int t = pair; ok && t >= 0 && t < num_tiles;
+           t = dyn ? rd.next(sched_full, sched_empty, tile_ring, abort_flag, true, lane == 0, rank != 0)
+                   : t + num_pairs) {
+        const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
+        const int row0 = wi.mb * 2 * G2_BM + int(rank) * G2_BM;
+        const int n0 = wi.n0;
+        const int ngroups = wi.bn / 64;
+        if (elected) {
+          tma_store_wait_read<1>();                      // the stores that last used this pair have read it
+          fetch(ucount, n0, row0);
+        }
+        if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
+#pragma unroll 1
+        for (int g = 0; g < ngroups; ++g) {
+          const uint32_t b = (ucount & 1) * 2;
+          if (elected && g + 1 < ngroups) {              // prefetch the next group's pair
+            tma_store_wait_read<0>();                    // the other pair's stores (previous group) have read it
+            fetch(ucount + 1, n0 + (g + 1) * 64, row0);
+          }
+          uint32_t v[64];
+          tmem_ld_32x32b_x32(taddr + g * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+          tmem_ld_32x32b_x32(taddr + g * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+          tmem_ld_wait();
+          if (g == ngroups - 1) {                        // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+          }
+          const uint32_t ph = (ucount >> 1) & 1;
+          if (!mbar_wait(&stage_ready[b], ph, abort_flag) || !mbar_wait(&stage_ready[b + 1], ph, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* grow = stg + b * G2_STG_BYTES + r * 128;
+          uint8_t* vrow = grow + G2_STG_BYTES;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint4* gp = reinterpret_cast<uint4*>(grow + ((uint32_t(c) ^ swz) << 4));
+            uint4* vp = reinterpret_cast<uint4*>(vrow + ((uint32_t(c) ^ swz) << 4));
+            uint4 gq = *gp, vq = *vp;
+            bf162* g2 = reinterpret_cast<bf162*>(&gq);
+            bf162* v2 = reinterpret_cast<bf162*>(&vq);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 gf = __bfloat1622float2(g2[e]), vf = __bfloat1622float2(v2[e]);
+              const float d0 = __uint_as_float(v[8 * c + 2 * e]), d1 = __uint_as_float(v[8 * c + 2 * e + 1]);
+              const float s0 = 1.f / (1.f + __expf(-gf.x)), s1 = 1.f / (1.f + __expf(-gf.y));
+              g2[e] = __floats2bfloat162_rn(d0 * vf.x * s0 * (1.f + gf.x * (1.f - s0)),
+                                            d1 * vf.y * s1 * (1.f + gf.y * (1.f - s1)));
+              v2[e] = __floats2bfloat162_rn(d0 * gf.x * s0, d1 * gf.y * s1);
+            }
+            *gp = gq;
+            *vp = vq;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync_128(1);
+          if (elected) {
+            const int x = n0 + g * 64;
+            if (x < p.sw_I) {
+              tma_store_2d(&tmD, stg + b * G2_STG_BYTES, x, row0);
+              tma_store_2d(&tmC, stg + (b + 1) * G2_STG_BYTES, x, row0);
+            }
+            tma_store_commit();
+          }
+          ++ucount;
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (elected) tma_store_wait<0>();
     } else
     if (p.flags & G2_TMA_OUT) {
       // Output through shared memory and TMA. A tile leaves in groups of 128 bytes per row (64 bf16
@@ -543,7 +646,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       // the same staging tile is first filled with the C tile by a TMA load. Two staging tiles
       // alternate, so the store of one group overlaps the conversion of the next.
       const int gcols = out_f32 ? 32 : 64;
-      uint8_t* stg = smem + G2_STG_OFF;
+      uint8_t* stg = smem + kStgOff;
       const int r = q * 32 + lane;
       const uint32_t swz = uint32_t(r & 7);
       const bool elected = (warp == 2 && lane == 0);
@@ -802,7 +905,7 @@ static int* next_sched_slot() {
 
 template <bool A_MN, bool B_MN, int EPI = EPI_PLAIN>
 static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtensorMap* tBh, const CUtensorMap* tD,
-                      const CUtensorMap* tC, const Gemm2Params& p, cudaStream_t stream) {
+                      const CUtensorMap* tC, const Gemm2Params& p, cudaStream_t stream, const CUtensorMap* tE = nullptr) {
   auto kern = gemm_bf16_tc2_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -829,7 +932,7 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
     q.sched = next_sched_slot();
     if (q.sched == nullptr) return static_cast<int>(cudaErrorInvalidValue);
   }
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tBh, *tD, *tC, q);
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(*tA, *tB, *tBh, *tD, *tC, tE ? *tE : *tA, q);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1005,4 +1108,30 @@ B200_API int b200_gemm_bf16_2cta_ce_dlogits(const void* A, const void* B, void* 
   const CUtensorMap* tD = get_tensor_map_2d(D, M, N, ldd, 128, 64, 2, SWIZZLE_128B_);
   if (!tA || !tB || !tD) return static_cast<int>(cudaErrorInvalidValue);
   return launch_tc2<false, false, EPI_CE_DLOGITS>(tA, tB, tB, tD, tD, p, stream);
+}
+
+// Backward of the fused SwiGLU: d(act) = DOUT W_out^T (DOUT [M, K] row-major, W_out [I, K] K-major) is formed in
+// tensor memory and never stored; the epilogue reads the forward's projection GV = [gate | value] ([M, 2 I]) tile by
+// tile through TMA and writes DGV = [d gate | d value] with
+//   d gate = d act * value * s * (1 + gate (1 - s)),  d value = d act * gate * s,  s = sigmoid(gate).
+// I a multiple of 8; every base 16-byte aligned, every pitch a multiple of 8 elements. GV and DGV may not alias.
+B200_API int b200_gemm_bf16_2cta_swiglu_bwd(const void* DOUT, const void* WOUT, const void* GV, void* DGV, int M, int I,
+                                            int K, int lda, int ldb, int ldgv, int lddgv, int flags,
+                                            cudaStream_t stream) {
+  if (M <= 0 || I <= 0) return 0;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(DOUT) | reinterpret_cast<uintptr_t>(WOUT) |
+                        reinterpret_cast<uintptr_t>(GV) | reinterpret_cast<uintptr_t>(DGV);
+  if (K <= 0 || (I % 8) != 0 || GV == nullptr || DGV == nullptr || GV == DGV || (all & 15) != 0 || (lda % 8) != 0 ||
+      (ldb % 8) != 0 || (ldgv % 8) != 0 || (lddgv % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p = base_params(DGV, nullptr, M, I, K, lddgv, 0, G2_WHOLE_TILES | G2_TMA_OUT, 1.0f);
+  p.sw_I = I;
+  const CUtensorMap* tA = get_tensor_map_2d(DOUT, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = get_tensor_map_2d(WOUT, I, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tG = get_tensor_map_2d(GV, M, I, ldgv, 128, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tV = get_tensor_map_2d(static_cast<const bf16*>(GV) + I, M, I, ldgv, 128, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tDG = get_tensor_map_2d(DGV, M, I, lddgv, 128, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tDV = get_tensor_map_2d(static_cast<bf16*>(DGV) + I, M, I, lddgv, 128, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB || !tG || !tV || !tDG || !tDV) return static_cast<int>(cudaErrorInvalidValue);
+  return launch_tc2<false, false, EPI_SWIGLU_BWD>(tA, tB, tG, tDG, tDV, p, stream, tV);
 }

@@ -14,7 +14,8 @@ import torch
 
 from . import native
 from .gemm import (gemm, gemm_ce_dlogits, gemm_ce_fusable, gemm_ce_stats, gemm_rope, gemm_rope_fusable,  # noqa: F401
-                   gemm_swiglu, gemm_swiglu_fusable, wgrad_gemm, wgrad_join)
+                   gemm_swiglu, gemm_swiglu_bwd, gemm_swiglu_bwd_fusable, gemm_swiglu_fusable, wgrad_gemm,
+                   wgrad_join)
 
 _f = ctypes.c_float
 

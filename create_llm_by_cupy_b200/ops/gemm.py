@@ -221,6 +221,32 @@ def gemm_swiglu(x: torch.Tensor, w_gate_val: torch.Tensor, keep_gv: bool = True)
     return gv, act
 
 
+def gemm_swiglu_bwd_fusable(dout: torch.Tensor, w_out: torch.Tensor, gv: torch.Tensor) -> bool:
+    """True when ``gemm_swiglu_bwd`` runs as one kernel (``dout`` [M, H], ``w_out`` [I, H], ``gv`` [M, 2 I], bf16)."""
+    if not (dout.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(dout, w_out, gv)):
+        return False
+    I = w_out.shape[0]
+    return dout.shape[0] >= 256 and I >= 256 and I % 8 == 0 and gv.shape == (dout.shape[0], 2 * I)
+
+
+def gemm_swiglu_bwd(dout: torch.Tensor, w_out: torch.Tensor, gv: torch.Tensor) -> torch.Tensor:
+    """``d[gate | value]`` [M, 2 I] from ``dout`` [M, H], the down projection ``w_out`` [I, H] and the forward's
+    projection ``gv``: the gradient of the activation, ``dout @ w_out^T``, exists only in tensor memory; the GEMM's
+    epilogue reads the gate / value tiles and writes the two gradients. Only where ``gemm_swiglu_bwd_fusable``."""
+    M, K = dout.shape
+    I = w_out.shape[0]
+    assert gemm_swiglu_bwd_fusable(dout, w_out, gv)
+    dgv = torch.empty_like(gv)
+    native.status_tensor()
+    _apply_dynamic()
+    rc = native.lib().b200_gemm_bf16_2cta_swiglu_bwd(
+        native.ptr(dout), native.ptr(w_out), native.ptr(gv), native.ptr(dgv), M, I, K, dout.stride(0), w_out.stride(0),
+        gv.stride(0), dgv.stride(0), 0, native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_swiglu_bwd")
+    native.bump()
+    return dgv
+
+
 def gemm_ce_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
     """True when the LM-head GEMMs with the loss epilogues run for ``x`` [M, K] and ``w`` [V, K] (bf16)."""
     return bool(x.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(x, w) and x.shape[0] >= 256 and w.shape[0] >= 256)

@@ -136,6 +136,27 @@ def test_gemm_with_swiglu_epilogue(M, I, K, keep_gv):
     del canary
 
 
+@pytest.mark.parametrize("M,I,K", [(256, 256, 64), (300, 688, 264), (1000, 1376, 136), (2048, 5504, 256), (512, 328, 72)])
+def test_gemm_with_swiglu_backward_epilogue(M, I, K):
+    """d(act) = dout W_out^T stays in tensor memory; the epilogue fetches gate / value tiles and writes their
+    gradients (ragged I: the last tile is half or mostly past the edge)."""
+    dout = bf(M, K, seed=41)
+    w_out = bf(I, K, scale=0.3, seed=42)
+    gv = bf(M, 2 * I, seed=43)
+    assert F.gemm_swiglu_bwd_fusable(dout.to(DEV), w_out.to(DEV), gv.to(DEV))
+    dact = dout.float() @ w_out.float().t()
+    g, v = gv[:, :I].float(), gv[:, I:].float()
+    sg = torch.sigmoid(g)
+    ref = torch.cat([dact * v * sg * (1 + g * (1 - sg)), dact * g * sg], 1)
+    out = F.gemm_swiglu_bwd(dout.to(DEV), w_out.to(DEV), gv.to(DEV))
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    close(out, ref, rtol=1e-2, atol=1e-2)
+    # and against the two-kernel path (which rounds d(act) to bf16 in between)
+    two = F.swiglu_bwd(F.gemm(dout.to(DEV), w_out.to(DEV), trans_b=True), gv.to(DEV))
+    close(out, two, rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("M,V,K", [(256, 256, 64), (300, 1000, 136), (1024, 4096, 256), (520, 2000, 72)])
 def test_lm_head_gemms_with_loss_epilogues(M, V, K):
     """Forward: logits never stored, per-tile row statistics merged into the row's log-sum-exp and the target's
