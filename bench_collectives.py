@@ -14,7 +14,8 @@ calls so that nothing is served from L2):
                   statistics kernel;
   rs_adam         the same kernel in its AdamW mode (reduced gradient never stored) against
                   ncclReduceScatter + statistics + AdamW kernels;
-  all_gather      pull kernel against ncclAllGather;
+  all_gather      copy engines (one cudaMemcpyAsync per peer slice, no SM) and the pull kernel against
+                  ncclAllGather;
   ag_gemm         K|Q|V projection of 8192 tokens with the gather done inside the GEMM - the whole unit,
                   or (the form the training step uses) only the chunks that hold K|Q|V while the
                   stand-alone kernel pulls the rest of the unit on another stream - against
@@ -133,6 +134,10 @@ def main():
         F.grad_stats(dst_ref, stats_ref)
         F.adamw_step(dst_ref, m, v, master, shard, step=1, grad_scale=1.0 / world, **hp)
 
+    def gather(copy_engine: bool):
+        fc.copy_engine = copy_engine
+        fc.all_gather(full, shard)
+
     adam = dict(m=m, v=v, master=master, param=shard, m_corr=1.0 / (1 - 0.9), v_corr=1.0 / (1 - 0.95),
                 grad_scale=1.0 / world, **hp)
     res = {}
@@ -141,7 +146,8 @@ def main():
     cases = [
         ("reduce_scatter", lambda: fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=True), nccl_rs),
         ("rs_adam", lambda: fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=True, adam=adam), nccl_rs_adam),
-        ("all_gather", lambda: fc.all_gather(full, shard), lambda: torch.distributed.all_gather_into_tensor(full_ref, shard)),
+        ("all_gather_copy_engine", lambda: gather(True), lambda: torch.distributed.all_gather_into_tensor(full_ref, shard)),
+        ("all_gather", lambda: gather(False), lambda: torch.distributed.all_gather_into_tensor(full_ref, shard)),
     ]
     for name, fused_fn, nccl_fn in cases:
         t_f = torch.tensor([median_ms(fused_fn, flush, sync)], device=dev)
@@ -158,11 +164,14 @@ def main():
     sync()
     fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=False)
     torch.distributed.reduce_scatter_tensor(dst_ref, bucket)
-    fc.all_gather(full, shard)
     torch.distributed.all_gather_into_tensor(full_ref, shard)
-    sync()
+    res["ag_equal_nccl"] = True
+    for ce in (True, False):
+        full.zero_()
+        gather(ce)
+        sync()
+        res["ag_equal_nccl"] = bool(res["ag_equal_nccl"] and torch.equal(full, full_ref))
     res["rs_max_abs_diff_vs_nccl"] = (dst.float() - dst_ref.float()).abs().max().item()
-    res["ag_equal_nccl"] = bool(torch.equal(full, full_ref))
 
     # all-gather fused into the K|Q|V projection
     x = torch.randn(M, H, device=dev, dtype=torch.bfloat16)

@@ -106,9 +106,12 @@ class GroupedQueryAttention:
         self.cache_kqv = True            # keep the projection (else re-project from x in backward)
         self.cache_attn = False          # dense path only: keep the [B,QH,T,T] probabilities
         self.flash_backend = "b200"      # "none" selects the dense verification path
-        # Residual-branch dropout (only built when dropout_rate != 0; the reference drops inside
-        # the attention probabilities, which would force the dense path, model/fast_layers.py:93-95)
+        # Two dropouts as in the reference (model/fast_layers.py:93-95, 316, 346), only built when
+        # dropout_rate != 0: on the attention probabilities - which forces the dense attention path while
+        # training, there is no dropout inside the flash kernels - and on the projected output.
+        self.drop_attn = TimeDropout(dropout_rate, dtype, generator) if dropout_rate else None
         self.drop = TimeDropout(dropout_rate, dtype, generator) if dropout_rate else None
+        self._dense = False              # the pass in flight runs the dense attention path
 
     # -- helpers ---------------------------------------------------------------------------
     def _split(self, kqv: torch.Tensor, B: int, T: int):
@@ -126,7 +129,7 @@ class GroupedQueryAttention:
         take Q and K already rotated: the rotary embedding is then applied in place to the [K|Q] columns of
         the packed projection (one pass over 5/6 of it) and undone on d[K|Q] in the epilogues of the
         backward kernels (head_dim 128) or by a pass after them."""
-        return x.is_cuda and self.flash_backend != "none" and F.flash_tc_forward_dim(self.D)
+        return x.is_cuda and not self._dense and F.flash_tc_forward_dim(self.D)
 
     def _project(self, x, T, tabs, first: bool):
         """K | Q | V projection; on the pre-rotating path K and Q leave it rotated - inside the GEMM's epilogue
@@ -141,12 +144,15 @@ class GroupedQueryAttention:
             F.rope_inplace(kqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0)
         return kqv
 
-    def _attend(self, q, k, v, valid_len, tabs):
+    def _attend(self, q, k, v, valid_len, tabs, train_flg: bool = False):
+        if self._dense:
+            o, lse, p, _, _ = F._attn_reference(q, k, v, valid_len, self.scale, tabs[0], tabs[1])
+            if self.drop_attn is not None and train_flg:
+                vx = v.float().repeat_interleave(self.QH // self.KVH, dim=2)
+                o = torch.einsum("bhts,bshd->bthd", self.drop_attn.forward(p, True), vx)
+            return o.to(q.dtype).contiguous(), lse
         if self._prerotate(q):
             return F.flash_attn_fwd(q, k, v, valid_len=valid_len, scale=self.scale, rope=None)
-        if self.flash_backend == "none":
-            o, lse, _, _, _ = F._attn_reference(q, k, v, valid_len, self.scale, tabs[0], tabs[1])
-            return o.to(q.dtype).contiguous(), lse
         return F.flash_attn_fwd(q, k, v, valid_len=valid_len, scale=self.scale, rope=tabs)
 
     # -- training path ---------------------------------------------------------------------
@@ -154,9 +160,10 @@ class GroupedQueryAttention:
                 train_flg: bool = True) -> torch.Tensor:
         """x: normed input [M, H]. Returns W_O(attn) (+ residual) as [M, H]."""
         tabs = self._rope(T, x.device)
+        self._dense = self.flash_backend == "none" or (self.drop_attn is not None and train_flg)
         kqv = self._project(x, T, tabs, True)
         q, k, v = self._split(kqv, B, T)
-        o, lse = self._attend(q, k, v, valid_len, tabs)
+        o, lse = self._attend(q, k, v, valid_len, tabs, train_flg)
         if self.drop is not None and train_flg:
             out = self.drop.forward(F.gemm(o.view(B * T, self.H), self.params[1]), True)
             out = F.add(out, residual) if residual is not None else out
@@ -178,19 +185,20 @@ class GroupedQueryAttention:
             kqv = self._project(x, T, tabs, False)
         q, k, v = self._split(kqv, B, T)
         if o is None:
+            if self._dense and self.drop_attn is not None:
+                raise RuntimeError("gqa_cache_out_value=False cannot be combined with attention dropout: the "
+                                   "recomputed forward would draw a new mask")
             o, lse = self._attend(q, k, v, valid_len, tabs)
         go = grad_out if grad_out else (None, None)
         dW_O = F.wgrad_gemm(o.view(B * T, self.H), dout, out=go[1])
         do = F.gemm(dout, self.params[1], trans_b=True)
         dkqv = torch.empty_like(kqv)
         dq, dk, dv = self._split(dkqv, B, T)
-        if self.flash_backend == "none":
-            res = F.flash_attn_bwd(do.view(B, T, self.QH, self.D).float().cpu(), q.float().cpu(), k.float().cpu(),
-                                   v.float().cpu(), o.float().cpu(), lse.cpu(),
-                                   valid_len=None if valid_len is None else valid_len.cpu(), scale=self.scale,
-                                   rope=tuple(t.cpu() for t in tabs))
-            for dst, src in zip((dq, dk, dv), res):
-                dst.copy_(src.to(dst.device, dst.dtype))
+        if self._dense:
+            # dense path (verification, or training with attention dropout): the fp32 restatement, on the
+            # device the tensors live on
+            F._attn_bwd_reference(do.view(B, T, self.QH, self.D), q, k, v, o, valid_len, self.scale, tabs[0], tabs[1],
+                                  out=(dq, dk, dv), p_drop=self.drop_attn)
         elif self._prerotate(x):
             fused = F.flash_bwd_can_unrotate(q)          # inverse RoPE in the kernels' epilogues
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
@@ -366,7 +374,7 @@ class ChunkedCrossEntropy_Share:
         tlogit = torch.zeros(M, dtype=torch.float32, device=x.device)
         kept = None
         if self._fused(x, W):
-            pmax, psum = F.gemm_ce_stats(x, W, t, tlogit)
+            pmax, psum = F.gemm_ce_stats(x, W, t, tlogit, vocab=W.shape[0])
             rmax, rsum = F.ce_merge(pmax, psum)
         else:
             rmax = torch.empty(M, dtype=torch.float32, device=x.device)
@@ -410,27 +418,42 @@ class ChunkedCrossEntropy_Share:
 
 
 class TimeDropout:
-    """Inverted dropout with a kept mask (model/fast_layers.py:616-673). Only built when
-    ``dropout_rate != 0``; the benchmark configurations use 0."""
+    """Inverted dropout whose mask is kept as packed bits, one bit per element
+    (model/fast_layers.py:616-673). The keep pattern is a counter-based function of (seed, running element
+    offset), identical on CPU and GPU. The seed is derived from the model generator's initial seed and the
+    layer's construction index; it does not draw from the generator, so a model with dropout starts from
+    the same weights as one without. Only built when ``dropout_rate != 0``; the benchmark configurations use 0."""
+
+    _built = 0
 
     def __init__(self, dropout_rate: float, dtype=torch.bfloat16, generator=None):
         self.p = float(dropout_rate)
-        self.mask = None
-        self.generator = generator
+        self.mask = None            # uint8 [(n + 7) / 8]
+        self.mask_shape = None
+        base = generator.initial_seed() if generator is not None else 0
+        TimeDropout._built += 1
+        self.seed = (base * 0x9E3779B97F4A7C15 + TimeDropout._built * 0xD1B54A32D192ED03) & ((1 << 62) - 1)
+        self.offset = 0
 
     def forward(self, x: torch.Tensor, train_flg: bool = True) -> torch.Tensor:
         if not train_flg or self.p <= 0.0:
             self.mask = None
             return x
-        keep = torch.rand(x.shape, device=x.device, generator=self.generator) >= self.p
-        self.mask = keep
-        return x * keep.to(x.dtype) * (1.0 / (1.0 - self.p))
+        out, self.mask = F.dropout_fwd(x, self.p, self.seed, self.offset)
+        self.mask_shape = tuple(x.shape)
+        self.offset += (x.numel() + 7) // 8 * 8
+        return out
+
+    def reapply(self, x: torch.Tensor) -> torch.Tensor:
+        """x * keep / (1 - p) with the mask of the last forward (kept for ``backward``)."""
+        return x if self.mask is None else F.dropout_bwd(x, self.mask, self.p)
 
     def backward(self, dout: torch.Tensor) -> torch.Tensor:
         if self.mask is None:
             return dout
-        out = dout * self.mask.to(dout.dtype) * (1.0 / (1.0 - self.p))
+        out = F.dropout_bwd(dout, self.mask, self.p)
         self.mask = None
+        self.mask_shape = None
         return out
 
 

@@ -238,7 +238,11 @@ class Cupa_ver4:
         defs = []
         per = 6
         for b in range(self.layernum):
-            defs.append((f"block{b}", list(range(b * per, (b + 1) * per))))
+            # Inside a block's unit the two norm gains come first, then the attention weights, then the MLP
+            # weights: the MLP part (the first gradients a block's backward completes) is then one contiguous
+            # tail that can be reduced ahead of the rest, and the rest is one contiguous head.
+            i0 = b * per
+            defs.append((f"block{b}", [i0 + 4, i0 + 5, i0, i0 + 1, i0 + 2, i0 + 3]))
         i = self.layernum * per
         defs.append(("embedding", [i]))
         i += 1
@@ -379,6 +383,10 @@ class Cupa_ver4:
                 gqa, feed, norm1, norm2 = mods[s:s + self.one_cycle_num]
                 manager.begin_grad_bucket(tag=f"block_{gi}_{s}", modules=[gqa, feed, norm1, norm2])
                 dn2 = feed.backward(dx, grad_out=manager.grad_views(feed))
+                if hasattr(manager, "flush_grad_ranges_async"):
+                    # the MLP weight gradients are complete once the side stream has run them: their part of
+                    # the bucket is reduced while the attention half of the block is still in backward
+                    manager.flush_grad_ranges_async([feed], tag=f"block_{gi}_{s}_mlp")
                 dx = norm2.backward(dn2, add=dx, grad_out=manager.grad_views(norm2))
                 dn1 = gqa.backward(dx, grad_out=manager.grad_views(gqa))
                 dx = norm1.backward(dn1, add=dx, grad_out=manager.grad_views(norm1))

@@ -18,7 +18,6 @@ from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent / "csrc"
 OUT_DIR = Path(__file__).resolve().parent
-LIB_NAME = "libb200llm.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -34,6 +33,8 @@ FAST_MATH_PREFIXES = ("flash_", "gemm_")
 # arguments check them (and report through the status word instead of touching memory) - the stand-in for
 # a memory checker. Objects of the two builds are kept apart by the flag's part in the digest.
 BOUNDS_CHECK = os.environ.get("B200_BOUNDS_CHECK") == "1"
+LIB_NAME = "libb200llm_dbg.so" if BOUNDS_CHECK else "libb200llm.so"
+OBJ_DIR_NAME = "build_dbg" if BOUNDS_CHECK else "build"
 
 
 def flags_for(src: Path) -> list[str]:
@@ -81,7 +82,7 @@ def is_current() -> bool:
     """True when the library exists and every object's stamp matches its source as it is now."""
     if not lib_path().exists():
         return False
-    obj_dir = OUT_DIR / "build"
+    obj_dir = OUT_DIR / OBJ_DIR_NAME
     for src in sources():
         stamp = obj_dir / (src.stem + ".sha1")
         if not stamp.exists() or stamp.read_text() != _digest(src):
@@ -94,7 +95,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     build at the same time (one per GPU at start-up) take turns on a lock file; the second one then finds
     everything up to date."""
     nvcc = _nvcc()
-    obj_dir = OUT_DIR / "build"
+    obj_dir = OUT_DIR / OBJ_DIR_NAME
     obj_dir.mkdir(exist_ok=True)
     import fcntl
     with open(obj_dir / ".lock", "w") as lock:

@@ -59,4 +59,24 @@ const CUtensorMap* get_tensor_map_bthd(const void* base, uint64_t B, uint64_t T,
 
 int num_sms();
 
+#ifdef __CUDACC__
+// A length or index that a kernel reads from device memory (valid key lengths, target ids) and then uses to bound
+// its loops or to pick a column. Every build clamps it into [0, hi]; the debug build (-DB200_BOUNDS_CHECK=1, made by
+// ``B200_BOUNDS_CHECK=1 python -m create_llm_by_cupy_b200.ops.build``) also reports a value outside that range through
+// the status word (error 4, the kernel id, the offending value) - the stand-in for a memory checker on arguments
+// that only exist on the device.
+__device__ __forceinline__ int checked_index(int v, int hi, int* status, int kernel_id) {
+#ifdef B200_BOUNDS_CHECK
+  if ((v < 0 || v > hi) && status != nullptr && atomicCAS(status, 0, 4) == 0) {
+    status[1] = kernel_id;
+    status[2] = v;
+  }
+#else
+  (void)status;
+  (void)kernel_id;
+#endif
+  return v < 0 ? 0 : (v > hi ? hi : v);
+}
+#endif
+
 }  // namespace b200

@@ -796,6 +796,89 @@ B200_API int b200_add_bf16(const void* a, const void* b, void* out, long long n,
   return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------ dropout with a bit-packed mask
+// Inverted dropout (model/fast_layers.py:616-673 of the reference keeps the mask as packed bits too). The keep
+// decision of element i is a pure function of (seed, i): a 64-bit mix of the seed and i / 4 yields four 16-bit
+// lanes, element i keeps when its lane >= round(p * 65536). Eight consecutive elements share one mask byte,
+// first element in the most significant bit (the order of numpy.packbits). The forward writes the mask bytes,
+// the backward only reads them: nothing of the size of the activations is kept besides one bit per element.
+__device__ __forceinline__ unsigned long long drop_mix(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dropout_fwd_kernel(const T* __restrict__ x, T* __restrict__ out, uint8_t* __restrict__ mask, size_t n,
+                   unsigned long long seed, unsigned long long offset, unsigned int threshold, float scale) {
+  const size_t nbytes = (n + 7) / 8;
+  for (size_t b = size_t(blockIdx.x) * blockDim.x + threadIdx.x; b < nbytes; b += size_t(gridDim.x) * blockDim.x) {
+    const size_t i0 = b * 8;
+    const unsigned long long r0 = drop_mix(seed ^ ((offset + i0) >> 2) * 0xD1342543DE82EF95ull);
+    const unsigned long long r1 = drop_mix(seed ^ (((offset + i0) >> 2) + 1) * 0xD1342543DE82EF95ull);
+    unsigned int bits = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned int lane = unsigned((j < 4 ? r0 >> (16 * j) : r1 >> (16 * (j - 4))) & 0xffffull);
+      const bool keep = lane >= threshold;
+      if (i0 + j < n) {
+        bits |= (keep ? 1u : 0u) << (7 - j);
+        out[i0 + j] = keep ? T(float(x[i0 + j]) * scale) : T(0.f);
+      }
+    }
+    mask[b] = uint8_t(bits);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dropout_bwd_kernel(const T* __restrict__ dout, const uint8_t* __restrict__ mask, T* __restrict__ out, size_t n,
+                   float scale) {
+  const size_t nbytes = (n + 7) / 8;
+  for (size_t b = size_t(blockIdx.x) * blockDim.x + threadIdx.x; b < nbytes; b += size_t(gridDim.x) * blockDim.x) {
+    const unsigned int bits = mask[b];
+    const size_t i0 = b * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i0 + j < n) out[i0 + j] = ((bits >> (7 - j)) & 1u) ? T(float(dout[i0 + j]) * scale) : T(0.f);
+  }
+}
+
+// x, out: n elements of bf16 (is_f32 == 0) or fp32; mask: (n + 7) / 8 bytes; offset must be a multiple of 8 (the
+// caller advances it by the padded element count of every call, so no two calls share random lanes).
+B200_API int b200_dropout_fwd(const void* x, void* out, void* mask, long long n, int is_f32, unsigned long long seed,
+                              unsigned long long offset, float p, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!(p >= 0.f && p < 1.f) || (offset & 7ull) != 0) return static_cast<int>(cudaErrorInvalidValue);
+  const unsigned int thr = static_cast<unsigned int>(p * 65536.f + 0.5f);
+  const float scale = 1.f / (1.f - p);
+  const int grid = grid_for(size_t(n + 7) / 8, 256);
+  if (is_f32)
+    dropout_fwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x), static_cast<float*>(out),
+                                                    static_cast<uint8_t*>(mask), size_t(n), seed, offset, thr, scale);
+  else
+    dropout_fwd_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(x), static_cast<bf16*>(out),
+                                                   static_cast<uint8_t*>(mask), size_t(n), seed, offset, thr, scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+B200_API int b200_dropout_bwd(const void* dout, const void* mask, void* out, long long n, int is_f32, float p,
+                              cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!(p >= 0.f && p < 1.f)) return static_cast<int>(cudaErrorInvalidValue);
+  const float scale = 1.f / (1.f - p);
+  const int grid = grid_for(size_t(n + 7) / 8, 256);
+  if (is_f32)
+    dropout_bwd_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(dout), static_cast<const uint8_t*>(mask),
+                                                    static_cast<float*>(out), size_t(n), scale);
+  else
+    dropout_bwd_kernel<bf16><<<grid, 256, 0, st>>>(static_cast<const bf16*>(dout), static_cast<const uint8_t*>(mask),
+                                                   static_cast<bf16*>(out), size_t(n), scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ------------------------------------------------------------------ allocation-free RMSNorm backward
 // See b200_noalloc.h. The scratch for the dgamma partial sums lives in this translation unit; in
 // host code the array's name only stands for the symbol, so its device address is looked up once

@@ -69,7 +69,7 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
   const int kvh = h / (p.QH / p.KVH);
   const int m0 = mtile * 128;
   const int T = p.T;
-  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 303) : T;
   const int n_tiles = min(mtile + 1, (max(vlen, 1) + 127) / 128);
 
   if (threadIdx.x == 0) {

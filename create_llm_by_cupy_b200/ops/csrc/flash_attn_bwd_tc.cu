@@ -171,7 +171,7 @@ flash_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int kvh = h / (p.QH / p.KVH);
   const int m0 = mtile * 128;
   const int T = p.T;
-  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 302) : T;
   const int n_tiles = min(mtile + 1, (max(vlen, 1) + 127) / 128);
 
   if (threadIdx.x == 0) {
@@ -411,7 +411,7 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
   const int T = p.T;
   const int R = p.QH / p.KVH;
-  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 302) : T;
   const int tile_of_pass[2] = {pair, p.pairing ? p.n_tiles - 1 - pair : pair};
   const int n_pass = tile_of_pass[0] == tile_of_pass[1] ? 1 : 2;
 

@@ -1,4 +1,4 @@
-// Causal GQA flash-attention forward on tcgen05, third generation (head_dim 128 or 64).
+// Causal GQA flash-attention forward on tcgen05 (head_dim 128 or 64).
 //
 // One CTA owns TWO consecutive 128-row query tiles of one (batch, head) and walks the key tiles
 // once for both. Each query tile has its own softmax warpgroup, its own score buffer and its own
@@ -139,7 +139,7 @@ flash_fwd_tc3_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (p.QH / p.KVH);
   const int T = p.T;
-  const int vlen = p.valid_len ? min(p.valid_len[b], T) : T;
+  const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 301) : T;
   const int kv_tiles = (max(vlen, 1) + 127) / 128;
   int nt[2];
 #pragma unroll

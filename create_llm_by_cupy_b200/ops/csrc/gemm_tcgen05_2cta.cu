@@ -99,6 +99,7 @@ struct Gemm2Params {
   const float* ce_lse;       // [M] log-sum-exp of the whole row (EPI_CE_DLOGITS)
   const float* ce_coef;      // [M] valid * gradient scale / number of valid rows
   int ce_col0, ce_nt0;       // vocabulary id of column 0; tile-column index of this call's first tile in pmax / psum
+  int ce_vocab;              // size of the whole vocabulary when the caller knows it (debug build: targets are checked)
 };
 
 // A work item: tile coordinates, first column and width.
@@ -426,7 +427,15 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const G2Item wi = g2_item(t, p.t_full, num_m, num_n);
         const int row = wi.mb * 2 * G2_BM + int(rank) * G2_BM + r;
         const int ncols = min(wi.bn, p.N - wi.n0);                       // valid columns of this tile
-        const int tcol = row < p.M ? __ldg(p.ce_targets + row) - p.ce_col0 - wi.n0 : -1;
+        int tcol = -1;
+        if (row < p.M) {
+          int tgt = __ldg(p.ce_targets + row);
+#ifdef B200_BOUNDS_CHECK
+          // a target beyond the vocabulary would silently count as "no target logit": the debug build reports it
+          if (p.ce_vocab > 0 && tgt >= 0) tgt = checked_index(tgt, p.ce_vocab - 1, p.status, 304);
+#endif
+          tcol = tgt - p.ce_col0 - wi.n0;
+        }
         if (!mbar_wait(&tfull[acc], acc_phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + acc * G2_BN;
@@ -1070,7 +1079,7 @@ B200_API int b200_gemm_bf16_2cta_swiglu(const void* A, const void* B, void* GV, 
 // the row's target writes that logit to tlogit[row]. A merge over the tile columns gives the row's log-sum-exp.
 B200_API int b200_gemm_bf16_2cta_ce_stats(const void* A, const void* B, int M, int N, int K, int lda, int ldb,
                                           const void* targets, void* pmax, void* psum, void* tlogit, int col0, int nt0,
-                                          cudaStream_t stream) {
+                                          int vocab, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) != 0 || (lda % 8) != 0 ||
       (ldb % 8) != 0 || !targets || !pmax || !psum || !tlogit)
@@ -1082,6 +1091,7 @@ B200_API int b200_gemm_bf16_2cta_ce_stats(const void* A, const void* B, int M, i
   p.ce_tlogit = static_cast<float*>(tlogit);
   p.ce_col0 = col0;
   p.ce_nt0 = nt0;
+  p.ce_vocab = vocab;
   const CUtensorMap* tA = get_tensor_map_2d(A, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
   const CUtensorMap* tB = get_tensor_map_2d(B, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
   if (!tA || !tB) return static_cast<int>(cudaErrorInvalidValue);

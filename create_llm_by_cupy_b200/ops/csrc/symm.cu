@@ -92,6 +92,9 @@ struct RsParams {
   RsAdam adam[SYMM_MAX_W];
   unsigned long long bucket_off; // byte offset of the bucket inside every heap
   long long n_slice;             // elements per rank slice (multiple of 8)
+  // Part of the BUCKET to reduce, [range_lo, range_hi) in elements (multiples of 8): every rank handles the
+  // intersection with its own slice, possibly nothing. The whole bucket is [0, W * n_slice).
+  long long range_lo, range_hi;
   int rank0, W, mode, dst_fp32, do_stats;
   uint32_t epoch;
   unsigned long long wait_ns;
@@ -167,18 +170,18 @@ __device__ __forceinline__ void rs_consume(const RsParams& p, int vr, long long 
 // The pull-and-sum loop. Every thread keeps W x U = 8 16-byte peer loads in flight (an NVLink round
 // trip is a few microseconds, so bandwidth is bought with outstanding loads, not with threads).
 template <int WT, int U>
-__device__ __forceinline__ void rs_loop(const RsParams& p, int vr, const uint4* const (&src)[SYMM_MAX_W], float& ss,
-                                        int& bad) {
+__device__ __forceinline__ void rs_loop(const RsParams& p, int vr, const uint4* const (&src)[SYMM_MAX_W], long long v_lo,
+                                        long long v_hi, float& ss, int& bad) {
   constexpr int WM = WT > 0 ? WT : SYMM_MAX_W;
   const int W = WT > 0 ? WT : p.W;
-  const long long nvec = p.n_slice / 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+  // vectors [v_lo, v_hi) of this rank's slice (8 gradients each)
+  for (long long i0 = v_lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < v_hi; i0 += stride * U) {
     uint4 raw[U][WM];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i = i0 + u * stride;
-      if (i < nvec) {
+      if (i < v_hi) {
 #pragma unroll
         for (int q = 0; q < WM; ++q)
           if (q < W) raw[u][q] = src[q][i];
@@ -187,7 +190,7 @@ __device__ __forceinline__ void rs_loop(const RsParams& p, int vr, const uint4* 
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const long long i = i0 + u * stride;
-      if (i >= nvec) break;
+      if (i >= v_hi) break;
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int q = 0; q < WM; ++q) {
@@ -223,11 +226,15 @@ __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
   }
   float ss = 0.f;
   int bad = 0;
+  // this rank's share of the requested bucket range, as vectors of its slice
+  const long long s0 = (long long)rank * p.n_slice;
+  const long long lo = min(max(p.range_lo - s0, 0ll), p.n_slice), hi = min(max(p.range_hi - s0, 0ll), p.n_slice);
+  const long long v_lo = lo / 8, v_hi = hi / 8;
   switch (W) {
-    case 2: rs_loop<2, 4>(p, vr, src, ss, bad); break;
-    case 4: rs_loop<4, 2>(p, vr, src, ss, bad); break;
-    case 8: rs_loop<8, 1>(p, vr, src, ss, bad); break;
-    default: rs_loop<0, 1>(p, vr, src, ss, bad); break;
+    case 2: rs_loop<2, 4>(p, vr, src, v_lo, v_hi, ss, bad); break;
+    case 4: rs_loop<4, 2>(p, vr, src, v_lo, v_hi, ss, bad); break;
+    case 8: rs_loop<8, 1>(p, vr, src, v_lo, v_hi, ss, bad); break;
+    default: rs_loop<0, 1>(p, vr, src, v_lo, v_hi, ss, bad); break;
   }
   if (p.do_stats && p.stats[vr] != nullptr) {
 #pragma unroll
@@ -348,12 +355,13 @@ static int fill_tables(SymmTable* dst, const void* const* bases, int W, int vran
 
 // mode: 0 store, 1 accumulate (fp32 dst), 2 adam. adam_ptrs: vranks x 4 pointers (m, v, master, param);
 // adam_f: lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale.
-B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0, int vranks,
-                                      unsigned long long bucket_off, long long n_slice, void* const* dst, int dst_fp32,
-                                      int mode, void* const* stats, int do_stats, void* const* adam_ptrs,
-                                      const float* adam_f, unsigned int epoch, unsigned long long wait_ns, int blocks,
-                                      cudaStream_t st) {
-  if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0)
+static int symm_reduce_scatter_impl(const void* const* bases, int W, int rank0, int vranks,
+                                    unsigned long long bucket_off, long long n_slice, long long range_lo,
+                                    long long range_hi, void* const* dst, int dst_fp32, int mode, void* const* stats,
+                                    int do_stats, void* const* adam_ptrs, const float* adam_f, unsigned int epoch,
+                                    unsigned long long wait_ns, int blocks, cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0 || range_lo < 0 ||
+      range_hi > (long long)W * n_slice || range_lo > range_hi || ((range_lo | range_hi) % 8) != 0)
     return static_cast<int>(cudaErrorInvalidValue);
   if (n_slice == 0) return 0;
   RsParams p = {};
@@ -368,12 +376,37 @@ B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0
     }
   }
   p.bucket_off = bucket_off; p.n_slice = n_slice; p.rank0 = rank0; p.W = W; p.mode = mode; p.dst_fp32 = dst_fp32;
+  p.range_lo = range_lo; p.range_hi = range_hi;
   p.do_stats = do_stats; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
   if (blocks < 1) blocks = 1;
   if (blocks > SYMM_MAX_BLOCKS) blocks = SYMM_MAX_BLOCKS;
   B200_PREFER_MAX_SMEM(rs_reduce_kernel);
   rs_reduce_kernel<<<dim3(blocks, vranks), 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
+}
+
+// mode: 0 store, 1 accumulate (fp32 dst), 2 adam. adam_ptrs: vranks x 4 pointers (m, v, master, param);
+// adam_f: lr, beta1, beta2, eps, weight_decay, m_corr, v_corr, grad_scale.
+B200_API int b200_symm_reduce_scatter(const void* const* bases, int W, int rank0, int vranks,
+                                      unsigned long long bucket_off, long long n_slice, void* const* dst, int dst_fp32,
+                                      int mode, void* const* stats, int do_stats, void* const* adam_ptrs,
+                                      const float* adam_f, unsigned int epoch, unsigned long long wait_ns, int blocks,
+                                      cudaStream_t st) {
+  return symm_reduce_scatter_impl(bases, W, rank0, vranks, bucket_off, n_slice, 0, (long long)W * n_slice, dst,
+                                  dst_fp32, mode, stats, do_stats, adam_ptrs, adam_f, epoch, wait_ns, blocks, st);
+}
+
+// The same restricted to the elements [range_lo, range_hi) of the bucket (multiples of 8): a gradient bucket
+// is reduced in parts as soon as each part is complete (sub-buckets), every rank taking what falls into its slice.
+// dst still points at the START of the rank's reduced slice.
+B200_API int b200_symm_reduce_scatter_range(const void* const* bases, int W, int rank0, int vranks,
+                                            unsigned long long bucket_off, long long n_slice, long long range_lo,
+                                            long long range_hi, void* const* dst, int dst_fp32, int mode,
+                                            void* const* stats, int do_stats, void* const* adam_ptrs,
+                                            const float* adam_f, unsigned int epoch, unsigned long long wait_ns,
+                                            int blocks, cudaStream_t st) {
+  return symm_reduce_scatter_impl(bases, W, rank0, vranks, bucket_off, n_slice, range_lo, range_hi, dst, dst_fp32,
+                                  mode, stats, do_stats, adam_ptrs, adam_f, epoch, wait_ns, blocks, st);
 }
 
 static int symm_all_gather_impl(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,

@@ -14,43 +14,38 @@ import torch
 
 from . import native
 from .gemm import (gemm, gemm_ce_dlogits, gemm_ce_fusable, gemm_ce_stats, gemm_rope, gemm_rope_fusable,  # noqa: F401
-                   gemm_swiglu, gemm_swiglu_bwd, gemm_swiglu_bwd_fusable, gemm_swiglu_fusable, wgrad_gemm,
-                   wgrad_join)
+                   gemm_swiglu, gemm_swiglu_bwd, gemm_swiglu_bwd_fusable, gemm_swiglu_fusable, wgrad_event,
+                   wgrad_gemm, wgrad_join)
 
 _f = ctypes.c_float
 
-# head_dim-128 attention forward with un-fused RoPE runs on the tcgen05 kernel; B200_FLASH_TC=0
-# keeps everything on the mma.sync kernels (A/B comparison).
 import os as _os
-FLASH_TC = _os.environ.get("B200_FLASH_TC", "1") != "0"
-FLASH_TC_BWD = _os.environ.get("B200_FLASH_TC_BWD", "1") != "0"
-# 1: one softmax warpgroup; 2: two warpgroups split the columns of a tile; 3: two query tiles per CTA,
-# one warpgroup each, output accumulated in TMEM
-FLASH_FWD_GEN = int(_os.environ.get("B200_FLASH_FWD_GEN", "3"))
 
-
+# Code-path switches. They are plain module attributes (tests and the benchmark's baseline arm flip them);
+# the only one read from the environment is the memory cap below.
+# head_dim 128 / 64 attention with un-fused RoPE runs on the tcgen05 kernels; False keeps everything on the
+# mma.sync kernels (A/B comparison).
+FLASH_TC = True
+FLASH_TC_BWD = True
 # dQ from stored dS: the dK/dV kernel writes dS^T (B * QH * Tp^2 bf16, Tp = T rounded up to 128) into a
 # workspace that is kept per shape, and dQ becomes a GEMM over it. When the whole batch does not fit the
-# limit the backward runs in chunks of batch elements that do.
-FLASH_DQ_GEMM = _os.environ.get("B200_FLASH_DQ_GEMM", "1") != "0"
+# limit (``B200_FLASH_DS_WS_GIB``, default 4) the backward runs in chunks of batch elements that do.
+FLASH_DQ_GEMM = True
 FLASH_DQ_GEMM_MAX_BYTES = int(float(_os.environ.get("B200_FLASH_DS_WS_GIB", "4")) * (1 << 30))
-# head_dim 64 on the tcgen05 kernels: the third-generation forward and the dK/dV kernel + dQ GEMM are
-# templates on the head dimension.
-FLASH_TC_D64 = _os.environ.get("B200_FLASH_TC_D64", "1") != "0"
+# head_dim 64 on the tcgen05 kernels: the forward and the dK/dV kernel + dQ GEMM are templates on the head dimension.
+FLASH_TC_D64 = True
 
 
 def flash_tc_forward_dim(D: int) -> bool:
     """True when the forward for this head_dim runs on the tcgen05 kernels (which take rotated q, k)."""
-    return bool(FLASH_TC and (D == 128 or (D == 64 and FLASH_TC_D64 and FLASH_FWD_GEN == 3)))
+    return bool(FLASH_TC and (D == 128 or (D == 64 and FLASH_TC_D64)))
 
 
 # Inverse rotary embedding of dQ and dK inside the epilogues of the tcgen05 backward kernels (fp32
-# accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns.
-FLASH_ROPE_EPILOGUE = _os.environ.get("B200_FLASH_ROPE_EPILOGUE", "1") != "0"
-# The same for head_dim 64. (With the tables read row by row this form was slower than the separate pass
-# on the 125 M model, 12.1 vs 11.8 ms per step; with the transposed tables the two are level and the
-# epilogue form saves a launch per layer.)
-FLASH_ROPE_EPILOGUE_D64 = _os.environ.get("B200_FLASH_ROPE_EPILOGUE_D64", "1") != "0"
+# accumulator rows) instead of a separate in-place pass over the [dK | dQ] columns; the second switch is the
+# same for head_dim 64.
+FLASH_ROPE_EPILOGUE = True
+FLASH_ROPE_EPILOGUE_D64 = True
 _ds_ws_cache: dict = {}
 
 
@@ -98,8 +93,8 @@ def set_unfused_baseline(on: bool) -> None:
 
 # SwiGLU inside the epilogue of the gate|value projection, and the loss statistics / logit gradients inside
 # the epilogues of the LM-head GEMMs (see ``gemm.gemm_swiglu`` / ``gemm.gemm_ce_stats`` / ``gemm.gemm_ce_dlogits``).
-SWIGLU_EPILOGUE = _os.environ.get("B200_SWIGLU_EPILOGUE", "1") != "0"
-CE_EPILOGUE = _os.environ.get("B200_CE_EPILOGUE", "1") != "0"
+SWIGLU_EPILOGUE = True
+CE_EPILOGUE = True
 
 
 def _lib():
@@ -309,6 +304,78 @@ def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> to
     return out
 
 
+# --------------------------------------------------------------------------- dropout (bit-packed mask)
+def _s64(v: int) -> int:
+    v &= (1 << 64) - 1
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _lsr(z: torch.Tensor, k: int) -> torch.Tensor:
+    return (z >> k) & ((1 << (64 - k)) - 1)
+
+
+def _drop_keep_reference(n: int, seed: int, offset: int, p: float, device="cpu") -> torch.Tensor:
+    """keep[i] of the dropout kernels as a bool tensor: a 64-bit mix of (seed, (offset + i) / 4) gives four
+    16-bit lanes, element i keeps when its lane >= round(p * 65536)."""
+    i = torch.arange(n, dtype=torch.int64, device=device) + int(offset)
+    z = (i >> 2) * _s64(0xD1342543DE82EF95)
+    z = z ^ _s64(seed)
+    z = z + _s64(0x9E3779B97F4A7C15)
+    z = (z ^ _lsr(z, 30)) * _s64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _s64(0x94D049BB133111EB)
+    z = z ^ _lsr(z, 31)
+    lane = (z >> ((i & 3) * 16)) & 0xFFFF
+    return lane >= int(p * 65536.0 + 0.5)
+
+
+def _packbits(keep: torch.Tensor) -> torch.Tensor:
+    """bool [n] -> uint8 [(n + 7) / 8], first element in the most significant bit (numpy.packbits order)."""
+    n = keep.numel()
+    pad = (-n) % 8
+    k = torch.cat([keep.reshape(-1), keep.new_zeros(pad)]).reshape(-1, 8).to(torch.int32)
+    w = torch.tensor([128, 64, 32, 16, 8, 4, 2, 1], dtype=torch.int32, device=keep.device)
+    return (k * w).sum(1).to(torch.uint8)
+
+
+def _unpackbits(mask: torch.Tensor, n: int) -> torch.Tensor:
+    w = torch.tensor([128, 64, 32, 16, 8, 4, 2, 1], dtype=torch.int32, device=mask.device)
+    return ((mask.to(torch.int32)[:, None] & w) != 0).reshape(-1)[:n]
+
+
+def dropout_fwd(x: torch.Tensor, p: float, seed: int, offset: int):
+    """Inverted dropout: returns (x * keep / (1 - p), mask) where ``mask`` holds one BIT per element (uint8
+    [(n + 7) / 8]). The keep pattern is a pure function of (seed, offset + element index); ``offset`` must be a
+    multiple of 8 and callers advance it by the padded element count of every call."""
+    n = x.numel()
+    if not x.is_cuda:
+        keep = _drop_keep_reference(n, seed, offset, p, x.device).view(x.shape)
+        return (x * keep.to(x.dtype) * (1.0 / (1.0 - p))).to(x.dtype), _packbits(keep)
+    assert x.dtype in (torch.bfloat16, torch.float32)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    mask = torch.empty((n + 7) // 8, dtype=torch.uint8, device=x.device)
+    native.check(_lib().b200_dropout_fwd(native.ptr(x), native.ptr(out), native.ptr(mask), ctypes.c_longlong(n),
+                                         int(x.dtype == torch.float32), ctypes.c_ulonglong(seed & ((1 << 64) - 1)),
+                                         ctypes.c_ulonglong(offset), _f(p), native.stream_ptr()), "dropout_fwd")
+    native.bump()
+    return out, mask
+
+
+def dropout_bwd(dout: torch.Tensor, mask: torch.Tensor, p: float) -> torch.Tensor:
+    """dout * keep / (1 - p) with ``keep`` read from the packed mask of ``dropout_fwd``."""
+    n = dout.numel()
+    if not dout.is_cuda:
+        keep = _unpackbits(mask, n).view(dout.shape)
+        return (dout * keep.to(dout.dtype) * (1.0 / (1.0 - p))).to(dout.dtype)
+    assert dout.dtype in (torch.bfloat16, torch.float32) and mask.dtype == torch.uint8
+    dout = dout.contiguous()
+    out = torch.empty_like(dout)
+    native.check(_lib().b200_dropout_bwd(native.ptr(dout), native.ptr(mask), native.ptr(out), ctypes.c_longlong(n),
+                                         int(dout.dtype == torch.float32), _f(p), native.stream_ptr()), "dropout_bwd")
+    native.bump()
+    return out
+
+
 # --------------------------------------------------------------------------- flash attention
 def _strides3(t: torch.Tensor) -> list[int]:
     """(batch, token, head) element strides of a [B, T, heads, D] view."""
@@ -343,6 +410,51 @@ def _attn_reference(q, k, v, valid_len, scale, cos, sin):
     return o, lse, p, qf, kf
 
 
+def _attn_bwd_reference(dout, q, k, v, o, valid_len, scale, cos, sin, unrotate=None, out=None, p_drop=None):
+    """Dense fp32 restatement of the attention backward on [B, T, heads, D] views, on whatever device the
+    tensors live (the CPU body of ``flash_attn_bwd`` and the dense verification path of the attention layer).
+    ``cos`` / ``sin``: q and k are un-rotated and rotated here; ``unrotate``: they are rotated already and the
+    gradients are rotated back. ``p_drop``: a dropout layer whose last forward masked the attention
+    probabilities (its packed mask is consumed here)."""
+    B, T, QH, D = q.shape
+    KVH = k.shape[2]
+    R = QH // KVH
+    _, _, p, qf, kf = _attn_reference(q, k, v, valid_len, scale, cos, sin)
+    dof = dout.float()
+    vx = v.float().repeat_interleave(R, dim=2)
+    kx = kf.repeat_interleave(R, dim=2)
+    if p_drop is not None and p_drop.mask is not None:
+        # o = (p * keep / (1 - p_drop)) v: dV sees the dropped probabilities, dP comes back through the mask,
+        # and the softmax Jacobian needs sum_s p dP itself (o was not formed from p)
+        dvx = torch.einsum("bhts,bthd->bshd", p_drop.reapply(p), dof)
+        dp = p_drop.backward(torch.einsum("bthd,bshd->bhts", dof, vx))
+        delta = (p * dp).sum(-1)                                    # [B, QH, T]
+    else:
+        dvx = torch.einsum("bhts,bthd->bshd", p, dof)
+        dp = torch.einsum("bthd,bshd->bhts", dof, vx)
+        delta = (dof * o.float()).sum(-1).permute(0, 2, 1)          # [B, QH, T]
+    ds = p * (dp - delta[..., None]) * scale
+    dqf = torch.einsum("bhts,bshd->bthd", ds, kx)
+    dkx = torch.einsum("bhts,bthd->bshd", ds, qf)
+    dk_ = dkx.reshape(B, T, KVH, R, D).sum(3)
+    dv_ = dvx.reshape(B, T, KVH, R, D).sum(3)
+    for tabs in ((cos, sin), unrotate):
+        if tabs is not None and tabs[0] is not None:
+            c = tabs[0][:T][None, :, None, :].float()
+            sn = tabs[1][:T][None, :, None, :].float()
+
+            def unrot(x):
+                y1, y2 = x[..., :D // 2], x[..., D // 2:]
+                return torch.cat([y1 * c + y2 * sn, y2 * c - y1 * sn], -1)
+            dqf, dk_ = unrot(dqf), unrot(dk_)
+    res = (dqf.to(q.dtype), dk_.to(q.dtype), dv_.to(q.dtype))
+    if out is not None:
+        for dst, src in zip(out, res):
+            dst.copy_(src)
+        return out
+    return res
+
+
 def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     """Causal GQA attention. q [B,T,QH,D], k/v [B,T,KVH,D] (any strides with unit last stride).
 
@@ -364,10 +476,9 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     if cos is None and flash_tc_forward_dim(D):
         # tcgen05 / TMEM kernel (inputs already rotated)
         arr = (ctypes.c_longlong * 12)(*strides)
-        fwd_fn = {3: _lib().b200_flash_fwd_tc3, 2: _lib().b200_flash_fwd_tc2}.get(FLASH_FWD_GEN, _lib().b200_flash_fwd_tc)
-        native.check(fwd_fn(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
-                                              native.ptr(lse), native.ptr(valid_len), arr, B, T, QH, KVH, D,
-                                              _f(scale), native.stream_ptr()), "flash_fwd_tc")
+        native.check(_lib().b200_flash_fwd_tc3(native.ptr(q), native.ptr(k), native.ptr(v), native.ptr(o),
+                                               native.ptr(lse), native.ptr(valid_len), arr, B, T, QH, KVH, D,
+                                               _f(scale), native.stream_ptr()), "flash_fwd_tc3")
         native.bump()
         return o, lse
     arr = (ctypes.c_longlong * 24)(*(strides + [0] * 12))
@@ -407,38 +518,7 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         scale = 1.0 / math.sqrt(D)
     cos, sin = rope if rope is not None else (None, None)
     if not q.is_cuda:
-        R = QH // KVH
-        _, _, p, qf, kf = _attn_reference(q, k, v, valid_len, scale, cos, sin)
-        dof = dout.float()
-        vx = v.float().repeat_interleave(R, dim=2)
-        kx = kf.repeat_interleave(R, dim=2)
-        dvx = torch.einsum("bhts,bthd->bshd", p, dof)
-        dp = torch.einsum("bthd,bshd->bhts", dof, vx)
-        delta = (dof * o.float()).sum(-1).permute(0, 2, 1)          # [B, QH, T]
-        ds = p * (dp - delta[..., None]) * scale
-        dqf = torch.einsum("bhts,bshd->bthd", ds, kx)
-        dkx = torch.einsum("bhts,bthd->bshd", ds, qf)
-        dk_ = dkx.reshape(B, T, KVH, R, D).sum(3)
-        dv_ = dvx.reshape(B, T, KVH, R, D).sum(3)
-        if cos is not None:
-            def unrot(x):
-                c, s = cos[:T][None, :, None, :], sin[:T][None, :, None, :]
-                y1, y2 = x[..., :D // 2], x[..., D // 2:]
-                return torch.cat([y1 * c + y2 * s, y2 * c - y1 * s], -1)
-            dqf, dk_ = unrot(dqf), unrot(dk_)
-        if unrotate is not None:
-            uc, us = unrotate[0][:T][None, :, None, :].float(), unrotate[1][:T][None, :, None, :].float()
-
-            def unrot2(x):
-                y1, y2 = x[..., :D // 2], x[..., D // 2:]
-                return torch.cat([y1 * uc + y2 * us, y2 * uc - y1 * us], -1)
-            dqf, dk_ = unrot2(dqf), unrot2(dk_)
-        res = (dqf.to(q.dtype), dk_.to(q.dtype), dv_.to(q.dtype))
-        if out is not None:
-            for dst, src in zip(out, res):
-                dst.copy_(src)
-            return out
-        return res
+        return _attn_bwd_reference(dout, q, k, v, o, valid_len, scale, cos, sin, unrotate, out)
     _bf16(dout, q, k, v, o)
     if dout.stride(3) != 1:
         dout = dout.contiguous()

@@ -15,17 +15,17 @@ GEMM_OUT_F32 = 1
 GEMM_ADD_C = 2
 GEMM_WHOLE_TILES = 8      # CTA-pair kernel: do not split the tiles of a part-filled last round
 
-import os as _os
+# Code-path switches (module attributes; tests and the benchmark's baseline arm set them).
 # "1cta": single-CTA 128x256 tiles; "2cta": CTA pairs (cta_group::2) on 256x256 tiles where the
 # problem is large enough, single-CTA otherwise.
-GEMM_IMPL = _os.environ.get("B200_GEMM_IMPL", "2cta")
-# Tile hand-out of the CTA-pair kernel: "1" = tiles beyond each pair's first come from a device
-# counter (pairs that start late draw fewer), "0" = fixed round-robin assignment.
-GEMM_DYNAMIC_TILES = int(_os.environ.get("B200_GEMM_DYNAMIC", "1"))
+GEMM_IMPL = "2cta"
+# Tile hand-out of the CTA-pair kernel: 1 = tiles beyond each pair's first come from a device
+# counter (pairs that start late draw fewer), 0 = fixed round-robin assignment.
+GEMM_DYNAMIC_TILES = 1
 _dynamic_applied = None
-# "1": when the last round of 256x256 tiles would fill less than half of the CTA pairs, those tiles
-# are split into 256x128 halves so that twice as many pairs work on it; "0": whole tiles only.
-GEMM_HALF_TILES = int(_os.environ.get("B200_GEMM_HALF_TILES", "1"))
+# 1: when the last round of 256x256 tiles would fill less than half of the CTA pairs, those tiles
+# are split into 256x128 halves so that twice as many pairs work on it; 0: whole tiles only.
+GEMM_HALF_TILES = 1
 _half_applied = None
 
 
@@ -129,7 +129,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
 
 
 # Rotary embedding in the epilogue of the CTA-pair kernel instead of an in-place pass over the output.
-GEMM_ROPE_EPILOGUE = _os.environ.get("B200_GEMM_ROPE_EPILOGUE", "1") != "0"
+GEMM_ROPE_EPILOGUE = True
 
 
 _rope_t_cache: dict = {}
@@ -252,10 +252,12 @@ def gemm_ce_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
     return bool(x.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(x, w) and x.shape[0] >= 256 and w.shape[0] >= 256)
 
 
-def gemm_ce_stats(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, tlogit: torch.Tensor, col0: int = 0):
+def gemm_ce_stats(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, tlogit: torch.Tensor, col0: int = 0,
+                  vocab: int = 0):
     """Logits ``x @ w^T`` that are never stored: returns per-tile row statistics ``(pmax, psum)``, each
     ``[ceil(V / 256), M]`` fp32 (maximum and sum of exp(logit - maximum) over the tile's columns), and writes the
-    target's logit of every row whose target lies in ``[col0, col0 + V)`` into ``tlogit`` [M] fp32."""
+    target's logit of every row whose target lies in ``[col0, col0 + V)`` into ``tlogit`` [M] fp32. ``vocab``
+    (size of the whole vocabulary, 0: unknown) lets the bounds-checking build report targets beyond it."""
     M, K = x.shape
     V = w.shape[0]
     assert gemm_ce_fusable(x, w) and targets.dtype == torch.int32 and targets.numel() == M
@@ -266,7 +268,7 @@ def gemm_ce_stats(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, tlogi
     _apply_dynamic()
     rc = native.lib().b200_gemm_bf16_2cta_ce_stats(
         native.ptr(x), native.ptr(w), M, V, K, x.stride(0), w.stride(0), native.ptr(targets), native.ptr(pmax),
-        native.ptr(psum), native.ptr(tlogit), col0, 0, native.stream_ptr())
+        native.ptr(psum), native.ptr(tlogit), col0, 0, int(vocab), native.stream_ptr())
     native.check(rc, "b200_gemm_bf16_2cta_ce_stats")
     native.bump()
     return pmax, psum
@@ -348,7 +350,7 @@ def ag_region(slice_bytes: int, world: int, b_offset_bytes: int, b_bytes: int) -
 # part-filled wave (e.g. 2048 x 3072 x 8192 is 1.3 waves of CTA pairs). The weight-gradient GEMMs
 # do not feed the activation-gradient chain, so issuing them on a side stream lets their first
 # CTAs start on SMs the other kernel has already left.
-WGRAD_OVERLAP = _os.environ.get("B200_WGRAD_OVERLAP", "1") != "0"
+WGRAD_OVERLAP = True
 _wgrad_streams: dict = {}
 _wgrad_pending: dict = {}     # device index -> a side-stream GEMM has been issued and not joined yet
 
@@ -375,6 +377,21 @@ def wgrad_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None
     a.record_stream(ws)
     b.record_stream(ws)
     return res
+
+
+def wgrad_event(device):
+    """An event after everything issued so far on the weight-gradient side stream of ``device`` (None when
+    that stream has never been used): what a consumer on a third stream waits for instead of joining."""
+    dev = torch.device(device)
+    if not WGRAD_OVERLAP or dev.type != "cuda":
+        return None
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    ws = _wgrad_streams.get(key)
+    if ws is None:
+        return None
+    ev = torch.cuda.Event()
+    ev.record(ws)
+    return ev
 
 
 def wgrad_join(device=None) -> None:

@@ -96,7 +96,7 @@ def init_distributed(rank: int, world_size: int, *, backend: str | None = None, 
     (which pins NCCL to the loopback interface, Main/main_sample3.py:4-14), and container
     hostnames do not always resolve.
     """
-    if world_size == 1 and not dist.is_initialized() and os.environ.get("B200_FORCE_DIST") != "1":
+    if world_size == 1 and not dist.is_initialized():
         return SingleProcessComm()
     if backend is None:
         backend = "nccl" if torch.cuda.is_available() else "gloo"

@@ -201,12 +201,17 @@ class FusedCollectives:
         return self.heap.alloc(n, dtype)
 
     def reduce_scatter_accumulate(self, dst: torch.Tensor, bucket: torch.Tensor, accumulate: bool, stream=None,
-                                  stats: torch.Tensor | None = None, do_stats: bool = False, adam: dict | None = None):
+                                  stats: torch.Tensor | None = None, do_stats: bool = False, adam: dict | None = None,
+                                  elem_range: tuple | None = None):
         """dst[n] (<- or +=) sum over ranks of their bucket[rank * n : (rank + 1) * n]; bucket is a
         bf16 heap tensor at the same offset on every rank. With ``adam`` (tensors m, v, master,
-        param and the scalar hyper-parameters) the reduced gradient goes straight into AdamW."""
+        param and the scalar hyper-parameters) the reduced gradient goes straight into AdamW.
+        ``elem_range`` = (lo, hi), multiples of 8: only those elements of the bucket are reduced (a
+        sub-bucket that is complete before the rest); each rank handles what falls into its slice."""
         n = dst.numel()
         assert bucket.numel() == n * self.world_size and bucket.dtype == torch.bfloat16 and n % 8 == 0
+        lo, hi = elem_range if elem_range is not None else (0, bucket.numel())
+        assert 0 <= lo <= hi <= bucket.numel() and lo % 8 == 0 and hi % 8 == 0
         self.rs_epoch += 1
         mode = 2 if adam is not None else (1 if accumulate else 0)
         if mode == 1:
@@ -219,9 +224,10 @@ class FusedCollectives:
             adam_f = (ctypes.c_float * 8)(adam["lr"], adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"],
                                           adam["m_corr"], adam["v_corr"], adam["grad_scale"])
         s = native.stream_ptr() if stream is None else ctypes.c_void_p(stream.cuda_stream)
-        rc = self.lib.b200_symm_reduce_scatter(
+        rc = self.lib.b200_symm_reduce_scatter_range(
             self.heap.table, self.world_size, self.rank, 1, ctypes.c_ulonglong(self.heap.offset_of(bucket)),
-            ctypes.c_longlong(n), _ptr_array([dst.data_ptr()]), int(dst.dtype == torch.float32), mode,
+            ctypes.c_longlong(n), ctypes.c_longlong(lo), ctypes.c_longlong(hi), _ptr_array([dst.data_ptr()]),
+            int(dst.dtype == torch.float32), mode,
             _ptr_array([stats.data_ptr() if stats is not None else 0]), int(do_stats), adam_ptrs, adam_f,
             ctypes.c_uint(self.rs_epoch), ctypes.c_ulonglong(self.wait_ns), self.rs_blocks, s)
         native.check(rc, "symm_reduce_scatter")
@@ -303,9 +309,10 @@ class LocalVirtualRanks:
         return off, [v[off:off + n * esz].view(dtype) for v in self.views]
 
     def reduce_scatter(self, bucket_off: int, n_slice: int, dsts, accumulate=False, stats=None, do_stats=False,
-                       adam=None, blocks: int = 4):
+                       adam=None, blocks: int = 4, elem_range: tuple | None = None):
         self.rs_epoch += 1
         W = self.world_size
+        lo, hi = elem_range if elem_range is not None else (0, W * n_slice)
         mode = 2 if adam is not None else (1 if accumulate else 0)
         adam_ptrs = adam_f = None
         if adam is not None:
@@ -316,9 +323,9 @@ class LocalVirtualRanks:
             adam_ptrs = _ptr_array(flat)
             adam_f = (ctypes.c_float * 8)(adam["lr"], adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"],
                                           adam["m_corr"], adam["v_corr"], adam["grad_scale"])
-        rc = self.lib.b200_symm_reduce_scatter(
-            self.tables, W, 0, W, ctypes.c_ulonglong(bucket_off), ctypes.c_longlong(n_slice),
-            _ptr_array([d.data_ptr() for d in dsts]), int(dsts[0].dtype == torch.float32), mode,
+        rc = self.lib.b200_symm_reduce_scatter_range(
+            self.tables, W, 0, W, ctypes.c_ulonglong(bucket_off), ctypes.c_longlong(n_slice), ctypes.c_longlong(lo),
+            ctypes.c_longlong(hi), _ptr_array([d.data_ptr() for d in dsts]), int(dsts[0].dtype == torch.float32), mode,
             _ptr_array([s.data_ptr() for s in stats] if stats is not None else [0] * W), int(do_stats), adam_ptrs, adam_f,
             ctypes.c_uint(self.rs_epoch), ctypes.c_ulonglong(self.wait_ns), blocks, native.stream_ptr())
         native.check(rc, "symm_reduce_scatter")

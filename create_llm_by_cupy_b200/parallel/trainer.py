@@ -43,7 +43,7 @@ class Trainer:
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
                  profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False,
                  profile_phases: bool = False, adam_overlap: bool = True, cuda_graph: bool = False,
-                 defer_host_read: bool = False):
+                 defer_host_read: bool = False, adam_overlap_ctas_per_sm: int = 2):
         self.rank, self.world_size = rank, world_size
         self.profile_phases = bool(profile_phases)
         self._phase_marks = []
@@ -92,7 +92,7 @@ class Trainer:
                                  and self.accum_step == 1 and self.replica_optimizer is None and not fused_adam)
         self._adam_stream = torch.cuda.Stream(device=self.device) if self.adam_overlap else None
         # AdamW CTAs per SM while it runs beside the forward: few enough that the GEMM CTAs still fit
-        self.adam_overlap_ctas_per_sm = int(os.environ.get("B200_ADAM_OVERLAP_CTAS", "2"))
+        self.adam_overlap_ctas_per_sm = int(adam_overlap_ctas_per_sm)
         self._adam_done = None
         # Whole-step CUDA graph (one GPU): forward, backward, gradient statistics and AdamW are captured
         # once and replayed; what changes from step to step (token ids, learning rate, bias corrections,

@@ -28,7 +28,7 @@ from .layout import FlatLayout, select_replicated_params
 
 
 class _Buf:
-    __slots__ = ("t", "free_event", "ready_event", "uid", "seg", "epoch")
+    __slots__ = ("t", "free_event", "ready_event", "uid", "seg", "epoch", "flushed")
 
     def __init__(self, t):
         self.t = t
@@ -37,6 +37,7 @@ class _Buf:
         self.uid = -1
         self.seg = None
         self.epoch = 0
+        self.flushed = []        # element ranges of a gradient bucket that were reduced ahead of the rest
 
 
 class _PendingGather:
@@ -167,6 +168,10 @@ class MemoryZeRO3Manager:
         self.enable_forward_param_prefetch = pf and bool(getattr(model, "zero3_forward_param_prefetch", True))
         self.enable_backward_param_prefetch = pf and bool(getattr(model, "zero3_backward_param_prefetch", True))
         self.enable_grad_bucket = bool(getattr(model, "zero3_grad_bucket", True))
+        # Largest number of elements one reduce-scatter launch takes (fused mode): a unit's gradient bucket that
+        # is larger is reduced in parts of at most this size, and the part that is complete first (the MLP
+        # weights of a block) goes out before the block's backward has finished.
+        self.grad_bucket_elems = int(getattr(model, "grad_bucket_elems", 0) or 0)
 
         if self.cuda:
             self.compute_stream = stream if stream is not None else torch.cuda.current_stream(self.device)
@@ -577,6 +582,7 @@ class MemoryZeRO3Manager:
             b = self.grad_pool.get(unit.padded)
             self._wait(self.compute_stream, b.free_event)
         b.uid = uid
+        b.flushed = []
         self.cur_grad[uid] = b
         return b
 
@@ -646,19 +652,10 @@ class MemoryZeRO3Manager:
             with self._comm_ctx():
                 self._wait(self.comm_stream, ev)
                 if self.fused is not None:
-                    adam = None
-                    if self.fused_adam is not None and self.micro_index == self.accum_steps - 1 and self.direct_grad:
-                        # reduce-scatter -> cast -> scale -> AdamW in ONE kernel: the reduced gradient
-                        # of this unit never goes to memory, the parameter slice is updated in place
-                        fa, opt = self.fused_adam, self.fused_adam["opt"]
-                        adam = dict(m=opt.m[lo:hi], v=opt.v[lo:hi], master=opt.master_weight_shard[lo:hi],
-                                    param=self.param_shard_f16[lo:hi], lr=fa["lr"], beta1=opt.beta1, beta2=opt.beta2,
-                                    eps=opt.epsilon, weight_decay=opt.weight_decay,
-                                    m_corr=1.0 / (1.0 - opt.beta1 ** opt.t), v_corr=1.0 / (1.0 - opt.beta2 ** opt.t),
-                                    grad_scale=fa["grad_scale"])
-                    self.fused.reduce_scatter_accumulate(dst, b.t, accumulate=not self.direct_grad,
-                                                         stream=self.comm_stream, stats=self._stats,
-                                                         do_stats=self.micro_index == self.accum_steps - 1, adam=adam)
+                    early = sum(e - a for a, e in b.flushed)
+                    for rng in self._unflushed_parts(b, unit.padded):
+                        self._fused_reduce(b, dst, lo, hi, rng)
+                    self.bytes_reduced -= early * (self.world_size - 1) // self.world_size * b.t.element_size()
                 elif self.direct_grad:
                     self.comm.reduce_scatter(dst, b.t)
                 else:
@@ -672,6 +669,81 @@ class MemoryZeRO3Manager:
         b.free_event = self._record(done_on)
         self.pending_reduce_handles.append((b.free_event, tag))
         self.grad_pool.put(b)
+
+    def _fused_reduce(self, b: _Buf, dst, lo: int, hi: int, elem_range):
+        """One launch of the fused reduce-scatter on the communication stream for ``elem_range`` of bucket ``b``
+        (shard range [lo, hi) of its unit)."""
+        adam = None
+        if self.fused_adam is not None and self.micro_index == self.accum_steps - 1 and self.direct_grad:
+            # reduce-scatter -> cast -> scale -> AdamW in ONE kernel: the reduced gradient
+            # of this unit never goes to memory, the parameter slice is updated in place
+            fa, opt = self.fused_adam, self.fused_adam["opt"]
+            adam = dict(m=opt.m[lo:hi], v=opt.v[lo:hi], master=opt.master_weight_shard[lo:hi],
+                        param=self.param_shard_f16[lo:hi], lr=fa["lr"], beta1=opt.beta1, beta2=opt.beta2,
+                        eps=opt.epsilon, weight_decay=opt.weight_decay,
+                        m_corr=1.0 / (1.0 - opt.beta1 ** opt.t), v_corr=1.0 / (1.0 - opt.beta2 ** opt.t),
+                        grad_scale=fa["grad_scale"])
+        self.fused.reduce_scatter_accumulate(dst, b.t, accumulate=not self.direct_grad, stream=self.comm_stream,
+                                             stats=self._stats, do_stats=self.micro_index == self.accum_steps - 1,
+                                             adam=adam, elem_range=elem_range)
+
+    def _split_range(self, lo: int, hi: int):
+        """[lo, hi) cut into parts of at most ``grad_bucket_elems`` elements (multiples of 8)."""
+        step = self.grad_bucket_elems // 8 * 8 if self.grad_bucket_elems > 0 else 0
+        if step <= 0 or hi - lo <= step:
+            return [(lo, hi)] if hi > lo else []
+        return [(a, min(a + step, hi)) for a in range(lo, hi, step)]
+
+    def _unflushed_parts(self, b: _Buf, padded: int):
+        """Element ranges of bucket ``b`` that have not been reduced yet, cut to the bucket limit."""
+        parts, pos = [], 0
+        for lo, hi in sorted(b.flushed):
+            parts += self._split_range(pos, lo)
+            pos = max(pos, hi)
+        return parts + self._split_range(pos, padded)
+
+    def flush_grad_ranges_async(self, modules, tag=None):
+        """Reduce the gradients of ``modules``' weights now, ahead of the rest of their unit's bucket (fused
+        collectives only; with NCCL, and for units within the bucket limit, the unit is reduced whole at the
+        end of its backward). The model calls this when a block's MLP backward has been issued: its
+        weight-gradient GEMMs run on the side stream, so the launch waits for that stream's event and for the
+        compute stream, not for the whole block."""
+        if self.fused is None or self.world_size == 1 or self.grad_bucket_elems <= 0:
+            return
+        for uid in self._unit_ids(modules):
+            b = self.cur_grad.get(uid)
+            unit = self.layout.units[uid]
+            if b is None or unit.padded <= self.grad_bucket_elems:
+                continue
+            lo_e, hi_e = None, None
+            for m in modules:
+                if self.uid_of_module.get(id(m)) != uid:
+                    continue
+                for idx in m._zero3_param_indices:
+                    s = self.layout.slots[idx]
+                    if s.unit != uid:
+                        continue
+                    a, e = s.offset // 8 * 8, (s.offset + s.size + 7) // 8 * 8
+                    lo_e = a if lo_e is None else min(lo_e, a)
+                    hi_e = e if hi_e is None else max(hi_e, e)
+            if lo_e is None:
+                continue
+            # the range must hold nothing but these modules' parameters (they are laid out back to back)
+            inside = [s for s in self.layout.slots if s.unit == uid and s.offset < hi_e and s.offset + s.size > lo_e]
+            owned = {idx for m in modules for idx in m._zero3_param_indices}
+            if any(s.index not in owned for s in inside):
+                continue
+            lo, hi = self.layout.unit_shard_range(uid)
+            dst = self.grad_shard_f16[lo:hi]
+            ev = self._record(self.compute_stream)
+            wev = F.wgrad_event(self.device)
+            with self._comm_ctx():
+                self._wait(self.comm_stream, ev)
+                self._wait(self.comm_stream, wev)
+                for rng in self._split_range(lo_e, hi_e):
+                    self._fused_reduce(b, dst, lo, hi, rng)
+            b.flushed.append((lo_e, hi_e))
+            self.bytes_reduced += (hi_e - lo_e) * (self.world_size - 1) // self.world_size * b.t.element_size()
 
     def flush_grad_bucket_async(self, tag=None):
         for uid in [u for u in list(self.cur_grad) if self.unit_names[u].startswith(("block", "final_norm"))]:

@@ -130,6 +130,48 @@ def test_dropout_branches_and_mask_adapters():
         pad_mask_to_valid_len(torch.tensor([[False, True, False, False]]), 4)
 
 
+def test_dropout_mask_is_bit_packed_and_attention_dropout_backward_matches_autograd():
+    from create_llm_by_cupy_b200.models.layers import TimeDropout
+    from create_llm_by_cupy_b200.ops import functional as F
+
+    gen = torch.Generator().manual_seed(3)
+    drop = TimeDropout(0.3, torch.float32, gen)
+    x = torch.randn(5, 7, 11, generator=gen)
+    y = drop.forward(x, True)
+    assert drop.mask.dtype == torch.uint8 and drop.mask.numel() == (x.numel() + 7) // 8     # one bit per element
+    keep = F._unpackbits(drop.mask, x.numel()).view(x.shape)
+    torch.testing.assert_close(y, x * keep / 0.7)
+    assert 0.55 < keep.float().mean() < 0.85
+    g = torch.randn(x.shape, generator=gen)
+    torch.testing.assert_close(drop.backward(g), g * keep / 0.7)
+    assert drop.mask is None
+    y2 = drop.forward(x, True)                         # the next call draws another mask
+    assert not torch.equal(y2 != 0, y != 0)
+    assert drop.forward(x, False) is x                 # inference: identity
+
+    # attention with dropout on the probabilities: manual backward against autograd with the same mask
+    B, T, QH, KVH, D = 2, 12, 4, 2, 8
+    q = torch.randn(B, T, QH, D, generator=gen, requires_grad=True)
+    k = torch.randn(B, T, KVH, D, generator=gen, requires_grad=True)
+    v = torch.randn(B, T, KVH, D, generator=gen, requires_grad=True)
+    do = torch.randn(B, T, QH, D, generator=gen)
+    cos, sin = F.rope_table(T, D, 10000.0, "cpu")
+    vl = torch.tensor([12, 9], dtype=torch.int32)
+    scale = D ** -0.5
+    adrop = TimeDropout(0.25, torch.float32, gen)
+    _, _, p, _, _ = F._attn_reference(q, k, v, vl, scale, cos, sin)
+    p_used = adrop.forward(p.detach(), True)
+    keep = F._unpackbits(adrop.mask, p.numel()).view(p.shape)
+    o = torch.einsum("bhts,bshd->bthd", p * keep / 0.75, v.repeat_interleave(QH // KVH, dim=2))
+    torch.testing.assert_close(o, torch.einsum("bhts,bshd->bthd", p_used, v.detach().repeat_interleave(QH // KVH, dim=2)))
+    (o * do).sum().backward()
+    dq, dk, dv = F._attn_bwd_reference(do, q.detach(), k.detach(), v.detach(), o.detach(), vl, scale, cos, sin,
+                                       p_drop=adrop)
+    torch.testing.assert_close(dq, q.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dk, k.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dv, v.grad, rtol=1e-4, atol=1e-5)
+
+
 def test_attention_backward_unrotate_equals_in_kernel_rope():
     """Two ways to the same gradients: (a) q, k un-rotated and ``rope=`` (rotation inside), (b) q, k rotated
     beforehand and ``unrotate=`` (inverse rotation of dq, dk on the way out) - the contract of the epilogue

@@ -121,6 +121,32 @@ def test_fused_epilogues_agree_with_the_separate_kernels_at_model_level():
         assert abs(a["grad_norm"] - b["grad_norm"]) < 3e-2 * b["grad_norm"], (a, b)
 
 
+def test_dense_attention_path_and_dropout_run_on_the_device():
+    """``flash_backend="none"`` (dense verification path, forward and backward on the GPU) gives the gradients of
+    the flash path; with dropout the model trains through the dense path with packed masks."""
+    gpu_f = Cupa_ver4(dict(CFG1, dtype="bf16", half_float=True), device="cuda")
+    gpu_d = Cupa_ver4(dict(CFG1, dtype="bf16", half_float=True, flash_backend="none"), device="cuda")
+    x, t, pa = (v.cuda() for v in data(1)[0])
+    lf = gpu_f.forward(x, t, pa)
+    ld = gpu_d.forward(x, t, pa)
+    assert abs(float(lf) - float(ld)) < 2e-2
+    gpu_f.backward(1.0)
+    gpu_d.backward(1.0)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for i, (a, b) in enumerate(zip(gpu_f.grads, gpu_d.grads)):
+        assert a.is_cuda and b.is_cuda
+        a, b = a.float(), b.float()
+        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-8) < 6e-2, f"param {i}"
+    drop = Cupa_ver4(dict(CFG1, dtype="bf16", half_float=True, dropout_rate=0.1), device="cuda")
+    l1 = float(drop.forward(x, t, pa))
+    drop.backward(1.0)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0) and math.isfinite(l1)
+    assert all(torch.isfinite(g.float()).all() for g in drop.grads)
+    assert abs(float(drop.predict(x, t, pa)) - float(gpu_f.predict(x, t, pa))) < 1e-6     # no dropout at inference
+
+
 def test_decode_with_kv_cache_matches_full_forward_logits():
     m = Cupa_ver4(dict(CFG1, dtype="bf16", half_float=True), device="cuda")
     prompt = [int(v) for v in synthetic_token_stream(1, 24, 512, "generation", 0, low=1)[0]]

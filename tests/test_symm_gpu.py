@@ -52,6 +52,34 @@ def test_virtual_ranks_reduce_scatter_store_accumulate_and_stats(W):
     vr.close()
 
 
+@pytest.mark.parametrize("W", [2, 8])
+def test_virtual_ranks_reduce_scatter_in_sub_bucket_ranges(W):
+    """A bucket reduced in three element ranges (each rank takes what falls into its slice, possibly nothing)
+    gives the result and the statistics of the one-launch reduce-scatter."""
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    vr = LocalVirtualRanks(W)
+    n_slice = 8 * 700
+    n = n_slice * W
+    off, buckets = vr.alloc(n, torch.bfloat16)
+    for r, b in enumerate(buckets):
+        b.copy_(torch.randn(n, generator=torch.Generator().manual_seed(50 + r)).to(torch.bfloat16))
+    whole = [torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    st_whole = [torch.zeros(2, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, whole, stats=st_whole, do_stats=True)
+    parts = [torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    st_parts = [torch.zeros(2, device="cuda") for _ in range(W)]
+    cuts = [0, 8 * 333, n_slice + 8 * 17, n]          # ranges that start and end inside slices
+    for lo, hi in reversed(list(zip(cuts[:-1], cuts[1:]))):     # any order
+        vr.reduce_scatter(off, n_slice, parts, stats=st_parts, do_stats=True, elem_range=(lo, hi))
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for r in range(W):
+        assert torch.equal(parts[r], whole[r])
+        assert abs(st_parts[r][0].item() - st_whole[r][0].item()) <= 1e-4 * st_whole[r][0].item()
+    vr.close()
+
+
 def test_virtual_ranks_fused_adam_matches_separate_kernels():
     from create_llm_by_cupy_b200.ops import functional as F
     from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks

@@ -243,6 +243,28 @@ def test_gradient_buffer_pool_rotates_two_buffers_deterministically():
     assert single.get(8).t.data_ptr() == x.t.data_ptr()
 
 
+def test_gradient_bucket_limit_splits_a_unit_into_parts_that_cover_it_once():
+    tr = Trainer(dict(TINY, grad_bucket_elems=1000), device="cpu", **HP)
+    mgr = tr.manager
+    assert mgr._split_range(0, 2504) == [(0, 1000), (1000, 2000), (2000, 2504)]
+    assert mgr._split_range(8, 8) == [] and mgr._split_range(16, 400) == [(16, 400)]
+
+    class B:
+        flushed = [(1200, 2400), (4000, 4800)]
+    parts = mgr._unflushed_parts(B, 5600)
+    covered = sorted(parts + B.flushed)
+    assert covered[0][0] == 0 and covered[-1][1] == 5600
+    assert all(a[1] == b[0] for a, b in zip(covered[:-1], covered[1:]))          # no gap, no overlap
+    assert all(hi - lo <= 1000 for lo, hi in parts)
+    # inside a block's unit the MLP weights are one contiguous tail (what the early flush reduces)
+    lay = mgr.layout
+    uid = mgr.uid_of_name["block0"]
+    feed = tr.model.block_modules(0)[1]
+    offs = sorted((lay.slots[i].offset, lay.slots[i].offset + lay.slots[i].size) for i in feed._zero3_param_indices)
+    others = [lay.slots[i] for i in lay.units[uid].param_indices if i not in feed._zero3_param_indices]
+    assert all(s.offset + s.size <= offs[0][0] for s in others)
+
+
 def test_forward_unit_order_and_ranges_cover_the_shard():
     from create_llm_by_cupy_b200.parallel.trainer import Trainer
     md = dict(vocab_size=64, hidden_size=32, layer_num=3, time_size=16, q_head=4, kv_head=2, ffn_size=64,
