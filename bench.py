@@ -78,6 +78,10 @@ def main():
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--no-phases", action="store_true", help="do not record the per-phase CUDA events")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
+    ap.add_argument("--bucket-elems", type=int, default=25_000_000,
+                    help="largest reduce-scatter launch in elements (0: every unit's bucket is reduced in one launch)")
+    ap.add_argument("--early-flush", action="store_true",
+                    help="reduce the MLP part of a block's gradient bucket before the block's backward has finished")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -121,7 +125,7 @@ def main():
     md = dict(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], layer_num=c["layer_num"],
               time_size=c["time_size"], q_head=c["q_head"], kv_head=c["kv_head"], ffn_size=c["ffn_size"],
               padding_id=pad, dropout_rate=0, half_float=True, dtype="bf16", tie_embeddings=True, init_std=0.02,
-              seed=0, grad_bucket_elems=25_000_000)
+              seed=0, grad_bucket_elems=args.bucket_elems, zero3_early_bucket_flush=args.early_flush)
     if c["zero"] == "2.5":
         md.update(zero25_replica_ratio=0.5, zero25_replica_policy="largest_first")
     if args.keep_params:

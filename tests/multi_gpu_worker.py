@@ -29,7 +29,8 @@ def main():
     accum = int(os.environ.get("B200_TEST_ACCUM", "2"))
     md = dict(vocab_size=2048, hidden_size=256, layer_num=3, time_size=256, q_head=4, kv_head=2, ffn_size=688,
               padding_id=0, dropout_rate=0, dtype="bf16", half_float=True, tie_embeddings=True, init_std=0.02, seed=1,
-              grad_bucket_elems=int(os.environ.get("B200_TEST_BUCKET", "300000")))     # blocks are reduced in parts
+              grad_bucket_elems=int(os.environ.get("B200_TEST_BUCKET", "300000")),     # blocks are reduced in parts,
+              zero3_early_bucket_flush=True)                                           # the MLP part ahead of the rest
     fused_adam = os.environ.get("B200_TEST_FUSED_ADAM", "0") == "1"
     tr = Trainer(md, rank=rank, world_size=world, comm=comm, device=dev, accum_step=accum, lr_max=1e-3, warm_up=1,
                  total_steps=6, beta2=0.95, fused=fused, profile_comm=True, fused_adam=fused_adam,
