@@ -80,6 +80,7 @@ def main():
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     ap.add_argument("--bucket-elems", type=int, default=25_000_000,
                     help="largest reduce-scatter launch in elements (0: every unit's bucket is reduced in one launch)")
+    ap.add_argument("--adam-ctas", type=int, default=2, help="AdamW CTAs per SM while it runs beside the next forward")
     ap.add_argument("--early-flush", action="store_true",
                     help="reduce the MLP part of a block's gradient bucket before the block's backward has finished")
     args = ap.parse_args()
@@ -173,7 +174,7 @@ def main():
                      warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
                      profile_comm=world > 1, profile_phases=not (args.no_phases or args.graph),
                      cuda_graph=args.graph and not plain, adam_overlap=not (args.no_adam_overlap or plain),
-                     defer_host_read=not (args.sync_read or plain))
+                     defer_host_read=not (args.sync_read or plain), adam_overlap_ctas_per_sm=args.adam_ctas)
         return tr, fused
 
     def timed(trainer, run_step):

@@ -384,6 +384,9 @@ __global__ void flash_delta_kernel(const FlashParams p, int D) {
 
 // The same with 16-byte loads: LPR = D / 8 lanes share a row, a warp covers 32 / LPR rows at a time and
 // every thread keeps U rows in flight. Needs 16-byte aligned rows (strides that are multiples of 8).
+// Rows are numbered with the head fastest, (b, t, h): in the packed [B, T, heads, D] layout consecutive
+// rows are then consecutive in memory, so a warp's loads cover whole contiguous lines (numbered with the
+// token fastest every 256-byte row sat one token pitch apart, and the pass ran at a third of the bandwidth).
 template <int LPR, int U>
 __global__ void __launch_bounds__(256) flash_delta_vec_kernel(const FlashParams p) {
   constexpr int RPW = 32 / LPR;                      // rows per warp and step
@@ -399,7 +402,7 @@ __global__ void __launch_bounds__(256) flash_delta_vec_kernel(const FlashParams 
     for (int u = 0; u < U; ++u) {
       row[u] = r0 + u * RPW + sub;
       if (row[u] < total) {
-        const int t = int(row[u] % p.T), h = int((row[u] / p.T) % p.QH), b = int(row[u] / ((long long)p.T * p.QH));
+        const int h = int(row[u] % p.QH), t = int((row[u] / p.QH) % p.T), b = int(row[u] / ((long long)p.T * p.QH));
         a[u] = *reinterpret_cast<const uint4*>(p.o + b * p.o_bs + (long long)t * p.o_ts + h * p.o_hs + li * 8);
         c[u] = *reinterpret_cast<const uint4*>(p.dout + b * p.do_bs + (long long)t * p.do_ts + h * p.do_hs + li * 8);
       }
@@ -419,7 +422,7 @@ __global__ void __launch_bounds__(256) flash_delta_vec_kernel(const FlashParams 
 #pragma unroll
       for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
       if (li == 0 && row[u] < total) {
-        const int t = int(row[u] % p.T), h = int((row[u] / p.T) % p.QH), b = int(row[u] / ((long long)p.T * p.QH));
+        const int h = int(row[u] % p.QH), t = int((row[u] / p.QH) % p.T), b = int(row[u] / ((long long)p.T * p.QH));
         p.delta[(size_t(b) * p.QH + h) * p.T + t] = s;
       }
     }
