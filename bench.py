@@ -75,6 +75,9 @@ def main():
     ap.add_argument("--keep-params", action="store_true",
                     help="keep gathered block parameters from the forward until their backward (one GPU only)")
     ap.add_argument("--opt", default=None, choices=["gpu", "cpu"], help="override the config's optimizer tier")
+    ap.add_argument("--delayed-offload", action="store_true",
+                    help="host optimizer (--opt cpu / config 7b): one-step delayed parameter update, the host AdamW "
+                         "runs under the next step's forward and backward")
     ap.add_argument("--graph", action="store_true", help="capture the whole step in a CUDA graph (one GPU)")
     ap.add_argument("--no-phases", action="store_true", help="do not record the per-phase CUDA events")
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
@@ -174,7 +177,8 @@ def main():
                      warm_up=100, total_steps=10000, beta1=0.9, beta2=0.95, max_grads=1.0, fused=fused,
                      profile_comm=world > 1, profile_phases=not (args.no_phases or args.graph),
                      cuda_graph=args.graph and not plain, adam_overlap=not (args.no_adam_overlap or plain),
-                     defer_host_read=not (args.sync_read or plain), adam_overlap_ctas_per_sm=args.adam_ctas)
+                     defer_host_read=not (args.sync_read or plain), adam_overlap_ctas_per_sm=args.adam_ctas,
+                     offload_delayed_update=args.delayed_offload and not plain)
         return tr, fused
 
     def timed(trainer, run_step):
@@ -266,6 +270,7 @@ def main():
             "config": {"model": c["name"], "global_batch": B * accum * world, "seq_len": T,
                        "parallelism": f"zero{c['zero']}-dp{world}", "params": n_par, "cuda_graph": cuda_graph,
                        "keep_params_until_backward": bool(args.keep_params), "collectives": collectives,
+                       "optimizer": c["opt"] + (" (one-step delayed update)" if args.delayed_offload and c["opt"] == "cpu" else ""),
                        "l2": f"not flushed: a step streams more than {28e-9 * n_par / world + 2e-9 * n_par:.1f} GB of weights and "
                              "optimizer state per GPU, far above the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "copy_engine_transfers_total": copies, "clocks": clocks,

@@ -154,6 +154,9 @@ class ZeRO_Adam_Offload(_AdamBase):
         self.grad_cpu = None
         self.out_cpu = torch.empty(n, dtype=param_shard.dtype, pin_memory=pin)
         self.threads = int(threads)
+        self._pending = None            # (thread, result) of a background update (delayed parameter update)
+        self._grad_snapshot = None
+        self._param_staging = None
         self.side_stream = torch.cuda.Stream(device=self.device) if pin else None
         self._lib = native.lib() if pin or _cpu_lib_ok() else None
 
@@ -162,11 +165,12 @@ class ZeRO_Adam_Offload(_AdamBase):
             self.grad_cpu = torch.empty(self.n, dtype=dtype, pin_memory=self.device.type == "cuda")
             self.grad_dtype = dtype
 
-    def _cpu_adam(self, lo: int, hi: int, lr: float, gmul: float):
+    def _cpu_adam(self, lo: int, hi: int, lr: float, gmul: float, step: int | None = None):
         g = self.grad_cpu[lo:hi]
         m, v, w, o = self.m[lo:hi], self.v[lo:hi], self.master_weight_shard[lo:hi], self.out_cpu[lo:hi]
-        m_corr = 1.0 / (1.0 - self.beta1 ** self.t)
-        v_corr = 1.0 / (1.0 - self.beta2 ** self.t)
+        step = self.t if step is None else step
+        m_corr = 1.0 / (1.0 - self.beta1 ** step)
+        v_corr = 1.0 / (1.0 - self.beta2 ** step)
         if self._lib is not None and g.dtype in (torch.bfloat16, torch.float32) and o.dtype in (torch.bfloat16, torch.float32):
             rc = self._lib.b200_cpu_adamw(
                 ctypes.c_void_p(g.data_ptr()), int(g.dtype == torch.float32), ctypes.c_void_p(m.data_ptr()),
@@ -234,7 +238,88 @@ class ZeRO_Adam_Offload(_AdamBase):
         self.v.zero_()
         self.t = 0
 
+    # ------------------------------------------------------------------ delayed parameter update
+    def update_async(self, grad_shard, scale: float, is_main_device: bool = True, stats=None,
+                     max_grad_norm: float = 0.0):
+        """Start this step's update in the background and return at once: a snapshot of the gradient shard is
+        taken on the device, a worker thread moves it to the host, runs the C++ AdamW and sends the new bf16
+        parameters into a device staging buffer. ``finish_pending(out_shard)`` later installs them. Used for the
+        one-step delayed parameter update: the host arithmetic of step k runs under the forward and backward of
+        step k + 1, which still see the parameters of step k - 1."""
+        import threading
+        assert grad_shard.is_cuda and self._pending is None
+        lr = self._update_learning_rate()
+        if self._grad_snapshot is None or self._grad_snapshot.dtype != grad_shard.dtype:
+            self._grad_snapshot = torch.empty_like(grad_shard)
+            self._param_staging = torch.empty(self.n, dtype=self.out_cpu.dtype, device=grad_shard.device)
+        self._grad_snapshot.copy_(grad_shard)
+        stats_snap = stats.detach().clone() if stats is not None else None
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        self._ensure_grad_staging(grad_shard.dtype)
+        result = {"done": None, "applied": False, "error": None}
+        t_step = self.t
+
+        def work():
+            try:
+                torch.cuda.set_device(self.device)
+                side = self.side_stream
+                side.wait_event(ready)
+                gmul = float(scale)
+                if stats_snap is not None:
+                    with torch.cuda.stream(side):
+                        s = stats_snap.float().cpu()
+                    if float(s[1]) != 0.0:
+                        return                               # non-finite gradient: this step changes nothing
+                    if max_grad_norm > 0:
+                        gmul *= min(1.0, max_grad_norm / (math.sqrt(float(s[0])) * float(scale) + 1e-6))
+                n = self.n
+                bounds = [(lo, min(lo + self.CHUNK, n)) for lo in range(0, n, self.CHUNK)]
+                events = []
+                with torch.cuda.stream(side):
+                    for lo, hi in bounds:
+                        self.grad_cpu[lo:hi].copy_(self._grad_snapshot[lo:hi], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(side)
+                        events.append(ev)
+                saved_t, self_t = self.t, t_step
+                for (lo, hi), ev in zip(bounds, events):
+                    ev.synchronize()
+                    self._cpu_adam(lo, hi, lr, gmul, step=self_t)
+                    with torch.cuda.stream(side):
+                        self._param_staging[lo:hi].copy_(self.out_cpu[lo:hi], non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(side)
+                result["done"] = done
+                result["applied"] = True
+                del saved_t
+            except BaseException as e:       # surfaced by finish_pending on the main thread
+                result["error"] = e
+
+        th = threading.Thread(target=work, name="b200-offload-adam", daemon=True)
+        th.start()
+        self._pending = (th, result)
+        self._log_lr(is_main_device)
+
+    def finish_pending(self, out_shard=None) -> bool:
+        """Wait for the background update (if one is running) and copy its parameters into ``out_shard``.
+        Returns True when parameters were installed."""
+        if self._pending is None:
+            return False
+        th, result = self._pending
+        self._pending = None
+        th.join()
+        if result["error"] is not None:
+            raise result["error"]
+        if not result["applied"]:
+            return False
+        torch.cuda.current_stream(self.device).wait_event(result["done"])
+        if out_shard is not None:
+            out_shard.copy_(self._param_staging)
+        return True
+
     def state_dict(self) -> dict:
+        self.finish_pending(None)
         return {"m": self.m, "v": self.v, "w_fp32": self.master_weight_shard, "t": self.t}
 
     def load_state_dict(self, sd: dict):

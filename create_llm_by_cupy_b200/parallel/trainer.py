@@ -43,7 +43,8 @@ class Trainer:
                  max_grads: float = 1.0, GradScale_dic: dict | None = None, logger=None, fused=None,
                  profile_comm: bool = False, param_path: str | None = None, fused_adam: bool = False,
                  profile_phases: bool = False, adam_overlap: bool = True, cuda_graph: bool = False,
-                 defer_host_read: bool = False, adam_overlap_ctas_per_sm: int = 2):
+                 defer_host_read: bool = False, adam_overlap_ctas_per_sm: int = 2,
+                 offload_delayed_update: bool = False):
         self.rank, self.world_size = rank, world_size
         self.profile_phases = bool(profile_phases)
         self._phase_marks = []
@@ -71,6 +72,13 @@ class Trainer:
         # bf16 has fp32's exponent range: loss scaling is kept for API parity and off by default
         self.scaler = ScaleGrad(gs.get("StartScale", 10.0), gs.get("UpRate", 2.0), gs.get("DownRate", 0.7),
                                 gs.get("Scale_Up_Step"), enabled=bool(gs.get("enabled", False)))
+        # Host-offloaded optimizer with a one-step delayed parameter update (the scheme of ZeRO-Offload): the host
+        # AdamW of step k runs in a worker thread under the forward and backward of step k + 1, which still use
+        # the parameters of step k - 1; its result is installed before step k + 2. The step then costs
+        # max(GPU work, host AdamW) instead of their sum, at the price of gradients computed on parameters that
+        # are one update old. Off by default (the update is then exact and on the critical path).
+        self.offload_delayed_update = bool(offload_delayed_update and optimizer_device == "cpu"
+                                           and self.device.type == "cuda" and self.replica_optimizer is None)
         self.iteration = 0
         self.last = {}
         # Deferred host read: the loss and the gradient statistics of step k are copied to pinned host
@@ -225,6 +233,12 @@ class Trainer:
         ev.synchronize()
         return self._account(slot.tolist(), n_micro, step_scale, scale, it)
 
+    def flush_delayed_update(self):
+        """Install a delayed host update that is still in flight (before anything reads the parameters for
+        another purpose than the next training step: checkpoint, validation, generation, the end of a run)."""
+        if self.offload_delayed_update and self.optimizer.finish_pending(self.manager.get_param_shard_view()):
+            self.manager.after_optimizer_step()
+
     def flush_host_read(self) -> dict:
         """Scalars of the most recent step (waits for it when the read was deferred)."""
         if self._pending_read is not None:
@@ -296,6 +310,11 @@ class Trainer:
                     self._adam_done.record(self._adam_stream)
                 native.lib().b200_adamw_max_blocks(prev)
                 stats_in.record_stream(self._adam_stream)
+            elif self.offload_delayed_update:
+                # install the update that has been running under this step, then start this step's
+                self.optimizer.finish_pending(mgr.get_param_shard_view())
+                self.optimizer.update_async(mgr.grad_shard_f16, step_scale, self.rank == 0, stats=stats,
+                                            max_grad_norm=self.max_grads)
             elif not self.fused_adam:
                 self.optimizer.update(mgr.grad_shard_f16, step_scale, self.rank == 0,
                                       out_shard=mgr.get_param_shard_view(), stats=stats,
@@ -319,6 +338,7 @@ class Trainer:
     @torch.no_grad()
     def validate(self, batches) -> float:
         """Mean validation loss over ``batches`` and over ranks (model/ZeRO3.py:388-449 intent)."""
+        self.flush_delayed_update()
         tot = torch.zeros(1, dtype=torch.float32, device=self.device)
         for (x, t, x_pa) in batches:
             tot += self.model.predict(x, t, x_pa, self.manager).float()
@@ -330,6 +350,7 @@ class Trainer:
 
     def generate(self, prompt, **kw):
         """Generation on a sharded model: gather everything, decode, release."""
+        self.flush_delayed_update()
         self.join_optimizer()
         self.manager.materialize_all()
         try:
@@ -339,6 +360,7 @@ class Trainer:
 
     # ------------------------------------------------------------------ checkpoint
     def save(self, directory: str, extra: dict | None = None):
+        self.flush_delayed_update()
         self.flush_host_read()
         gen = getattr(self.model, "_gen", None)
         state = {"iteration": self.iteration, "scaler": self.scaler.state_dict(),
@@ -379,6 +401,7 @@ class Trainer:
     def close(self):
         """Release what outlives the Python objects: the symmetric heap of the fused collectives
         (checked for overwritten guard blocks on the way out)."""
+        self.flush_delayed_update()
         self.flush_host_read()
         self.join_optimizer()
         self.manager.synchronize()

@@ -210,3 +210,31 @@ def test_pipelined_optimizer_and_cuda_graph_reproduce_the_plain_step():
         assert d.max().item() <= 2 ** -6 and d.mean().item() < 5e-5, (d.max().item(), d.mean().item())
     assert native.read_status() == (0, 0)
     assert tr_g.optimizer.t == 8 and tr_o.optimizer.t == 8
+
+
+def test_host_optimizer_exact_and_with_one_step_delayed_update():
+    """Host-offloaded AdamW: the exact form follows the GPU optimizer; with the delayed parameter update the host
+    arithmetic of step k runs under step k + 1, so the same batch fed twice gives the same loss twice (the
+    parameters of step k - 1 are still in place) and the update shows one step later."""
+    md = dict(CFG1, dtype="bf16", half_float=True)
+    hp = dict(lr_max=2e-3, lr_mini=2e-4, weight_decay=0.1, warm_up=0, total_steps=10, beta1=0.9, beta2=0.95,
+              epsilon=1e-6, max_grads=1.0)
+    x, t, pa = (v.cuda() for v in data(1)[0])
+    runs = {}
+    for name, kw in (("gpu", dict(optimizer_device="gpu", adam_overlap=False)),
+                     ("cpu", dict(optimizer_device="cpu")),
+                     ("delayed", dict(optimizer_device="cpu", offload_delayed_update=True))):
+        tr = Trainer(md, device="cuda", **hp, **kw)
+        losses = [tr.train_step([(x, t, pa)])["loss"] for _ in range(4)]
+        tr.flush_delayed_update()
+        tr.manager.synchronize()
+        runs[name] = (losses, tr.manager.get_param_shard_view().float().cpu().clone(), tr)
+    assert native.read_status() == (0, 0)
+    g, c, d = runs["gpu"][0], runs["cpu"][0], runs["delayed"][0]
+    for a, b in zip(g, c):
+        assert abs(a - b) < 2e-2, (g, c)
+    assert (runs["gpu"][1] - runs["cpu"][1]).abs().max().item() < 2e-2
+    assert runs["delayed"][2].offload_delayed_update
+    assert abs(d[0] - g[0]) < 1e-6 and abs(d[1] - d[0]) < 1e-6       # step 1 still sees the initial parameters
+    assert d[2] < d[0] - 1e-3 and d[3] < d[2]                        # the updates arrive one step late
+    assert abs(d[2] - g[1]) < 5e-2                                   # step 2 runs on the parameters of update 0
