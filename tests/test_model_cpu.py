@@ -205,3 +205,37 @@ def test_attention_backward_unrotate_equals_in_kernel_rope():
     assert F._ds_batch_chunk(4, 16, 2048) == 4
     assert F._ds_batch_chunk(8, 32, 4096) == cap // (32 * 4096 * 4096 * 2)
     assert F._ds_batch_chunk(8, 32, 16384) == (1 if cap >= 32 * 16384 * 16384 * 2 else 0)
+
+
+def test_reference_flash_attention_signatures():
+    """``model.flash_attention`` keeps the reference's grouped layout and argument order."""
+    from model.flash_attention import cupy_flash_gqa_backward, cupy_flash_gqa_forward, triton_flash_gqa_forward
+    from create_llm_by_cupy_b200.ops import functional as F
+
+    g = torch.Generator().manual_seed(2)
+    B, KVH, R, T, D = 2, 2, 3, 10, 8
+    Q = torch.randn(B, KVH, R, T, D, generator=g)
+    K = torch.randn(B, KVH, T, D, generator=g)
+    V = torch.randn(B, KVH, T, D, generator=g)
+    dO = torch.randn(B, KVH, R, T, D, generator=g)
+    lens = torch.tensor([10, 7], dtype=torch.int32)
+    pad = torch.zeros(B, 1, 1, T)
+    pad[1, ..., 7:] = float("-inf")
+    scale = D ** -0.5
+    O, LSE = cupy_flash_gqa_forward(Q, K, V, pad, scale, block_m=4, block_n=4)
+    assert O.shape == (B, KVH, R, T, D) and LSE.shape == (B, KVH, R, T)
+    # dense restatement in the grouped layout
+    s = torch.einsum("bgrtd,bgsd->bgrts", Q, K) * scale
+    mask = torch.ones(T, T, dtype=torch.bool).tril()[None, None, None] & (torch.arange(T)[None, :] < lens[:, None])[:, None, None, None, :]
+    s = s.masked_fill(~mask, float("-inf"))
+    torch.testing.assert_close(O, torch.einsum("bgrts,bgsd->bgrtd", torch.softmax(s, -1), V), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(LSE, torch.logsumexp(s, -1), rtol=1e-4, atol=1e-5)
+    O2, _ = triton_flash_gqa_forward(Q, K, V, lens, scale)
+    torch.testing.assert_close(O2, O)
+    Qa, Ka, Va = (t.clone().requires_grad_() for t in (Q, K, V))
+    sa = (torch.einsum("bgrtd,bgsd->bgrts", Qa, Ka) * scale).masked_fill(~mask, float("-inf"))
+    (torch.einsum("bgrts,bgsd->bgrtd", torch.softmax(sa, -1), Va) * dO).sum().backward()
+    dQ, dK, dV = cupy_flash_gqa_backward(Q, K, V, dO, O, LSE, pad, scale)
+    torch.testing.assert_close(dQ, Qa.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dK, Ka.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dV, Va.grad, rtol=1e-4, atol=1e-5)
