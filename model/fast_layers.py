@@ -21,6 +21,7 @@ def apply_rotary_pos_emb_inplace(x, cos, sin):
     x1, x2 = x[..., :d], x[..., d:]
     c, s = cos.to(torch.float32), sin.to(torch.float32)
     a, b = x1.float(), x2.float()
-    x1.copy_((a * c - b * s).to(x.dtype))
-    x2.copy_((b * c + a * s).to(x.dtype))
+    n1, n2 = a * c - b * s, b * c + a * s            # both halves from the old values before either is written
+    x1.copy_(n1.to(x.dtype))
+    x2.copy_(n2.to(x.dtype))
     return x

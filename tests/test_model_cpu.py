@@ -239,3 +239,18 @@ def test_reference_flash_attention_signatures():
     torch.testing.assert_close(dQ, Qa.grad, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(dK, Ka.grad, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(dV, Va.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_reference_rotary_helper_signatures():
+    from model.fast_layers import apply_rotary_pos_emb_inplace, precompute_freqs_cis
+    from create_llm_by_cupy_b200.ops import functional as F
+
+    cos, sin = precompute_freqs_cis(8, 6)
+    assert cos.shape == (6, 4)
+    x = torch.randn(2, 3, 6, 8, generator=torch.Generator().manual_seed(0))
+    y = apply_rotary_pos_emb_inplace(x.clone(), cos, sin)
+    # same rotation as the packed in-place kernel front end ([M, heads * D] with token-major rows)
+    buf = x.permute(0, 2, 1, 3).reshape(12, 24).clone()
+    F.rope_inplace(buf, cos, sin, 6, 3, 8)
+    torch.testing.assert_close(y, buf.view(2, 6, 3, 8).permute(0, 2, 1, 3))
+    torch.testing.assert_close(apply_rotary_pos_emb_inplace(y, cos, -sin), x, rtol=1e-5, atol=1e-6)
