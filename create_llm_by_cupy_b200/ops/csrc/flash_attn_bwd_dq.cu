@@ -8,10 +8,13 @@
 // the dQ kernel that works from Q, K, V and dO has to do (3 MMAs and a softmax-gradient pass per
 // tile instead of this kernel's one MMA).
 //
-// One CTA per (128-query tile, head, batch element): warp 0 streams dS^T and K tiles of the key tiles
-// at or below the diagonal through a 3-stage TMA ring (64 KiB per stage), warp 1 issues the MMAs into
-// a 128 x 128 fp32 accumulator in tensor memory, warps 2..5 convert and store the tile. The kernel
-// is bound by reading dS (T^2 / 2 bf16 per head) from HBM. Every wait is bounded (see ptx.cuh).
+// One CTA per (128-query tile, head, batch element): warp 0 streams dS^T and K of the keys at or below the
+// diagonal, 64 keys at a time, through a 3-stage TMA ring (32 KiB per stage), warp 1 issues the MMAs into
+// a 128 x 128 fp32 accumulator in tensor memory, warps 2..5 convert and store the tile. With 96 KiB of
+// shared memory and 128 tensor-memory columns two CTAs share an SM: one streams while the other is in its
+// prologue or stores its tile (with one 192 KiB CTA per SM those phases - about a third of a CTA's life
+// at T = 2048 - left the memory system idle). The kernel is bound by reading dS (T^2 / 2 bf16 per head)
+// from HBM. Every wait is bounded (see ptx.cuh).
 #include "common.cuh"
 #include "ptx.cuh"
 #include "flash_rope_epilogue.cuh"
@@ -20,7 +23,9 @@ namespace b200 {
 
 constexpr int DQG_THREADS = 192;
 constexpr int DQG_STAGES = 3;
-constexpr int DQG_TILE = 128 * 128 * 2;                 // 32 KiB: one dS^T tile, one K tile
+constexpr int DQG_KEYS = 64;                            // keys per stage
+constexpr int DQG_TILE = DQG_KEYS * 128 * 2;            // 16 KiB: 64 keys x 128 queries of dS^T, 64 keys x 128 d of K
+constexpr int DQG_BOX = DQG_KEYS * 64 * 2;              // 8 KiB: one TMA box, 64 keys x 64 contiguous elements
 constexpr int DQG_STAGE_BYTES = 2 * DQG_TILE;
 
 struct DqGemmParams {
@@ -44,7 +49,7 @@ struct DqGemmSmem {
 
 // kD: head dimension (128, or 64: one 64-column box of K per key tile, N = 64, 64 output columns).
 template <int kD>
-__global__ void __launch_bounds__(DQG_THREADS, 1)
+__global__ void __launch_bounds__(DQG_THREADS, 2)
 flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_constant__ CUtensorMap tmK,
                          const DqGemmParams p) {
   extern __shared__ uint8_t dqg_smem_raw[];
@@ -70,7 +75,8 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
   const int m0 = mtile * 128;
   const int T = p.T;
   const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 303) : T;
-  const int n_tiles = min(mtile + 1, (max(vlen, 1) + 127) / 128);
+  // 64-key steps: everything up to the end of the diagonal tile, cut at the valid length
+  const int n_tiles = min(2 * (mtile + 1), (max(vlen, 1) + DQG_KEYS - 1) / DQG_KEYS);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < DQG_STAGES; ++s) {
@@ -96,18 +102,18 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
         if (!mbar_wait(&empty[s], ((j / DQG_STAGES) & 1) ^ 1, abort_flag)) break;
         uint8_t* sA = smem + s * DQG_STAGE_BYTES;
         uint8_t* sK = sA + DQG_TILE;
-        mbar_expect_tx(&full[s], DQG_TILE + 128 * kD * 2);
-        // dS^T tile: key rows j * 128 .., query columns m0 .. (two boxes of 64 queries)
-        tma_load_4d(sA, &tmDS, &full[s], m0, h, j * 128, b);
-        tma_load_4d(sA + 16384, &tmDS, &full[s], m0 + 64, h, j * 128, b);
-        tma_load_4d(sK, &tmK, &full[s], 0, kvh, j * 128, b);
-        if (kD == 128) tma_load_4d(sK + 16384, &tmK, &full[s], 64, kvh, j * 128, b);
+        mbar_expect_tx(&full[s], DQG_TILE + DQG_KEYS * kD * 2);
+        // dS^T: key rows j * 64 .., query columns m0 .. (two boxes of 64 queries); K: the same key rows
+        tma_load_4d(sA, &tmDS, &full[s], m0, h, j * DQG_KEYS, b);
+        tma_load_4d(sA + DQG_BOX, &tmDS, &full[s], m0 + 64, h, j * DQG_KEYS, b);
+        tma_load_4d(sK, &tmK, &full[s], 0, kvh, j * DQG_KEYS, b);
+        if (kD == 128) tma_load_4d(sK + DQG_BOX, &tmK, &full[s], 64, kvh, j * DQG_KEYS, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // A = dS^T tile [128 keys (k) x 128 queries (m)], B = K tile [128 keys (k) x 128 d (n)]: both MN-major,
-      // 64-element chunks of the contiguous dimension 16 KiB apart, 16 key rows per k-step (2 KiB)
+      // A = dS^T [64 keys (k) x 128 queries (m)], B = K [64 keys (k) x 128 d (n)]: both MN-major, 64-element
+      // chunks of the contiguous dimension one box (8 KiB) apart, 16 key rows per k-step (2 KiB)
       constexpr uint32_t idesc = umma_idesc_bf16(128, kD, 1, 1);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -116,9 +122,9 @@ flash_bwd_dq_gemm_kernel(const __grid_constant__ CUtensorMap tmDS, const __grid_
         tc_fence_after();
         const uint32_t aA = smem_u32(smem + s * DQG_STAGE_BYTES), aK = aA + DQG_TILE;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ss(tmem_base, umma_smem_desc(aA + kk * 2048, 16384, 1024), umma_smem_desc(aK + kk * 2048, 16384, 1024),
-                       idesc, (j | kk) != 0);
+        for (int kk = 0; kk < DQG_KEYS / 16; ++kk)
+          umma_bf16_ss(tmem_base, umma_smem_desc(aA + kk * 2048, DQG_BOX, 1024),
+                       umma_smem_desc(aK + kk * 2048, DQG_BOX, 1024), idesc, (j | kk) != 0);
         umma_commit(&empty[s]);
       }
       if (ok) umma_commit(done);
@@ -174,8 +180,9 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
   if (D != 128 && D != 64) return static_cast<int>(cudaErrorInvalidValue);
   const int nt = (T + 127) / 128;
   const unsigned long long Tp = (unsigned long long)nt * 128;
-  const CUtensorMap* tds = get_tensor_map_bthd(ds, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, 128, 64);
-  const CUtensorMap* tk = get_tensor_map_bthd(k, B, T, KVH, D, ks[0], ks[1], ks[2], 128, 64);
+  const CUtensorMap* tds =
+      get_tensor_map_bthd(ds, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, DQG_KEYS, 64);
+  const CUtensorMap* tk = get_tensor_map_bthd(k, B, T, KVH, D, ks[0], ks[1], ks[2], DQG_KEYS, 64);
   if (!tds || !tk) return static_cast<int>(cudaErrorInvalidValue);
   DqGemmParams p;
   p.dq = static_cast<bf16*>(dq);

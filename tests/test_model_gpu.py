@@ -235,6 +235,8 @@ def test_host_optimizer_exact_and_with_one_step_delayed_update():
         assert abs(a - b) < 2e-2, (g, c)
     assert (runs["gpu"][1] - runs["cpu"][1]).abs().max().item() < 2e-2
     assert runs["delayed"][2].offload_delayed_update
-    assert abs(d[0] - g[0]) < 1e-6 and abs(d[1] - d[0]) < 1e-6       # step 1 still sees the initial parameters
-    assert d[2] < d[0] - 1e-3 and d[3] < d[2]                        # the updates arrive one step late
-    assert abs(d[2] - g[1]) < 5e-2                                   # step 2 runs on the parameters of update 0
+    # (the loss is summed with floating-point atomics: equal up to the order of the additions)
+    assert abs(d[0] - g[0]) < 1e-4, (d, g)
+    assert abs(d[1] - d[0]) < 1e-4, (d, g)                           # step 1 still sees the initial parameters
+    assert d[2] < d[0] - 1e-3 and d[3] < d[2], (d, g)                # the updates arrive one step late
+    assert abs(d[2] - g[1]) < 5e-2, (d, g)                           # step 2 runs on the parameters of update 0
