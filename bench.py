@@ -83,6 +83,8 @@ def main():
     ap.add_argument("--comm-blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     ap.add_argument("--bucket-elems", type=int, default=25_000_000,
                     help="largest reduce-scatter launch in elements (0: every unit's bucket is reduced in one launch)")
+    ap.add_argument("--peer-wait-s", type=float, default=0.0,
+                    help="budget of one cross-GPU wait of the fused collectives in seconds (0: the library default)")
     ap.add_argument("--adam-ctas", type=int, default=2, help="AdamW CTAs per SM while it runs beside the next forward")
     ap.add_argument("--early-flush", action="store_true",
                     help="reduce the MLP part of a block's gradient bucket before the block's backward has finished")
@@ -97,6 +99,9 @@ def main():
     real_stdout = os.dup(1)
     os.dup2(2, 1)
 
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        # before CUDA is touched: no kernel is loaded lazily while kernels that wait for a peer are in flight
+        os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     import torch
 
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -165,6 +170,8 @@ def main():
             try:
                 from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
                 kw = dict(rs_blocks=args.comm_blocks, ag_blocks=args.comm_blocks) if args.comm_blocks > 0 else {}
+                if args.peer_wait_s > 0:
+                    kw["wait_ns"] = int(args.peer_wait_s * 1e9)
                 fused = FusedCollectives(comm, device, gather_mode=args.ag, **kw)
             except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
                 if args.fused == 1:
@@ -213,17 +220,23 @@ def main():
             return trainer.train_step(batches)["loss"]
         return step
 
+    def note(msg):
+        print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     # ---- product arm: device-resident inputs, then end to end through the public API ------------------------
     trainer, fused = make_trainer(plain=False)
+    note("product arm built")
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
     ms_dev, launches, exposed, phases = timed(trainer, dev_step(trainer))
     clocks = sampler.stop() if sampler else None
+    note(f"device-resident phase done: {ms_dev:.2f} ms/step")
     last = dict(trainer.last)
     e2e = None
     if not args.no_e2e:
         ms_e2e, _, _, _ = timed(trainer, e2e_step(trainer))
+        note(f"end-to-end phase done: {ms_e2e:.2f} ms/step")
         e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": stager.h2d_bytes * accum, "d2h_bytes_per_step": 12,
                "host_read": "deferred by one step" if trainer.defer_host_read else "every step before the next"}
@@ -235,6 +248,7 @@ def main():
     copies = fused.copies if fused is not None else 0
     trainer.close()
     del trainer, fused
+    note("product arm closed")
 
     # ---- baseline arm: the framework's own plain path on the same box ---------------------------------------
     baseline = None
@@ -243,7 +257,9 @@ def main():
         gc.collect()
         torch.cuda.empty_cache()
         btr, _ = make_trainer(plain=True)
+        note("baseline arm built")
         ms_b, launches_b, exposed_b, phases_b = timed(btr, dev_step(btr))
+        note(f"baseline arm done: {ms_b:.2f} ms/step")
         native.raise_on_status()
         baseline = {"value": tokens / (ms_b / 1e3), "unit": "tokens/s", "ms_per_step": ms_b, "gpu_launches": launches_b,
                     "exposed_comm_ms_per_step": exposed_b, "phases_ms": phases_b,

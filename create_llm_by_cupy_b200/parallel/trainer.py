@@ -211,12 +211,20 @@ class Trainer:
         """One host read per step (loss, gradient statistics) and the host-side bookkeeping. With
         ``defer_host_read`` the read is of the PREVIOUS step (see the constructor); the first call then
         returns a placeholder with ``pending`` set."""
-        dev = torch.cat([loss_acc.reshape(1).float(), stats.reshape(-1)])
+        parts = [loss_acc.reshape(1).float(), stats.reshape(-1)]
+        if self.device.type == "cuda":
+            # the native status word travels with the step's scalars: a kernel that gave up a bounded wait (a peer
+            # that never arrived) ends the run at the next read instead of after minutes of stacked time-outs
+            from ..ops import native
+            parts.append(native.status_tensor(self.device)[:2].float())
+        dev = torch.cat(parts)
         self.iteration += 1
         if not self.defer_host_read:
-            return self._account(dev.tolist(), n_micro, step_scale, scale, self.iteration)
+            host = dev.tolist()
+            self._check_status(host)
+            return self._account(host, n_micro, step_scale, scale, self.iteration)
         if self._host_slots is None:
-            self._host_slots = [torch.zeros(3, dtype=torch.float32).pin_memory() for _ in range(2)]
+            self._host_slots = [torch.zeros(dev.numel(), dtype=torch.float32).pin_memory() for _ in range(2)]
         slot = self._host_slots[self._host_slot_i]
         self._host_slot_i ^= 1
         slot.copy_(dev, non_blocking=True)
@@ -228,10 +236,18 @@ class Trainer:
                     "lr": self.optimizer.current_lr, "iteration": 0, "pending": True}
         return self._read_pending(prev)
 
+    def _check_status(self, host):
+        if len(host) >= 5 and host[3] != 0.0:
+            from ..ops import native
+            raise native.NativeError(f"native kernel {int(host[4])} reported error {int(host[3])} during a training step "
+                                     f"(1: mbarrier wait timed out, 2: wait for another GPU timed out, 4: index out of range)")
+
     def _read_pending(self, rec) -> dict:
         slot, ev, n_micro, step_scale, scale, it = rec
         ev.synchronize()
-        return self._account(slot.tolist(), n_micro, step_scale, scale, it)
+        host = slot.tolist()
+        self._check_status(host)
+        return self._account(host, n_micro, step_scale, scale, it)
 
     def flush_delayed_update(self):
         """Install a delayed host update that is still in flight (before anything reads the parameters for
@@ -412,6 +428,15 @@ class Trainer:
 
 
 # ------------------------------------------------------------------------------- worker
+def prefer_eager_module_loading():
+    """Ask the CUDA runtime to load every kernel when its module is registered instead of at first launch
+    (``CUDA_MODULE_LOADING=EAGER``; call before the process touches CUDA). A multi-GPU job keeps kernels in
+    flight that wait for a peer GPU; loading a kernel lazily at its first launch can need a context-wide
+    synchronisation, and a host that sits in such a load cannot launch the kernel its peer is waiting for. Costs
+    about 3 s of start-up and 0.7 GB per process (measured); single-GPU runs keep the lazy default."""
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
+
 class InjectedFault(RuntimeError):
     pass
 
@@ -444,6 +469,8 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
     the epoch / iteration loop with logging, validation and checkpoints."""
     a = args
     use_devices = a.get("use_devices") or list(range(world_size))
+    if world_size > 1:
+        prefer_eager_module_loading()
     on_gpu = torch.cuda.is_available() and a.get("backend", None) != "gloo"
     device = "cpu"
     if on_gpu:
@@ -628,6 +655,7 @@ class TrainMultiGPU:
         import tempfile
         import torch.multiprocessing as mp
         a = self.args
+        prefer_eager_module_loading()       # inherited by the workers, which set it again before they touch CUDA
         hb_dir = a.get("heartbeat_dir") or tempfile.mkdtemp(prefix="b200_hb_")
         a["heartbeat_dir"] = hb_dir
         a.setdefault("master_port", 29500 + (os.getpid() % 2000))

@@ -957,8 +957,15 @@ class MemoryZeRO3Manager:
             if self._replica_bucket is not None:
                 self._replica_bucket.copy_(self.replica_grad_f16)        # fp32 accumulation -> bf16 bucket
                 bucket = self._replica_bucket
-            self.fused.reduce_scatter_accumulate(out, bucket, accumulate=False, stream=self.compute_stream,
-                                                 stats=self._stats, do_stats=True)
+            # On the communication stream, behind the unit reductions: two reduce-scatter kernels must never be
+            # in flight at once, they share the barrier flags (a later epoch written into a flag an earlier
+            # kernel still waits on, then overwritten by the peer's earlier epoch, leaves the later one waiting).
+            ev = self._record(self.compute_stream)
+            with self._comm_ctx():
+                self._wait(self.comm_stream, ev)
+                self.fused.reduce_scatter_accumulate(out, bucket, accumulate=False, stream=self.comm_stream,
+                                                     stats=self._stats, do_stats=True)
+            self._wait(self.compute_stream, self._record(self.comm_stream))
             self._replica_stats_fused = True
             self.bytes_reduced += (bucket.numel() - n) * bucket.element_size()
         else:

@@ -147,21 +147,38 @@ def padding_proceccing(xdata, xvalid, padding_ID: int, out=None):
 
 
 class BatchStager:
-    """Pinned host staging for one micro-batch and its asynchronous copy to the device."""
+    """Pinned host staging for micro-batches and their asynchronous copy to the device.
 
-    def __init__(self, batch_size: int, time_size: int, device):
+    A small ring of pinned buffer sets: the host may run several steps ahead of the device, so the set of
+    micro-batch i must not be rewritten before its host-to-device copy has executed. Every set carries the event
+    of its last copy, and the host waits for that event (normally long past) before it reuses the set."""
+
+    def __init__(self, batch_size: int, time_size: int, device, depth: int = 4):
         self.device = torch.device(device)
         pin = self.device.type == "cuda"
-        self.host = (torch.empty((batch_size, time_size), dtype=torch.int32, pin_memory=pin),
-                     torch.empty((batch_size, time_size), dtype=torch.int32, pin_memory=pin),
-                     torch.empty((batch_size,), dtype=torch.int32, pin_memory=pin))
+
+        def make():
+            return (torch.empty((batch_size, time_size), dtype=torch.int32, pin_memory=pin),
+                    torch.empty((batch_size, time_size), dtype=torch.int32, pin_memory=pin),
+                    torch.empty((batch_size,), dtype=torch.int32, pin_memory=pin))
+        self.ring = [[make(), None] for _ in range(max(int(depth), 1) if pin else 1)]
+        self.pos = 0
+        self.host = self.ring[0][0]
         self.h2d_bytes = sum(t.numel() * t.element_size() for t in self.host)
 
     def stage(self, xdata, xvalid, padding_ID: int):
-        padding_proceccing(xdata, xvalid, padding_ID, out=self.host)
+        slot = self.ring[self.pos]
+        self.pos = (self.pos + 1) % len(self.ring)
+        host, ev = slot
+        if ev is not None:
+            ev.synchronize()                     # the copy that last read this set has run
+        padding_proceccing(xdata, xvalid, padding_ID, out=host)
         if self.device.type != "cuda":
-            return tuple(t.clone() for t in self.host)
-        return tuple(t.to(self.device, non_blocking=True) for t in self.host)
+            return tuple(t.clone() for t in host)
+        out = tuple(t.to(self.device, non_blocking=True) for t in host)
+        slot[1] = torch.cuda.Event()
+        slot[1].record(torch.cuda.current_stream(self.device))
+        return out
 
 
 class SplitDataset:

@@ -5,6 +5,8 @@ import sys
 
 sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(__file__), "..")))
 
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")     # see parallel.trainer.prefer_eager_module_loading
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
