@@ -149,7 +149,7 @@ def main():
     # distinct synthetic batches per rank and per step (seed 0 stream, partitioned by rank)
     ids = synthetic_token_stream(n_steps_total * accum * B * world, T, c["vocab_size"], "train", pad, low=1)
     ids = ids[rank::world]
-    stager = BatchStager(B, T, device)
+    stager = BatchStager(B, T, device, depth=max(4, 2 * accum))
     vl = np.full(B, T, dtype=np.int32)
 
     def host_batch(i):

@@ -529,7 +529,7 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
         tr_ids, tr_vl = shard_for_rank(*ds.train, rank, world_size)
         va_ids, va_vl = shard_for_rank(*ds.val, rank, world_size)
         gen_ids, gen_vl = ds.gen
-        stager = BatchStager(B, T, device)
+        stager = BatchStager(B, T, device, depth=max(4, 2 * accum))      # the host stages a whole step ahead
         val_batches = None
         tokens_per_step = B * T * accum * world_size
         losses = {}
