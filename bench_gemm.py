@@ -11,6 +11,8 @@ script launches the kernel exactly (warm + 1) times, which is the form used unde
               against the GEMM followed by the activation kernel (--n is I);
   swiglu_bwd  down-projection dgrad (x @ W_out^T, N = I, K = H) whose epilogue turns d(act) into d(gate|value),
               against the GEMM followed by the activation-backward kernel;
+  delta       output-projection dgrad (dY @ W_O^T, N = heads x 128, rows = batch x 2048) whose epilogue also leaves the
+              attention backward's delta = rowsum(dO * O), against the GEMM followed by the delta kernel;
   ce          LM head (x @ W^T, N = vocabulary): statistics epilogue (no logits stored) plus merge, then the
               logit-gradient epilogue, against fp32 logits + row-statistics kernel + logit-gradient kernel.
 """
@@ -74,6 +76,24 @@ def fused_epilogue(a):
         if not a.no_ref:
             t2 = run(lambda: F.swiglu_bwd(gemm(dout, w_out, trans_b=True), gv))
             res.update(separate_ms=t2, separate_tflops=fl / t2 / 1e9)
+    elif a.epilogue == "delta":
+        T, D = 2048, 128
+        assert M % T == 0 and N % D == 0
+        dy = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        w_o = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+        o = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+        fl = 2.0 * M * N * K
+        t = run(lambda: F.gemm_delta(dy, w_o, o, T, D))
+        res.update(fused_ms=t, fused_tflops=fl / t / 1e9)
+        if not a.no_ref:
+            o4 = o.view(M // T, T, N // D, D)
+            dl = torch.empty(M // T, N // D, T, device=dev)
+
+            def sep():
+                do = gemm(dy, w_o, trans_b=True)
+                F.flash_delta(o4, do.view_as(o4), dl)
+            t2 = run(sep)
+            res.update(separate_ms=t2, separate_tflops=fl / t2 / 1e9)
     else:
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
         w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
@@ -123,7 +143,7 @@ def main():
     ap.add_argument("--warm", type=int, default=2)
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--no-ref", action="store_true")
-    ap.add_argument("--epilogue", default="none", choices=["none", "swiglu", "swiglu_bwd", "ce"])
+    ap.add_argument("--epilogue", default="none", choices=["none", "swiglu", "swiglu_bwd", "delta", "ce"])
     a = ap.parse_args()
     dev = "cuda"
     if a.epilogue != "none":

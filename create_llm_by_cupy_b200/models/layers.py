@@ -191,7 +191,14 @@ class GroupedQueryAttention:
             o, lse = self._attend(q, k, v, valid_len, tabs)
         go = grad_out if grad_out else (None, None)
         dW_O = F.wgrad_gemm(o.view(B * T, self.H), dout, out=go[1])
-        do = F.gemm(dout, self.params[1], trans_b=True)
+        delta = None
+        o2d = o.view(B * T, self.H)
+        if (F.DELTA_EPILOGUE and not self._dense and self._prerotate(x)
+                and F.gemm_delta_fusable(dout, self.params[1], o2d, T, self.D)):
+            # d(attention output) and the backward's row sums sum_d dO * O from one GEMM
+            do, delta = F.gemm_delta(dout, self.params[1], o2d, T, self.D)
+        else:
+            do = F.gemm(dout, self.params[1], trans_b=True)
         dkqv = torch.empty_like(kqv)
         dq, dk, dv = self._split(dkqv, B, T)
         if self._dense:
@@ -202,7 +209,8 @@ class GroupedQueryAttention:
         elif self._prerotate(x):
             fused = F.flash_bwd_can_unrotate(q)          # inverse RoPE in the kernels' epilogues
             F.flash_attn_bwd(do.view(B, T, self.QH, self.D), q, k, v, o, lse, valid_len=valid_len,
-                             scale=self.scale, rope=None, out=(dq, dk, dv), unrotate=tabs if fused else None)
+                             scale=self.scale, rope=None, out=(dq, dk, dv), unrotate=tabs if fused else None,
+                             delta=delta)
             if not fused:
                 F.rope_inplace(dkqv, tabs[0], tabs[1], T, self.KVH + self.QH, self.D, col0=0, inverse=True)
         else:

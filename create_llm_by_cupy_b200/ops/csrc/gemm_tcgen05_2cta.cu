@@ -63,8 +63,10 @@ enum Gemm2Flags : int { G2_OUT_F32 = 1, G2_ADD_C = 2, G2_TMA_OUT = 4, G2_WHOLE_T
 //   EPI_CE_DLOGITS LM head again: (exp(logit - lse) - onehot) * coef leaves as bf16
 //   EPI_SWIGLU_BWD D = A B^T is d(activation); the epilogue fetches the stored gate / value tiles by TMA and
 //                  leaves d(gate), d(value) (the backward of silu(gate) * value), d(activation) is never stored
+//   EPI_DELTA      D = A B^T is d(attention output) [tokens, heads x head_dim]; the epilogue also fetches the forward's
+//                  output tile by TMA and leaves delta[b, head, t] = sum_d dO O, which the attention backward needs
 enum Gemm2Epi : int {
-  EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_CE_STATS = 3, EPI_CE_DLOGITS = 4, EPI_SWIGLU_BWD = 5
+  EPI_PLAIN = 0, EPI_ROPE = 1, EPI_SWIGLU = 2, EPI_CE_STATS = 3, EPI_CE_DLOGITS = 4, EPI_SWIGLU_BWD = 5, EPI_DELTA = 6
 };
 
 struct Gemm2Params {
@@ -100,6 +102,10 @@ struct Gemm2Params {
   const float* ce_coef;      // [M] valid * gradient scale / number of valid rows
   int ce_col0, ce_nt0;       // vocabulary id of column 0; tile-column index of this call's first tile in pmax / psum
   int ce_vocab;              // size of the whole vocabulary when the caller knows it (debug build: targets are checked)
+  // EPI_DELTA: row = b * dl_T + t, column = head * dl_dim + d (dl_dim 128 or 64); the forward output O is read through
+  // the map in the tmC slot; dl_out [batch][dl_heads][dl_T] fp32.
+  float* dl_out;
+  int dl_T, dl_heads, dl_dim;
 };
 
 // A work item: tile coordinates, first column and width.
@@ -662,7 +668,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       uint32_t gcount = 0;
       auto arm = [&](uint32_t gc, int x, int y) {       // make staging tile gc & 1 ready for group gc
         const uint32_t b = gc & 1;
-        if (add_c) {
+        if (add_c || EPI == EPI_DELTA) {
           mbar_expect_tx(&stage_ready[b], G2_STG_BYTES);
           tma_load_2d(stg + b * G2_STG_BYTES, &tmC, &stage_ready[b], x, y);
         } else {
@@ -692,6 +698,7 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           ce_coef = __ldg(p.ce_coef + row);
           ce_t = __ldg(p.ce_targets + row) - p.ce_col0;
         }
+        float dl_sum = 0.f;                     // EPI_DELTA: dO . O over the head's columns seen so far
         if (elected) {
           tma_store_wait_read<1>();                      // the store that last used this staging tile has read it
           arm(gcount, n0, row0);
@@ -788,7 +795,29 @@ gemm_bf16_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               bf162* o2 = reinterpret_cast<bf162*>(&o);
 #pragma unroll
               for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+              if constexpr (EPI == EPI_DELTA) {
+                // the staging tile holds the forward output; the product uses dO as it is stored (rounded)
+                const uint4 cc = *dst;
+                const bf162* c2 = reinterpret_cast<const bf162*>(&cc);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 of = __bfloat1622float2(c2[e]), df = __bfloat1622float2(o2[e]);
+                  dl_sum = fmaf(df.x, of.x, fmaf(df.y, of.y, dl_sum));
+                }
+              }
               *dst = o;
+            }
+            if constexpr (EPI == EPI_DELTA) {
+              const int col_end = n0 + (g + 1) * 64;
+              if (col_end % p.dl_dim == 0) {                 // the head is complete
+                const int row = row0 + r;
+                const int head = col_end / p.dl_dim - 1;
+                if (row < p.M && head < p.dl_heads) {
+                  const int bi = row / p.dl_T;
+                  p.dl_out[(size_t(bi) * p.dl_heads + head) * size_t(p.dl_T) + size_t(row - bi * p.dl_T)] = dl_sum;
+                }
+                dl_sum = 0.f;
+              }
             }
           }
           fence_proxy_async_smem();
@@ -926,7 +955,7 @@ static int launch_tc2(const CUtensorMap* tA, const CUtensorMap* tB, const CUtens
   const int all_pairs = num_sms() / 2;
   // a last round that fills less than half of the pairs is run on half tiles (plain and rotary epilogues only)
   int halved = 0;
-  if (g_half_tiles && EPI <= EPI_ROPE && !(p.flags & G2_WHOLE_TILES) && whole > all_pairs) {
+  if (g_half_tiles && (EPI <= EPI_ROPE || EPI == EPI_DELTA) && !(p.flags & G2_WHOLE_TILES) && whole > all_pairs) {
     const int rem = whole % all_pairs;
     if (rem > 0 && 2 * rem <= all_pairs) halved = rem;
   }
@@ -1144,4 +1173,33 @@ B200_API int b200_gemm_bf16_2cta_swiglu_bwd(const void* DOUT, const void* WOUT, 
   const CUtensorMap* tDV = get_tensor_map_2d(static_cast<bf16*>(DGV) + I, M, I, lddgv, 128, 64, 2, SWIZZLE_128B_);
   if (!tA || !tB || !tG || !tV || !tDG || !tDV) return static_cast<int>(cudaErrorInvalidValue);
   return launch_tc2<false, false, EPI_SWIGLU_BWD>(tA, tB, tG, tDG, tDV, p, stream, tV);
+}
+
+// d(attention output) and delta in one pass: DO[M, N] (bf16) = DY W_O^T for DY [M, K] row-major and W_O [N, K] K-major,
+// where row = b * T + t and column = head * head_dim + d; the epilogue reads the forward's attention output O
+// ([M, N], pitch ldo) tile by tile through TMA and also leaves DELTA[b][head][t] = sum_d DO O (fp32, computed from DO as
+// it is stored). head_dim 128 or 64, N = heads * head_dim, M a multiple of T; every base 16-byte aligned, every pitch
+// a multiple of 8 elements. O and DO may not alias.
+B200_API int b200_gemm_bf16_2cta_delta(const void* DY, const void* WO, void* DO, const void* O, void* DELTA, int M, int N,
+                                       int K, int lda, int ldb, int lddo, int ldo, int T, int head_dim, int flags,
+                                       cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(DY) | reinterpret_cast<uintptr_t>(WO) |
+                        reinterpret_cast<uintptr_t>(DO) | reinterpret_cast<uintptr_t>(O);
+  if (K <= 0 || T <= 0 || (M % T) != 0 || (head_dim != 128 && head_dim != 64) || (N % head_dim) != 0 || DO == nullptr ||
+      O == nullptr || DELTA == nullptr || DO == O || (all & 15) != 0 || (lda % 8) != 0 || (ldb % 8) != 0 ||
+      (lddo % 8) != 0 || (ldo % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  Gemm2Params p = base_params(DO, O, M, N, K, lddo, ldo, (flags & G2_WHOLE_TILES) | G2_TMA_OUT, 1.0f);
+  p.dl_out = static_cast<float*>(DELTA);
+  p.dl_T = T;
+  p.dl_heads = N / head_dim;
+  p.dl_dim = head_dim;
+  const CUtensorMap* tA = get_tensor_map_2d(DY, M, K, lda, G2_BM, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tB = get_tensor_map_2d(WO, N, K, ldb, G2_BN / 2, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tBh = get_tensor_map_2d(WO, N, K, ldb, G2_BN / 4, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tD = get_tensor_map_2d(DO, M, N, lddo, 128, 64, 2, SWIZZLE_128B_);
+  const CUtensorMap* tO = get_tensor_map_2d(O, M, N, ldo, 128, 64, 2, SWIZZLE_128B_);
+  if (!tA || !tB || !tBh || !tD || !tO) return static_cast<int>(cudaErrorInvalidValue);
+  return launch_tc2<false, false, EPI_DELTA>(tA, tB, tBh, tD, tO, p, stream);
 }

@@ -13,7 +13,8 @@ import math
 import torch
 
 from . import native
-from .gemm import (gemm, gemm_ce_dlogits, gemm_ce_fusable, gemm_ce_stats, gemm_rope, gemm_rope_fusable,  # noqa: F401
+from .gemm import (gemm, gemm_ce_dlogits, gemm_ce_fusable, gemm_ce_stats, gemm_delta, gemm_delta_fusable,  # noqa: F401
+                   gemm_rope, gemm_rope_fusable,
                    gemm_swiglu, gemm_swiglu_bwd, gemm_swiglu_bwd_fusable, gemm_swiglu_fusable, wgrad_event,
                    wgrad_gemm, wgrad_join)
 
@@ -74,14 +75,15 @@ _fusion_defaults: dict = {}
 def set_unfused_baseline(on: bool) -> None:
     """Switch the epilogue fusions and stream overlaps off (``on``) or back to their defaults: rotary
     embedding in the K|Q|V GEMM epilogue and in the attention-backward epilogues, SwiGLU in the gate|value
-    GEMM epilogue, loss statistics / logit gradients in the LM-head GEMM epilogues, weight-gradient GEMMs on
+    GEMM epilogue, the attention backward's delta in the output projection's dgrad epilogue, loss statistics / logit gradients in the LM-head GEMM epilogues, weight-gradient GEMMs on
     a side stream. With all of them off every one of these steps is a separate kernel on one stream: the
     plain path the benchmark measures the product against."""
     from . import gemm as _g
-    global FLASH_ROPE_EPILOGUE, FLASH_ROPE_EPILOGUE_D64, SWIGLU_EPILOGUE, CE_EPILOGUE
+    global FLASH_ROPE_EPILOGUE, FLASH_ROPE_EPILOGUE_D64, SWIGLU_EPILOGUE, CE_EPILOGUE, DELTA_EPILOGUE
     if not _fusion_defaults:
         _fusion_defaults.update(rope=_g.GEMM_ROPE_EPILOGUE, wgrad=_g.WGRAD_OVERLAP, frope=FLASH_ROPE_EPILOGUE,
-                                frope64=FLASH_ROPE_EPILOGUE_D64, swiglu=SWIGLU_EPILOGUE, ce=CE_EPILOGUE)
+                                frope64=FLASH_ROPE_EPILOGUE_D64, swiglu=SWIGLU_EPILOGUE, ce=CE_EPILOGUE,
+                                delta=DELTA_EPILOGUE)
     d = _fusion_defaults
     _g.GEMM_ROPE_EPILOGUE = False if on else d["rope"]
     _g.WGRAD_OVERLAP = False if on else d["wgrad"]
@@ -89,12 +91,16 @@ def set_unfused_baseline(on: bool) -> None:
     FLASH_ROPE_EPILOGUE_D64 = False if on else d["frope64"]
     SWIGLU_EPILOGUE = False if on else d["swiglu"]
     CE_EPILOGUE = False if on else d["ce"]
+    DELTA_EPILOGUE = False if on else d["delta"]
 
 
 # SwiGLU inside the epilogue of the gate|value projection, and the loss statistics / logit gradients inside
 # the epilogues of the LM-head GEMMs (see ``gemm.gemm_swiglu`` / ``gemm.gemm_ce_stats`` / ``gemm.gemm_ce_dlogits``).
 SWIGLU_EPILOGUE = True
 CE_EPILOGUE = True
+# delta = rowsum(dO * O) of the attention backward inside the epilogue of the output projection's dgrad GEMM
+# (``gemm.gemm_delta``) instead of a pass of its own.
+DELTA_EPILOGUE = True
 
 
 def _lib():
@@ -489,6 +495,17 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     return o, lse
 
 
+def flash_delta(o: torch.Tensor, dout: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """``delta[b, h, t] = sum_d dout * o`` for [B, T, heads, D] bf16 tensors (fp32 result, [B, heads, T]): the
+    stand-alone form of what ``gemm.gemm_delta`` leaves from the output projection's dgrad epilogue."""
+    B, T, QH, D = o.shape
+    arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
+    native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
+                                         native.stream_ptr()), "flash_delta")
+    native.bump()
+    return delta
+
+
 def flash_bwd_can_unrotate(q: torch.Tensor) -> bool:
     """True when ``flash_attn_bwd(..., unrotate=...)`` applies the inverse rotary embedding inside the
     attention-backward kernels (tcgen05 path: head_dim 128, or head_dim 64 with its dS workspace) for this
@@ -502,13 +519,16 @@ def flash_bwd_can_unrotate(q: torch.Tensor) -> bool:
                 and _ds_batch_chunk(q.shape[0], q.shape[2], q.shape[1]) >= 1)
 
 
-def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None, unrotate=None):
+def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=None, out=None, unrotate=None,
+                   delta=None):
     """Gradients (dq, dk, dv) w.r.t. the UN-rotated q, k and v.
 
     ``rope=(cos, sin)``: q and k are given un-rotated and rotated on the fly. ``unrotate=(cos, sin)``: q and
     k are given ROTATED (``rope`` must be None) and dq, dk are un-rotated in the kernels' epilogues - only
     where ``flash_bwd_can_unrotate`` holds (and in the CPU restatement). ``out`` may give three
-    preallocated [B,T,heads,D] views (e.g. slices of a packed d(KQV) buffer) to write into.
+    preallocated [B,T,heads,D] views (e.g. slices of a packed d(KQV) buffer) to write into. ``delta``
+    ([B, q heads, T] fp32, ``sum_d dout * o``): already computed by the caller (``gemm.gemm_delta``); used by the
+    tcgen05 path, which otherwise computes it with a kernel of its own.
     """
     if unrotate is not None and rope is not None:
         raise ValueError("flash_attn_bwd: rope and unrotate are exclusive")
@@ -528,7 +548,11 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         dv_ = torch.empty((B, T, KVH, D), dtype=q.dtype, device=q.device)
     else:
         dq, dk_, dv_ = out
-    delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
+    have_delta = delta is not None
+    if have_delta:
+        assert delta.shape == (B, QH, T) and delta.dtype == torch.float32 and delta.is_contiguous()
+    else:
+        delta = torch.empty((B, QH, T), dtype=torch.float32, device=q.device)
     if unrotate is not None and not flash_bwd_can_unrotate(q):
         raise ValueError("flash_attn_bwd: unrotate= is only fused on the tcgen05 path (see flash_bwd_can_unrotate)")
     # Batch elements per call whose dS^T workspace stays within the limit; when not even one fits, KV-head
@@ -540,9 +564,8 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
         kc = min(KVH, _ds_batch_chunk(KVH, QH // KVH, T))       # a KV-head group holds QH / KVH query heads
     if cos is None and FLASH_TC and FLASH_TC_BWD and (D == 128 or (D == 64 and (bc >= 1 or kc >= 1))):
         # tcgen05 / TMEM kernels (q, k already rotated; dq, dk are w.r.t. the rotated tensors)
-        arr6 = (ctypes.c_longlong * 6)(*(_strides3(o) + _strides3(dout)))
-        native.check(_lib().b200_flash_delta(native.ptr(o), native.ptr(dout), native.ptr(delta), arr6, B, T, QH, D,
-                                             native.stream_ptr()), "flash_delta")
+        if not have_delta:
+            flash_delta(o, dout, delta)
         s21 = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(dout) + _strides3(dq) + _strides3(dk_) +
                _strides3(dv_))
         arr21 = (ctypes.c_longlong * 21)(*s21)
@@ -583,7 +606,7 @@ def flash_attn_bwd(dout, q, k, v, o, lse, *, valid_len=None, scale=None, rope=No
                                                   arr21, b1 - b0, T, (g1 - g0) * R, g1 - g0, D, _f(scale), native.ptr(ws),
                                                   native.ptr(ucos), native.ptr(usin), uld, native.stream_ptr()),
                          "flash_bwd_tc")
-        native.bump(1 + 2 * len(chunks))
+        native.bump(2 * len(chunks))
         return dq, dk_, dv_
     strides = (_strides3(q) + _strides3(k) + _strides3(v) + _strides3(o) + _strides3(dout) +
                _strides3(dq) + _strides3(dk_) + _strides3(dv_))

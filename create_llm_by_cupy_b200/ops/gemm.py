@@ -247,6 +247,35 @@ def gemm_swiglu_bwd(dout: torch.Tensor, w_out: torch.Tensor, gv: torch.Tensor) -
     return dgv
 
 
+def gemm_delta_fusable(dout: torch.Tensor, w_o: torch.Tensor, o: torch.Tensor, T: int, head_dim: int) -> bool:
+    """True when ``gemm_delta`` runs as one kernel (``dout`` [M, H], ``w_o`` [heads * head_dim, H], ``o`` [M, heads *
+    head_dim], bf16; M = batch * T)."""
+    if not (dout.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(dout, w_o, o)):
+        return False
+    N = w_o.shape[0]
+    return (head_dim in (64, 128) and N % head_dim == 0 and dout.shape[0] >= 256 and N >= 256 and T > 0
+            and dout.shape[0] % T == 0 and o.shape == (dout.shape[0], N))
+
+
+def gemm_delta(dout: torch.Tensor, w_o: torch.Tensor, o: torch.Tensor, T: int, head_dim: int):
+    """Gradient of the attention output and the row sums the attention backward needs, from ONE GEMM:
+    ``do = dout @ w_o^T`` [M, heads * head_dim] and ``delta[b, head, t] = sum_d do * o`` (fp32, [batch, heads, T]); the
+    epilogue reads the forward's output ``o`` tile by tile. Only where ``gemm_delta_fusable`` holds."""
+    M, K = dout.shape
+    N = w_o.shape[0]
+    assert gemm_delta_fusable(dout, w_o, o, T, head_dim)
+    do = torch.empty((M, N), dtype=torch.bfloat16, device=dout.device)
+    delta = torch.empty((M // T, N // head_dim, T), dtype=torch.float32, device=dout.device)
+    native.status_tensor()
+    _apply_dynamic()
+    rc = native.lib().b200_gemm_bf16_2cta_delta(
+        native.ptr(dout), native.ptr(w_o), native.ptr(do), native.ptr(o), native.ptr(delta), M, N, K, dout.stride(0),
+        w_o.stride(0), N, o.stride(0), T, head_dim, _whole_tiles_flag(dout.device), native.stream_ptr())
+    native.check(rc, "b200_gemm_bf16_2cta_delta")
+    native.bump()
+    return do, delta
+
+
 def gemm_ce_fusable(x: torch.Tensor, w: torch.Tensor) -> bool:
     """True when the LM-head GEMMs with the loss epilogues run for ``x`` [M, K] and ``w`` [V, K] (bf16)."""
     return bool(x.is_cuda and GEMM_IMPL == "2cta" and _tma_ok(x, w) and x.shape[0] >= 256 and w.shape[0] >= 256)

@@ -157,6 +157,28 @@ def test_gemm_with_swiglu_backward_epilogue(M, I, K):
     close(out, two, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("B,T,heads,D,K", [(1, 256, 2, 128, 64), (3, 200, 3, 128, 136), (2, 1024, 16, 128, 256),
+                                           (4, 96, 5, 64, 72), (2, 512, 12, 64, 264), (20, 512, 4, 128, 128)])
+def test_gemm_with_delta_epilogue(B, T, heads, D, K):
+    """dO = dY W_O^T and delta[b, h, t] = sum_d dO * O from one GEMM (ragged M and N, both head widths, a
+    last round of half tiles for the largest case)."""
+    M, N = B * T, heads * D
+    dy = bf(M, K, seed=51)
+    w_o = bf(N, K, scale=0.3, seed=52)
+    o = bf(M, N, seed=53)
+    assert F.gemm_delta_fusable(dy.to(DEV), w_o.to(DEV), o.to(DEV), T, D)
+    do_ref = dy.float() @ w_o.float().t()
+    do, delta = F.gemm_delta(dy.to(DEV), w_o.to(DEV), o.to(DEV), T, D)
+    torch.cuda.synchronize()
+    assert F.native.read_status() == (0, 0)
+    close(do, do_ref, rtol=1e-2, atol=1e-2)
+    assert torch.equal(do, F.gemm(dy.to(DEV), w_o.to(DEV), trans_b=True))      # same bits as the plain GEMM
+    # delta from dO as stored (bf16), like the stand-alone kernel
+    ref = (do.float().cpu().view(B, T, heads, D) * o.float().view(B, T, heads, D)).sum(-1).permute(0, 2, 1)
+    assert delta.shape == (B, heads, T)
+    close(delta, ref, rtol=2e-3, atol=2e-3, frob=1e-3)
+
+
 @pytest.mark.parametrize("M,V,K", [(256, 256, 64), (300, 1000, 136), (1024, 4096, 256), (520, 2000, 72)])
 def test_lm_head_gemms_with_loss_epilogues(M, V, K):
     """Forward: logits never stored, per-tile row statistics merged into the row's log-sum-exp and the target's
