@@ -68,6 +68,8 @@ def main():
     ap.add_argument("--ag", default="copy", choices=["nccl", "pull", "gemm", "copy"],
                     help="parameter gather with --fused: copy engines (cudaMemcpyAsync per peer slice), P2P pull "
                          "kernel, NCCL all-gather, or pulled inside the consuming GEMM")
+    ap.add_argument("--rs", default="pull", choices=["pull", "copy"],
+                    help="gradient reduce-scatter: peer loads inside the summing kernel, or copy engines + a local kernel")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the plain-path arm (vs_baseline stays null)")
     ap.add_argument("--sync-read", action="store_true", help="read the loss of every step before the next one starts")
@@ -172,7 +174,7 @@ def main():
                 kw = dict(rs_blocks=args.comm_blocks, ag_blocks=args.comm_blocks) if args.comm_blocks > 0 else {}
                 if args.peer_wait_s > 0:
                     kw["wait_ns"] = int(args.peer_wait_s * 1e9)
-                fused = FusedCollectives(comm, device, gather_mode=args.ag, **kw)
+                fused = FusedCollectives(comm, device, gather_mode=args.ag, reduce_mode=args.rs, **kw)
             except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
                 if args.fused == 1:
                     raise

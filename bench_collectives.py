@@ -11,7 +11,8 @@ calls so that nothing is served from L2):
 
   reduce_scatter  fused kernel (pull every peer's slice of the gradient bucket, fp32 sum, bf16 store,
                   sum of squares and non-finite flag) against ncclReduceScatter + the separate
-                  statistics kernel;
+                  statistics kernel; reduce_scatter_copy_engine: the peers' parts are brought into local
+                  memory by the copy engines between two barriers and the same kernel sums local memory;
   rs_adam         the same kernel in its AdamW mode (reduced gradient never stored) against
                   ncclReduceScatter + statistics + AdamW kernels;
   all_gather      copy engines (one cudaMemcpyAsync per peer slice, no SM) and the pull kernel against
@@ -138,13 +139,20 @@ def main():
         fc.copy_engine = copy_engine
         fc.all_gather(full, shard)
 
+    def reduce(mode: str):
+        fc.reduce_mode = mode
+        fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=True)
+
+    fc.reserve_stage(n)
+
     adam = dict(m=m, v=v, master=master, param=shard, m_corr=1.0 / (1 - 0.9), v_corr=1.0 / (1 - 0.95),
                 grad_scale=1.0 / world, **hp)
     res = {}
     recv = (world - 1) / world * pad * 2          # bytes every rank receives over NVLink
     bound_ms = recv / (LINK_GBS * 1e9) * 1e3
     cases = [
-        ("reduce_scatter", lambda: fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=True), nccl_rs),
+        ("reduce_scatter", lambda: reduce("pull"), nccl_rs),
+        ("reduce_scatter_copy_engine", lambda: reduce("copy"), nccl_rs),
         ("rs_adam", lambda: fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=True, adam=adam), nccl_rs_adam),
         ("all_gather_copy_engine", lambda: gather(True), lambda: torch.distributed.all_gather_into_tensor(full_ref, shard)),
         ("all_gather", lambda: gather(False), lambda: torch.distributed.all_gather_into_tensor(full_ref, shard)),
@@ -164,6 +172,12 @@ def main():
     sync()
     fc.reduce_scatter_accumulate(dst, bucket, accumulate=False, stats=stats, do_stats=False)
     torch.distributed.reduce_scatter_tensor(dst_ref, bucket)
+    dst_staged = torch.empty_like(dst)
+    fc.reduce_mode = "copy"
+    fc.reduce_scatter_accumulate(dst_staged, bucket, accumulate=False, stats=stats, do_stats=False)
+    fc.reduce_mode = "pull"
+    sync()
+    res["rs_copy_engine_equals_pull"] = bool(torch.equal(dst_staged, dst))
     torch.distributed.all_gather_into_tensor(full_ref, shard)
     res["ag_equal_nccl"] = True
     for ce in (True, False):

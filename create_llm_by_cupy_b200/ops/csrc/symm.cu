@@ -25,6 +25,8 @@
 // that the multi-rank protocol can be exercised as ONE kernel on a single GPU.
 #include <string.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -99,6 +101,11 @@ struct RsParams {
   uint32_t epoch;
   unsigned long long wait_ns;
   int* status;
+  // Staged form (one real rank per launch): the peers' parts of this rank's slice have already been copied into
+  // LOCAL memory by the copy engines, peer (rank + 1 + q) % W at stage + q * stage_stride elements, element 0 of a
+  // part being element stage_first of the slice. The kernel then touches no peer memory and has no barrier.
+  const bf16* stage;
+  long long stage_stride, stage_first;
 };
 
 __device__ __forceinline__ void adam_apply(float g, float& m, float& v, float& w, const RsAdam& a) {
@@ -214,7 +221,8 @@ __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
   const int rank = p.rank0 + vr;
   const SymmTable& tab = p.tab[vr];
   const int W = p.W;
-  if (!peer_block_barrier(tab, rank, W, 0, 2 * p.epoch - 1, p.wait_ns, p.status, 201)) return;
+  const bool staged = p.stage != nullptr;
+  if (!staged && !peer_block_barrier(tab, rank, W, 0, 2 * p.epoch - 1, p.wait_ns, p.status, 201)) return;
 
   const uint4* src[SYMM_MAX_W];
 #pragma unroll
@@ -223,6 +231,10 @@ __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
     const int peer = (rank + 1 + q) % W;
     src[q] = reinterpret_cast<const uint4*>(static_cast<const char*>(tab.base[q < W ? peer : rank]) + p.bucket_off) +
              size_t(rank) * (p.n_slice / 8);
+    // staged: the same summation order, but the peers' parts are read from the local staging buffer (indexed like
+    // the slice: the pointer is moved back by the part's first element)
+    if (staged && q < W - 1)
+      src[q] = reinterpret_cast<const uint4*>(p.stage + size_t(q) * size_t(p.stage_stride)) - p.stage_first / 8;
   }
   float ss = 0.f;
   int bad = 0;
@@ -248,7 +260,7 @@ __global__ void __launch_bounds__(256, 2) rs_reduce_kernel(const RsParams p) {
     }
   }
   // all of this block's reads (and parameter writes) are done before peers are told so
-  peer_block_barrier(tab, rank, W, 0, 2 * p.epoch, p.wait_ns, p.status, 202);
+  if (!staged) peer_block_barrier(tab, rank, W, 0, 2 * p.epoch, p.wait_ns, p.status, 202);
 }
 
 struct AgParams {
@@ -359,7 +371,8 @@ static int symm_reduce_scatter_impl(const void* const* bases, int W, int rank0, 
                                     unsigned long long bucket_off, long long n_slice, long long range_lo,
                                     long long range_hi, void* const* dst, int dst_fp32, int mode, void* const* stats,
                                     int do_stats, void* const* adam_ptrs, const float* adam_f, unsigned int epoch,
-                                    unsigned long long wait_ns, int blocks, cudaStream_t st) {
+                                    unsigned long long wait_ns, int blocks, cudaStream_t st,
+                                    const void* stage = nullptr, long long stage_stride = 0, long long stage_first = 0) {
   if (W < 1 || W > SYMM_MAX_W || vranks < 1 || vranks > SYMM_MAX_W || (n_slice % 8) != 0 || range_lo < 0 ||
       range_hi > (long long)W * n_slice || range_lo > range_hi || ((range_lo | range_hi) % 8) != 0)
     return static_cast<int>(cudaErrorInvalidValue);
@@ -378,8 +391,9 @@ static int symm_reduce_scatter_impl(const void* const* bases, int W, int rank0, 
   p.bucket_off = bucket_off; p.n_slice = n_slice; p.rank0 = rank0; p.W = W; p.mode = mode; p.dst_fp32 = dst_fp32;
   p.range_lo = range_lo; p.range_hi = range_hi;
   p.do_stats = do_stats; p.epoch = epoch; p.wait_ns = wait_ns; p.status = status_ptr();
+  p.stage = static_cast<const bf16*>(stage); p.stage_stride = stage_stride; p.stage_first = stage_first;
   if (blocks < 1) blocks = 1;
-  if (blocks > SYMM_MAX_BLOCKS) blocks = SYMM_MAX_BLOCKS;
+  if (blocks > SYMM_MAX_BLOCKS && stage == nullptr) blocks = SYMM_MAX_BLOCKS;     // barrier slots; none when staged
   B200_PREFER_MAX_SMEM(rs_reduce_kernel);
   rs_reduce_kernel<<<dim3(blocks, vranks), 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
@@ -407,6 +421,54 @@ B200_API int b200_symm_reduce_scatter_range(const void* const* bases, int W, int
                                             int blocks, cudaStream_t st) {
   return symm_reduce_scatter_impl(bases, W, rank0, vranks, bucket_off, n_slice, range_lo, range_hi, dst, dst_fp32,
                                   mode, stats, do_stats, adam_ptrs, adam_f, epoch, wait_ns, blocks, st);
+}
+
+B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int vranks, int channel, unsigned int epoch,
+                               unsigned long long wait_ns, cudaStream_t st);
+
+// Reduce-scatter with the copy engines doing the moving: (1) barrier - every rank's bucket is complete; (2) one
+// cudaMemcpyAsync per peer brings that peer's part of THIS rank's slice into the local staging buffer; (3) barrier -
+// every rank has read what it needs, the buckets may be rewritten; (4) a local kernel sums the staged parts and the
+// rank's own part in the order of the pull kernel (bit-identical result) and stores / accumulates / applies AdamW,
+// with the statistics. No SM waits on a peer or on NVLink: the kernel of step 4 runs at HBM speed. `stage` holds
+// W - 1 parts of `stage_stride` elements (>= the rank's share of [range_lo, range_hi), a multiple of 8). `barriers`
+// 0 leaves steps 1 and 3 out (single-GPU tests that run the ranks one after the other). Channel `channel` (>= 1) with
+// epochs 2 * epoch - 1 and 2 * epoch.
+B200_API int b200_symm_reduce_scatter_staged(const void* const* bases, int W, int rank, unsigned long long bucket_off,
+                                             long long n_slice, long long range_lo, long long range_hi, void* dst,
+                                             int dst_fp32, int mode, void* stats, int do_stats, void* const* adam_ptrs,
+                                             const float* adam_f, void* stage, long long stage_stride, int barriers,
+                                             int channel, unsigned int epoch, unsigned long long wait_ns, int blocks,
+                                             cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || rank < 0 || rank >= W || (n_slice % 8) != 0 || range_lo < 0 ||
+      range_hi > (long long)W * n_slice || range_lo > range_hi || ((range_lo | range_hi) % 8) != 0 || stage == nullptr ||
+      (stage_stride % 8) != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (n_slice == 0) return 0;
+  const long long s0 = (long long)rank * n_slice;
+  const long long lo = std::min(std::max(range_lo - s0, 0ll), n_slice), hi = std::min(std::max(range_hi - s0, 0ll), n_slice);
+  if (hi - lo > stage_stride) return static_cast<int>(cudaErrorInvalidValue);
+  if (barriers) {
+    const int rc = b200_symm_barrier(bases, W, rank, 1, channel, 2 * epoch - 1, wait_ns, st);
+    if (rc != 0) return rc;
+  }
+  if (hi > lo) {
+    for (int q = 0; q < W - 1; ++q) {
+      const int peer = (rank + 1 + q) % W;
+      const char* src = static_cast<const char*>(bases[peer]) + bucket_off + size_t(s0 + lo) * 2;
+      char* d = static_cast<char*>(stage) + size_t(q) * size_t(stage_stride) * 2;
+      B200_CHECK(cudaMemcpyAsync(d, src, size_t(hi - lo) * 2, cudaMemcpyDeviceToDevice, st));
+    }
+  }
+  if (barriers) {
+    const int rc = b200_symm_barrier(bases, W, rank, 1, channel, 2 * epoch, wait_ns, st);
+    if (rc != 0) return rc;
+  }
+  if (hi <= lo) return 0;
+  void* dsts[1] = {dst};
+  void* sts[1] = {stats};
+  return symm_reduce_scatter_impl(bases, W, rank, 1, bucket_off, n_slice, range_lo, range_hi, dsts, dst_fp32, mode, sts,
+                                  do_stats, adam_ptrs, adam_f, 0, wait_ns, blocks, st, stage, stage_stride, lo);
 }
 
 static int symm_all_gather_impl(const void* const* bases, int W, int rank0, int vranks, unsigned long long shard_off,

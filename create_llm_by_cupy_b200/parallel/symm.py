@@ -151,16 +151,21 @@ class FusedCollectives:
 
     def __init__(self, comm, device, heap_bytes: int | None = None, rs_blocks: int = 64, ag_blocks: int = 64,
                  wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "copy", n_copy: int = 8,
-                 copy_min_bytes: int = 1 << 20):
+                 copy_min_bytes: int = 1 << 20, reduce_mode: str = "pull", rs_local_blocks: int = 0):
         """``gather_mode`` selects how parameter units are gathered: ``"copy"`` (one ``cudaMemcpyAsync``
         per peer slice on the communication stream: the copy engines move the unit and no SM is taken
         from the GEMMs; slices below ``copy_min_bytes`` use the pull kernel), ``"pull"`` (the P2P pull
         kernel), ``"nccl"`` (ncclAllGather) or ``"gemm"`` (transformer-block units are pulled inside the
-        first GEMM that consumes them; the other units use the pull kernel). Gradient reduction always
-        uses the fused kernel. ``heap_bytes`` None: the heap is created on the first ``reserve`` /
+        first GEMM that consumes them; the other units use the pull kernel). ``reduce_mode`` selects how
+        gradient buckets are reduced: ``"pull"`` (the fused kernel reads the peers' slices over NVLink while it
+        sums) or ``"copy"`` (the copy engines bring the peers' parts of this rank's slice into a local staging
+        buffer between two barriers and the same kernel then sums local memory only: no SM ever waits on the
+        link; parts below ``copy_min_bytes`` use the pull form). ``heap_bytes`` None: the heap is created on the first ``reserve`` /
         ``alloc`` (the ZeRO manager reserves what its layout needs)."""
         if gather_mode not in ("nccl", "pull", "gemm", "copy"):
             raise ValueError(f"unknown gather_mode {gather_mode!r}")
+        if reduce_mode not in ("pull", "copy"):
+            raise ValueError(f"unknown reduce_mode {reduce_mode!r}")
         self.comm = comm
         self.device = torch.device(device)
         self.world_size = comm.world_size
@@ -178,7 +183,14 @@ class FusedCollectives:
         self.copy_engine = gather_mode == "copy"
         self.copy_min_bytes = int(copy_min_bytes)
         self.n_copy = n_copy                # CTAs of that GEMM that copy instead of multiply
+        self.reduce_mode = reduce_mode
+        if not rs_local_blocks:
+            rs_local_blocks = (2 * torch.cuda.get_device_properties(self.device).multi_processor_count
+                               if self.device.type == "cuda" else 8)
+        self.rs_local_blocks = int(rs_local_blocks)
+        self._stage = None                  # staging buffer of the copy-engine reduce-scatter (local memory)
         self.rs_epoch = 0
+        self.stage_epoch = 0
         self.barrier_epoch = 0
         self.launches = 0                   # kernels of this module launched so far
         self.copies = 0                     # copy-engine transfers issued so far
@@ -199,6 +211,16 @@ class FusedCollectives:
 
     def alloc(self, n: int, dtype) -> torch.Tensor:
         return self.heap.alloc(n, dtype)
+
+    def reserve_stage(self, part_elems: int):
+        """Make the staging buffer of the copy-engine reduce-scatter hold W - 1 parts of ``part_elems`` bf16
+        elements (the largest share of one launch that falls into a rank's slice). Called before the first
+        collective so that no device allocation happens while peers wait in a kernel."""
+        part = (int(part_elems) + 7) // 8 * 8
+        need = part * max(self.world_size - 1, 1)
+        if self._stage is None or self._stage.numel() < need:
+            self._stage = torch.empty(need, dtype=torch.bfloat16, device=self.device)
+        return self._stage
 
     def reduce_scatter_accumulate(self, dst: torch.Tensor, bucket: torch.Tensor, accumulate: bool, stream=None,
                                   stats: torch.Tensor | None = None, do_stats: bool = False, adam: dict | None = None,
@@ -224,6 +246,24 @@ class FusedCollectives:
             adam_f = (ctypes.c_float * 8)(adam["lr"], adam["beta1"], adam["beta2"], adam["eps"], adam["weight_decay"],
                                           adam["m_corr"], adam["v_corr"], adam["grad_scale"])
         s = native.stream_ptr() if stream is None else ctypes.c_void_p(stream.cuda_stream)
+        # the rank's share of this launch; every rank computes every rank's share, so all take the same branch
+        shares = [max(0, min(hi, (r + 1) * n) - max(lo, r * n)) for r in range(self.world_size)]
+        if self.reduce_mode == "copy" and self.world_size > 1 and max(shares) * 2 >= self.copy_min_bytes:
+            part = (max(shares) + 7) // 8 * 8
+            stage = self.reserve_stage(part)
+            self.stage_epoch += 1
+            rc = self.lib.b200_symm_reduce_scatter_staged(
+                self.heap.table, self.world_size, self.rank, ctypes.c_ulonglong(self.heap.offset_of(bucket)),
+                ctypes.c_longlong(n), ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_void_p(dst.data_ptr()),
+                int(dst.dtype == torch.float32), mode, ctypes.c_void_p(stats.data_ptr() if stats is not None else 0),
+                int(do_stats), adam_ptrs, adam_f, ctypes.c_void_p(stage.data_ptr()), ctypes.c_longlong(part), 1, 2,
+                ctypes.c_uint(self.stage_epoch), ctypes.c_ulonglong(self.wait_ns), self.rs_local_blocks, s)
+            native.check(rc, "symm_reduce_scatter_staged")
+            native.bump(3 if shares[self.rank] > 0 else 2)
+            self.launches += 3 if shares[self.rank] > 0 else 2
+            if shares[self.rank] > 0:
+                self.copies += self.world_size - 1
+            return
         rc = self.lib.b200_symm_reduce_scatter_range(
             self.heap.table, self.world_size, self.rank, 1, ctypes.c_ulonglong(self.heap.offset_of(bucket)),
             ctypes.c_longlong(n), ctypes.c_longlong(lo), ctypes.c_longlong(hi), _ptr_array([dst.data_ptr()]),
@@ -329,6 +369,27 @@ class LocalVirtualRanks:
             _ptr_array([s.data_ptr() for s in stats] if stats is not None else [0] * W), int(do_stats), adam_ptrs, adam_f,
             ctypes.c_uint(self.rs_epoch), ctypes.c_ulonglong(self.wait_ns), blocks, native.stream_ptr())
         native.check(rc, "symm_reduce_scatter")
+
+    def reduce_scatter_staged(self, bucket_off: int, n_slice: int, dsts, accumulate=False, stats=None, do_stats=False,
+                              blocks: int = 8, elem_range: tuple | None = None):
+        """The copy-engine form of the reduce-scatter, the ranks one after the other on this device: per rank the
+        W - 1 staging copies and the local summing kernel, without the cross-rank barriers (nothing runs
+        concurrently here, and kernels that wait on one another may not be separate launches on one GPU)."""
+        W = self.world_size
+        lo, hi = elem_range if elem_range is not None else (0, W * n_slice)
+        part = max(max(0, min(hi, (r + 1) * n_slice) - max(lo, r * n_slice)) for r in range(W))
+        part = max((part + 7) // 8 * 8, 8)
+        stage = torch.empty(part * max(W - 1, 1), dtype=torch.bfloat16, device=self.device)
+        for r in range(W):
+            rc = self.lib.b200_symm_reduce_scatter_staged(
+                _ptr_array(self.bases), W, r, ctypes.c_ulonglong(bucket_off), ctypes.c_longlong(n_slice),
+                ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_void_p(dsts[r].data_ptr()),
+                int(dsts[r].dtype == torch.float32), 1 if accumulate else 0,
+                ctypes.c_void_p(stats[r].data_ptr() if stats is not None else 0), int(do_stats), None, None,
+                ctypes.c_void_p(stage.data_ptr()), ctypes.c_longlong(part), 0, 2, ctypes.c_uint(1),
+                ctypes.c_ulonglong(self.wait_ns), blocks, native.stream_ptr())
+            native.check(rc, "symm_reduce_scatter_staged")
+        torch.cuda.synchronize(self.device)      # the staging buffer is freed on return
 
     def all_gather(self, shard_off: int, n_slice: int, outs, blocks: int = 4):
         rc = self.lib.b200_symm_all_gather(self.tables, self.world_size, 0, self.world_size,

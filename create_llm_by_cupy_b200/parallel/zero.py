@@ -243,6 +243,14 @@ class MemoryZeRO3Manager:
         that wait for a peer) happens while such kernels are in flight: per distinct unit size two gradient
         buckets (the rotation) and as many gather buffers as are live at once (two where several units
         share the size: the unit in use and the prefetched one)."""
+        if self.fused is not None and getattr(self.fused, "reduce_mode", "pull") == "copy":
+            # staging buffer of the copy-engine reduce-scatter: the largest share of one launch in a rank's slice
+            W = self.world_size
+            part = max([u.padded // W for u in self.layout.units if not u.empty] + [8])
+            if self.grad_bucket_elems > 0:
+                part = min(part, self.grad_bucket_elems // 8 * 8)
+            part = max(part, self.layout.replica_padded_total // W)
+            self.fused.reserve_stage(part)
         count = collections.Counter(u.padded for u in self.layout.units if not u.empty)
         for n in sorted(count):
             bufs = [self.grad_pool.get(n) for _ in range(self.grad_pool.rotate)]

@@ -80,6 +80,42 @@ def test_virtual_ranks_reduce_scatter_in_sub_bucket_ranges(W):
     vr.close()
 
 
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_virtual_ranks_copy_engine_reduce_scatter_equals_the_pull_kernel(W):
+    """The staged form (copy-engine transfers of the peers' parts into local memory, then the summing kernel
+    on local memory only) gives the bits and the statistics of the pull kernel: whole bucket, element
+    ranges, bf16 store and fp32 accumulation."""
+    from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
+
+    vr = LocalVirtualRanks(W)
+    n_slice = 8 * 900 + 8
+    n = n_slice * W
+    off, buckets = vr.alloc(n, torch.bfloat16)
+    for r, b in enumerate(buckets):
+        b.copy_(torch.randn(n, generator=torch.Generator().manual_seed(70 + r)).to(torch.bfloat16))
+    pull = [torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    st_pull = [torch.zeros(2, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, pull, stats=st_pull, do_stats=True)
+    staged = [torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    st_staged = [torch.zeros(2, device="cuda") for _ in range(W)]
+    vr.reduce_scatter_staged(off, n_slice, staged, stats=st_staged, do_stats=True)
+    parts = [torch.zeros(n_slice, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    cuts = [0, 8 * 411, n_slice + 8 * 23, n]
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        vr.reduce_scatter_staged(off, n_slice, parts, elem_range=(lo, hi))
+    acc_pull = [torch.ones(n_slice, device="cuda") for _ in range(W)]
+    acc_staged = [torch.ones(n_slice, device="cuda") for _ in range(W)]
+    vr.reduce_scatter(off, n_slice, acc_pull, accumulate=True)
+    vr.reduce_scatter_staged(off, n_slice, acc_staged, accumulate=True)
+    torch.cuda.synchronize()
+    assert native.read_status() == (0, 0)
+    for r in range(W):
+        assert torch.equal(staged[r], pull[r]) and torch.equal(parts[r], pull[r])
+        assert torch.equal(acc_staged[r], acc_pull[r])
+        assert abs(st_staged[r][0].item() - st_pull[r][0].item()) <= 1e-4 * st_pull[r][0].item()
+    vr.close()
+
+
 def test_virtual_ranks_fused_adam_matches_separate_kernels():
     from create_llm_by_cupy_b200.ops import functional as F
     from create_llm_by_cupy_b200.parallel.symm import LocalVirtualRanks
@@ -200,11 +236,12 @@ def test_wait_on_a_flag_nobody_sets_times_out_with_an_error_status():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("gather", ["copy", "gemm"])
-def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path, gather):
+@pytest.mark.parametrize("gather,reduce", [("copy", "pull"), ("gemm", "pull"), ("copy", "copy")])
+def test_two_gpu_fused_training_matches_nccl_baseline(tmp_path, gather, reduce):
     """Gradient accumulation over two micro-batches; parameters gathered by the copy engines or inside
-    the first consuming GEMM."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_GATHER=gather)
+    the first consuming GEMM; gradients reduced by the pull kernel or by copy engines + the local kernel."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", B200_TEST_GATHER=gather,
+               B200_TEST_REDUCE=reduce, B200_TEST_COPY_MIN="0" if reduce == "copy" else str(1 << 20))
     script = os.path.join(os.path.dirname(__file__), "multi_gpu_worker.py")
     outs = {}
     for mode in ("nccl", "fused"):
