@@ -191,7 +191,7 @@ class FusedCollectives:
         self._stage = None                  # staging buffer of the copy-engine reduce-scatter (local memory)
         self.rs_epoch = 0
         self.stage_epoch = 0
-        self.barrier_epoch = 0
+        self.barrier_epochs = {}            # channel -> barriers issued on it so far
         self.launches = 0                   # kernels of this module launched so far
         self.copies = 0                     # copy-engine transfers issued so far
 
@@ -302,10 +302,15 @@ class FusedCollectives:
         self.launches += 1
 
     def barrier(self, stream=None, channel: int = 1):
-        self.barrier_epoch += 1
+        """Cross-GPU barrier kernel on ``stream``. A channel has its own flags and its own epoch count, and all
+        barriers of one channel must be issued on ONE stream: two barrier kernels of a channel in flight at once
+        can overwrite each other's epochs in a peer's flag word (the later one then waits until its time-out).
+        Channel 1: the optimizer's stream (per-unit "slice updated"); channel 2: the communication stream (the
+        copy-engine reduce-scatter); channel 3: the compute stream (whole-step fences)."""
+        self.barrier_epochs[channel] = self.barrier_epochs.get(channel, 0) + 1
         s = native.stream_ptr() if stream is None else ctypes.c_void_p(stream.cuda_stream)
         rc = self.lib.b200_symm_barrier(self.heap.table, self.world_size, self.rank, 1, channel,
-                                        ctypes.c_uint(self.barrier_epoch), ctypes.c_ulonglong(self.wait_ns), s)
+                                        ctypes.c_uint(self.barrier_epochs[channel]), ctypes.c_ulonglong(self.wait_ns), s)
         native.check(rc, "symm_barrier")
         native.bump()
         self.launches += 1

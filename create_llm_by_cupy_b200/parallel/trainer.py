@@ -310,7 +310,7 @@ class Trainer:
 
                 def unit_done(i):
                     if mgr.fused is not None and self.world_size > 1:
-                        mgr.fused.barrier(self._adam_stream)      # peers pull this slice straight from the shard
+                        mgr.fused.barrier(self._adam_stream, channel=1)   # peers pull this slice straight from the shard
                     ev = torch.cuda.Event()
                     ev.record(self._adam_stream)
                     mgr.unit_ready[order[i]] = ev

@@ -923,7 +923,7 @@ class MemoryZeRO3Manager:
         if not self.cuda or self.world_size == 1:
             return
         if self.fused is not None:
-            self.fused.barrier(self.compute_stream)
+            self.fused.barrier(self.compute_stream, channel=3)
         self._params_ready_event = self._record(self.compute_stream)
 
     def get_param_shard_view(self):
@@ -988,7 +988,9 @@ class MemoryZeRO3Manager:
             return
         mine = self.get_replica_optimizer_shard_view()
         if self.fused is not None and self.fused.gather:
-            self.fused.barrier(self.compute_stream)       # every rank has finished writing its slice
+            # every rank has finished writing its slice (channel 3: the optimizer's stream may have its own
+            # per-unit barriers in flight on channel 1 at this moment)
+            self.fused.barrier(self.compute_stream, channel=3)
             self.fused.all_gather(self.replica_param_f16, mine, self.compute_stream)
         elif getattr(self.comm, "backend", "") == "gloo":
             self.comm.all_gather_into(self.replica_param_f16, mine.clone())

@@ -68,3 +68,53 @@ def test_missing_rank_times_out_with_an_error_status():
     errors, status, log = run(4, steps=3, absent=2, timeout_s=0.3)
     assert time.time() - t0 < 10
     assert status[2] == 0 and all(status[r] == 2 for r in (0, 1, 3)) and not log
+
+
+def test_two_streams_need_two_channels():
+    """Why every stream that issues barrier kernels has a channel of its own. Rank 0 runs barrier A (epoch 1,
+    the optimizer's stream) and barrier B (epoch 2, the compute stream) at the same time; when their signal
+    stores land in the order B, A the shared flag word ends at 1 and rank 1's barrier B can never pass, while
+    rank 1's barrier A passed before rank 0 had reached it. With one flag word per channel both are exact."""
+    # one shared flag word (what rank 1 sees from rank 0): B's store, then A's store
+    shared = 0
+    shared = 2                       # rank 0, barrier B: st.release epoch 2
+    passed_a_early = shared - 1 >= 0        # rank 1 waits in A for epoch 1 and sees 2: passes although A has not run
+    shared = 1                       # rank 0, barrier A: st.release epoch 1 overwrites the 2
+    b_can_pass = shared - 2 >= 0
+    assert passed_a_early and not b_can_pass
+    # a flag word per channel, each with its own epoch count
+    chan = {1: 0, 3: 0}
+    chan[3] = 1                      # barrier B is the first barrier of channel 3
+    a_passes_before_a = chan[1] - 1 >= 0
+    chan[1] = 1                      # barrier A is the first barrier of channel 1
+    assert not a_passes_before_a and chan[1] - 1 >= 0 and chan[3] - 1 >= 0
+
+
+def test_fused_collectives_count_epochs_per_channel():
+    """``FusedCollectives.barrier`` keeps one epoch count per channel (the kernels compare a channel's flag
+    words with that channel's count); checked on the bookkeeping alone, with the launch stubbed out."""
+    from create_llm_by_cupy_b200.parallel import symm as S
+
+    calls = []
+
+    class Lib:
+        def b200_symm_barrier(self, table, W, rank, vr, channel, epoch, wait, stream):
+            calls.append((channel, epoch.value))
+            return 0
+
+    fc = S.FusedCollectives.__new__(S.FusedCollectives)
+    fc.lib, fc.world_size, fc.rank, fc.wait_ns, fc.launches, fc.barrier_epochs = Lib(), 2, 0, 1, 0, {}
+    fc._heap = type("H", (), {"table": None})()
+
+    class St:
+        cuda_stream = 0
+
+    real_bump, real_check = S.native.bump, S.native.check
+    S.native.bump = lambda *a, **k: None
+    S.native.check = lambda rc, what: None
+    try:
+        for ch in (1, 1, 3, 1, 3, 2):
+            fc.barrier(St(), channel=ch)
+    finally:
+        S.native.bump, S.native.check = real_bump, real_check
+    assert calls == [(1, 1), (1, 2), (3, 1), (1, 3), (3, 2), (2, 1)]
