@@ -44,6 +44,9 @@ def parse():
     ap.add_argument("--gather", default="copy", choices=["copy", "pull", "gemm", "nccl"],
                     help="parameter gather with --collectives fused: copy engines, P2P pull kernel, inside the "
                          "consuming GEMM, or ncclAllGather")
+    ap.add_argument("--reduce", default="copy", choices=["copy", "pull"],
+                    help="gradient reduce-scatter with --collectives fused: copy engines + a local summing kernel, "
+                         "or the kernel that pulls the peers' slices while it sums")
     ap.add_argument("--validate-every", type=int, default=0,
                     help="validation loss and a generation sample every N iterations (0: off)")
     return ap.parse_args()
@@ -66,7 +69,7 @@ if __name__ == "__main__":
         "gqa_cache_out_value": True, "swiglu_cache_gate": True,
         "zero3_param_prefetch": True, "zero3_grad_bucket": True, "zero3_max_pending_reduces": 8,
         "grad_bucket_elems": 25_000_000, "zero3_sync_gather": False, "flash_backend": "b200",
-        "zero3_fused_collectives": a.collectives == "fused", "zero3_gather_mode": a.gather,
+        "zero3_fused_collectives": a.collectives == "fused", "zero3_gather_mode": a.gather, "zero3_reduce_mode": a.reduce,
     }
     if a.backend == "gloo":
         model_dic.update(dtype="fp32", half_float=False)

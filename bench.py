@@ -68,7 +68,7 @@ def main():
     ap.add_argument("--ag", default="copy", choices=["nccl", "pull", "gemm", "copy"],
                     help="parameter gather with --fused: copy engines (cudaMemcpyAsync per peer slice), P2P pull "
                          "kernel, NCCL all-gather, or pulled inside the consuming GEMM")
-    ap.add_argument("--rs", default="pull", choices=["pull", "copy"],
+    ap.add_argument("--rs", default="copy", choices=["pull", "copy"],
                     help="gradient reduce-scatter: peer loads inside the summing kernel, or copy engines + a local kernel")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the plain-path arm (vs_baseline stays null)")
@@ -245,7 +245,7 @@ def main():
     native.raise_on_status()
     n_par = trainer.n_params
     cuda_graph = bool(trainer.cuda_graph)
-    collectives = (f"fused reduce-scatter+stats, gather={args.ag}" if fused is not None
+    collectives = (f"fused reduce-scatter+stats ({args.rs}), gather={args.ag}" if fused is not None
                    else ("nccl" if world > 1 else "none"))
     copies = fused.copies if fused is not None else 0
     trainer.close()

@@ -151,14 +151,14 @@ class FusedCollectives:
 
     def __init__(self, comm, device, heap_bytes: int | None = None, rs_blocks: int = 64, ag_blocks: int = 64,
                  wait_ns: int = _DEFAULT_WAIT_NS, gather_mode: str = "copy", n_copy: int = 8,
-                 copy_min_bytes: int = 1 << 20, reduce_mode: str = "pull", rs_local_blocks: int = 0):
+                 copy_min_bytes: int = 1 << 20, reduce_mode: str = "copy", rs_local_blocks: int = 0):
         """``gather_mode`` selects how parameter units are gathered: ``"copy"`` (one ``cudaMemcpyAsync``
         per peer slice on the communication stream: the copy engines move the unit and no SM is taken
         from the GEMMs; slices below ``copy_min_bytes`` use the pull kernel), ``"pull"`` (the P2P pull
         kernel), ``"nccl"`` (ncclAllGather) or ``"gemm"`` (transformer-block units are pulled inside the
         first GEMM that consumes them; the other units use the pull kernel). ``reduce_mode`` selects how
         gradient buckets are reduced: ``"pull"`` (the fused kernel reads the peers' slices over NVLink while it
-        sums) or ``"copy"`` (the copy engines bring the peers' parts of this rank's slice into a local staging
+        sums) or ``"copy"`` (the default: the copy engines bring the peers' parts of this rank's slice into a local staging
         buffer between two barriers and the same kernel then sums local memory only: no SM ever waits on the
         link; parts below ``copy_min_bytes`` use the pull form). ``heap_bytes`` None: the heap is created on the first ``reserve`` /
         ``alloc`` (the ZeRO manager reserves what its layout needs)."""

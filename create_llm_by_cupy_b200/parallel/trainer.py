@@ -499,7 +499,7 @@ def training_worker_nccl_stream(rank: int, world_size: int, args: dict):
             if md.get("zero3_copy_min_bytes") is not None:       # smaller slices use the pull kernel
                 fkw["copy_min_bytes"] = int(md["zero3_copy_min_bytes"])
             fused = FusedCollectives(comm, device, gather_mode=str(md.get("zero3_gather_mode", "copy")),
-                                     reduce_mode=str(md.get("zero3_reduce_mode", "pull")), **fkw)
+                                     reduce_mode=str(md.get("zero3_reduce_mode", "copy")), **fkw)
         trainer = Trainer(md, rank=rank, world_size=world_size, comm=comm, device=device,
                           zero_stage=a.get("zero_stage", "3"), optimizer_device=a.get("optimizer_device", "gpu"),
                           accum_step=accum, lr_max=a.get("lr_max", 3e-4), lr_mini=a.get("lr_mini", 3e-5),

@@ -28,7 +28,7 @@ def main():
         from create_llm_by_cupy_b200.parallel.symm import FusedCollectives
         fused = FusedCollectives(comm, dev, heap_bytes=512 << 20, wait_ns=5_000_000_000,
                                  gather_mode=os.environ.get("B200_TEST_GATHER", "copy"),
-                                 reduce_mode=os.environ.get("B200_TEST_REDUCE", "pull"),
+                                 reduce_mode=os.environ.get("B200_TEST_REDUCE", "copy"),
                                  copy_min_bytes=int(os.environ.get("B200_TEST_COPY_MIN", str(1 << 20))))
     accum = int(os.environ.get("B200_TEST_ACCUM", "2"))
     md = dict(vocab_size=2048, hidden_size=256, layer_num=3, time_size=256, q_head=4, kv_head=2, ffn_size=688,
