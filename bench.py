@@ -70,6 +70,10 @@ def main():
                          "kernel, NCCL all-gather, or pulled inside the consuming GEMM")
     ap.add_argument("--rs", default="copy", choices=["pull", "copy"],
                     help="gradient reduce-scatter: peer loads inside the summing kernel, or copy engines + a local kernel")
+    ap.add_argument("--one-comm-stream", action="store_true",
+                    help="A/B: parameter gathers on the stream of the gradient reductions instead of their own")
+    ap.add_argument("--parallel-copies", action="store_true",
+                    help="A/B: the peer copies of a gather / reduction side by side on helper streams")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the plain-path arm (vs_baseline stays null)")
     ap.add_argument("--sync-read", action="store_true", help="read the loss of every step before the next one starts")
@@ -136,7 +140,8 @@ def main():
     md = dict(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], layer_num=c["layer_num"],
               time_size=c["time_size"], q_head=c["q_head"], kv_head=c["kv_head"], ffn_size=c["ffn_size"],
               padding_id=pad, dropout_rate=0, half_float=True, dtype="bf16", tie_embeddings=True, init_std=0.02,
-              seed=0, grad_bucket_elems=args.bucket_elems, zero3_early_bucket_flush=args.early_flush)
+              seed=0, grad_bucket_elems=args.bucket_elems, zero3_early_bucket_flush=args.early_flush,
+              zero3_gather_stream=not args.one_comm_stream)
     if c["zero"] == "2.5":
         md.update(zero25_replica_ratio=0.5, zero25_replica_policy="largest_first")
     if args.keep_params:
@@ -175,6 +180,8 @@ def main():
                 if args.peer_wait_s > 0:
                     kw["wait_ns"] = int(args.peer_wait_s * 1e9)
                 fused = FusedCollectives(comm, device, gather_mode=args.ag, reduce_mode=args.rs, **kw)
+                if args.parallel_copies:
+                    fused.lib.b200_symm_parallel_copies(1)
             except Exception as e:  # the NCCL path is the fallback only when the fused runtime cannot start
                 if args.fused == 1:
                     raise

@@ -92,6 +92,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--virtual", type=int, default=0)
+    ap.add_argument("--parallel-copies", action="store_true", help="peer copies side by side on helper streams (A/B)")
     ap.add_argument("--blocks", type=int, default=0, help="CTAs of the fused collective kernels (0: default)")
     args = ap.parse_args()
     if args.virtual:
@@ -104,6 +105,8 @@ def main():
     comm = init_distributed(rank, world, backend="nccl", device_id=local, master_port=int(os.environ["MASTER_PORT"]))
     kw = dict(rs_blocks=args.blocks, ag_blocks=args.blocks) if args.blocks > 0 else {}
     fc = FusedCollectives(comm, dev, heap_bytes=2 << 30, **kw)
+    if args.parallel_copies:
+        fc.lib.b200_symm_parallel_copies(1)
     total = sum(SIZES)
     pad = (total + world * 128 - 1) // (world * 128) * (world * 128)
     n = pad // world

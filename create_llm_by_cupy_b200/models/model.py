@@ -204,6 +204,7 @@ class Cupa_ver4:
         self.zero3_fused_collectives = bool(g("zero3_fused_collectives", True))
         self.zero3_gather_mode = str(g("zero3_gather_mode", "copy"))
         self.zero3_reduce_mode = str(g("zero3_reduce_mode", "copy"))
+        self.zero3_gather_stream = bool(g("zero3_gather_stream", True))
         self.grad_bucket_elems = int(g("grad_bucket_elems", 25_000_000))
         self.zero3_early_bucket_flush = bool(g("zero3_early_bucket_flush", False))
         backend = str(g("flash_backend", "b200"))

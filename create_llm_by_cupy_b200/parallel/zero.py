@@ -182,8 +182,14 @@ class MemoryZeRO3Manager:
         if self.cuda:
             self.compute_stream = stream if stream is not None else torch.cuda.current_stream(self.device)
             self.comm_stream = torch.cuda.Stream(device=self.device) if self.world_size > 1 else self.compute_stream
+            # Parameter gathers that do not go through NCCL get a stream of their own: a prefetch then never
+            # queues behind a gradient reduction (they touch different buffers and the gathers have no barrier
+            # kernel). NCCL collectives stay on one stream: a communicator wants one issue order on every rank.
+            own = (self.world_size > 1 and fused is not None and fused.gather
+                   and bool(getattr(model, "zero3_gather_stream", True)))
+            self.gather_stream = torch.cuda.Stream(device=self.device) if own else self.comm_stream
         else:
-            self.compute_stream = self.comm_stream = None
+            self.compute_stream = self.comm_stream = self.gather_stream = None
 
         self._tag_model_param_indices()
         self._build_layout()
@@ -366,6 +372,11 @@ class MemoryZeRO3Manager:
             return torch.cuda.stream(self.comm_stream)
         return _NullCtx()
 
+    def _gather_ctx(self):
+        if self.cuda and self.gather_stream is not self.compute_stream:
+            return torch.cuda.stream(self.gather_stream)
+        return _NullCtx()
+
     # ------------------------------------------------------------------ parameter gather
     def _unit_ids(self, modules):
         seen, out = set(), []
@@ -405,28 +416,28 @@ class MemoryZeRO3Manager:
                 esz = b.t.element_size()
                 region = ag_region((unit.padded // self.world_size) * esz, self.world_size, slot.offset * esz,
                                    slot.size * esz)
-                with self._comm_ctx():
-                    self._wait(self.comm_stream, b.free_event)
-                    self._wait(self.comm_stream, ready)
-                    self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.comm_stream, skip=region)
-                    rest_ready = self._record(self.comm_stream)
+                with self._gather_ctx():
+                    self._wait(self.gather_stream, b.free_event)
+                    self._wait(self.gather_stream, ready)
+                    self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.gather_stream, skip=region)
+                    rest_ready = self._record(self.gather_stream)
                 self.bytes_gathered += (unit.padded - unit.padded // self.world_size) * esz
             b.ready_event = None
             self.pending_gather[uid] = b
             self.deferred[uid] = _PendingGather(self, uid, b, pidx, region, rest_ready)
             return
-        with self._comm_ctx():
-            self._wait(self.comm_stream, b.free_event)
-            self._wait(self.comm_stream, self.unit_ready.get(uid, self._params_ready_event))
+        with self._gather_ctx():
+            self._wait(self.gather_stream, b.free_event)
+            self._wait(self.gather_stream, self.unit_ready.get(uid, self._params_ready_event))
             if self.fused is not None and self.fused.gather:
-                self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.comm_stream)
+                self.fused.all_gather(b.t, self.param_shard_f16[lo:hi], self.gather_stream)
             else:
                 self.comm.all_gather_into(b.t, self.param_shard_f16[lo:hi])
-            b.ready_event = self._record(self.comm_stream)
+            b.ready_event = self._record(self.gather_stream)
         self.bytes_gathered += (unit.padded - unit.padded // self.world_size) * b.t.element_size()
         self.pending_gather[uid] = b
         if self.sync_gather and self.cuda:
-            self.comm_stream.synchronize()
+            self.gather_stream.synchronize()
 
     def _finish_gather(self, uid: int):
         if uid in self.live:
@@ -830,6 +841,8 @@ class MemoryZeRO3Manager:
         if self.cuda:
             if self.comm_stream is not self.compute_stream:
                 self.compute_stream.wait_stream(self.comm_stream)
+            if self.gather_stream is not self.compute_stream and self.gather_stream is not self.comm_stream:
+                self.compute_stream.wait_stream(self.gather_stream)
             self.compute_stream.synchronize()
 
     def end_microbatch(self):
