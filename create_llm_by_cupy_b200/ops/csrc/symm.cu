@@ -601,6 +601,31 @@ B200_API int b200_symm_all_gather_copy(const void* const* bases, int W, int rank
   return fan_copies(0, c, n, st);
 }
 
+// The copy-engine gather without the byte range [lo, hi) of the gather buffer (the consuming GEMM fills that part
+// itself while it runs): per peer slice the bytes before and after the range, at most two copies.
+B200_API int b200_symm_all_gather_copy_skip(const void* const* bases, int W, int rank, unsigned long long shard_off,
+                                            long long n_slice, int elem_bytes, void* out, unsigned long long lo,
+                                            unsigned long long hi, cudaStream_t st) {
+  if (W < 1 || W > SYMM_MAX_W || rank < 0 || rank >= W || n_slice < 0 || elem_bytes < 1 || lo > hi)
+    return static_cast<int>(cudaErrorInvalidValue);
+  const size_t bytes = size_t(n_slice) * size_t(elem_bytes);
+  if (bytes == 0) return 0;
+  for (int q = 1; q <= W; ++q) {
+    const int peer = (rank + q) % W;
+    const size_t a = size_t(peer) * bytes, b = a + bytes;
+    const char* src = static_cast<const char*>(bases[peer]) + shard_off;
+    char* dst = static_cast<char*>(out);
+    const size_t cuts[2][2] = {{a, std::min<size_t>(b, lo)}, {std::max<size_t>(a, hi), b}};
+    for (int c = 0; c < 2; ++c) {
+      if (cuts[c][1] <= cuts[c][0]) continue;
+      if (src + (cuts[c][0] - a) == dst + cuts[c][0]) continue;
+      B200_CHECK(cudaMemcpyAsync(dst + cuts[c][0], src + (cuts[c][0] - a), cuts[c][1] - cuts[c][0],
+                                 cudaMemcpyDeviceToDevice, st));
+    }
+  }
+  return 0;
+}
+
 B200_API int b200_symm_barrier(const void* const* bases, int W, int rank0, int vranks, int channel, unsigned int epoch,
                                unsigned long long wait_ns, cudaStream_t st) {
   if (W < 1 || W > SYMM_MAX_W || channel < 1 || channel >= SYMM_CHANNELS) return static_cast<int>(cudaErrorInvalidValue);

@@ -155,8 +155,9 @@ class FusedCollectives:
         """``gather_mode`` selects how parameter units are gathered: ``"copy"`` (one ``cudaMemcpyAsync``
         per peer slice on the communication stream: the copy engines move the unit and no SM is taken
         from the GEMMs; slices below ``copy_min_bytes`` use the pull kernel), ``"pull"`` (the P2P pull
-        kernel), ``"nccl"`` (ncclAllGather) or ``"gemm"`` (transformer-block units are pulled inside the
-        first GEMM that consumes them; the other units use the pull kernel). ``reduce_mode`` selects how
+        kernel), ``"nccl"`` (ncclAllGather) or ``"gemm"`` (the first GEMM that consumes a
+        transformer-block unit pulls its own weight while it runs; the rest of the unit and the other units go
+        through the copy engines). ``reduce_mode`` selects how
         gradient buckets are reduced: ``"pull"`` (the fused kernel reads the peers' slices over NVLink while it
         sums) or ``"copy"`` (the default: the copy engines bring the peers' parts of this rank's slice into a local staging
         buffer between two barriers and the same kernel then sums local memory only: no SM ever waits on the
@@ -180,7 +181,7 @@ class FusedCollectives:
         self.gather_mode = gather_mode
         self.gather = gather_mode != "nccl"
         self.gemm_fusion = gather_mode == "gemm"   # pull block units inside their first consuming GEMM
-        self.copy_engine = gather_mode == "copy"
+        self.copy_engine = gather_mode in ("copy", "gemm")     # "gemm": what the GEMM does not pull itself
         self.copy_min_bytes = int(copy_min_bytes)
         self.n_copy = n_copy                # CTAs of that GEMM that copy instead of multiply
         self.reduce_mode = reduce_mode
@@ -285,6 +286,14 @@ class FusedCollectives:
                                                     ctypes.c_ulonglong(self.heap.offset_of(shard_slice)),
                                                     ctypes.c_longlong(n), 2, ctypes.c_void_p(out.data_ptr()), s)
             native.check(rc, "symm_all_gather_copy")
+            self.copies += self.world_size - 1
+            return
+        if self.copy_engine and skip is not None and only is None and n * 2 >= self.copy_min_bytes:
+            rc = self.lib.b200_symm_all_gather_copy_skip(
+                self.heap.table, self.world_size, self.rank, ctypes.c_ulonglong(self.heap.offset_of(shard_slice)),
+                ctypes.c_longlong(n), 2, ctypes.c_void_p(out.data_ptr()), ctypes.c_ulonglong(skip[0]),
+                ctypes.c_ulonglong(skip[1]), s)
+            native.check(rc, "symm_all_gather_copy_skip")
             self.copies += self.world_size - 1
             return
         if skip is None and only is None:
