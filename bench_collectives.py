@@ -81,9 +81,16 @@ def run_virtual(W: int):
     sync = torch.cuda.synchronize
     rs = median_ms(lambda: vr.reduce_scatter(boff, n, dsts, stats=stats, do_stats=True, blocks=64 // W), flush, sync)
     ag = median_ms(lambda: vr.all_gather(soff, n, outs, blocks=64 // W), flush, sync)
+    # the copy form as ONE rank runs it: W - 1 device-to-device copies into the staging buffer, then the summing kernel
+    # on local memory (2 CTAs per SM)
+    stage = torch.empty(n * max(W - 1, 1), dtype=torch.bfloat16, device="cuda")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rs_staged = median_ms(lambda: vr.reduce_scatter_staged(boff, n, dsts, stats=stats, do_stats=True, blocks=2 * sms,
+                                                           ranks=[0], stage=stage), flush, sync)
     ref = sum(b.float().view(W, n)[0] for b in buckets)
     err = (dsts[0].float() - ref).abs().max().item()
     print(json.dumps({"mode": f"virtual{W}", "unit_bytes": pad * 2, "reduce_scatter_ms": rs, "all_gather_ms": ag,
+                      "reduce_scatter_staged_one_rank_ms": rs_staged,
                       "rs_max_err": err, "status": native.read_status()}))
     vr.close()
 

@@ -385,16 +385,20 @@ class LocalVirtualRanks:
         native.check(rc, "symm_reduce_scatter")
 
     def reduce_scatter_staged(self, bucket_off: int, n_slice: int, dsts, accumulate=False, stats=None, do_stats=False,
-                              blocks: int = 8, elem_range: tuple | None = None):
+                              blocks: int = 8, elem_range: tuple | None = None, ranks=None, stage=None):
         """The copy-engine form of the reduce-scatter, the ranks one after the other on this device: per rank the
         W - 1 staging copies and the local summing kernel, without the cross-rank barriers (nothing runs
-        concurrently here, and kernels that wait on one another may not be separate launches on one GPU)."""
+        concurrently here, and kernels that wait on one another may not be separate launches on one GPU).
+        ``ranks``: only these ranks (default all); ``stage``: a staging buffer to reuse (timing loops)."""
         W = self.world_size
         lo, hi = elem_range if elem_range is not None else (0, W * n_slice)
         part = max(max(0, min(hi, (r + 1) * n_slice) - max(lo, r * n_slice)) for r in range(W))
         part = max((part + 7) // 8 * 8, 8)
-        stage = torch.empty(part * max(W - 1, 1), dtype=torch.bfloat16, device=self.device)
-        for r in range(W):
+        own_stage = stage is None
+        if own_stage:
+            stage = torch.empty(part * max(W - 1, 1), dtype=torch.bfloat16, device=self.device)
+        assert stage.numel() >= part * max(W - 1, 1)
+        for r in (range(W) if ranks is None else ranks):
             rc = self.lib.b200_symm_reduce_scatter_staged(
                 _ptr_array(self.bases), W, r, ctypes.c_ulonglong(bucket_off), ctypes.c_longlong(n_slice),
                 ctypes.c_longlong(lo), ctypes.c_longlong(hi), ctypes.c_void_p(dsts[r].data_ptr()),
@@ -403,7 +407,8 @@ class LocalVirtualRanks:
                 ctypes.c_void_p(stage.data_ptr()), ctypes.c_longlong(part), 0, 2, ctypes.c_uint(1),
                 ctypes.c_ulonglong(self.wait_ns), blocks, native.stream_ptr())
             native.check(rc, "symm_reduce_scatter_staged")
-        torch.cuda.synchronize(self.device)      # the staging buffer is freed on return
+        if own_stage:
+            torch.cuda.synchronize(self.device)      # the staging buffer is freed on return
 
     def all_gather(self, shard_off: int, n_slice: int, outs, blocks: int = 4):
         rc = self.lib.b200_symm_all_gather(self.tables, self.world_size, 0, self.world_size,
