@@ -484,13 +484,39 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const int m0 = (d.i_first + it % d.n_qt) * FKV_BQ;
         if (!mbar_wait(&q_empty[s], ((g / FKV_ST) & 1) ^ 1, abort_flag)) { ok = false; break; }
         float* st = reinterpret_cast<float*>(smem + FdkvSmem::kStats + s * 2 * FKV_BQ * 4);
-        for (int r = lane; r < FKV_BQ; r += 32) {
-          const int row = m0 + r;
+        float lv[FKV_BQ / 32], dv[FKV_BQ / 32];      // every load in flight before the first store
+#pragma unroll
+        for (int j = 0; j < FKV_BQ / 32; ++j) {
+          const int row = m0 + lane + 32 * j;
           const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
-          st[r] = (row < T) ? p.lse[idx] * kFbLog2e : INFINITY;     // +inf => P = 0 for rows past T
-          st[FKV_BQ + r] = (row < T) ? p.delta[idx] * p.scale : 0.f;
+          lv[j] = __ldg(p.lse + idx);
+          dv[j] = __ldg(p.delta + idx);
+        }
+#pragma unroll
+        for (int j = 0; j < FKV_BQ / 32; ++j) {
+          const int r = lane + 32 * j;
+          st[r] = (m0 + r < T) ? lv[j] * kFbLog2e : INFINITY;       // +inf => P = 0 for rows past T
+          st[FKV_BQ + r] = (m0 + r < T) ? dv[j] * p.scale : 0.f;
         }
         mbar_arrive(&st_full[s]);
+      }
+    }
+  } else if (warp == 2) {
+    // stores the dS^T staging tiles: iteration g belongs to warpgroup g & 1 (g counts on across the passes)
+    if (lane == 0 && p.ds != nullptr) {
+      int g = 0;
+      bool ok = true;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkvPass d = dkv_pass(tile_of_pass[ps], T, R, vlen);
+        for (int it = 0; it < d.iters && ok; ++it, ++g) {
+          const int w = g & 1;
+          const int m0 = (d.i_first + it % d.n_qt) * FKV_BQ;
+          if (!mbar_wait(&stg_full[w], (g >> 1) & 1, abort_flag)) { ok = false; break; }
+          tma_store_4d_ds(&tmDS, smem + FdkvSmem::kStage + w * FKV_STG, m0, kvh * R + it / d.n_qt, d.n0, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(&stg_free[w]);
+        }
       }
     }
   } else if (warp == 1) {
@@ -632,16 +658,9 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&pds_full[s]);
-        if (ds_on) {
+        if (ds_on) {              // warp 2 stores the tile: no math warp waits for the TMA engine
           fence_proxy_async_smem();
           mbar_arrive(&stg_full[wg]);
-          if (q == 0 && lane == 0) {
-            if (!mbar_wait(&stg_full[wg], stg_uses & 1, abort_flag)) { ok = false; break; }
-            tma_store_4d_ds(&tmDS, smem + FdkvSmem::kStage + wg * FKV_STG, m0, kvh * R + it / d.n_qt, n0, b);
-            tma_store_commit();
-            tma_store_wait_read<0>();
-            mbar_arrive(&stg_free[wg]);
-          }
           ++stg_uses;
         }
       }
@@ -686,6 +705,446 @@ flash_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   }
 }
 
+// =================================================================== dK, dV with 128-query iterations
+// The same work with a different schedule (head_dim 128). A tcgen05.mma of 64 columns costs about 62 clocks
+// where its arithmetic needs 32, one of 128 columns about 78 for 64 (measured with back-to-back instructions),
+// so the score products want N = 128. S^T and dP^T of a 128-query tile then take 128 tensor-memory columns
+// each, which with the two 128-column accumulators is all there is: nothing is double-buffered. Instead the
+// five products of consecutive iterations are interleaved so that the tensor pipe always has one to run while
+// the math warps work on another:
+//     tensor pipe:   dV(i)   S^T(i+1)   | dK(i)    dP^T(i+1) | dV(i+1) ...
+//     math warps :   dS^T(i)            | P^T(i+1)           | dS^T(i+1) ...
+// P^T(i) overwrites S^T(i) in place and is consumed by dV(i) before S^T(i+1) is written (the pipe runs the
+// products in issue order); dS^T(i) overwrites dP^T(i) and is consumed by dK(i) before dP^T(i+1). Both math
+// warpgroups work on every iteration, warpgroup w on query columns [64 w, 64 w + 64) of the tile: a thread owns
+// one key row, computes P for its 64 columns, keeps it (packed bf16) in registers and forms dS from it when dP^T
+// is there. Its packed columns go to the first 32 columns of its own 64 (columns [0, 32) and [64, 96) of the
+// tile hold P^T: every k-step of the gradient products names its A address, so the gap does not matter).
+constexpr int FKW_BQ = 128;                      // query rows per iteration
+constexpr int FKW_TILE = FKW_BQ * FB_D * 2;      // 32 KiB
+struct FdkwSmem {
+  static constexpr int kK = 0, kV = FB_TILE, kQ = 2 * FB_TILE;             // stage s: Q_i (32 KiB), dO_i (32 KiB)
+  static constexpr int kStage = kQ + 2 * 2 * FKW_TILE;                      // [2] dS^T staging tiles (one per warpgroup)
+  static constexpr int kStats = kStage + 2 * FKV_STG;                       // stage s: lse2[128], delta * scale [128]
+  static constexpr int kBar = kStats + 2 * 2 * FKW_BQ * 4;
+  // kv_full, q_full[2], q_empty[2], st_full[2], s_full, dp_full, p_ready, ds_ready, acc_done, acc_free,
+  // stg_full[2], stg_free[2] = 17
+  static constexpr int kUsed = kBar + 17 * 8 + 16;
+  // All the shared memory of an SM: the tiles leave less than the 1 KiB a worst-case alignment of the base would
+  // take, so the kernel checks that what it needs fits behind the aligned base and reports an error otherwise.
+  static constexpr int kTotal = 232448;
+};
+static_assert(FdkwSmem::kUsed <= FdkwSmem::kTotal, "dK/dV kernel: shared memory");
+
+struct DkwPass {
+  int n0, i_first, n_qt, iters;
+};
+__device__ __forceinline__ DkwPass dkw_pass(int ntile, int T, int R, int vlen) {
+  DkwPass d;
+  d.n0 = ntile * 128;
+  d.i_first = ntile;                                          // first 128-query tile at / below the diagonal
+  d.n_qt = (T + FKW_BQ - 1) / FKW_BQ - d.i_first;
+  d.iters = (d.n0 < vlen) ? R * d.n_qt : 0;
+  return d;
+}
+
+// P^T for 16 query columns of one key row, packed to bf16 pairs; lse2 points at the 16 per-query values.
+template <bool kMask>
+__device__ __forceinline__ void fb_p_chunk(const uint32_t (&rs)[16], uint32_t (&pk)[8], float sl2, const float* lse2,
+                                           int q_base, int key, bool key_dead) {
+#pragma unroll
+  for (int e = 0; e < 16; e += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + e);
+    const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+    float pv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float pe = exp2f(fmaf(__uint_as_float(rs[e + u]), sl2, -lv[u]));
+      if (kMask) {
+        if (key_dead || key > q_base + e + u) pe = 0.f;
+      }
+      pv[u] = pe;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      const bf162 t0 = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+      pk[(e + u) >> 1] = *reinterpret_cast<const uint32_t*>(&t0);
+    }
+  }
+}
+
+// dS^T = P^T * (dP^T * scale - delta * scale) for the same 16 columns, from the packed P^T.
+__device__ __forceinline__ void fb_ds_from_p_chunk(const uint32_t (&rp)[16], const uint32_t (&pk)[8], uint32_t (&dk)[8],
+                                                   float scale, const float* dlt_s) {
+#pragma unroll
+  for (int e = 0; e < 16; e += 4) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dlt_s + e);
+    const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      const float2 pf = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pk[(e + u) >> 1]));
+      const float d0 = pf.x * fmaf(__uint_as_float(rp[e + u]), scale, -dl[u]);
+      const float d1 = pf.y * fmaf(__uint_as_float(rp[e + u + 1]), scale, -dl[u + 1]);
+      const bf162 t1 = __floats2bfloat162_rn(d0, d1);
+      dk[(e + u) >> 1] = *reinterpret_cast<const uint32_t*>(&t1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(FBT_THREADS, 1)
+flash_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                          const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                          const __grid_constant__ CUtensorMap tmDS, const FlashBwdTcParams p) {
+  constexpr int kD = FB_D;
+  extern __shared__ uint8_t fb_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fb_smem_raw) + 1023) & ~uintptr_t(1023));
+  if (smem + FdkwSmem::kUsed > fb_smem_raw + FdkwSmem::kTotal) {      // the same for every thread of every CTA
+    if (threadIdx.x == 0 && p.status != nullptr && atomicCAS(p.status, 0, int(ERR_BAD_ARGUMENT)) == 0) p.status[1] = 313;
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FdkwSmem::kBar);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;                    // [2]
+  uint64_t* q_empty = q_full + 2;                 // [2]
+  uint64_t* st_full = q_empty + 2;                // [2] statistics staged
+  uint64_t* s_full = st_full + 2;                 // S^T of the iteration is in tensor memory
+  uint64_t* dp_full = s_full + 1;                 // dP^T of the iteration is in tensor memory
+  uint64_t* p_ready = dp_full + 1;                // every math thread has written its P^T columns
+  uint64_t* ds_ready = p_ready + 1;               // ... its dS^T columns
+  uint64_t* acc_done = ds_ready + 1;              // every MMA of a pass has completed
+  uint64_t* acc_free = acc_done + 1;              // the dK / dV accumulators of a pass have been stored
+  uint64_t* stg_full = acc_free + 1;              // [2]
+  uint64_t* stg_free = stg_full + 2;              // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stg_free + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int pair, kvh, b;                               // grid mapping as in flash_bwd_dkv_tc_kernel
+  {
+    const int n_pairs = p.pairing ? (p.n_tiles + 1) / 2 : p.n_tiles;
+    const int per_chunk = n_pairs * p.KVH * p.bchunk;
+    const int chunk = int(blockIdx.x) / per_chunk, r = int(blockIdx.x) - chunk * per_chunk;
+    const int hb = p.KVH * min(p.bchunk, p.B - chunk * p.bchunk);
+    pair = r / hb;
+    kvh = (r % hb) % p.KVH;
+    b = chunk * p.bchunk + (r % hb) / p.KVH;
+  }
+  const int T = p.T;
+  const int R = p.QH / p.KVH;
+  const int vlen = p.valid_len ? checked_index(p.valid_len[b], T, p.status, 302) : T;
+  const int tile_of_pass[2] = {pair, p.pairing ? p.n_tiles - 1 - pair : pair};
+  const int n_pass = tile_of_pass[0] == tile_of_pass[1] ? 1 : 2;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); mbar_init(&st_full[s], 32); }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, 256);
+    mbar_init(ds_ready, 256);
+    mbar_init(acc_done, 1);
+    mbar_init(acc_free, 256);
+    for (int s = 0; s < 2; ++s) { mbar_init(&stg_full[s], 128); mbar_init(&stg_free[s], 1); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmDO); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDS);
+  }
+  if (warp == 2) tmem_alloc(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColST = 0, kColDPT = 128, kColDV = 256, kColDK = 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int g = 0;
+      bool ok = true;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkwPass d = dkw_pass(tile_of_pass[ps], T, R, vlen);
+        if (d.iters == 0) continue;
+        if (ps > 0) {             // K / V of the previous pass are read by its MMAs until they have all completed
+          if (!mbar_wait(acc_done, (ps - 1) & 1, abort_flag)) break;
+        }
+        mbar_expect_tx(kv_full, 2 * FB_TILE);
+        tma_load_4d(smem + FdkwSmem::kK, &tmK, kv_full, 0, kvh, d.n0, b);
+        tma_load_4d(smem + FdkwSmem::kK + 16384, &tmK, kv_full, 64, kvh, d.n0, b);
+        tma_load_4d(smem + FdkwSmem::kV, &tmV, kv_full, 0, kvh, d.n0, b);
+        tma_load_4d(smem + FdkwSmem::kV + 16384, &tmV, kv_full, 64, kvh, d.n0, b);
+        for (int it = 0; it < d.iters; ++it, ++g) {
+          const int s = g & 1;
+          const int h = kvh * R + it / d.n_qt;
+          const int m0 = (d.i_first + it % d.n_qt) * FKW_BQ;
+          if (!mbar_wait(&q_empty[s], ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sQ = smem + FdkwSmem::kQ + s * 2 * FKW_TILE;
+          uint8_t* sDO = sQ + FKW_TILE;
+          mbar_expect_tx(&q_full[s], 2 * FKW_TILE);
+          tma_load_4d(sQ, &tmQ, &q_full[s], 0, h, m0, b);
+          tma_load_4d(sQ + 16384, &tmQ, &q_full[s], 64, h, m0, b);
+          tma_load_4d(sDO, &tmDO, &q_full[s], 0, h, m0, b);
+          tma_load_4d(sDO + 16384, &tmDO, &q_full[s], 64, h, m0, b);
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // stages the per-query statistics (lse in log2 units, delta * scale) of each query tile in shared memory
+    int g = 0;
+    bool ok = true;
+    for (int ps = 0; ps < n_pass && ok; ++ps) {
+      const DkwPass d = dkw_pass(tile_of_pass[ps], T, R, vlen);
+      for (int it = 0; it < d.iters; ++it, ++g) {
+        const int s = g & 1;
+        const int h = kvh * R + it / d.n_qt;
+        const int m0 = (d.i_first + it % d.n_qt) * FKW_BQ;
+        if (!mbar_wait(&q_empty[s], ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        float* st = reinterpret_cast<float*>(smem + FdkwSmem::kStats + s * 2 * FKW_BQ * 4);
+        // all eight loads in flight before the first store: one after the other (a store to shared memory may not
+        // pass a later global load the compiler cannot tell apart from it) they cost four round trips to L2 per
+        // iteration, which made this warp the slowest part of the kernel
+        float lv[FKW_BQ / 32], dv[FKW_BQ / 32];
+#pragma unroll
+        for (int j = 0; j < FKW_BQ / 32; ++j) {
+          const int row = m0 + lane + 32 * j;
+          const size_t idx = (size_t(b) * p.QH + h) * T + min(row, T - 1);
+          lv[j] = __ldg(p.lse + idx);
+          dv[j] = __ldg(p.delta + idx);
+        }
+#pragma unroll
+        for (int j = 0; j < FKW_BQ / 32; ++j) {
+          const int r = lane + 32 * j;
+          st[r] = (m0 + r < T) ? lv[j] * kFbLog2e : INFINITY;       // +inf => P = 0 for rows past T
+          st[FKW_BQ + r] = (m0 + r < T) ? dv[j] * p.scale : 0.f;
+        }
+        mbar_arrive(&st_full[s]);
+      }
+    }
+  } else if (warp == 2) {
+    // stores the dS^T staging tiles of both warpgroups (a math warp that did this itself spent a quarter of
+    // every iteration waiting for its warpgroup and for the TMA engine, and held the next P^T back)
+    if (lane == 0 && p.ds != nullptr) {
+      uint32_t uses = 0;
+      bool ok = true;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkwPass d = dkw_pass(tile_of_pass[ps], T, R, vlen);
+        for (int it = 0; it < d.iters && ok; ++it, ++uses) {
+          const int m0 = (d.i_first + it % d.n_qt) * FKW_BQ;
+          for (int w = 0; w < 2; ++w) {
+            if (!mbar_wait(&stg_full[w], uses & 1, abort_flag)) { ok = false; break; }
+            tma_store_4d_ds(&tmDS, smem + FdkwSmem::kStage + w * FKV_STG, m0 + w * 64, kvh * R + it / d.n_qt, d.n0, b);
+            tma_store_commit();
+          }
+          if (!ok) break;
+          tma_store_wait_read<0>();
+          mbar_arrive(&stg_free[0]);
+          mbar_arrive(&stg_free[1]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, FKW_BQ, 0, 0);   // [128 keys x 128 q], K-major operands
+      constexpr uint32_t idesc_g = umma_idesc_bf16(128, kD, 0, 1);       // [128 keys x d], B MN-major
+      const uint32_t aK = smem_u32(smem + FdkwSmem::kK), aV = smem_u32(smem + FdkwSmem::kV);
+      auto stage_q = [&](int g) { return smem_u32(smem + FdkwSmem::kQ + (g & 1) * 2 * FKW_TILE); };
+      auto issue_s = [&](int g) {
+        const uint32_t aQ = stage_q(g);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;       // 128-row tiles, 64-column halves
+          umma_bf16_ss(tmem_base + kColST, umma_smem_desc(aK + off, 16, 1024), umma_smem_desc(aQ + off, 16, 1024),
+                       idesc_s, kk != 0);
+        }
+        umma_commit(s_full);
+      };
+      auto issue_dp = [&](int g) {
+        const uint32_t aDO = stage_q(g) + FKW_TILE;
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16_ss(tmem_base + kColDPT, umma_smem_desc(aV + off, 16, 1024), umma_smem_desc(aDO + off, 16, 1024),
+                       idesc_s, kk != 0);
+        }
+        umma_commit(dp_full);
+      };
+      bool ok = true;
+      int g0 = 0, kv_loads = 0;
+      for (int ps = 0; ps < n_pass && ok; ++ps) {
+        const DkwPass d = dkw_pass(tile_of_pass[ps], T, R, vlen);
+        if (d.iters > 0) {
+          if (!mbar_wait(kv_full, kv_loads & 1, abort_flag)) { ok = false; break; }
+          ++kv_loads;
+          if (!mbar_wait(&q_full[g0 & 1], (g0 >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(g0);
+          issue_dp(g0);
+          if (ps > 0) {           // the accumulators still hold the previous pass until its rows are stored
+            if (!mbar_wait(acc_free, (ps - 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
+        }
+        for (int it = 0; it < d.iters && ok; ++it) {
+          const int g = g0 + it;
+          const uint32_t aQ = stage_q(g), aDO = aQ + FKW_TILE;
+          // dV += P^T dO: A = the packed P^T columns (k-step kk: 16 queries = 8 columns; queries 64.. sit at column
+          // 64), B = dO read MN-major (16 query rows per k-step, 64-d halves 16 KiB apart)
+          if (!mbar_wait(p_ready, g & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < FKW_BQ / 16; ++kk) {
+            const uint32_t acol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;
+            umma_bf16_ts(tmem_base + kColDV, tmem_base + kColST + acol, umma_smem_desc(aDO + kk * 2048, 16384, 1024),
+                         idesc_g, (it | kk) != 0);
+          }
+          if (it + 1 < d.iters) {   // S^T of the next tile may overwrite P^T once dV has read it: issue order
+            if (!mbar_wait(&q_full[(g + 1) & 1], ((g + 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(g + 1);
+          }
+          if (!mbar_wait(ds_ready, g & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < FKW_BQ / 16; ++kk) {
+            const uint32_t acol = kk < 4 ? kk * 8 : 64 + (kk - 4) * 8;
+            umma_bf16_ts(tmem_base + kColDK, tmem_base + kColDPT + acol, umma_smem_desc(aQ + kk * 2048, 16384, 1024),
+                         idesc_g, (it | kk) != 0);
+          }
+          umma_commit(&q_empty[g & 1]);
+          if (it + 1 < d.iters) issue_dp(g + 1);
+        }
+        if (ok && d.iters == 0 && ps > 0) {
+          if (!mbar_wait(acc_free, (ps - 1) & 1, abort_flag)) { ok = false; break; }
+        }
+        if (ok) umma_commit(acc_done);
+        g0 += d.iters;
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp & 3;
+    const int wg = (warp - 4) >> 2;           // query columns [64 wg, 64 wg + 64) of every tile
+    const int half = wg;                      // dK / dV columns this warpgroup stores at the end of a pass
+    const uint32_t lane_sel = uint32_t(q * 32) << 16;
+    const float sl2 = p.scale * kFbLog2e;
+    uint8_t* stg_row = smem + FdkwSmem::kStage + wg * FKV_STG + (q * 32 + lane) * 128;
+    const uint32_t swz = uint32_t(lane & 7);
+    const bool ds_on = p.ds != nullptr;
+    const uint32_t tS = tmem_base + lane_sel + kColST + wg * 64, tP = tmem_base + lane_sel + kColDPT + wg * 64;
+    uint32_t stg_uses = 0;
+    bool ok = true;
+    int g0 = 0;
+    for (int ps = 0; ps < n_pass && ok; ++ps) {
+      const DkwPass d = dkw_pass(tile_of_pass[ps], T, R, vlen);
+      const int n0 = d.n0;
+      const int key = n0 + q * 32 + lane;
+      const bool key_dead = key >= vlen;
+      for (int it = 0; it < d.iters && ok; ++it) {
+        const int g = g0 + it, s2 = g & 1;
+        const int m0 = (d.i_first + it % d.n_qt) * FKW_BQ;
+        const int qb = m0 + wg * 64;                                     // first query column of this warpgroup
+        const float* st = reinterpret_cast<const float*>(smem + FdkwSmem::kStats + s2 * 2 * FKW_BQ * 4) + wg * 64;
+        const bool need_mask = (m0 < n0 + 128) || (n0 + 128 > vlen);     // the diagonal tile or the padded tail
+        uint32_t pk[4][8];                                               // this thread's P^T, 64 columns packed
+        uint32_t ra[16], rb[16];
+        if (!mbar_wait(&st_full[s2], (g >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(s_full, g & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        auto p_chunk = [&](const uint32_t (&rs)[16], int c) {
+          if (need_mask) fb_p_chunk<true>(rs, pk[c], sl2, st + c * 16, qb + c * 16, key, key_dead);
+          else fb_p_chunk<false>(rs, pk[c], sl2, st + c * 16, 0, 0, false);
+          tmem_st_32x32b_x8(tS + c * 8, pk[c]);
+        };
+        tmem_ld_32x32b_x16(tS, ra);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 16, rb);
+        p_chunk(ra, 0);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 32, ra);
+        p_chunk(rb, 1);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tS + 48, rb);
+        p_chunk(ra, 2);
+        tmem_ld_wait();
+        p_chunk(rb, 3);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_ready);
+        // ---- dS^T from dP^T and the kept P^T
+        if (!mbar_wait(dp_full, g & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (ds_on) {              // the store of this warpgroup's previous tile must have read the staging tile
+          if (!mbar_wait(&stg_free[wg], (stg_uses & 1) ^ 1, abort_flag)) { ok = false; break; }
+        }
+        auto ds_chunk = [&](const uint32_t (&rp)[16], int c) {
+          uint32_t dk_[8];
+          fb_ds_from_p_chunk(rp, pk[c], dk_, p.scale, st + FKW_BQ + c * 16);
+          tmem_st_32x32b_x8(tP + c * 8, dk_);
+          if (ds_on) {            // 16 queries = two 16-byte chunks of this key's 128-byte staging row
+            *reinterpret_cast<uint4*>(stg_row + ((uint32_t(2 * c) ^ swz) << 4)) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+            *reinterpret_cast<uint4*>(stg_row + ((uint32_t(2 * c + 1) ^ swz) << 4)) = make_uint4(dk_[4], dk_[5], dk_[6], dk_[7]);
+          }
+        };
+        tmem_ld_32x32b_x16(tP, ra);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tP + 16, rb);
+        ds_chunk(ra, 0);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tP + 32, ra);
+        ds_chunk(rb, 1);
+        tmem_ld_wait();
+        tmem_ld_32x32b_x16(tP + 48, rb);
+        ds_chunk(ra, 2);
+        tmem_ld_wait();
+        ds_chunk(rb, 3);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(ds_ready);
+        if (ds_on) {              // warp 2 stores the tile: no math warp waits for the TMA engine
+          fence_proxy_async_smem();
+          mbar_arrive(&stg_full[wg]);
+          ++stg_uses;
+        }
+      }
+      if (!ok) break;
+      g0 += d.iters;
+      // end of the pass: the accumulators of this key tile are complete once every MMA has run
+      if (!mbar_wait(acc_done, ps & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool live = key < T;
+      bf16* krow = p.dk + b * p.dk_bs + (long long)min(key, T - 1) * p.dk_ts + kvh * p.dk_hs;
+      bf16* vrow = p.dv + b * p.dv_bs + (long long)min(key, T - 1) * p.dv_ts + kvh * p.dv_hs;
+      constexpr int kHalfCols = kD / 2;          // dK / dV columns each warpgroup stores
+      if (d.iters > 0) {
+        if (p.unrot_cos != nullptr) {
+          const int pos = min(key, T - 1);
+          store_row_unrot_from_tmem<kD>(tmem_base + lane_sel + kColDK, krow, half * (kD / 4), kD / 4,
+                                        p.unrot_cos + pos, p.unrot_sin + pos, p.unrot_ld, live);
+        } else {
+          store_row_from_tmem(tmem_base + lane_sel + kColDK, krow, half * kHalfCols, (half + 1) * kHalfCols, live);
+        }
+        store_row_from_tmem(tmem_base + lane_sel + kColDV, vrow, half * kHalfCols, (half + 1) * kHalfCols, live);
+      } else if (live) {
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (int c = half * kHalfCols; c < (half + 1) * kHalfCols; c += 8) {
+          *reinterpret_cast<uint4*>(krow + c) = z;
+          *reinterpret_cast<uint4*>(vrow + c) = z;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_free);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, int(*abort_flag)) == 0) p.status[1] = 314;
+  }
+}
+
 // One helper stream (and the two events that tie it to the caller's stream) per device.
 struct SideStream {
   cudaStream_t stream = nullptr;
@@ -709,6 +1168,8 @@ static SideStream* side_stream() {
 int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* valid_len, const long long* ks,
                          const long long* dqs, int B, int T, int QH, int KVH, int D, int bchunk,
                          const float* unrot_cos, const float* unrot_sin, int unrot_ld, cudaStream_t st);
+
+static int g_dkv_wide = 1;
 
 }  // namespace b200
 
@@ -754,6 +1215,8 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
                                     FdkvSmem::kTotal));
     B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     FdkvSmem::kTotal));
+    B200_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FdkwSmem::kTotal));
     configured = true;
   }
   const int nt = (T + 127) / 128;
@@ -783,7 +1246,9 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   // few key tiles per SM: pair a long and a short one per CTA (equal work, no tail); many: one per CTA
   p.pairing = nt * KVH * B < 3 * num_sms() ? 1 : 0;
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
-  if (D == 128)
+  if (D == 128 && g_dkv_wide)
+    flash_bwd_dkv_wide_kernel<<<dkv_ctas, FBT_THREADS, FdkwSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, *tds, p);
+  else if (D == 128)
     flash_bwd_dkv_tc_kernel<128><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
   else
     flash_bwd_dkv_tc_kernel<64><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
@@ -803,4 +1268,12 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   B200_CHECK(cudaEventRecord(side->join, side->stream));
   B200_CHECK(cudaStreamWaitEvent(st, side->join, 0));
   return 0;
+}
+
+// 1 (default): head_dim 128 runs the dK/dV kernel with 128-query iterations (flash_bwd_dkv_wide_kernel); 0: the
+// kernel with double-buffered 64-query iterations. Returns the previous setting; a negative argument only reads it.
+B200_API int b200_flash_bwd_wide(int on) {
+  const int old = g_dkv_wide;
+  if (on >= 0) g_dkv_wide = on != 0;
+  return old;
 }

@@ -495,6 +495,13 @@ def flash_attn_fwd(q, k, v, *, valid_len=None, scale=None, rope=None):
     return o, lse
 
 
+def set_flash_bwd_wide(on: bool) -> bool:
+    """head_dim 128: run the dK/dV kernel with 128-query iterations and interleaved products (default), or
+    (``on`` False) the kernel with double-buffered 64-query iterations that head_dim 64 uses. Returns the
+    previous setting. For A/B runs and tests."""
+    return bool(_lib().b200_flash_bwd_wide(1 if on else 0))
+
+
 def flash_delta(o: torch.Tensor, dout: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """``delta[b, h, t] = sum_d dout * o`` for [B, T, heads, D] bf16 tensors (fp32 result, [B, heads, T]): the
     stand-alone form of what ``gemm.gemm_delta`` leaves from the output projection's dgrad epilogue."""

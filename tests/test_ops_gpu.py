@@ -469,6 +469,31 @@ def test_flash_attention_tcgen05_multi_tile(T, vl):
         close(a, b, rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("B,T,QH,KVH,vl", [(1, 256, 2, 1, None), (2, 520, 4, 2, [520, 300]), (2, 1024, 8, 2, None),
+                                          (3, 384, 4, 4, [384, 129, 1])])
+def test_flash_backward_both_dkv_schedules_match_the_reference(B, T, QH, KVH, vl):
+    """head_dim 128: the dK/dV kernel with 128-query iterations (default) and the one with double-buffered
+    64-query iterations against the fp32 restatement, with ragged lengths and a padded tail."""
+    D = 128
+    q, k, v, do = (bf(B, T, h, D, seed=60 + i).to(DEV) for i, h in enumerate((QH, KVH, KVH, QH)))
+    valid = None if vl is None else torch.tensor(vl, dtype=torch.int32, device=DEV)
+    o, lse = F.flash_attn_fwd(q, k, v, valid_len=valid)
+    qc, kc, vc = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    vlc = None if valid is None else valid.cpu()
+    o_r, lse_r = F.flash_attn_fwd(qc, kc, vc, valid_len=vlc)
+    ref = F.flash_attn_bwd(do.float().cpu(), qc, kc, vc, o_r, lse_r, valid_len=vlc)
+    try:
+        for wide in (True, False):
+            F.set_flash_bwd_wide(wide)
+            got = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=valid)
+            torch.cuda.synchronize()
+            assert F.native.read_status() == (0, 0)
+            for a, b in zip(got, ref):
+                close(a, b, rtol=3e-2, atol=3e-2, frob=2e-2)
+    finally:
+        F.set_flash_bwd_wide(True)
+
+
 def test_flash_backward_unpaired_key_tile_schedule():
     """With at least three key tiles per SM in flight (here 8 x 8 x 8 = 512 on 148 SMs) a dK/dV CTA owns ONE key
     tile; smaller problems pair tiles i and n - 1 - i. This is the schedule the 1.3 B training step runs."""
