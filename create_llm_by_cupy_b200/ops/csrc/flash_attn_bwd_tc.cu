@@ -13,6 +13,9 @@
 //        S^T = K Q_i^T (SS)    dP^T = V dO_i^T (SS)   P^T, dS^T -> bf16 into TMEM
 //        dV += P^T dO_i        dK += dS^T Q_i      (A from TMEM, B = the same Q_i / dO_i tiles read
 //                                                   MN-major), accumulated in TMEM over all i
+//   flash_bwd_dkv_wide : the same for head_dim 128 with 128-query iterations: every product is an N = 128 MMA, S^T,
+//        dP^T, dV and dK take all 512 tensor-memory columns, and the products of consecutive iterations are
+//        interleaved instead of double-buffered (see the comment above that kernel). The default for head_dim 128.
 // Q and K are expected already rotated; dQ and dK are gradients w.r.t. the rotated tensors unless the
 // caller passes the rotary tables, in which case the epilogues apply the inverse rotation
 // (flash_rope_epilogue.cuh). No atomics and no fp32 scratch. When the caller gives a workspace the
