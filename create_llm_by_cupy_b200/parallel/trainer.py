@@ -118,6 +118,12 @@ class Trainer:
         # step, no replicated parameters, and a non-finite step cannot be skipped after the fact.
         self.fused_adam = bool(fused_adam and fused is not None and self.max_grads <= 0 and self.accum_step == 1
                                and optimizer_device != "cpu" and self.replica_optimizer is None and world_size > 1)
+        if fused is not None and world_size > 1 and self.device.type == "cuda":
+            # The ranks enter their first step together: the first peer-memory kernel waits for the other ranks
+            # with a bounded wait, and construction (module loading, allocations, optimizer state) can leave the
+            # ranks seconds apart.
+            torch.cuda.synchronize(self.device)
+            self.comm.barrier()
 
     # ------------------------------------------------------------------ one optimizer step
     # ------------------------------------------------------------------ phase timing (optional)

@@ -298,7 +298,7 @@ def test_launcher_trains_on_the_fused_collectives_by_default_and_matches_nccl(tm
         kw = dict(zero25_replica_ratio=ratio) if zero == "2.5" else {}
         launcher = cls(dict(md, zero3_fused_collectives=mode == "fused"), use_devices=[0, 1], batch_size=2,
                        accum_step=1, console=False, result_dir=str(out), synthetic_samples=64, lr_max=1e-3, warm_up=1,
-                       beta2=0.95, peer_wait_s=5.0, collective_timeout_s=120.0, heartbeat_timeout_s=300.0,
+                       beta2=0.95, peer_wait_s=10.0, collective_timeout_s=120.0, heartbeat_timeout_s=300.0,
                        master_port=24000 + (os.getpid() % 2000) + 7 * k + (50 if zero == "2.5" else 0), **kw)
         assert launcher.fit(2 * 2 * 6) == [0, 0]
         res[mode] = ckpt.read_pickle_gzip(str(out / "result_rank0.pkl.gz"))
