@@ -1173,6 +1173,7 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
                          const float* unrot_cos, const float* unrot_sin, int unrot_ld, cudaStream_t st);
 
 static int g_dkv_wide = 1;
+static int g_dkv_pairing = -1;      // -1: by the number of key tiles per SM; 0 / 1: forced (A/B runs)
 
 }  // namespace b200
 
@@ -1246,8 +1247,11 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
     tds = get_tensor_map_bthd(ds_ws, B, Tp, QH, Tp, (unsigned long long)QH * Tp * Tp, Tp, Tp * Tp, 128, 64);
     if (!tds) return static_cast<int>(cudaErrorInvalidValue);
   }
-  // few key tiles per SM: pair a long and a short one per CTA (equal work, no tail); many: one per CTA
-  p.pairing = nt * KVH * B < 3 * num_sms() ? 1 : 0;
+  // Between one and three key tiles per SM: pair a long and a short one per CTA (equal work, one balanced wave:
+  // 0.32 against 0.38 ms at 256 tiles). Fewer tiles than SMs: one per CTA, every tile gets an SM of its own (0.13
+  // against 0.15 ms at 128 tiles); many tiles per SM: one per CTA, longest first.
+  const int n_key_tiles = nt * KVH * B;
+  p.pairing = g_dkv_pairing >= 0 ? g_dkv_pairing : ((n_key_tiles > num_sms() && n_key_tiles < 3 * num_sms()) ? 1 : 0);
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
   if (D == 128 && g_dkv_wide)
     flash_bwd_dkv_wide_kernel<<<dkv_ctas, FBT_THREADS, FdkwSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, *tds, p);
@@ -1278,5 +1282,13 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
 B200_API int b200_flash_bwd_wide(int on) {
   const int old = g_dkv_wide;
   if (on >= 0) g_dkv_wide = on != 0;
+  return old;
+}
+
+// Key-tile pairing of the dK/dV kernels: -1 chooses by the number of key tiles per SM (the default), 0 gives every
+// CTA one key tile (grid ordered longest first), 1 gives every CTA tiles i and n - 1 - i. Returns the previous value.
+B200_API int b200_flash_bwd_pairing(int mode) {
+  const int old = g_dkv_pairing;
+  if (mode >= -1 && mode <= 1) g_dkv_pairing = mode;
   return old;
 }

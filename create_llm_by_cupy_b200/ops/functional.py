@@ -502,6 +502,12 @@ def set_flash_bwd_wide(on: bool) -> bool:
     return bool(_lib().b200_flash_bwd_wide(1 if on else 0))
 
 
+def set_flash_bwd_pairing(mode: int) -> int:
+    """Key-tile pairing of the dK/dV kernels: -1 (default) pairs tiles i and n - 1 - i in one CTA when there are
+    between one and three key tiles per SM, 0 never, 1 always. Returns the previous value. For A/B runs and tests."""
+    return int(_lib().b200_flash_bwd_pairing(int(mode)))
+
+
 def flash_delta(o: torch.Tensor, dout: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """``delta[b, h, t] = sum_d dout * o`` for [B, T, heads, D] bf16 tensors (fp32 result, [B, heads, T]): the
     stand-alone form of what ``gemm.gemm_delta`` leaves from the output projection's dgrad epilogue."""

@@ -484,19 +484,22 @@ def test_flash_backward_both_dkv_schedules_match_the_reference(B, T, QH, KVH, vl
     ref = F.flash_attn_bwd(do.float().cpu(), qc, kc, vc, o_r, lse_r, valid_len=vlc)
     try:
         for wide in (True, False):
-            F.set_flash_bwd_wide(wide)
-            got = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=valid)
-            torch.cuda.synchronize()
-            assert F.native.read_status() == (0, 0)
-            for a, b in zip(got, ref):
-                close(a, b, rtol=3e-2, atol=3e-2, frob=2e-2)
+            for pairing in (0, 1):       # one key tile per CTA, or tiles i and n - 1 - i (the training step's schedule)
+                F.set_flash_bwd_wide(wide)
+                F.set_flash_bwd_pairing(pairing)
+                got = F.flash_attn_bwd(do, q, k, v, o, lse, valid_len=valid)
+                torch.cuda.synchronize()
+                assert F.native.read_status() == (0, 0)
+                for a, b in zip(got, ref):
+                    close(a, b, rtol=3e-2, atol=3e-2, frob=2e-2)
     finally:
         F.set_flash_bwd_wide(True)
+        F.set_flash_bwd_pairing(-1)
 
 
 def test_flash_backward_unpaired_key_tile_schedule():
     """With at least three key tiles per SM in flight (here 8 x 8 x 8 = 512 on 148 SMs) a dK/dV CTA owns ONE key
-    tile; smaller problems pair tiles i and n - 1 - i. This is the schedule the 1.3 B training step runs."""
+    tile, longest first; between one and three per SM a CTA owns tiles i and n - 1 - i (the 1.3 B training step)."""
     B, T, QH, KVH, D = 8, 1024, 8, 8, 128
     g = torch.Generator().manual_seed(5)
     q = torch.randn(B, T, QH, D, generator=g).to(torch.bfloat16).to(DEV)
