@@ -305,3 +305,76 @@ def test_fused_gather_region_is_the_chunks_that_hold_the_weight():
     b_bytes = 2 * chunk
     lib.b200_ag_region(ctypes.c_ulonglong(slice_bytes), W, ctypes.c_ulonglong(b_off), ctypes.c_ulonglong(b_bytes), out)
     assert out[0] == 4 * chunk and out[1] == slice_bytes + chunk and out[2] == 3     # chunks (0,4), (0,5 short), (1,0)
+
+
+def test_copy_form_reduce_scatter_takes_a_bucket_whole_and_every_rank_takes_the_same_branch():
+    """The copy-engine form of the reduce-scatter is not cut by ``grad_bucket_elems`` (a range covers only some
+    ranks' slices and every part costs two cross-GPU barriers) unless parts are flushed early; and the choice
+    between the copy and the pull form depends only on numbers every rank computes alike."""
+    from create_llm_by_cupy_b200.parallel import symm as S
+
+    tr = Trainer(dict(TINY, grad_bucket_elems=1000), device="cpu", **HP)
+    mgr = tr.manager
+
+    class Fake:
+        reduce_mode = "copy"
+    mgr.fused = Fake()
+    try:
+        assert mgr._split_range(0, 2504) == [(0, 2504)]
+        mgr.early_bucket_flush = True
+        assert mgr._split_range(0, 2504) == [(0, 1000), (1000, 2000), (2000, 2504)]
+        mgr.early_bucket_flush = False
+        Fake.reduce_mode = "pull"
+        assert mgr._split_range(0, 2504) == [(0, 1000), (1000, 2000), (2000, 2504)]
+    finally:
+        mgr.fused = None
+
+    # branch selection and the share arithmetic of FusedCollectives.reduce_scatter_accumulate, launches stubbed out
+    calls = []
+
+    class Lib:
+        def b200_symm_reduce_scatter_staged(self, *a):
+            calls.append(("copy", a[5].value, a[6].value, a[15].value))      # lo, hi, part
+            return 0
+
+        def b200_symm_reduce_scatter_range(self, *a):
+            calls.append(("pull", a[6].value, a[7].value))
+            return 0
+
+    class T:      # the few tensor attributes the method reads
+        def __init__(self, n, dtype=torch.bfloat16):
+            self._n, self.dtype = n, dtype
+
+        def numel(self):
+            return self._n
+
+        def data_ptr(self):
+            return 256
+
+    class Heap:
+        table = None
+
+        def offset_of(self, t):
+            return 0
+
+    picks = []
+    for rank in (0, 1, 2, 3):
+        fc = S.FusedCollectives.__new__(S.FusedCollectives)
+        fc.lib, fc.world_size, fc.rank, fc.wait_ns, fc.launches, fc.copies = Lib(), 4, rank, 1, 0, 0
+        fc.reduce_mode, fc.copy_min_bytes, fc.rs_epoch, fc.stage_epoch, fc.rs_blocks, fc.rs_local_blocks = "copy", 1024, 0, 0, 4, 8
+        fc._heap, fc._stage, fc.device = Heap(), None, torch.device("cpu")
+        fc.reserve_stage = lambda part, fc=fc: T(part * 3)
+        real_bump, real_check, real_stream = S.native.bump, S.native.check, S.native.stream_ptr
+        S.native.bump = lambda *a, **k: None
+        S.native.check = lambda rc, what: None
+        S.native.stream_ptr = lambda: None
+        try:
+            calls.clear()
+            fc.reduce_scatter_accumulate(T(1000), T(4000), False)                              # 2000 B per share: copy
+            fc.reduce_scatter_accumulate(T(1000), T(4000), False, elem_range=(0, 1200))       # largest share 1000: copy
+            fc.reduce_scatter_accumulate(T(1000), T(4000), False, elem_range=(992, 1200))     # largest share 200: pull
+        finally:
+            S.native.bump, S.native.check, S.native.stream_ptr = real_bump, real_check, real_stream
+        picks.append([c[0] for c in calls])
+        assert calls[0] == ("copy", 0, 4000, 1000) and calls[1] == ("copy", 0, 1200, 1000) and calls[2][0] == "pull"
+    assert all(p == picks[0] for p in picks)          # every rank takes the same branch for the same call
