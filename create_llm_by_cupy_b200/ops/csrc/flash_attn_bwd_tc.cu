@@ -1173,6 +1173,34 @@ int flash_bwd_dq_from_ds(const void* ds, const void* k, void* dq, const void* va
                          const float* unrot_cos, const float* unrot_sin, int unrot_ld, cudaStream_t st);
 
 static int g_dkv_wide = 1;
+
+// The wide dK/dV kernel needs all but 872 bytes of an SM's shared memory, so it only fits when the dynamic
+// shared memory of a kernel starts within that many bytes of a 1 KiB boundary. That offset is a property of the
+// platform (it was 0 on every B200 seen): it is measured once per device with a one-warp kernel, and where it
+// does not fit head_dim 128 stays on the 64-query kernel.
+__global__ void smem_base_probe_kernel(int* out) {
+  extern __shared__ uint8_t probe_raw[];
+  if (threadIdx.x == 0) *out = int(reinterpret_cast<uintptr_t>(probe_raw) & 1023);
+}
+static bool dkv_wide_fits() {
+  static std::mutex mu;
+  static int fits[64];            // 0 unknown, 1 yes, -1 no
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fits[dev] == 0) {
+    int* d = nullptr;
+    int off = -1;
+    if (cudaMalloc(&d, sizeof(int)) == cudaSuccess) {
+      smem_base_probe_kernel<<<1, 32, 1024>>>(d);
+      if (cudaMemcpy(&off, d, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) off = -1;
+      cudaFree(d);
+    }
+    const int pad = off < 0 ? 1024 : (1024 - off) & 1023;        // bytes lost to the round-up of the base
+    fits[dev] = (FdkwSmem::kUsed + pad <= FdkwSmem::kTotal) ? 1 : -1;
+  }
+  return fits[dev] > 0;
+}
 static int g_dkv_pairing = -1;      // -1: by the number of key tiles per SM; 0 / 1: forced (A/B runs)
 
 }  // namespace b200
@@ -1253,7 +1281,7 @@ B200_API int b200_flash_bwd_tc(const void* q, const void* k, const void* v, cons
   const int n_key_tiles = nt * KVH * B;
   p.pairing = g_dkv_pairing >= 0 ? g_dkv_pairing : ((n_key_tiles > num_sms() && n_key_tiles < 3 * num_sms()) ? 1 : 0);
   const int dkv_ctas = (p.pairing ? (nt + 1) / 2 : nt) * KVH * B;
-  if (D == 128 && g_dkv_wide)
+  if (D == 128 && g_dkv_wide && dkv_wide_fits())
     flash_bwd_dkv_wide_kernel<<<dkv_ctas, FBT_THREADS, FdkwSmem::kTotal, st>>>(*tq128, *tdo128, *tk, *tv, *tds, p);
   else if (D == 128)
     flash_bwd_dkv_tc_kernel<128><<<dkv_ctas, FBT_THREADS, FdkvSmem::kTotal, st>>>(*tq64, *tdo64, *tk, *tv, *tds, p);
@@ -1292,3 +1320,6 @@ B200_API int b200_flash_bwd_pairing(int mode) {
   if (mode >= -1 && mode <= 1) g_dkv_pairing = mode;
   return old;
 }
+
+// 1 when head_dim 128 runs the 128-query dK/dV kernel on the current device (switched on and its shared memory fits).
+B200_API int b200_flash_bwd_wide_active() { return (g_dkv_wide && dkv_wide_fits()) ? 1 : 0; }

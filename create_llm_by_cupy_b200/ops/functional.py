@@ -502,6 +502,12 @@ def set_flash_bwd_wide(on: bool) -> bool:
     return bool(_lib().b200_flash_bwd_wide(1 if on else 0))
 
 
+def flash_bwd_wide_active() -> bool:
+    """True when head_dim 128 runs the dK/dV kernel with 128-query iterations on the current device: switched on
+    and its shared memory (all but 872 bytes of an SM's) fits behind the kernel's dynamic shared-memory base."""
+    return bool(_lib().b200_flash_bwd_wide_active())
+
+
 def set_flash_bwd_pairing(mode: int) -> int:
     """Key-tile pairing of the dK/dV kernels: -1 (default) pairs tiles i and n - 1 - i in one CTA when there are
     between one and three key tiles per SM, 0 never, 1 always. Returns the previous value. For A/B runs and tests."""
