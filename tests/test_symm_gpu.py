@@ -304,10 +304,15 @@ def test_launcher_trains_on_the_fused_collectives_by_default_and_matches_nccl(tm
                            heartbeat_timeout_s=300.0,
                            master_port=24000 + (os.getpid() % 2000) + 7 * k + (50 if zero == "2.5" else 0) + 100 * attempt,
                            **kw)
-            codes = launcher.fit(2 * 2 * 6)
+            try:
+                codes = launcher.fit(2 * 2 * 6)
+            except Exception as e:      # WorkerFailure: a rank exited with an error or stopped answering
+                codes = None
+                print(f"launcher attempt {attempt} failed: {e}", file=sys.stderr)
+                if attempt == 1:
+                    raise
             if codes == [0, 0]:
                 break
-            print(f"launcher attempt {attempt}: exit codes {codes}", file=sys.stderr)
         assert codes == [0, 0]
         res[mode] = ckpt.read_pickle_gzip(str(out / "result_rank0.pkl.gz"))
     f, n = res["fused"], res["nccl"]
